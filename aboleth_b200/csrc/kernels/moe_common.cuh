@@ -1,0 +1,143 @@
+// Device helpers shared by the MoE kernels: router softmax/top-k in one warp,
+// 1 x group block-scaled e4m3 quantisation, and the record geometry.
+//
+// Record layout (one record per (token, destination rank); reference:
+// python/aboleth/moe/compiled_plan.py:101-107, python/aboleth/moe/kernels.py:98-143):
+//   payload row  : hidden x {bf16 | e4m3}
+//   metadata row : int32 [token, n_selected, expert_id x k, weight_bits x k, scale_bits x cols]
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace ab::moe {
+
+constexpr int kMaxTopK = 16;
+constexpr int kMaxWorld = 32;
+constexpr int kMaxExpertsPerLane = 16;  // experts <= 512
+constexpr float kFp8Max = 448.0f;
+
+__device__ __forceinline__ float bf16_lo(std::uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(std::uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+__device__ __forceinline__ std::uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<std::uint32_t *>(&v);
+}
+
+// scale = max(amax, floor) / 448, optionally rounded UP to a power of two.
+__device__ __forceinline__ float quant_scale(float amax, float floor_, int round_pow2) {
+    float scale = fmaxf(amax, floor_) / kFp8Max;
+    if (round_pow2) {
+        std::uint32_t bits = __float_as_uint(scale);
+        if (bits & 0x007fffffu)
+            bits = (bits & 0xff800000u) + 0x00800000u;
+        scale = __uint_as_float(bits);
+    }
+    return scale;
+}
+
+__device__ __forceinline__ std::uint32_t fp8x4(float a, float b, float c, float d, float scale) {
+    const float lo = -kFp8Max, hi = kFp8Max;
+    a = fminf(fmaxf(a / scale, lo), hi);
+    b = fminf(fmaxf(b / scale, lo), hi);
+    c = fminf(fmaxf(c / scale, lo), hi);
+    d = fminf(fmaxf(d / scale, lo), hi);
+    const std::uint32_t p0 = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const std::uint32_t p1 = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return p0 | (p1 << 16);
+}
+
+// Sixteen bf16 values (two 16-byte vectors) -> absolute maximum.
+__device__ __forceinline__ float amax16(const uint4 &a, const uint4 &b) {
+    float m = 0.f;
+    const std::uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        m = fmaxf(m, fmaxf(fabsf(bf16_lo(w[i])), fabsf(bf16_hi(w[i]))));
+    return m;
+}
+
+__device__ __forceinline__ uint4 quant16(const uint4 &a, const uint4 &b, float scale) {
+    uint4 q;
+    q.x = fp8x4(bf16_lo(a.x), bf16_hi(a.x), bf16_lo(a.y), bf16_hi(a.y), scale);
+    q.y = fp8x4(bf16_lo(a.z), bf16_hi(a.z), bf16_lo(a.w), bf16_hi(a.w), scale);
+    q.z = fp8x4(bf16_lo(b.x), bf16_hi(b.x), bf16_lo(b.y), bf16_hi(b.y), scale);
+    q.w = fp8x4(bf16_lo(b.z), bf16_hi(b.z), bf16_lo(b.w), bf16_hi(b.w), scale);
+    return q;
+}
+
+// Reduce a maximum over the `width` consecutive lanes (power of two <= 32)
+// that share one quantisation group.
+__device__ __forceinline__ float group_max(float v, int width) {
+    for (int off = width >> 1; off > 0; off >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    return v;
+}
+
+// One warp: softmax over `experts` logits and the `top_k` largest, ties to
+// the lower index.  Lane l holds experts l, l+32, ...  On return lane j < top_k
+// holds (id, weight) of the j-th choice.  `renormalize` divides the selected
+// probabilities by their sum.
+__device__ __forceinline__ void warp_softmax_topk(const float *logits, int experts, int top_k,
+                                                  int renormalize, int &out_id, float &out_w) {
+    const int lane = threadIdx.x & 31;
+    float v[kMaxExpertsPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = e < experts ? logits[e] : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+    }
+    for (int off = 16; off > 0; off >>= 1)
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i)
+        sum += (lane + 32 * i) < experts ? __expf(v[i] - mx) : 0.f;
+    for (int off = 16; off > 0; off >>= 1)
+        sum += __shfl_xor_sync(0xffffffffu, sum, off);
+
+    out_id = -1;
+    out_w = 0.f;
+    float picked_sum = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+            const int e = lane + 32 * i;
+            if (e < experts && v[i] > best) {
+                best = v[i];
+                best_e = e;
+            }
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+            if (ob > best || (ob == best && oe < best_e)) {
+                best = ob;
+                best_e = oe;
+            }
+        }
+        const float w = __expf(best - mx) / sum;
+        picked_sum += w;
+        if (lane == j) {
+            out_id = best_e;
+            out_w = w;
+        }
+        if ((best_e & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < kMaxExpertsPerLane; ++i)
+                if (i == (best_e >> 5))
+                    v[i] = -INFINITY;
+        }
+    }
+    if (renormalize && picked_sum > 0.f)
+        out_w /= picked_sum;
+}
+
+}  // namespace ab::moe

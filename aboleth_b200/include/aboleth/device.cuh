@@ -1,0 +1,406 @@
+// Tier 1: one-sided transport callable from any CUDA kernel (sm_100a).
+//
+//   aboleth::DeviceContext ctx{endpoint_handles, nullptr, status_words};
+//   aboleth::put(ctx, peer, remote_row, local_row, bytes);
+//   aboleth::put_inline(ctx, peer, remote_word, value);
+//   aboleth::signal(ctx, peer, remote_flag, epoch);
+//   aboleth::quiet(ctx, peer);
+//   aboleth::wait_signal(ctx, local_flag, epoch);
+//
+// The call shapes are those of the reference facade
+// (include/aboleth/device.cuh:40-125) and of the header its generator renders
+// (python/aboleth/emit/tier1_header.py:497-813: open, put_signal, put_many,
+// put_many_signal, put_many_flush, put_warp).  Addresses come from the rank's
+// peer-region table (World.exchange_regions); there is no symmetric heap.
+//
+// What is different on purpose:
+//  * This header is written by hand for NVLink peer memory.  A put is a
+//    vectorised copy into the peer's mapping, a signal is one
+//    `st.release.sys` that publishes every store the calling thread (or, for
+//    the *_block forms, the calling CTA) made before it, and nothing else is
+//    fenced: the release is the only ordering point of a chain.
+//  * No wait is unbounded and nothing traps.  A wait that runs out of time
+//    records Status::Timeout in `ctx.status[0]` (when given) and returns; an
+//    endpoint kind this header cannot serve records Status::Malformed.
+//  * The queue transports (rdma, efa, ionic, proxy) are served through the
+//    host-proxy ring (aboleth/proxy_device.cuh) when the handle's kind bits
+//    say so.
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "aboleth/abi/endpoint_abi.h"
+#include "aboleth/abi/proxy_abi.h"
+
+#ifndef ABOLETH_WAIT_TIMEOUT_NS
+// Default bound of every device-side wait: two seconds of %globaltimer.
+#define ABOLETH_WAIT_TIMEOUT_NS 2000000000ull
+#endif
+
+#define ABOLETH_TIER1_ABI 2
+#define ABOLETH_TIER1_GENERATED 0
+#define ABOLETH_TIER1_PUT_MANY 1
+#define ABOLETH_TIER1_PUT_SIGNAL 1
+#define ABOLETH_TIER1_PUT_MANY_FLUSH 1
+#define ABOLETH_TIER1_HAS_P2P 1
+#define ABOLETH_TIER1_HAS_PROXY 1
+#define ABOLETH_TIER1_HAS_RDMA 0
+#define ABOLETH_TIER1_BOUNDED_WAITS 1
+
+namespace aboleth {
+
+using abi::PutDesc;
+
+enum class Status : std::uint32_t {
+    Ok = 0,
+    Timeout = 1,
+    CompletionFailure = 2,
+    Malformed = 3,
+};
+
+struct LocalRegion {
+    std::uint64_t address;
+    std::uint32_t key;
+};
+
+struct RemoteRegion {
+    std::uint64_t address;
+    std::uint32_t key;
+};
+
+// Kernel-argument view of one rank's endpoints.  `endpoints[peer]` is the
+// handle table World.exchange_regions() returns (low three bits = kind).
+// `status`, when non-null, is one 64-bit word that receives the first
+// non-zero Status any call on this context produced.
+struct DeviceContext {
+    const std::uint64_t *endpoints;
+    std::uint32_t *doorbell_locks;
+    unsigned long long *status = nullptr;
+};
+
+struct PeerRef {
+    std::uint64_t handle;  // kind bits stripped
+    std::uint32_t kind;
+};
+
+namespace detail {
+
+__device__ __forceinline__ std::uint64_t globaltimer_ns() {
+    std::uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ std::uint64_t ld_acquire_sys(const std::uint64_t *p) {
+    std::uint64_t v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ std::uint64_t ld_relaxed_sys(const std::uint64_t *p) {
+    std::uint64_t v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_release_sys(std::uint64_t *p, std::uint64_t v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ void st_relaxed_sys(std::uint64_t *p, std::uint64_t v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ void fence_acq_rel_sys() {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+}
+
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_stream16(void *p, const uint4 &v) {
+    asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ void record(const DeviceContext &ctx, Status s) {
+    if (ctx.status != nullptr && s != Status::Ok)
+        atomicCAS(ctx.status, 0ull, static_cast<unsigned long long>(s));
+}
+
+// Copy `bytes` with `nthreads` cooperating threads (this thread is `tid`).
+// 16-byte vectors, four in flight per thread, when everything is 16-byte
+// aligned; 8-byte words when 8-byte aligned; bytes otherwise.
+__device__ __forceinline__ void copy_strided(
+    std::uint8_t *dst, const std::uint8_t *src, std::uint64_t bytes,
+    unsigned tid, unsigned nthreads) {
+    const std::uint64_t mix =
+        reinterpret_cast<std::uint64_t>(dst) | reinterpret_cast<std::uint64_t>(src);
+    if ((mix & 15) == 0) {
+        const std::uint64_t vecs = bytes >> 4;
+        std::uint64_t i = tid;
+        for (; i + 3ull * nthreads < vecs; i += 4ull * nthreads) {
+            uint4 a = ld_stream16(src + (i << 4));
+            uint4 b = ld_stream16(src + ((i + nthreads) << 4));
+            uint4 c = ld_stream16(src + ((i + 2ull * nthreads) << 4));
+            uint4 d = ld_stream16(src + ((i + 3ull * nthreads) << 4));
+            st_stream16(dst + (i << 4), a);
+            st_stream16(dst + ((i + nthreads) << 4), b);
+            st_stream16(dst + ((i + 2ull * nthreads) << 4), c);
+            st_stream16(dst + ((i + 3ull * nthreads) << 4), d);
+        }
+        for (; i < vecs; i += nthreads)
+            st_stream16(dst + (i << 4), ld_stream16(src + (i << 4)));
+        for (std::uint64_t b = (vecs << 4) + tid; b < bytes; b += nthreads)
+            dst[b] = src[b];
+    } else if ((mix & 7) == 0) {
+        const std::uint64_t words = bytes >> 3;
+        for (std::uint64_t i = tid; i < words; i += nthreads)
+            reinterpret_cast<std::uint64_t *>(dst)[i] =
+                reinterpret_cast<const std::uint64_t *>(src)[i];
+        for (std::uint64_t b = (words << 3) + tid; b < bytes; b += nthreads)
+            dst[b] = src[b];
+    } else {
+        for (std::uint64_t b = tid; b < bytes; b += nthreads)
+            dst[b] = src[b];
+    }
+}
+
+}  // namespace detail
+
+}  // namespace aboleth
+
+#include "aboleth/proxy_device.cuh"
+
+namespace aboleth {
+
+__device__ __forceinline__ PeerRef open(const DeviceContext &ctx, int peer) {
+    const std::uint64_t raw = ctx.endpoints[peer];
+    return PeerRef{raw & ~abi::kKindMask, static_cast<std::uint32_t>(raw & abi::kKindMask)};
+}
+
+// ---- bounded receiver-side wait ------------------------------------------------
+
+// Wait until *flag >= epoch (epochs are monotonic, a later one satisfies an
+// earlier wait) or `timeout_ns` of %globaltimer elapsed.
+__device__ __forceinline__ Status wait_signal_status(
+    const std::uint64_t *flag, std::uint64_t epoch,
+    std::uint64_t timeout_ns = ABOLETH_WAIT_TIMEOUT_NS) {
+    if (detail::ld_acquire_sys(flag) >= epoch)
+        return Status::Ok;
+    const std::uint64_t start = detail::globaltimer_ns();
+    unsigned spins = 0;
+    while (true) {
+        if (detail::ld_acquire_sys(flag) >= epoch)
+            return Status::Ok;
+        if (++spins > 32) {
+            __nanosleep(64);
+            if (detail::globaltimer_ns() - start > timeout_ns)
+                return Status::Timeout;
+        }
+    }
+}
+
+__device__ __forceinline__ void wait_signal(
+    const DeviceContext &ctx, const std::uint64_t *flag, std::uint64_t epoch) {
+    detail::record(ctx, wait_signal_status(flag, epoch));
+}
+
+// ---- single-thread forms (the Tier-1 contract: any one thread may call) --------
+
+__device__ __forceinline__ void put(
+    const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
+    const LocalRegion &src, std::uint32_t bytes) {
+    if (ref.kind == abi::kKindP2P) {
+        detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
+                             reinterpret_cast<const std::uint8_t *>(src.address),
+                             bytes, 0, 1);
+    } else if (ref.kind == abi::kKindProxy) {
+        abi::ProxyCommand cmd{src.address, dst.address, bytes, src.key, dst.key,
+                              abi::kProxyCommandWrite};
+        detail::record(ctx, proxy::submit(ref.handle, &cmd, 1, nullptr));
+    } else {
+        detail::record(ctx, Status::Malformed);
+    }
+}
+
+__device__ __forceinline__ void put(
+    const DeviceContext &ctx, int peer, const RemoteRegion &dst,
+    const LocalRegion &src, std::uint32_t bytes) {
+    put(ctx, open(ctx, peer), dst, src, bytes);
+}
+
+// Eight bytes straight out of a register.
+__device__ __forceinline__ void put_inline(
+    const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
+    std::uint64_t value) {
+    if (ref.kind == abi::kKindP2P) {
+        detail::st_relaxed_sys(reinterpret_cast<std::uint64_t *>(dst.address), value);
+    } else if (ref.kind == abi::kKindProxy) {
+        // The ring carries an 8-byte inline value as a weak signal command.
+        abi::ProxyCommand cmd{value, dst.address, 8, 0, dst.key,
+                              abi::kProxyCommandWeakSignal};
+        detail::record(ctx, proxy::submit(ref.handle, &cmd, 1, nullptr));
+    } else {
+        detail::record(ctx, Status::Malformed);
+    }
+}
+
+__device__ __forceinline__ void put_inline(
+    const DeviceContext &ctx, int peer, const RemoteRegion &dst, std::uint64_t value) {
+    put_inline(ctx, open(ctx, peer), dst, value);
+}
+
+// Strong publication: a peer that observes `epoch` in `flag` observes every
+// store this thread made to that peer before the call.
+__device__ __forceinline__ void signal(
+    const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &flag,
+    std::uint64_t epoch) {
+    if (ref.kind == abi::kKindP2P) {
+        detail::st_release_sys(reinterpret_cast<std::uint64_t *>(flag.address), epoch);
+    } else if (ref.kind == abi::kKindProxy) {
+        abi::ProxyCommand cmd{epoch, flag.address, 8, 0, flag.key,
+                              abi::kProxyCommandStrongSignal};
+        detail::record(ctx, proxy::submit(ref.handle, &cmd, 1, nullptr));
+    } else {
+        detail::record(ctx, Status::Malformed);
+    }
+}
+
+__device__ __forceinline__ void signal(
+    const DeviceContext &ctx, int peer, const RemoteRegion &flag, std::uint64_t epoch) {
+    signal(ctx, open(ctx, peer), flag, epoch);
+}
+
+// put then signal as ONE chain: one release (p2p) or one two-command batch
+// with a single reservation and a single ready store (proxy).
+__device__ __forceinline__ void put_signal(
+    const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
+    const LocalRegion &src, std::uint32_t bytes, const RemoteRegion &flag,
+    std::uint64_t epoch) {
+    if (ref.kind == abi::kKindP2P) {
+        detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
+                             reinterpret_cast<const std::uint8_t *>(src.address),
+                             bytes, 0, 1);
+        detail::st_release_sys(reinterpret_cast<std::uint64_t *>(flag.address), epoch);
+    } else if (ref.kind == abi::kKindProxy) {
+        abi::ProxyCommand cmds[2] = {
+            {src.address, dst.address, bytes, src.key, dst.key, abi::kProxyCommandWrite},
+            {epoch, flag.address, 8, 0, flag.key, abi::kProxyCommandStrongSignal}};
+        detail::record(ctx, proxy::submit(ref.handle, cmds, 2, nullptr));
+    } else {
+        detail::record(ctx, Status::Malformed);
+    }
+}
+
+__device__ __forceinline__ void put_signal(
+    const DeviceContext &ctx, int peer, const RemoteRegion &dst,
+    const LocalRegion &src, std::uint32_t bytes, const RemoteRegion &flag,
+    std::uint64_t epoch) {
+    put_signal(ctx, open(ctx, peer), dst, src, bytes, flag, epoch);
+}
+
+// `count` puts as one batch; nothing is published.
+__device__ __forceinline__ void put_many(
+    const DeviceContext &ctx, const PeerRef &ref, const PutDesc *descs, int count) {
+    if (ref.kind == abi::kKindP2P) {
+        for (int i = 0; i < count; ++i)
+            detail::copy_strided(reinterpret_cast<std::uint8_t *>(descs[i].dst),
+                                 reinterpret_cast<const std::uint8_t *>(descs[i].src),
+                                 descs[i].bytes, 0, 1);
+    } else if (ref.kind == abi::kKindProxy) {
+        detail::record(ctx, proxy::submit_puts(ref.handle, descs, count, nullptr, 0, nullptr));
+    } else {
+        detail::record(ctx, Status::Malformed);
+    }
+}
+
+// `count` puts closed by ONE signal: the chain pays one release / one
+// reservation, however long it is.
+__device__ __forceinline__ void put_many_signal(
+    const DeviceContext &ctx, const PeerRef &ref, const PutDesc *descs, int count,
+    const RemoteRegion &flag, std::uint64_t epoch) {
+    if (ref.kind == abi::kKindP2P) {
+        for (int i = 0; i < count; ++i)
+            detail::copy_strided(reinterpret_cast<std::uint8_t *>(descs[i].dst),
+                                 reinterpret_cast<const std::uint8_t *>(descs[i].src),
+                                 descs[i].bytes, 0, 1);
+        detail::st_release_sys(reinterpret_cast<std::uint64_t *>(flag.address), epoch);
+    } else if (ref.kind == abi::kKindProxy) {
+        detail::record(ctx, proxy::submit_puts(ref.handle, descs, count, &flag, epoch, nullptr));
+    } else {
+        detail::record(ctx, Status::Malformed);
+    }
+}
+
+// Sender-side completion of everything posted to the peer so far.  Peer
+// stores read their source when they issue, so on p2p the source is already
+// reusable and this is a no-op; on the ring it waits for the host to retire
+// the last batch this endpoint reserved.
+__device__ __forceinline__ void quiet(const DeviceContext &ctx, const PeerRef &ref) {
+    if (ref.kind == abi::kKindProxy)
+        detail::record(ctx, proxy::drain(ref.handle));
+    else if (ref.kind != abi::kKindP2P)
+        detail::record(ctx, Status::Malformed);
+}
+
+__device__ __forceinline__ void quiet(const DeviceContext &ctx, int peer) {
+    quiet(ctx, open(ctx, peer));
+}
+
+__device__ __forceinline__ void put_many_flush(
+    const DeviceContext &ctx, const PeerRef &ref, const PutDesc *descs, int count) {
+    put_many(ctx, ref, descs, count);
+    quiet(ctx, ref);
+}
+
+// ---- cooperative forms (p2p only) -----------------------------------------------
+
+// One full warp copies; ends with a warp barrier and a system fence so the
+// bytes are placed when the call returns (no signal has to follow).
+__device__ __forceinline__ void put_warp(
+    const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
+    const LocalRegion &src, std::uint32_t bytes) {
+    if (ref.kind != abi::kKindP2P) {
+        if ((threadIdx.x & 31) == 0)
+            put(ctx, ref, dst, src, bytes);
+        __syncwarp();
+        return;
+    }
+    detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
+                         reinterpret_cast<const std::uint8_t *>(src.address), bytes,
+                         threadIdx.x & 31, 32);
+    __syncwarp();
+    detail::fence_acq_rel_sys();
+}
+
+// The whole CTA copies.  No fence: a following signal_block publishes it.
+__device__ __forceinline__ void put_block(
+    const RemoteRegion &dst, const LocalRegion &src, std::uint64_t bytes) {
+    const unsigned tid = threadIdx.x + blockDim.x * (threadIdx.y + blockDim.y * threadIdx.z);
+    const unsigned n = blockDim.x * blockDim.y * blockDim.z;
+    detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
+                         reinterpret_cast<const std::uint8_t *>(src.address), bytes, tid, n);
+}
+
+// CTA barrier, then one thread's fence + release store: every thread's earlier
+// peer stores are visible to whoever acquires `epoch` from `flag`.  The CTA
+// barrier orders the CTA's stores before thread 0 (CTA-scope causality), and
+// the system-scope fence makes that order cumulative for the remote observer.
+__device__ __forceinline__ void signal_block(const RemoteRegion &flag, std::uint64_t epoch) {
+    __syncthreads();
+    if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+        detail::fence_acq_rel_sys();
+        detail::st_relaxed_sys(reinterpret_cast<std::uint64_t *>(flag.address), epoch);
+    }
+}
+
+}  // namespace aboleth

@@ -1,0 +1,33 @@
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs at least one CUDA device")
+    config.addinivalue_line("markers", "multigpu: needs at least two CUDA devices")
+
+
+def pytest_collection_modifyitems(config, items):
+    import torch
+
+    have = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    for item in items:
+        if "gpu" in item.keywords and have < 1:
+            item.add_marker(pytest.mark.skip(reason="no CUDA device"))
+        if "multigpu" in item.keywords and have < 2:
+            item.add_marker(pytest.mark.skip(reason="needs two CUDA devices"))
+
+
+@pytest.fixture
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
