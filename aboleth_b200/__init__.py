@@ -7,4 +7,6 @@ from .runtime import (AllocationHandle, AllocationProvider, Endpoint, EndpointTa
                       connection_transport, provider_caps)
 from .world import AutoTransportPolicy, LocalRegion, PeerRegionTable, TopologyInfo, World
 
+from . import abi, moe, ops, parallel  # noqa: E402,F401
+
 __version__ = "0.1.0"

@@ -1,0 +1,245 @@
+"""Measurement helpers shared by ``bench.py`` and the benchmark scripts.
+
+Timing rules used everywhere here: CUDA events on the launching stream after
+warm-up, ``torch.cuda.synchronize`` on both sides, the maximum over ranks for
+anything multi-GPU, and either inputs that rotate through more than the L2
+capacity or an explicit L2 flush between timed iterations.
+"""
+from __future__ import annotations
+
+import json
+import statistics
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+from .moe import MoESpec
+from .moe.reference import standin_layer_reference
+from .parallel.ep import ExpertParallelLayer
+from .world import World
+
+L2_BYTES = 126 * 1024 * 1024
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool
+
+
+def measured_peaks() -> dict:
+    path = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    if path.exists():
+        return {**json.loads(path.read_text()), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+def sync_ranks(distributed: bool) -> None:
+    """Device-side alignment of the ranks (one-element all-reduce), then a host sync."""
+    if distributed:
+        import torch.distributed as dist
+        token = torch.zeros(1, device="cuda")
+        dist.all_reduce(token)
+    torch.cuda.synchronize()
+
+
+def device_max(value: float, distributed: bool) -> float:
+    if not distributed:
+        return float(value)
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def device_max_vector(values: list[float], distributed: bool) -> list[float]:
+    if not distributed:
+        return list(values)
+    import torch.distributed as dist
+    t = torch.tensor(values, dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+class L2Flusher:
+    def __init__(self, device):
+        self.buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
+
+    def __call__(self) -> None:
+        self.buf.fill_(1)
+
+
+class EpLayerBench:
+    """DeepSeek-V3-shape MoE layer with seeded synthetic inputs."""
+
+    def __init__(self, world: World, *, tokens: int, hidden: int, experts: int, top_k: int,
+                 group: int, seed: int, tag: str = "bench"):
+        self.world, self.tokens = world, tokens
+        self.spec = MoESpec(capacity=tokens, hidden=hidden, top_k=top_k, experts=experts,
+                            ranks=world.world_size, value_type="f8E4M3FN", scale_group=group)
+        self.layer = ExpertParallelLayer(world, self.spec, tag=tag)
+        dev = world.torch_device
+        per_copy = tokens * hidden * 2
+        self.copies = min(8, max(2, -(-2 * L2_BYTES // per_copy)))
+        self.l2_policy = (f"inputs rotate through {self.copies} buffers "
+                          f"({self.copies * per_copy >> 20} MiB) and the receive segments exceed L2")
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.x = [torch.randn(tokens, hidden, generator=g, device=dev).to(torch.bfloat16)
+                  for _ in range(self.copies)]
+        self.logits = [torch.randn(tokens, experts, generator=g, device=dev)
+                       for _ in range(self.copies)]
+        self.counter = 0
+        self.flusher: Optional[L2Flusher] = None
+
+    def step(self) -> torch.Tensor:
+        i = self.counter % self.copies
+        self.counter += 1
+        return self.layer.forward(self.x[i], self.logits[i])
+
+    def check(self) -> None:
+        torch.cuda.synchronize()
+        self.layer.check()
+
+    def verify(self) -> int:
+        """Rows of one step's output outside the fp8 tolerance of the fp32 oracle."""
+        out = self.layer.forward(self.x[0], self.logits[0]).float()
+        torch.cuda.synchronize()
+        ids = self.layer.slot.topk_ids[: self.tokens]
+        weights = self.layer.slot.topk_weights[: self.tokens]
+        expected, tol = standin_layer_reference(self.x[0], ids.long(), weights, fp8=True,
+                                                group=self.spec.scale_group,
+                                                amax_floor=self.spec.quant_amax_floor)
+        err = (out - expected).abs().amax(dim=-1)
+        bad = int((~(err <= tol)).sum().item())  # NaN rows count as errors
+        return bad
+
+    def _traffic(self) -> dict:
+        """Bytes this rank moved in the last step (records it sent / got back)."""
+        s, slot = self.spec, self.layer.slot
+        slots = slot.source_slots[: self.tokens]
+        sent = (slots >= 0).sum(dim=0).tolist()
+        remote = sum(n for d, n in enumerate(sent) if d != slot.rank)
+        total = sum(sent)
+        record = s.row_bytes + s.metadata_words * 4
+        return {"records_total": total, "records_remote": remote,
+                "dispatch_remote_bytes": remote * record, "combine_remote_bytes": remote * s.hidden * 2,
+                "dispatch_local_hbm_bytes": self.tokens * s.hidden * 2 + total * record,
+                "combine_local_hbm_bytes": total * s.hidden * 2 * 2 + self.tokens * s.hidden * 2}
+
+    def phase_times(self, *, steps: int, distributed: bool, flush: bool = False) -> dict:
+        slot, layer = self.layer.slot, self.layer
+        if flush and self.flusher is None:
+            self.flusher = L2Flusher(self.world.torch_device)
+        ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+        d_ms, c_ms = [], []
+        for it in range(steps + 3):
+            i = self.counter % self.copies
+            self.counter += 1
+            if flush:
+                self.flusher()
+            sync_ranks(distributed)
+            e0, e1, e2, e3 = ev(), ev(), ev(), ev()
+            e0.record()
+            res = slot.dispatch(self.x[i], logits=self.logits[i])
+            e1.record()
+            layer.standin_experts(res, slot.expert_output)
+            if flush:
+                self.flusher()
+            sync_ranks(distributed)
+            e2.record()
+            slot.combine(slot.expert_output)
+            e3.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                d_ms.append(e0.elapsed_time(e1))
+                c_ms.append(e2.elapsed_time(e3))
+        d = statistics.median(device_max_vector(d_ms, distributed)) * 1e3
+        c = statistics.median(device_max_vector(c_ms, distributed)) * 1e3
+        self.check()
+        traffic = self._traffic()
+        peaks = measured_peaks()
+        roof = {"traffic": traffic, "denominators": peaks["source"]}
+        if self.world.world_size > 1:
+            td = traffic["dispatch_remote_bytes"] / (NVLINK_GBS * 1e3)  # us
+            tc = traffic["combine_remote_bytes"] / (NVLINK_GBS * 1e3)
+            roof.update({"bound": "nvlink 770 GB/s per direction (measured peer copy)",
+                         "dispatch_roof_us": td, "combine_roof_us": tc,
+                         "dispatch_frac": td / d if d else None, "combine_frac": tc / c if c else None})
+        else:
+            td = traffic["dispatch_local_hbm_bytes"] / (peaks["hbm_gbs"] * 1e3)
+            tc = traffic["combine_local_hbm_bytes"] / (peaks["hbm_gbs"] * 1e3)
+            roof.update({"bound": f"hbm {peaks['hbm_gbs']} GB/s ({peaks['source']} copy)",
+                         "dispatch_roof_us": td, "combine_roof_us": tc,
+                         "dispatch_frac": td / d if d else None, "combine_frac": tc / c if c else None})
+        return {"dispatch_us": d, "combine_us": c, "tokens_per_rank": self.tokens, "roofline": roof,
+                "l2": "flushed before each bracket" if flush else self.l2_policy}
+
+    def end_to_end(self, *, steps: int, distributed: bool) -> dict:
+        s = self.spec
+        hosts = [(x.cpu().pin_memory(), l.cpu().pin_memory()) for x, l in zip(self.x, self.logits)]
+        for k in range(3):
+            self.layer.forward_from_host(*hosts[k % len(hosts)])
+        torch.cuda.synchronize()
+        sync_ranks(distributed)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for k in range(steps):
+            result = self.layer.forward_from_host(*hosts[k % len(hosts)])
+            torch.cuda.current_stream().synchronize()  # the caller reads the result every step
+            if int(result[0]) != 0:
+                raise RuntimeError(f"transport status {result.tolist()}")
+        stop.record()
+        torch.cuda.synchronize()
+        ms = device_max(start.elapsed_time(stop), distributed) / steps
+        value = self.world.world_size * self.tokens / (ms * 1e-3)
+        return {"value": value, "unit": "tokens/s", "ms_per_step": ms,
+                "h2d_bytes_per_step": self.tokens * s.hidden * 2 + self.tokens * s.experts * 4,
+                "d2h_bytes_per_step": 32}
+
+
+def alltoall_sweep(world: World, distributed: bool, sizes=None, *, rounds: int = 20) -> list[dict]:
+    """Bus bandwidth of the all-to-all kernel; ``busbw = (n-1) * S / t`` with t the
+    mean round time of the slowest rank (definition: experiments/bench/README.md:111-131
+    of the reference)."""
+    from .ops import alltoall, check_payload, fill_payload
+
+    n, rank, dev = world.world_size, world.rank, world.torch_device
+    sizes = sizes or [1 << 10, 1 << 14, 1 << 18, 1 << 22, 1 << 26]
+    top = max(sizes)
+    max_lanes = 32
+    arena = world.runtime.allocate(2 * n * top + n * max_lanes * 8)
+    reg = world.register(arena, network=False)
+    recv = world.region("a2a_recv", reg, offset=n * top, length=n * top)
+    flags = world.region("a2a_flags", reg, offset=2 * n * top, length=n * max_lanes * 8)
+    table = world.exchange_regions([recv, flags], tag="a2a")
+    send = arena[: n * top]
+    my_flags = arena[2 * n * top:].view(torch.int64)
+    status = torch.zeros(2, dtype=torch.int64, device=dev)
+    errors = torch.zeros(1, dtype=torch.int64, device=dev)
+    out, epoch = [], 0
+    for size in sizes:
+        for p in range(n):
+            fill_payload(send[p * top:], size, 4242, rank, p)
+        for mode in ("vector", "bulk"):
+            lanes = max(1, min(max_lanes, size // 16384))
+            my_flags.zero_()
+            epoch = 0
+            sync_ranks(distributed)
+            kwargs = dict(stride=top, nbytes=size, rank=rank, world=n, lanes=lanes, mode=mode)
+            alltoall(send, table.addresses("a2a_recv"), table.addresses("a2a_flags"), my_flags,
+                     status, epoch0=epoch, rounds=3, **kwargs)
+            epoch += 3
+            sync_ranks(distributed)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            alltoall(send, table.addresses("a2a_recv"), table.addresses("a2a_flags"), my_flags,
+                     status, epoch0=epoch, rounds=rounds, **kwargs)
+            stop.record()
+            torch.cuda.synchronize()
+            t = device_max(start.elapsed_time(stop), distributed) / rounds * 1e-3
+            for s in range(n):
+                if s != rank:
+                    check_payload(arena[n * top + s * top:], size, 4242, s, rank, errors)
+            sync_ranks(distributed)
+            bus = (n - 1) * size / t / 1e9
+            out.append({"bytes_per_peer": size, "mode": mode, "lanes": lanes, "round_us": t * 1e6,
+                        "busbw_gbs": bus, "frac_of_770": bus / NVLINK_GBS,
+                        "wrong_words": int(errors.item()), "status": status.tolist()})
+    return out

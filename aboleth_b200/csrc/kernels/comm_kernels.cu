@@ -28,7 +28,7 @@ struct AllToAllParams {
     std::uint64_t stride;                // bytes between per-peer slices
     std::uint64_t bytes;                 // payload bytes per peer
     std::uint64_t epoch0;                // epoch of round 0 is epoch0 + 1
-    int rank, world, lanes, chain, batched, rounds, include_self;
+    int rank, world, lanes, chain, batched, rounds, include_self, wait;
 };
 
 __device__ __forceinline__ std::uint64_t align_down16(std::uint64_t x) { return x & ~15ull; }
@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(1024) alltoall_kernel(AllToAllParams p) {
                                       epoch);
         }
         aboleth::signal_block(RemoteRegion{reinterpret_cast<std::uint64_t>(remote_flag), 0}, epoch);
-        if (threadIdx.x == 0) {
+        if (p.wait && threadIdx.x == 0) {
             const Status s = aboleth::wait_signal_status(local_flag, epoch);
             ab::set_status(p.status, s, 0x200 + peer);
         }
@@ -250,13 +250,13 @@ AB_EXPORT int ab_alltoall(const void *send, const std::uint64_t *peer_recv,
                           const std::uint64_t *peer_flags, const std::uint64_t *my_flags,
                           unsigned long long *status, std::uint64_t stride, std::uint64_t bytes,
                           std::uint64_t epoch0, int rank, int world, int lanes, int chain,
-                          int batched, int rounds, int include_self, int mode, int threads,
-                          cudaStream_t stream) {
+                          int batched, int rounds, int include_self, int wait, int mode,
+                          int threads, cudaStream_t stream) {
     if (world < 1 || lanes < 1 || chain < 1 || rounds < 1 || threads < 32 || threads > 1024)
         return -1;
     AllToAllParams p{static_cast<const std::uint8_t *>(send), peer_recv, peer_flags, my_flags,
                      status, stride, bytes, epoch0, rank, world, lanes, chain, batched, rounds,
-                     include_self};
+                     include_self, wait};
     const int peers = include_self ? world : world - 1;
     if (peers == 0)
         return 0;

@@ -1,0 +1,280 @@
+"""Executor of the fused expert-parallel dispatch and combine.
+
+``NativeMoESlot`` owns one set of buffers (one in-flight layer) on one rank:
+the peer-visible receive/return segments and flags, registered with the World
+and exchanged once, plus the local routing state.  ``dispatch`` and ``combine``
+are one kernel launch each (csrc/kernels/moe_kernels.cu); the epoch lives in
+device memory and is advanced by the combine kernel, so the pair can be
+captured in a CUDA graph.  API shape follows the reference's executor
+(python/aboleth/moe/native.py:34-178,433-615).
+
+``LocalMoEGroup`` runs several ranks on ONE device inside one process by
+launching every rank's send half before any rank's receive half; it exists for
+tests and single-GPU development, not for performance.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from ..ops._kernels import call, ptr, stream_ptr
+from ..world import World
+from .spec import MoESpec
+
+PHASE_SEND, PHASE_RECV = 1, 2
+_REGIONS = ("recv_payload", "recv_meta", "recv_counts", "dispatch_flags", "returned", "return_flags")
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+@dataclass
+class DispatchResult:
+    """What the expert stage consumes.  Rows are ``[ranks * capacity]``; rows of
+    source rank ``r`` start at ``r * capacity`` and ``recv_counts[r]`` are live."""
+
+    expert_input: torch.Tensor      # [ranks*capacity, hidden] e4m3 or bf16
+    expert_scales: Optional[torch.Tensor]  # [ranks*capacity, hidden/group] fp32
+    expert_ids: torch.Tensor        # [ranks*capacity, k] int32
+    expert_weights: torch.Tensor    # [ranks*capacity, k] fp32
+    expert_pos: torch.Tensor        # [ranks*capacity, k] int32 position inside its expert, -1 unused
+    expert_counts: torch.Tensor     # [experts] int32
+    recv_counts: torch.Tensor       # [ranks] int64
+    topk_ids: torch.Tensor          # [capacity, k] int32 (this rank's tokens)
+    topk_weights: torch.Tensor      # [capacity, k] fp32
+
+
+class MoEBuffers:
+    """Carves one rank's arena.  ``arena`` must be zero-initialised."""
+
+    def __init__(self, spec: MoESpec, arena: torch.Tensor):
+        s = spec
+        rows = s.ranks * s.capacity
+        sizes = {
+            "recv_payload": rows * s.row_bytes,
+            "recv_meta": rows * s.metadata_words * 4,
+            "recv_counts": s.ranks * 8,
+            "dispatch_flags": s.ranks * 8,
+            "returned": rows * s.hidden * 2,
+            "return_flags": s.ranks * 8,
+        }
+        self.offsets, cursor = {}, 0
+        for name in _REGIONS:
+            self.offsets[name] = (cursor, sizes[name])
+            cursor += _align(sizes[name])
+        self.nbytes = cursor
+        if arena.numel() < cursor:
+            raise ValueError(f"arena holds {arena.numel()} bytes, {cursor} are needed")
+        self.arena = arena
+
+    @staticmethod
+    def arena_bytes(spec: MoESpec) -> int:
+        rows = spec.ranks * spec.capacity
+        sizes = [rows * spec.row_bytes, rows * spec.metadata_words * 4, spec.ranks * 8,
+                 spec.ranks * 8, rows * spec.hidden * 2, spec.ranks * 8]
+        return sum(_align(x) for x in sizes)
+
+    def view(self, name: str) -> torch.Tensor:
+        start, size = self.offsets[name]
+        return self.arena[start:start + size]
+
+
+class NativeMoESlot:
+    def __init__(self, spec: MoESpec, rank: int, arena: torch.Tensor,
+                 peer_tables: dict[str, torch.Tensor], *, placement="linear", grid: Optional[int] = None):
+        self.spec, self.rank = spec, int(rank)
+        dev = arena.device
+        self.device = dev
+        self.buffers = MoEBuffers(spec, arena)
+        s, rows = spec, spec.ranks * spec.capacity
+        b = self.buffers
+        self.recv_payload = b.view("recv_payload").view(spec.payload_dtype).view(rows, s.hidden)
+        self.recv_meta = b.view("recv_meta").view(torch.int32).view(rows, s.metadata_words)
+        self.recv_counts = b.view("recv_counts").view(torch.int64)
+        self.dispatch_flags = b.view("dispatch_flags").view(torch.int64)
+        self.returned = b.view("returned").view(torch.bfloat16).view(rows, s.hidden)
+        self.return_flags = b.view("return_flags").view(torch.int64)
+        self.peer_tables = peer_tables  # name -> int64 [ranks] addresses
+        owners = placement if isinstance(placement, (list, tuple)) else spec.owners(placement)
+        self.owners_list = list(owners)
+        self.owners = torch.tensor(self.owners_list, dtype=torch.int32, device=dev)
+        foreign = [e for e, o in enumerate(self.owners_list) if o != self.rank]
+        # Unused choice slots name an expert some other rank owns, at weight 0.
+        self.placeholder = foreign[0] if foreign else -1
+        z = lambda *shape, dtype: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
+        self.source_slots = torch.full((s.capacity, s.ranks), -1, dtype=torch.int32, device=dev)
+        self.send_counts = z(s.ranks, dtype=torch.int64)
+        self.done = z(4, dtype=torch.int32)
+        self.overflow = z(1, dtype=torch.int32)
+        self.epoch = torch.ones(1, dtype=torch.int64, device=dev)
+        self.status = z(2, dtype=torch.int64)
+        self.expert_ids = z(rows, s.top_k, dtype=torch.int32)
+        self.expert_weights = z(rows, s.top_k, dtype=torch.float32)
+        self.expert_pos = torch.full((rows, s.top_k), -1, dtype=torch.int32, device=dev)
+        self.expert_counts = z(s.experts, dtype=torch.int32)
+        self.expert_scales = z(rows, s.scale_cols, dtype=torch.float32) if s.fp8 else None
+        self.topk_ids = z(s.capacity, s.top_k, dtype=torch.int32)
+        self.topk_weights = z(s.capacity, s.top_k, dtype=torch.float32)
+        self.expert_output = z(rows, s.hidden, dtype=torch.bfloat16)
+        self.final_output = z(s.capacity, s.hidden, dtype=torch.bfloat16)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.grid = int(grid) if grid else sms * 4
+        self._ints = (ctypes.c_int * 16)()
+        self._ptrs = (ctypes.c_uint64 * 32)()
+        self._table = None
+
+    # -- construction over a World ------------------------------------------------
+    @classmethod
+    def create(cls, world: World, spec: MoESpec, *, tag: str = "moe", **kwargs) -> "NativeMoESlot":
+        """Allocate, register and exchange one slot's buffers over ``world``."""
+        if spec.ranks != world.world_size:
+            raise ValueError("spec.ranks must equal the world size")
+        arena = world.runtime.allocate(MoEBuffers.arena_bytes(spec))
+        registration = world.register(arena, network=False)
+        layout = MoEBuffers(spec, arena)
+        regions = [world.region(name, registration, offset=layout.offsets[name][0],
+                                length=layout.offsets[name][1]) for name in _REGIONS]
+        table = world.exchange_regions(regions, tag=tag)
+        slot = cls(spec, world.rank, arena, {name: table.addresses(name) for name in _REGIONS},
+                   **kwargs)
+        slot._table = table
+        return slot
+
+    # -- launches ---------------------------------------------------------------------
+    def _geometry(self, num_tokens: int, routing: int, renormalize: bool, phases: int,
+                  weighted: int = 0):
+        s, i = self.spec, self._ints
+        values = [self.rank, s.ranks, s.experts, s.top_k, s.hidden, s.scale_group, s.capacity,
+                  int(s.fp8), int(s.round_scale), self.placeholder, num_tokens, routing,
+                  int(renormalize), phases, weighted, 0]
+        for k, v in enumerate(values):
+            i[k] = v
+        return i
+
+    def _fill(self, pointers: Sequence) -> ctypes.Array:
+        for k, p in enumerate(pointers):
+            self._ptrs[k] = p if isinstance(p, int) else ptr(p)
+        return self._ptrs
+
+    def dispatch(self, tokens: torch.Tensor, ids: Optional[torch.Tensor] = None,
+                 weights: Optional[torch.Tensor] = None, *, logits: Optional[torch.Tensor] = None,
+                 num_tokens: Optional[int] = None, renormalize: bool = False,
+                 phases: int = PHASE_SEND | PHASE_RECV) -> DispatchResult:
+        """Route, quantise and send this rank's tokens; receive and unpack the peers'.
+
+        Give either ``logits`` (fp32 ``[n, experts]``: the router softmax and
+        top-k run inside the kernel) or ``ids`` (int32 ``[n, k]``, -1 = unused)
+        with ``weights`` (fp32 ``[n, k]``).
+        """
+        s = self.spec
+        n = tokens.shape[0] if num_tokens is None else int(num_tokens)
+        if n > s.capacity:
+            raise ValueError(f"{n} tokens exceed the slot capacity {s.capacity}")
+        if tokens.dtype != torch.bfloat16 or tokens.shape[-1] != s.hidden or not tokens.is_contiguous():
+            raise ValueError("tokens must be contiguous bf16 [n, hidden]")
+        routing = 1 if logits is not None else 0
+        if routing:
+            if logits.dtype != torch.float32 or logits.shape[-1] != s.experts:
+                raise ValueError("logits must be fp32 [n, experts]")
+        elif ids is None or weights is None or ids.dtype != torch.int32 or weights.dtype != torch.float32:
+            raise ValueError("ids (int32) and weights (fp32) are required without logits")
+        t = self.peer_tables
+        pointers = [tokens, logits, ids, weights, self.topk_ids, self.topk_weights, self.owners,
+                    self.source_slots, self.send_counts, self.done, self.overflow, self.epoch,
+                    self.status, t["recv_payload"], t["recv_meta"], t["recv_counts"],
+                    t["dispatch_flags"], self.recv_meta, self.recv_counts, self.dispatch_flags,
+                    self.expert_ids, self.expert_weights, self.expert_pos, self.expert_counts,
+                    self.expert_scales]
+        call("ab_ep_dispatch", self._geometry(n, routing, renormalize, phases),
+             ctypes.c_float(s.quant_amax_floor), self._fill(pointers), self.grid, stream_ptr())
+        self._last_tokens = n
+        return DispatchResult(self.recv_payload, self.expert_scales, self.expert_ids,
+                              self.expert_weights, self.expert_pos, self.expert_counts,
+                              self.recv_counts, self.topk_ids, self.topk_weights)
+
+    def combine(self, expert_output: Optional[torch.Tensor] = None, *,
+                expert_offsets: Optional[torch.Tensor] = None, num_tokens: Optional[int] = None,
+                out: Optional[torch.Tensor] = None,
+                phases: int = PHASE_SEND | PHASE_RECV) -> torch.Tensor:
+        """Return expert results to their source ranks and reduce them per token.
+
+        Without ``expert_offsets`` the rows of ``expert_output`` are one partial
+        per received record (``[ranks*capacity, hidden]``, already gate-weighted)
+        and are summed over ranks.  With ``expert_offsets`` (int32 ``[experts]``)
+        ``expert_output`` is in expert-contiguous order and the gate-weighted
+        sum over each record's experts is taken inside the kernel.
+        """
+        s = self.spec
+        n = getattr(self, "_last_tokens", s.capacity) if num_tokens is None else int(num_tokens)
+        y = self.expert_output if expert_output is None else expert_output
+        if y.dtype != torch.bfloat16 or y.shape[-1] != s.hidden or not y.is_contiguous():
+            raise ValueError("expert_output must be contiguous bf16 [rows, hidden]")
+        out = self.final_output if out is None else out
+        t = self.peer_tables
+        pointers = [y, self.expert_ids, self.expert_pos, self.expert_weights, expert_offsets,
+                    self.recv_meta, self.recv_counts, t["returned"], t["return_flags"],
+                    self.return_flags, self.returned, self.source_slots, out, self.done,
+                    self.expert_counts, self.epoch, self.status]
+        call("ab_ep_combine", self._geometry(n, 0, False, phases, int(expert_offsets is not None)),
+             ctypes.c_float(s.quant_amax_floor), self._fill(pointers), self.grid, stream_ptr())
+        return out[:n]
+
+    def reset(self) -> None:
+        """Clear per-layer counters (only needed when a dispatch is not followed by a combine)."""
+        self.expert_counts.zero_()
+        self.send_counts.zero_()
+        self.done.zero_()
+
+    def check(self) -> None:
+        """Raise if a kernel recorded a timeout / malformed record, or a segment overflowed."""
+        status = self.status.tolist()
+        if status[0]:
+            names = {1: "timeout", 2: "completion failure", 3: "malformed record"}
+            raise RuntimeError(f"MoE transport {names.get(status[0], status[0])} "
+                               f"(detail {status[1]:#x}) on rank {self.rank}")
+        if int(self.overflow.item()):
+            raise RuntimeError(f"a destination segment overflowed on rank {self.rank}")
+
+    def manifest(self) -> dict:
+        s = self.spec
+        return {"rank": self.rank, "ranks": s.ranks, "capacity": s.capacity, "hidden": s.hidden,
+                "top_k": s.top_k, "experts": s.experts, "value_type": s.value_type,
+                "metadata_words": s.metadata_words, "arena_bytes": self.buffers.nbytes,
+                "launches_per_layer": 2, "grid": self.grid}
+
+
+class LocalMoEGroup:
+    """``ranks`` slots on one device in one process (tests, single-GPU development)."""
+
+    def __init__(self, spec: MoESpec, device="cuda:0", **kwargs):
+        device = torch.device(device)
+        self.spec = spec
+        arenas = [torch.zeros(MoEBuffers.arena_bytes(spec), dtype=torch.uint8, device=device)
+                  for _ in range(spec.ranks)]
+        layouts = [MoEBuffers(spec, a) for a in arenas]
+        tables = {name: torch.tensor([l.view(name).data_ptr() for l in layouts], dtype=torch.int64,
+                                     device=device) for name in _REGIONS}
+        self.slots = [NativeMoESlot(spec, r, arenas[r], tables, **kwargs) for r in range(spec.ranks)]
+
+    def dispatch(self, tokens: Sequence[torch.Tensor], **per_rank) -> list[DispatchResult]:
+        kw = lambda r: {k: (v[r] if v is not None else None) for k, v in per_rank.items()}  # noqa: E731
+        for r, slot in enumerate(self.slots):
+            slot.dispatch(tokens[r], phases=PHASE_SEND, **kw(r))
+        return [slot.dispatch(tokens[r], phases=PHASE_RECV, **kw(r))
+                for r, slot in enumerate(self.slots)]
+
+    def combine(self, expert_outputs: Sequence[Optional[torch.Tensor]], *,
+                expert_offsets: Optional[Sequence[torch.Tensor]] = None) -> list[torch.Tensor]:
+        off = lambda r: None if expert_offsets is None else expert_offsets[r]  # noqa: E731
+        for r, slot in enumerate(self.slots):
+            slot.combine(expert_outputs[r], expert_offsets=off(r), phases=PHASE_SEND)
+        return [slot.combine(expert_outputs[r], expert_offsets=off(r), phases=PHASE_RECV)
+                for r, slot in enumerate(self.slots)]
+
+    def check(self) -> None:
+        for slot in self.slots:
+            slot.check()

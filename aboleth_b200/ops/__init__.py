@@ -1,0 +1,4 @@
+"""Python entry points of the hand-written sm_100a kernels."""
+from .comm import alltoall, check_payload, fill_payload, pingpong, tier1_exercise
+from .moe_ops import expert_offsets, permute, quant_fp8, router_topk, standin_expert, unpermute
+from ._kernels import launch_count

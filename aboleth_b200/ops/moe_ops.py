@@ -1,0 +1,83 @@
+"""Standalone MoE pieces: fp8 1xG quantisation, router top-k, permute/unpermute.
+
+Kernels: csrc/kernels/moe_kernels.cu.  The fused dispatch and combine live in
+``aboleth_b200.moe``.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ._kernels import call, ptr, stream_ptr
+
+
+def quant_fp8(x: torch.Tensor, *, group: int = 128, amax_floor: float = 1e-4,
+              round_scale: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """bf16 ``[rows, hidden]`` -> (e4m3 ``[rows, hidden]``, fp32 scales ``[rows, hidden/group]``).
+
+    ``scale = max(amax, floor) / 448`` (rounded up to a power of two on request),
+    ``q = clamp(x / scale, +-448)`` rounded to nearest even.
+    """
+    assert x.dtype == torch.bfloat16 and x.is_cuda and x.is_contiguous() and x.dim() == 2
+    rows, hidden = x.shape
+    q = torch.empty(rows, hidden, dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.empty(rows, hidden // group, dtype=torch.float32, device=x.device)
+    call("ab_quant_fp8", ptr(x), ptr(q), ptr(scales), rows, hidden, group, amax_floor,
+         int(round_scale), stream_ptr())
+    return q, scales
+
+
+def router_topk(logits: torch.Tensor, top_k: int, *, renormalize: bool = False
+                ) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 ``[tokens, experts]`` -> (int32 ids ``[tokens, k]``, fp32 softmax weights)."""
+    assert logits.dtype == torch.float32 and logits.is_cuda and logits.is_contiguous()
+    tokens, experts = logits.shape
+    ids = torch.empty(tokens, top_k, dtype=torch.int32, device=logits.device)
+    weights = torch.empty(tokens, top_k, dtype=torch.float32, device=logits.device)
+    call("ab_router_topk", ptr(logits), ptr(ids), ptr(weights), tokens, experts, top_k,
+         int(renormalize), stream_ptr())
+    return ids, weights
+
+
+def expert_offsets(counts: torch.Tensor, *, align: int = 1) -> tuple[torch.Tensor, torch.Tensor]:
+    """Exclusive scan of int32 ``counts`` (each rounded up to ``align``) -> (offsets, total)."""
+    offsets = torch.empty_like(counts)
+    total = torch.empty(1, dtype=torch.int32, device=counts.device)
+    call("ab_expert_offsets", ptr(counts), ptr(offsets), ptr(total), counts.numel(), align,
+         stream_ptr())
+    return offsets, total
+
+
+def permute(src: torch.Tensor, dst: torch.Tensor, expert_ids: torch.Tensor,
+            expert_pos: torch.Tensor, offsets: torch.Tensor, recv_counts: torch.Tensor, *,
+            world: int, capacity: int, src_scales: Optional[torch.Tensor] = None,
+            dst_scales: Optional[torch.Tensor] = None,
+            perm_row: Optional[torch.Tensor] = None) -> None:
+    """Gather received rows into expert-contiguous order (``dst[offsets[e] + pos] = src[row]``)."""
+    top_k = expert_ids.shape[-1]
+    row_bytes = src.shape[-1] * src.element_size()
+    cols = 0 if src_scales is None else src_scales.shape[-1]
+    call("ab_permute", ptr(src), ptr(dst), ptr(src_scales), ptr(dst_scales), ptr(expert_ids),
+         ptr(expert_pos), ptr(offsets), ptr(recv_counts), ptr(perm_row), world, capacity, top_k,
+         row_bytes, cols, stream_ptr())
+
+
+def unpermute(y: torch.Tensor, out: torch.Tensor, expert_ids: torch.Tensor,
+              expert_pos: torch.Tensor, expert_weights: torch.Tensor, offsets: torch.Tensor,
+              recv_counts: torch.Tensor, *, world: int, capacity: int) -> None:
+    """``out[row] = sum_j w[row, j] * y[offsets[id] + pos]`` in fp32, bf16 result."""
+    call("ab_unpermute", ptr(y), ptr(out), ptr(expert_ids), ptr(expert_pos), ptr(expert_weights),
+         ptr(offsets), ptr(recv_counts), world, capacity, expert_ids.shape[-1], y.shape[-1],
+         stream_ptr())
+
+
+def standin_expert(payload: torch.Tensor, scales: Optional[torch.Tensor], y: torch.Tensor,
+                   expert_ids: torch.Tensor, expert_weights: torch.Tensor,
+                   expert_pos: torch.Tensor, recv_counts: torch.Tensor, *, world: int,
+                   capacity: int, group: int) -> None:
+    """Benchmark expert ``f_e(x) = x * (1 + (e mod 7) / 8)``, gate-weighted, record layout."""
+    fp8 = payload.dtype == torch.float8_e4m3fn
+    call("ab_standin_expert", ptr(payload), ptr(scales), ptr(y), ptr(expert_ids),
+         ptr(expert_weights), ptr(expert_pos), ptr(recv_counts), world, capacity,
+         expert_ids.shape[-1], y.shape[-1], group, int(fp8), stream_ptr())

@@ -1,0 +1,2 @@
+"""Parallelism strategies built on the put/signal substrate: expert and tensor parallel."""
+from .ep import ExpertParallelLayer

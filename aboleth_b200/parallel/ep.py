@@ -1,0 +1,75 @@
+"""Expert parallelism: one MoE layer's dispatch -> experts -> combine over a World.
+
+This is the call a user of the framework makes.  ``ExpertParallelLayer`` owns
+one :class:`~aboleth_b200.moe.NativeMoESlot` and runs two communication
+launches per layer around a caller-supplied expert stage.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+
+from ..moe import DispatchResult, MoESpec, NativeMoESlot
+from ..ops import standin_expert
+from ..world import World
+
+ExpertFn = Callable[[DispatchResult, torch.Tensor], Optional[torch.Tensor]]
+
+
+class ExpertParallelLayer:
+    def __init__(self, world: World, spec: MoESpec, *, tag: str = "ep", grid: Optional[int] = None):
+        self.world, self.spec = world, spec
+        self.slot = NativeMoESlot.create(world, spec, tag=tag, grid=grid)
+        self._host_result = torch.zeros(4, dtype=torch.int64).pin_memory()
+        self._staging_x: Optional[torch.Tensor] = None
+        self._staging_logits: Optional[torch.Tensor] = None
+
+    def standin_experts(self, result: DispatchResult, y: torch.Tensor) -> None:
+        """The benchmark's expert stage, ``f_e(x) = x * (1 + (e mod 7)/8)``, gate-weighted."""
+        s = self.spec
+        standin_expert(result.expert_input, result.expert_scales, y, result.expert_ids,
+                       result.expert_weights, result.expert_pos, result.recv_counts,
+                       world=s.ranks, capacity=s.capacity, group=s.scale_group)
+        return None
+
+    def forward(self, tokens: torch.Tensor, logits: torch.Tensor, experts: Optional[ExpertFn] = None,
+                *, renormalize: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``tokens`` bf16 ``[n, hidden]`` and router ``logits`` fp32 ``[n, experts]`` on the device.
+
+        ``experts(result, y)`` either fills ``y`` (one gate-weighted partial row per
+        received record) and returns None, or returns int32 ``[experts]`` offsets when
+        it wrote ``y`` in expert-contiguous order and wants the combine kernel to apply
+        the gates.
+        """
+        result = self.slot.dispatch(tokens, logits=logits, renormalize=renormalize)
+        y = self.slot.expert_output
+        offsets = (experts or self.standin_experts)(result, y)
+        return self.slot.combine(y, expert_offsets=offsets, out=out)
+
+    def forward_from_host(self, tokens_host: torch.Tensor, logits_host: torch.Tensor,
+                          experts: Optional[ExpertFn] = None) -> torch.Tensor:
+        """Same, from pinned host tensors; returns a pinned int64[4] summary
+        (status, detail, overflow, output checksum bits) after the stream drained."""
+        if self._staging_x is None or self._staging_x.shape != tokens_host.shape:
+            dev = self.world.torch_device
+            self._staging_x = torch.empty_like(tokens_host, device=dev)
+            self._staging_logits = torch.empty_like(logits_host, device=dev)
+            self._summary = torch.zeros(4, dtype=torch.int64, device=dev)
+        self._staging_x.copy_(tokens_host, non_blocking=True)
+        self._staging_logits.copy_(logits_host, non_blocking=True)
+        out = self.forward(self._staging_x, self._staging_logits, experts)
+        self._summary[:2].copy_(self.slot.status)
+        self._summary[2:3].copy_(self.slot.overflow)
+        self._summary[3:4].copy_(out.view(torch.int16).to(torch.int64).sum().view(1))
+        self._host_result.copy_(self._summary, non_blocking=True)
+        return self._host_result
+
+    @property
+    def h2d_bytes(self) -> int:
+        s = self.spec
+        return 0 if self._staging_x is None else (
+            self._staging_x.numel() * 2 + self._staging_logits.numel() * 4)
+
+    def check(self) -> None:
+        self.slot.check()
