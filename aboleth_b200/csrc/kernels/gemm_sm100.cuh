@@ -1,0 +1,374 @@
+// tcgen05 / TMEM / TMA building blocks and the persistent warp-specialised GEMM
+// main loop shared by the plain, grouped, all-gather->GEMM and
+// GEMM->reduce-scatter kernels.
+//
+//   C[M, N] (+)= A[M, K] * B[N, K]^T      A, B bf16 K-major, fp32 accumulate in TMEM
+//
+// CTA = 192 threads: warp 0 issues TMA loads (one lane), warp 1 allocates TMEM
+// and issues tcgen05.mma (one lane), warps 2..5 are the epilogue (each owns the
+// 32 TMEM lanes its warp id selects).  One CTA per SM, persistent over tiles of
+// 128 x 256; the accumulator is double buffered in TMEM (2 x 256 columns) so
+// the epilogue of tile i overlaps the main loop of tile i+1.  Operands travel
+// global -> shared by TMA (cp.async.bulk.tensor, 128-byte swizzle, never
+// multicast) through a 4-stage ring of 48 KiB stages.
+//
+// Every wait is bounded.  A role that gives up sets the CTA's abort flag; all
+// roles then leave their loops, the CTA lets copies in flight land, frees its
+// TMEM and returns with Status::Timeout recorded.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace ab::gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;   // 64 bf16 = 128 bytes = one swizzle atom row
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr unsigned kStageBytesA = BM * BK * 2;
+constexpr unsigned kStageBytesB = BN * BK * 2;
+constexpr unsigned kStageBytes = kStageBytesA + kStageBytesB;
+constexpr unsigned kTmemCols = 512;
+constexpr unsigned kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+
+struct SharedState {
+    std::uint64_t full[kStages];
+    std::uint64_t empty[kStages];
+    std::uint64_t tmem_full[2];
+    std::uint64_t tmem_empty[2];
+    std::uint32_t tmem_base;
+    volatile int abort;
+};
+
+// ---- tcgen05 wrappers --------------------------------------------------------------
+
+__device__ __forceinline__ void tmem_alloc(std::uint32_t *holder, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(holder)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(std::uint32_t base, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]; accumulate selects += over =.
+__device__ __forceinline__ void umma_bf16(std::uint32_t d_tmem, std::uint64_t a_desc,
+                                          std::uint64_t b_desc, std::uint32_t idesc,
+                                          std::uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// mbarrier arrives once every tcgen05 operation issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(std::uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets row i.
+__device__ __forceinline__ void tmem_ld32(std::uint32_t addr, float *v) {
+    std::uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+        v[i] = __uint_as_float(r[i]);
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, both K-major.
+__host__ __device__ constexpr std::uint32_t idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<std::uint32_t>(n >> 3) << 17) |
+           (static_cast<std::uint32_t>(m >> 4) << 24);
+}
+
+// Shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte
+// swizzle, 8-row groups 1024 bytes apart; the tile base is 1024-byte aligned.
+__device__ __forceinline__ std::uint64_t smem_desc_sw128(std::uint32_t smem_addr) {
+    return static_cast<std::uint64_t>((smem_addr & 0x3ffffu) >> 4) | (1ull << 16) |
+           (static_cast<std::uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// ---- TMA (tiled, no multicast) --------------------------------------------------------
+
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y,
+                                            std::uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// ---- tile description handed out by a policy -------------------------------------------
+
+struct Tile {
+    int a_row;       // first row of the A tile in the A tensor map
+    int b_row;       // first row of the B tile in the B tensor map
+    int k_blocks;    // K / BK
+    int c_row;       // first output row
+    int c_col;       // first output column
+    int rows_valid;  // output rows of this tile that exist (<= BM)
+    int cols_valid;  // output columns that exist (<= BN)
+    int tag;         // policy-defined (expert, source rank, ...)
+};
+
+// Policy concept:
+//   __device__ bool next(int iteration, Tile &t)          - tile `iteration` of this CTA, false when done
+//   __device__ bool ready(const Tile &t)                  - producer-side gate before loading A (bounded)
+//   __device__ void store(const Tile &t, int row, int col0, const float (&v)[32], bool row_ok)
+//   __device__ void tile_done(const Tile &t)              - called by ONE epilogue thread after the
+//                                                           whole tile was stored (CTA-wide ordered)
+template <typename Policy>
+__device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap *map_a,
+                                              const CUtensorMap *map_b,
+                                              unsigned long long *status) {
+    extern __shared__ std::uint8_t smem_raw[];
+    __shared__ SharedState st;
+    std::uint8_t *tiles = reinterpret_cast<std::uint8_t *>(
+        (reinterpret_cast<std::uintptr_t>(smem_raw) + 1023) & ~static_cast<std::uintptr_t>(1023));
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&st.full[s], 1);
+            mbar_init(&st.empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&st.tmem_full[b], 1);
+            mbar_init(&st.tmem_empty[b], kEpilogueWarps);
+        }
+        st.abort = 0;
+        mbar_fence_init();
+        prefetch_tensormap(map_a);
+        prefetch_tensormap(map_b);
+    }
+    if (warp == 1)
+        tmem_alloc(&st.tmem_base, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const std::uint32_t tmem_base = st.tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            unsigned phase = 0;
+            Tile t;
+            for (int it = 0; !st.abort && policy.next(it, t); ++it) {
+                if (!policy.ready(t)) {
+                    st.abort = 1;
+                    set_status(status, aboleth::Status::Timeout, 0x3000 + t.tag);
+                    break;
+                }
+                for (int kb = 0; kb < t.k_blocks; ++kb) {
+                    if (!mbar_wait(&st.empty[stage], phase ^ 1) || st.abort) {
+                        st.abort = 1;
+                        set_status(status, aboleth::Status::Timeout, 0x3100 + stage);
+                        break;
+                    }
+                    std::uint8_t *sa = tiles + stage * kStageBytes;
+                    mbar_expect_tx(&st.full[stage], kStageBytes);
+                    tma_load_2d(sa, map_a, kb * BK, t.a_row, &st.full[stage]);
+                    tma_load_2d(sa + kStageBytesA, map_b, kb * BK, t.b_row, &st.full[stage]);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr std::uint32_t idesc = idesc_bf16(BM, BN);
+            int stage = 0;
+            unsigned phase = 0;
+            Tile t;
+            for (int it = 0; !st.abort && policy.next(it, t); ++it) {
+                const int buf = it & 1;
+                const unsigned use = (it >> 1) & 1;
+                if (!mbar_wait(&st.tmem_empty[buf], use ^ 1)) {
+                    st.abort = 1;
+                    set_status(status, aboleth::Status::Timeout, 0x3200 + buf);
+                    break;
+                }
+                tc_fence_after();
+                const std::uint32_t d = tmem_base + buf * BN;
+                for (int kb = 0; kb < t.k_blocks && !st.abort; ++kb) {
+                    if (!mbar_wait(&st.full[stage], phase)) {
+                        st.abort = 1;
+                        set_status(status, aboleth::Status::Timeout, 0x3300 + stage);
+                        break;
+                    }
+                    tc_fence_after();
+                    const std::uint32_t sa = smem_u32(tiles + stage * kStageBytes);
+                    const std::uint64_t da = smem_desc_sw128(sa);
+                    const std::uint64_t db = smem_desc_sw128(sa + kStageBytesA);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 bf16 = 32 bytes further along K inside the swizzle atom.
+                        umma_bf16(d, da + (k * UMMA_K * 2 >> 4), db + (k * UMMA_K * 2 >> 4), idesc,
+                                  (kb | k) != 0);
+                    }
+                    umma_commit(&st.empty[stage]);  // stage reusable once these MMAs read it
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                umma_commit(&st.tmem_full[buf]);  // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31
+        Tile t;
+        for (int it = 0; !st.abort && policy.next(it, t); ++it) {
+            const int buf = it & 1;
+            const unsigned use = (it >> 1) & 1;
+            if (!mbar_wait(&st.tmem_full[buf], use)) {
+                st.abort = 1;
+                set_status(status, aboleth::Status::Timeout, 0x3400 + buf);
+                break;
+            }
+            tc_fence_after();
+            const int row = quarter * 32 + lane;
+            const bool row_ok = row < t.rows_valid;
+            const std::uint32_t taddr = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) +
+                                        buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                if (c * 32 >= t.cols_valid)
+                    break;
+                float v[32];
+                tmem_ld32(taddr + c * 32, v);
+                policy.store(t, row, c * 32, v, row_ok);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&st.tmem_empty[buf]);
+            // Tile-complete hook: needs all four epilogue warps' stores.
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == 2 && lane == 0)
+                policy.tile_done(t);
+        }
+    }
+
+    // ---------------- teardown ----------------
+    __syncwarp();
+    if (st.abort) {
+        // Let TMA copies that are still in flight land before the CTA's shared
+        // memory is handed to another CTA.
+        const std::uint64_t t0 = aboleth::detail::globaltimer_ns();
+        while (aboleth::detail::globaltimer_ns() - t0 < 2000000ull)
+            __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1)
+        tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---- host: tensor maps ---------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// bf16 [rows, cols] row-major with `ld` elements between rows; box = box_rows x 64 columns.
+inline bool make_map_bf16(CUtensorMap *map, const void *base, std::uint64_t rows, std::uint64_t cols,
+                          std::uint64_t ld, unsigned box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr)
+        return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
+                           strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS)
+        fprintf(stderr, "aboleth_b200: cuTensorMapEncodeTiled failed with CUresult %d\n", static_cast<int>(rc));
+    return rc == CUDA_SUCCESS;
+}
+
+// Convert 32 fp32 to bf16 and store 64 contiguous bytes (row-major C).
+__device__ __forceinline__ void store_row32_bf16(__nv_bfloat16 *dst, const float (&v)[32],
+                                                 int cols_left) {
+    if (cols_left >= 32 && (reinterpret_cast<std::uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[q * 8 + 0], v[q * 8 + 1]);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
+            o.x = *reinterpret_cast<std::uint32_t *>(&p0);
+            o.y = *reinterpret_cast<std::uint32_t *>(&p1);
+            o.z = *reinterpret_cast<std::uint32_t *>(&p2);
+            o.w = *reinterpret_cast<std::uint32_t *>(&p3);
+            *reinterpret_cast<uint4 *>(dst + q * 8) = o;
+        }
+    } else {
+        for (int i = 0; i < 32 && i < cols_left; ++i)
+            dst[i] = __float2bfloat16_rn(v[i]);
+    }
+}
+
+}  // namespace ab::gemm

@@ -15,7 +15,8 @@ def quant_fp8_reference(x: torch.Tensor, group: int = 128, amax_floor: float = 1
     rows, hidden = x.shape
     xf = x.float().view(rows, hidden // group, group)
     amax = xf.abs().amax(dim=-1).clamp_min(amax_floor)
-    scale = amax / FP8_MAX
+    # IEEE division (torch would multiply by a rounded reciprocal for a scalar divisor).
+    scale = (amax.double() / FP8_MAX).float()
     if round_scale:
         bits = scale.view(torch.int32)
         bumped = (bits & ~0x7FFFFF) + 0x800000
