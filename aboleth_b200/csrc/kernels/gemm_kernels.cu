@@ -1,0 +1,156 @@
+// Plain and grouped (per-expert) bf16 GEMM on tcgen05 / TMEM / TMA.
+//
+//   plain  : C[M, N] = A[M, K] * B[N, K]^T
+//   grouped: for each expert e with rows [offsets[e], offsets[e] + counts[e]) of A:
+//            C[rows, :] = A[rows, :] * W[e][N, K]^T
+//
+// The grouped form is the expert stage between EP dispatch and combine: A is
+// the expert-contiguous activation matrix the permute kernel builds, counts and
+// offsets stay on the device (no host round trip), and a CTA finds its tiles by
+// walking the expert list.  The reference has no GEMM; the baseline for these
+// kernels is cuBLAS through torch.matmul.
+#include "gemm_sm100.cuh"
+
+namespace {
+
+using namespace ab::gemm;
+
+struct PlainPolicy {
+    __nv_bfloat16 *c;
+    int m, n, k, ldc;
+    int tiles_n, tiles_total;
+
+    __device__ __forceinline__ bool next(int it, Tile &t) const {
+        const int idx = blockIdx.x + it * gridDim.x;
+        if (idx >= tiles_total)
+            return false;
+        const int tm = idx / tiles_n, tn = idx - tm * tiles_n;
+        t.a_row = tm * BM;
+        t.b_row = tn * BN;
+        t.k_blocks = (k + BK - 1) / BK;
+        t.c_row = tm * BM;
+        t.c_col = tn * BN;
+        t.rows_valid = min(BM, m - tm * BM);
+        t.cols_valid = min(BN, n - tn * BN);
+        t.tag = 0;
+        return true;
+    }
+    __device__ __forceinline__ bool ready(const Tile &) const { return true; }
+    __device__ __forceinline__ void store(const Tile &t, int row, int col0, const float (&v)[32], bool row_ok) const {
+        if (row_ok)
+            store_row32_bf16(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col0, v,
+                             t.cols_valid - col0);
+    }
+    __device__ __forceinline__ void tile_done(const Tile &) const {}
+};
+
+struct GroupedPolicy {
+    __nv_bfloat16 *c;
+    const int *counts, *offsets;
+    int experts, n, k, ldc, tiles_n;
+    // cursor (per thread): expert `e` starts at linear tile `base`
+    int e, base;
+
+    __device__ __forceinline__ bool next(int it, Tile &t) {
+        const int idx = blockIdx.x + it * gridDim.x;
+        while (e < experts) {
+            const int tiles_e = ((counts[e] + BM - 1) / BM) * tiles_n;
+            if (idx < base + tiles_e)
+                break;
+            base += tiles_e;
+            ++e;
+        }
+        if (e >= experts)
+            return false;
+        const int local = idx - base;
+        const int tm = local / tiles_n, tn = local - tm * tiles_n;
+        const int row0 = offsets[e] + tm * BM;
+        t.a_row = row0;
+        t.b_row = e * n + tn * BN;
+        t.k_blocks = (k + BK - 1) / BK;
+        t.c_row = row0;
+        t.c_col = tn * BN;
+        t.rows_valid = min(BM, counts[e] - tm * BM);
+        t.cols_valid = min(BN, n - tn * BN);
+        t.tag = e;
+        return true;
+    }
+    __device__ __forceinline__ bool ready(const Tile &) const { return true; }
+    __device__ __forceinline__ void store(const Tile &t, int row, int col0, const float (&v)[32], bool row_ok) const {
+        if (row_ok)
+            store_row32_bf16(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col0, v,
+                             t.cols_valid - col0);
+    }
+    __device__ __forceinline__ void tile_done(const Tile &) const {}
+};
+
+template <typename Policy>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b, Policy params,
+                    unsigned long long *status) {
+    Policy policy = params;
+    gemm_mainloop(policy, &map_a, &map_b, status);
+}
+
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    }
+    return sms;
+}
+
+template <typename Kernel>
+bool configure(Kernel kernel) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) ==
+           cudaSuccess;
+}
+
+}  // namespace
+
+// C[M,N] = A[M,K] * B[N,K]^T, all bf16 row-major, lda/ldb/ldc in elements.
+// K and the leading dimensions must be multiples of 8 (16-byte TMA strides).
+AB_EXPORT int ab_gemm_bf16(const void *a, const void *b, void *c, int m, int n, int k, int lda,
+                           int ldb, int ldc, unsigned long long *status, cudaStream_t stream) {
+    if (m < 1 || n < 1 || k < 1 || k % 8 || lda % 8 || ldb % 8 || ldc % 8 ||
+        (reinterpret_cast<std::uintptr_t>(a) | reinterpret_cast<std::uintptr_t>(b) |
+         reinterpret_cast<std::uintptr_t>(c)) & 15)
+        return -1;
+    CUtensorMap map_a, map_b;
+    if (!make_map_bf16(&map_a, a, m, k, lda, BM) || !make_map_bf16(&map_b, b, n, k, ldb, BN))
+        return -2;
+    static bool configured = configure(gemm_tcgen05_kernel<PlainPolicy>);
+    if (!configured)
+        return -3;
+    PlainPolicy p{static_cast<__nv_bfloat16 *>(c), m, n, k, ldc, (n + BN - 1) / BN, 0};
+    p.tiles_total = ((m + BM - 1) / BM) * p.tiles_n;
+    const int grid = p.tiles_total < sm_count() ? p.tiles_total : sm_count();
+    gemm_tcgen05_kernel<PlainPolicy><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p, status);
+    return ab::launch_result("gemm_bf16");
+}
+
+// Grouped GEMM over `experts` problems that share N and K.  a: [total_rows, K],
+// w: [experts, N, K], c: [total_rows, N]; counts/offsets: device int32 [experts].
+AB_EXPORT int ab_grouped_gemm_bf16(const void *a, const void *w, void *c, const int *counts,
+                                   const int *offsets, int experts, int total_rows, int n, int k,
+                                   unsigned long long *status, cudaStream_t stream) {
+    if (experts < 1 || total_rows < 1 || n < 1 || k < 1 || k % 8 || n % 8 ||
+        (reinterpret_cast<std::uintptr_t>(a) | reinterpret_cast<std::uintptr_t>(w) |
+         reinterpret_cast<std::uintptr_t>(c)) & 15)
+        return -1;
+    CUtensorMap map_a, map_b;
+    if (!make_map_bf16(&map_a, a, total_rows, k, k, BM) ||
+        !make_map_bf16(&map_b, w, static_cast<std::uint64_t>(experts) * n, k, k, BN))
+        return -2;
+    static bool configured = configure(gemm_tcgen05_kernel<GroupedPolicy>);
+    if (!configured)
+        return -3;
+    GroupedPolicy p{static_cast<__nv_bfloat16 *>(c), counts, offsets, experts, n, k, n,
+                    (n + BN - 1) / BN, 0, 0};
+    gemm_tcgen05_kernel<GroupedPolicy><<<sm_count(), kThreads, kSmemBytes, stream>>>(map_a, map_b, p,
+                                                                                    status);
+    return ab::launch_result("grouped_gemm_bf16");
+}

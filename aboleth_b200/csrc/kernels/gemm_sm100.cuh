@@ -366,8 +366,10 @@ __device__ __forceinline__ void store_row32_bf16(__nv_bfloat16 *dst, const float
             *reinterpret_cast<uint4 *>(dst + q * 8) = o;
         }
     } else {
-        for (int i = 0; i < 32 && i < cols_left; ++i)
-            dst[i] = __float2bfloat16_rn(v[i]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < cols_left)
+                dst[i] = __float2bfloat16_rn(v[i]);
     }
 }
 

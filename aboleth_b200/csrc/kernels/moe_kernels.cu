@@ -43,6 +43,7 @@ struct EpGeometry {
 struct DispatchParams {
     EpGeometry g;
     int num_tokens, routing, renormalize, phases;
+    int by_warp;                   // 1: one warp per token (throughput), 0: one CTA per token (latency)
     const std::uint32_t *x;        // [T, hidden] bf16
     const float *logits;           // [T, experts]       (routing == 1)
     const int *ids_in;             // [T, k]             (routing == 0)
@@ -103,6 +104,147 @@ __device__ __forceinline__ bool wait_all_peers(const std::uint64_t *flags, int w
     return *s_fail == 0;
 }
 
+// Per-warp scratch of the warp-per-token path.
+struct alignas(16) WarpScratch {
+    int meta[2 + 2 * kMaxTopK + 128 + 2];
+    float scale[128];
+};
+
+__device__ __forceinline__ std::uint64_t shfl_u64(std::uint64_t v, int src) {
+    const unsigned lo = __shfl_sync(0xffffffffu, static_cast<unsigned>(v), src);
+    const unsigned hi = __shfl_sync(0xffffffffu, static_cast<unsigned>(v >> 32), src);
+    return (static_cast<std::uint64_t>(hi) << 32) | lo;
+}
+
+// One warp sends one token: route, reserve slots, quantise, store payload and
+// metadata rows to every destination.  No CTA-level synchronisation.
+__device__ __forceinline__ void send_token_by_warp(const DispatchParams &p, int t, WarpScratch &ws) {
+    const EpGeometry &g = p.g;
+    const int lane = threadIdx.x & 31;
+    const int cols = g.value_fp8 ? g.hidden / g.scale_group : 0;
+    const int words = meta_words(g);
+    const int row_bytes = g.value_fp8 ? g.hidden : g.hidden * 2;
+
+    int id = -1;
+    float w = 0.f;
+    if (p.routing == 1) {
+        warp_softmax_topk(p.logits + static_cast<std::size_t>(t) * g.experts, g.experts, g.top_k,
+                          p.renormalize, id, w);
+    } else if (lane < g.top_k) {
+        id = p.ids_in[t * g.top_k + lane];
+        w = p.weights_in[t * g.top_k + lane];
+    }
+    const bool valid = lane < g.top_k && id >= 0 && id < g.experts;
+    const int owner = valid ? p.owners[id] : -1;
+    if (lane < g.top_k) {
+        if (p.ids_out != nullptr)
+            p.ids_out[t * g.top_k + lane] = id;
+        if (p.weights_out != nullptr)
+            p.weights_out[t * g.top_k + lane] = w;
+    }
+    // Lane d decides for destination rank d.
+    int nsel = 0;
+    for (int j = 0; j < g.top_k; ++j)
+        nsel += __shfl_sync(0xffffffffu, owner, j) == lane;
+    int slot = -1;
+    std::uint64_t my_row = 0, my_meta = 0;
+    if (lane < g.world) {
+        if (nsel > 0) {
+            const unsigned long long got = atomicAdd(p.send_counts + lane, 1ull);
+            if (got < static_cast<unsigned long long>(g.capacity))
+                slot = static_cast<int>(got);
+            else
+                *p.overflow = 1;
+        }
+        p.source_slots[t * g.world + lane] = slot;
+        if (slot >= 0) {
+            const std::size_t row = static_cast<std::size_t>(g.rank) * g.capacity + slot;
+            my_row = p.peer_payload[lane] + row * row_bytes;
+            my_meta = p.peer_meta[lane] + row * words * 4;
+        }
+    }
+    const unsigned live = __ballot_sync(0xffffffffu, slot >= 0);
+
+    // ---- payload: two 512-element steps in flight ----
+    const std::uint32_t *xrow = p.x + static_cast<std::size_t>(t) * (g.hidden / 2);
+    const int chunks = g.hidden / 16;
+    const int lanes_per_group = g.scale_group / 16;
+    for (int base = 0; base < chunks; base += 64) {
+        uint4 a[2], b[2];
+        bool ok[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int c = base + u * 32 + lane;
+            ok[u] = c < chunks;
+            a[u] = make_uint4(0, 0, 0, 0);
+            b[u] = a[u];
+            if (ok[u]) {
+                a[u] = aboleth::detail::ld_stream16(xrow + c * 8);
+                b[u] = aboleth::detail::ld_stream16(xrow + c * 8 + 4);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int c = base + u * 32 + lane;
+            if (g.value_fp8) {
+                const float amax = group_max(amax16(a[u], b[u]), lanes_per_group);
+                const float scale = quant_scale(amax, g.amax_floor, g.round_scale);
+                const uint4 q = quant16(a[u], b[u], scale);
+                if (ok[u] && c % lanes_per_group == 0)
+                    ws.scale[c / lanes_per_group] = scale;
+                for (unsigned m = live; m; m &= m - 1) {
+                    const std::uint64_t row = shfl_u64(my_row, __ffs(m) - 1);
+                    if (ok[u])
+                        aboleth::detail::st_stream16(reinterpret_cast<void *>(row + c * 16), q);
+                }
+            } else {
+                for (unsigned m = live; m; m &= m - 1) {
+                    const std::uint64_t row = shfl_u64(my_row, __ffs(m) - 1);
+                    if (ok[u]) {
+                        aboleth::detail::st_stream16(reinterpret_cast<void *>(row + c * 32), a[u]);
+                        aboleth::detail::st_stream16(reinterpret_cast<void *>(row + c * 32 + 16), b[u]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- metadata rows ----
+    __syncwarp();
+    if (lane == 0)
+        ws.meta[0] = t;
+    for (int c = lane; c < cols; c += 32)
+        ws.meta[2 + 2 * g.top_k + c] = __float_as_int(ws.scale[c]);
+    for (unsigned m = live; m; m &= m - 1) {
+        const int d = __ffs(m) - 1;
+        const bool mine = lane < g.top_k && owner == d;
+        const unsigned sel = __ballot_sync(0xffffffffu, mine);
+        const int n = __popc(sel);
+        if (lane == 0)
+            ws.meta[1] = n;
+        if (mine) {
+            const int idx = __popc(sel & ((1u << lane) - 1));
+            ws.meta[2 + idx] = id;
+            ws.meta[2 + g.top_k + idx] = __float_as_int(w);
+        }
+        if (lane >= n && lane < g.top_k) {
+            ws.meta[2 + lane] = -1;
+            ws.meta[2 + g.top_k + lane] = 0;
+        }
+        __syncwarp();
+        const std::uint64_t dst = shfl_u64(my_meta, d);
+        if ((words & 1) == 0) {
+            for (int i = lane; i < words / 2; i += 32)
+                reinterpret_cast<std::uint64_t *>(dst)[i] =
+                    reinterpret_cast<const std::uint64_t *>(ws.meta)[i];
+        } else {
+            for (int i = lane; i < words; i += 32)
+                reinterpret_cast<int *>(dst)[i] = ws.meta[i];
+        }
+        __syncwarp();
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) ep_dispatch_kernel(DispatchParams p) {
     const EpGeometry &g = p.g;
     __shared__ int s_id[kMaxTopK];
@@ -123,8 +265,14 @@ __global__ void __launch_bounds__(kThreads) ep_dispatch_kernel(DispatchParams p)
     const int words = meta_words(g);
     const int row_bytes = g.value_fp8 ? g.hidden : g.hidden * 2;
 
+    if ((p.phases & kPhaseSend) && p.by_warp) {
+        __shared__ WarpScratch scratch[kThreads / 32];
+        const int warps = gridDim.x * (kThreads / 32);
+        for (int t = blockIdx.x * (kThreads / 32) + warp; t < p.num_tokens; t += warps)
+            send_token_by_warp(p, t, scratch[warp]);
+    }
     if (p.phases & kPhaseSend) {
-        for (int t = blockIdx.x; t < p.num_tokens; t += gridDim.x) {
+        for (int t = blockIdx.x; t < p.num_tokens && !p.by_warp; t += gridDim.x) {
             // ---- routing and slot reservation (warp 0) ----
             if (warp == 0) {
                 int id = -1;
@@ -308,7 +456,7 @@ __global__ void __launch_bounds__(kThreads) ep_dispatch_kernel(DispatchParams p)
 
 struct CombineParams {
     EpGeometry g;
-    int num_tokens, phases, weighted;
+    int num_tokens, phases, weighted, by_warp;
     // expert side
     const std::uint32_t *expert_out;   // bf16 rows: weighted ? [pairs, hidden] : [world*capacity, hidden]
     const int *expert_ids, *expert_pos;
@@ -329,6 +477,113 @@ struct CombineParams {
     unsigned long long *status;
 };
 
+__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4 &y, float w) {
+    acc[0] += w * bf16_lo(y.x); acc[1] += w * bf16_hi(y.x);
+    acc[2] += w * bf16_lo(y.y); acc[3] += w * bf16_hi(y.y);
+    acc[4] += w * bf16_lo(y.z); acc[5] += w * bf16_hi(y.z);
+    acc[6] += w * bf16_lo(y.w); acc[7] += w * bf16_hi(y.w);
+}
+
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&acc)[8]) {
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    return o;
+}
+
+// One warp returns one received record to its source rank.
+__device__ __forceinline__ void return_row_by_warp(const CombineParams &p, int row, int src, int slot) {
+    const EpGeometry &g = p.g;
+    const int lane = threadIdx.x & 31;
+    const int vecs = g.hidden / 8;
+    std::uint8_t *dst = reinterpret_cast<std::uint8_t *>(p.peer_return[src]) +
+        (static_cast<std::size_t>(g.rank) * g.capacity + slot) * g.hidden * 2;
+    if (!p.weighted) {
+        const std::uint32_t *y = p.expert_out + static_cast<std::size_t>(row) * (g.hidden / 2);
+        int v = lane;
+        for (; v + 96 < vecs; v += 128) {
+            const uint4 a = aboleth::detail::ld_stream16(y + v * 4);
+            const uint4 b = aboleth::detail::ld_stream16(y + (v + 32) * 4);
+            const uint4 c = aboleth::detail::ld_stream16(y + (v + 64) * 4);
+            const uint4 d = aboleth::detail::ld_stream16(y + (v + 96) * 4);
+            aboleth::detail::st_stream16(dst + v * 16, a);
+            aboleth::detail::st_stream16(dst + (v + 32) * 16, b);
+            aboleth::detail::st_stream16(dst + (v + 64) * 16, c);
+            aboleth::detail::st_stream16(dst + (v + 96) * 16, d);
+        }
+        for (; v < vecs; v += 32)
+            aboleth::detail::st_stream16(dst + v * 16, aboleth::detail::ld_stream16(y + v * 4));
+        return;
+    }
+    int n = p.recv_meta[static_cast<std::size_t>(row) * meta_words(g) + 1];
+    n = n < 0 ? 0 : (n > g.top_k ? g.top_k : n);
+    int my_row = -1;
+    float my_gate = 0.f;
+    if (lane < n) {
+        const int pos = p.expert_pos[row * g.top_k + lane];
+        if (pos >= 0)
+            my_row = p.expert_offsets[p.expert_ids[row * g.top_k + lane]] + pos;
+        my_gate = p.expert_weights[row * g.top_k + lane];
+    }
+    for (int base = 0; base < vecs; base += 64) {
+        float acc[2][8] = {};
+        for (int j = 0; j < n; ++j) {
+            const int r = __shfl_sync(0xffffffffu, my_row, j);
+            const float w = __shfl_sync(0xffffffffu, my_gate, j);
+            if (r < 0)
+                continue;
+            const std::uint32_t *y = p.expert_out + static_cast<std::size_t>(r) * (g.hidden / 2);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int v = base + u * 32 + lane;
+                if (v < vecs)
+                    add_bf16x8(acc[u], aboleth::detail::ld_stream16(y + v * 4), w);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int v = base + u * 32 + lane;
+            if (v < vecs)
+                aboleth::detail::st_stream16(dst + v * 16, pack_bf16x8(acc[u]));
+        }
+    }
+}
+
+// One warp reduces one token's partial rows over the ranks that hold one.
+__device__ __forceinline__ void reduce_token_by_warp(const CombineParams &p, int t) {
+    const EpGeometry &g = p.g;
+    const int lane = threadIdx.x & 31;
+    const int vecs = g.hidden / 8;
+    int slot = -1;
+    if (lane < g.world)
+        slot = p.source_slots[t * g.world + lane];
+    const unsigned live = __ballot_sync(0xffffffffu, slot >= 0);
+    const std::uint32_t *my_src = p.returned +
+        (static_cast<std::size_t>(lane < g.world ? lane : 0) * g.capacity + (slot < 0 ? 0 : slot)) * (g.hidden / 2);
+    std::uint32_t *out = p.out + static_cast<std::size_t>(t) * (g.hidden / 2);
+    for (int base = 0; base < vecs; base += 64) {
+        float acc[2][8] = {};
+        for (unsigned m = live; m; m &= m - 1) {
+            const std::uint32_t *y = reinterpret_cast<const std::uint32_t *>(
+                shfl_u64(reinterpret_cast<std::uint64_t>(my_src), __ffs(m) - 1));
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int v = base + u * 32 + lane;
+                if (v < vecs)
+                    add_bf16x8(acc[u], aboleth::detail::ld_stream16(y + v * 4), 1.0f);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int v = base + u * 32 + lane;
+            if (v < vecs)
+                *reinterpret_cast<uint4 *>(out + v * 4) = pack_bf16x8(acc[u]);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
     const EpGeometry &g = p.g;
     __shared__ int s_flag;
@@ -339,8 +594,17 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
     const int vecs = g.hidden / 8;  // 16-byte vectors per bf16 row
     const int words = meta_words(g);
 
+    if ((p.phases & kPhaseSend) && p.by_warp) {
+        const int warps = gridDim.x * (kThreads / 32);
+        const int gw = blockIdx.x * (kThreads / 32) + (tid >> 5);
+        for (int src = 0; src < g.world; ++src) {
+            const int count = static_cast<int>(ab::min64(p.recv_counts[src], g.capacity));
+            for (int slot = gw; slot < count; slot += warps)
+                return_row_by_warp(p, src * g.capacity + slot, src, slot);
+        }
+    }
     if (p.phases & kPhaseSend) {
-        const int total = g.world * g.capacity;
+        const int total = p.by_warp ? 0 : g.world * g.capacity;
         for (int row = blockIdx.x; row < total; row += gridDim.x) {
             const int src = row / g.capacity;
             const int slot = row - src * g.capacity;
@@ -406,7 +670,12 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
     if (p.phases & kPhaseRecv) {
         if (!wait_all_peers(p.return_flags, g.world, epoch, p.status, &s_flag, 0x2000))
             return;
-        for (int t = blockIdx.x; t < p.num_tokens; t += gridDim.x) {
+        if (p.by_warp) {
+            const int warps = gridDim.x * (kThreads / 32);
+            for (int t = blockIdx.x * (kThreads / 32) + (tid >> 5); t < p.num_tokens; t += warps)
+                reduce_token_by_warp(p, t);
+        }
+        for (int t = blockIdx.x; t < p.num_tokens && !p.by_warp; t += gridDim.x) {
             for (int v = tid; v < vecs; v += kThreads) {
                 float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                 for (int d = 0; d < g.world; ++d) {
@@ -672,8 +941,13 @@ AB_EXPORT int ab_ep_dispatch(const int *ints, float amax_floor, const std::uint6
     p.routing = ints[11];
     p.renormalize = ints[12];
     p.phases = ints[13];
-    if (!geometry_ok(p.g) || p.num_tokens < 0 || p.num_tokens > p.g.capacity || grid < 1)
+    p.by_warp = ints[15];
+    if (!geometry_ok(p.g) || p.num_tokens < 0 || p.num_tokens > p.g.capacity || grid < 0)
         return -1;
+    if (grid == 0)  // auto: enough CTAs for the tokens, never fewer than 32 for the unpack
+        grid = p.by_warp ? (p.num_tokens + kThreads / 32 - 1) / (kThreads / 32) : p.num_tokens;
+    if (grid < 32)
+        grid = 32;
     int i = 0;
     p.x = reinterpret_cast<const std::uint32_t *>(ptrs[i++]);
     p.logits = reinterpret_cast<const float *>(ptrs[i++]);
@@ -712,8 +986,11 @@ AB_EXPORT int ab_ep_combine(const int *ints, float amax_floor, const std::uint64
     p.num_tokens = ints[10];
     p.phases = ints[13];
     p.weighted = ints[14];
-    if (!geometry_ok(p.g) || p.num_tokens < 0 || p.num_tokens > p.g.capacity || grid < 1)
+    p.by_warp = ints[15];
+    if (!geometry_ok(p.g) || p.num_tokens < 0 || p.num_tokens > p.g.capacity || grid < 0)
         return -1;
+    if (grid == 0)
+        grid = p.by_warp ? 1 << 20 : (p.num_tokens * 8 < 32 ? 32 : p.num_tokens * 8);
     int i = 0;
     p.expert_out = reinterpret_cast<const std::uint32_t *>(ptrs[i++]);
     p.expert_ids = reinterpret_cast<const int *>(ptrs[i++]);

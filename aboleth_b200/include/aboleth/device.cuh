@@ -196,17 +196,17 @@ __device__ __forceinline__ Status wait_signal_status(
     std::uint64_t timeout_ns = ABOLETH_WAIT_TIMEOUT_NS) {
     if (detail::ld_acquire_sys(flag) >= epoch)
         return Status::Ok;
+    // Poll with relaxed loads (cheap), then acquire once the epoch is there.
     const std::uint64_t start = detail::globaltimer_ns();
     unsigned spins = 0;
-    while (true) {
-        if (detail::ld_acquire_sys(flag) >= epoch)
-            return Status::Ok;
-        if (++spins > 32) {
-            __nanosleep(64);
-            if (detail::globaltimer_ns() - start > timeout_ns)
+    while (detail::ld_relaxed_sys(flag) < epoch) {
+        if (++spins > 64) {
+            __nanosleep(32);
+            if ((spins & 15) == 0 && detail::globaltimer_ns() - start > timeout_ns)
                 return Status::Timeout;
         }
     }
+    return detail::ld_acquire_sys(flag) >= epoch ? Status::Ok : Status::Timeout;
 }
 
 __device__ __forceinline__ void wait_signal(

@@ -121,8 +121,12 @@ class NativeMoESlot:
         self.topk_weights = z(s.capacity, s.top_k, dtype=torch.float32)
         self.expert_output = z(rows, s.hidden, dtype=torch.bfloat16)
         self.final_output = z(s.capacity, s.hidden, dtype=torch.bfloat16)
-        sms = torch.cuda.get_device_properties(dev).multi_processor_count
-        self.grid = int(grid) if grid else sms * 4
+        # 0 lets the launcher size the grid from the token count.  `by_warp`
+        # selects one warp per token / row (throughput) over one CTA per token
+        # (latency); None decides per call from the token count.
+        self.grid = int(grid) if grid else 0
+        self.by_warp: Optional[bool] = None
+        self.by_warp_threshold = 512
         self._ints = (ctypes.c_int * 16)()
         self._ptrs = (ctypes.c_uint64 * 32)()
         self._table = None
@@ -148,9 +152,10 @@ class NativeMoESlot:
     def _geometry(self, num_tokens: int, routing: int, renormalize: bool, phases: int,
                   weighted: int = 0):
         s, i = self.spec, self._ints
+        by_warp = (num_tokens > self.by_warp_threshold) if self.by_warp is None else self.by_warp
         values = [self.rank, s.ranks, s.experts, s.top_k, s.hidden, s.scale_group, s.capacity,
                   int(s.fp8), int(s.round_scale), self.placeholder, num_tokens, routing,
-                  int(renormalize), phases, weighted, 0]
+                  int(renormalize), phases, weighted, int(by_warp)]
         for k, v in enumerate(values):
             i[k] = v
         return i

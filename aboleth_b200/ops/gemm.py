@@ -1,0 +1,58 @@
+"""bf16 GEMMs on tcgen05 / TMEM / TMA (kernels: csrc/kernels/gemm_kernels.cu)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ._kernels import _I, _VP, call, declare, ptr, stream_ptr
+
+declare("ab_gemm_bf16", [_VP, _VP, _VP] + [_I] * 6 + [_VP, _VP])
+declare("ab_grouped_gemm_bf16", [_VP] * 5 + [_I] * 4 + [_VP, _VP])
+
+_status: dict[torch.device, torch.Tensor] = {}
+
+
+def gemm_status(device) -> torch.Tensor:
+    """int64[2] status words shared by the GEMM launches on ``device`` (0 = ok)."""
+    device = torch.device(device)
+    if device not in _status:
+        _status[device] = torch.zeros(2, dtype=torch.int64, device=device)
+    return _status[device]
+
+
+def check_gemm_status(device) -> None:
+    status = gemm_status(device).tolist()
+    if status[0]:
+        raise RuntimeError(f"GEMM kernel gave up waiting (status {status[0]}, detail {status[1]:#x})")
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[M, N] = a[M, K] @ b[N, K].T`` with fp32 accumulation in tensor memory."""
+    assert a.dtype == b.dtype == torch.bfloat16 and a.is_cuda and a.dim() == b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1 and a.shape[1] == b.shape[1]
+    m, k = a.shape
+    n = b.shape[0]
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    assert out.stride(1) == 1 and out.shape == (m, n)
+    call("ab_gemm_bf16", ptr(a), ptr(b), ptr(out), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+         ptr(gemm_status(a.device)), stream_ptr())
+    return out
+
+
+def grouped_gemm_bf16(a: torch.Tensor, w: torch.Tensor, counts: torch.Tensor,
+                      offsets: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-expert GEMM: rows ``[offsets[e], offsets[e]+counts[e])`` of ``a`` times ``w[e].T``.
+
+    ``a`` is bf16 ``[rows, K]`` in expert-contiguous order, ``w`` bf16 ``[E, N, K]``,
+    ``counts`` / ``offsets`` int32 ``[E]`` on the device (never read by the host).
+    """
+    assert a.dtype == w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
+    experts, n, k = w.shape
+    assert a.shape[1] == k and counts.dtype == offsets.dtype == torch.int32
+    if out is None:
+        out = torch.empty(a.shape[0], n, dtype=torch.bfloat16, device=a.device)
+    call("ab_grouped_gemm_bf16", ptr(a), ptr(w), ptr(out), ptr(counts), ptr(offsets), experts,
+         a.shape[0], n, k, ptr(gemm_status(a.device)), stream_ptr())
+    return out

@@ -1,0 +1,56 @@
+"""tcgen05 GEMM kernels against fp32 PyTorch references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_err(got, want):
+    return ((got.float() - want).norm() / want.norm().clamp_min(1e-6)).item()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 512), (256, 512, 1024),
+                                   (300, 520, 264), (1024, 3584, 2048), (77, 40, 72)])
+def test_gemm_bf16_matches_fp32(m, n, k):
+    from aboleth_b200.ops import check_gemm_status, gemm_bf16
+
+    g = torch.Generator(device="cuda").manual_seed(m * 7 + n)
+    a = torch.randn(m, k, generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randn(n, k, generator=g, device="cuda").to(torch.bfloat16)
+    out = gemm_bf16(a, b)
+    torch.cuda.synchronize()
+    check_gemm_status("cuda")
+    want = a.float() @ b.float().t()
+    assert _rel_err(out, want) < 5e-3
+    # An exact case: small integers are exact in bf16 and in the fp32 accumulator.
+    ai = torch.randint(-3, 4, (m, k), generator=g, device="cuda").to(torch.bfloat16)
+    bi = torch.randint(-3, 4, (n, k), generator=g, device="cuda").to(torch.bfloat16)
+    exact = (ai.float() @ bi.float().t())
+    got = gemm_bf16(ai, bi).float()
+    torch.cuda.synchronize()
+    assert torch.equal(got, exact.to(torch.bfloat16).float())
+
+
+def test_grouped_gemm_matches_loop_of_matmuls():
+    from aboleth_b200.ops import check_gemm_status, grouped_gemm_bf16
+
+    experts, n, k = 6, 512, 320
+    counts = torch.tensor([0, 5, 128, 200, 1, 131], dtype=torch.int32, device="cuda")
+    align = 8
+    padded = (counts + align - 1) // align * align
+    offsets = (torch.cumsum(padded, 0) - padded).to(torch.int32)
+    rows = int(padded.sum())
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(rows, k, generator=g, device="cuda").to(torch.bfloat16)
+    w = torch.randn(experts, n, k, generator=g, device="cuda").to(torch.bfloat16)
+    out = torch.full((rows, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    grouped_gemm_bf16(a, w, counts, offsets, out)
+    torch.cuda.synchronize()
+    check_gemm_status("cuda")
+    for e in range(experts):
+        lo, cnt = int(offsets[e]), int(counts[e])
+        want = a[lo:lo + cnt].float() @ w[e].float().t()
+        if cnt:
+            assert _rel_err(out[lo:lo + cnt], want) < 5e-3
+        pad = out[lo + cnt:lo + int(padded[e])]
+        assert bool((pad == 7.0).all())  # rows outside the expert are never written

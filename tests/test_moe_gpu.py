@@ -27,15 +27,18 @@ def _inputs(spec, n_per_rank, seed, device, integer=False):
     return toks, ids, wts
 
 
+@pytest.mark.parametrize("by_warp", [False, True])
 @pytest.mark.parametrize("value_type", ["f8E4M3FN", "bf16"])
 @pytest.mark.parametrize("ranks,counts", [(1, [7]), (2, [16, 5]), (4, [0, 1, 9, 16])])
-def test_dispatch_standin_combine_matches_oracle(value_type, ranks, counts):
+def test_dispatch_standin_combine_matches_oracle(value_type, ranks, counts, by_warp):
     from aboleth_b200.moe import LocalMoEGroup, MoESpec
     from aboleth_b200.moe.reference import standin_layer_reference
     from aboleth_b200.ops import standin_expert
 
     spec = MoESpec(capacity=16, hidden=256, top_k=2, experts=16, ranks=ranks, value_type=value_type)
     group = LocalMoEGroup(spec)
+    for slot in group.slots:
+        slot.by_warp = by_warp
     toks, ids, wts = _inputs(spec, counts, 1, "cuda")
     for r in range(ranks):  # some unused choices
         if counts[r] > 1:
@@ -59,11 +62,14 @@ def test_dispatch_standin_combine_matches_oracle(value_type, ranks, counts):
         assert [int(s.epoch.item()) for s in group.slots] == [layer + 2] * ranks
 
 
-def test_dispatch_records_are_rank_deduplicated_and_exact():
+@pytest.mark.parametrize("by_warp", [False, True])
+def test_dispatch_records_are_rank_deduplicated_and_exact(by_warp):
     from aboleth_b200.moe import LocalMoEGroup, MoESpec
 
     spec = MoESpec(capacity=8, hidden=128, top_k=4, experts=8, ranks=2, value_type="bf16")
     group = LocalMoEGroup(spec)
+    for slot in group.slots:
+        slot.by_warp = by_warp
     toks, ids, wts = _inputs(spec, [8, 3], 2, "cuda", integer=True)
     results = group.dispatch(toks, ids=ids, weights=wts)
     torch.cuda.synchronize()
@@ -100,12 +106,15 @@ def test_dispatch_records_are_rank_deduplicated_and_exact():
     assert torch.equal(counts, expect)
 
 
-def test_weighted_combine_with_permute_is_exact_for_integers():
+@pytest.mark.parametrize("by_warp", [False, True])
+def test_weighted_combine_with_permute_is_exact_for_integers(by_warp):
     from aboleth_b200.moe import LocalMoEGroup, MoESpec
     from aboleth_b200.ops import expert_offsets, permute
 
     spec = MoESpec(capacity=8, hidden=128, top_k=2, experts=4, ranks=2, value_type="bf16")
     group = LocalMoEGroup(spec)
+    for slot in group.slots:
+        slot.by_warp = by_warp
     toks, ids, _ = _inputs(spec, [8, 6], 3, "cuda", integer=True)
     wts = [torch.ones_like(i, dtype=torch.float32) for i in ids]
     results = group.dispatch(toks, ids=ids, weights=wts)
@@ -130,6 +139,38 @@ def test_weighted_combine_with_permute_is_exact_for_integers():
     for r in range(2):
         mult = (ids[r].float() + 1).sum(dim=-1, keepdim=True)
         assert torch.equal(outs[r].float(), toks[r].float() * mult)
+
+
+def test_full_width_rows_by_warp_and_by_cta_agree():
+    """hidden 7168 (14 warp steps, 56 scale groups): both send paths give identical records."""
+    from aboleth_b200.moe import LocalMoEGroup, MoESpec
+
+    spec = MoESpec(capacity=24, hidden=7168, top_k=8, experts=64, ranks=2)
+    toks, ids, wts = _inputs(spec, [24, 17], 11, "cuda")
+    outs = []
+    for by_warp in (False, True):
+        group = LocalMoEGroup(spec)
+        for slot in group.slots:
+            slot.by_warp = by_warp
+        res = group.dispatch(toks, ids=ids, weights=wts)
+        torch.cuda.synchronize()
+        group.check()
+        per_rank = []
+        for r in range(2):
+            slot = group.slots[r]
+            rows = []
+            for src in range(2):
+                n = int(res[r].recv_counts[src])
+                seg = slice(src * 24, src * 24 + n)
+                order = torch.argsort(slot.recv_meta[seg, 0])
+                rows.append((slot.recv_meta[seg][order].cpu(),
+                             slot.recv_payload[seg].view(torch.uint8)[order].cpu()))
+            per_rank.append(rows)
+        outs.append(per_rank)
+    for r in range(2):
+        for src in range(2):
+            assert torch.equal(outs[0][r][src][0], outs[1][r][src][0])
+            assert torch.equal(outs[0][r][src][1], outs[1][r][src][1])
 
 
 def test_fused_router_matches_standalone_and_torch():
