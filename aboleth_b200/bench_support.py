@@ -136,6 +136,9 @@ class EpLayerBench:
                 self.flusher()
             sync_ranks(distributed)
             e0, e1, e2, e3 = ev(), ev(), ev(), ev()
+            # Keep the GPU busy while the host enqueues, so that the bracket
+            # measures the kernel and not the host's launch latency.
+            torch.cuda._sleep(100_000)
             e0.record()
             res = slot.dispatch(self.x[i], logits=self.logits[i])
             e1.record()
@@ -143,6 +146,7 @@ class EpLayerBench:
             if flush:
                 self.flusher()
             sync_ranks(distributed)
+            torch.cuda._sleep(100_000)
             e2.record()
             slot.combine(slot.expert_output)
             e3.record()

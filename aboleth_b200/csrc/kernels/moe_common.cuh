@@ -39,12 +39,24 @@ __device__ __forceinline__ float quant_scale(float amax, float floor_, int round
     return scale;
 }
 
+// x / scale.  The default is the hardware's approximate division (about 2 ulp,
+// far below an e4m3 quantum; a value that sits on a rounding tie may land on
+// the other neighbour than IEEE division would pick).  Define
+// ABOLETH_EXACT_QUANT_DIV for bit-exact IEEE division at several times the cost.
+__device__ __forceinline__ float quant_div(float x, float scale) {
+#ifdef ABOLETH_EXACT_QUANT_DIV
+    return x / scale;
+#else
+    return __fdividef(x, scale);
+#endif
+}
+
 __device__ __forceinline__ std::uint32_t fp8x4(float a, float b, float c, float d, float scale) {
     const float lo = -kFp8Max, hi = kFp8Max;
-    a = fminf(fmaxf(a / scale, lo), hi);
-    b = fminf(fmaxf(b / scale, lo), hi);
-    c = fminf(fmaxf(c / scale, lo), hi);
-    d = fminf(fmaxf(d / scale, lo), hi);
+    a = fminf(fmaxf(quant_div(a, scale), lo), hi);
+    b = fminf(fmaxf(quant_div(b, scale), lo), hi);
+    c = fminf(fmaxf(quant_div(c, scale), lo), hi);
+    d = fminf(fmaxf(quant_div(d, scale), lo), hi);
     const std::uint32_t p0 = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
     const std::uint32_t p1 = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
     return p0 | (p1 << 16);
@@ -81,8 +93,10 @@ __device__ __forceinline__ float group_max(float v, int width) {
 // the lower index.  Lane l holds experts l, l+32, ...  On return lane j < top_k
 // holds (id, weight) of the j-th choice.  `renormalize` divides the selected
 // probabilities by their sum.
-__device__ __forceinline__ void warp_softmax_topk(const float *logits, int experts, int top_k,
-                                                  int renormalize, int &out_id, float &out_w) {
+template <int PER_LANE>
+__device__ __forceinline__ void warp_softmax_topk_n(const float *logits, int experts, int top_k,
+                                                    int renormalize, int &out_id, float &out_w) {
+    constexpr int kMaxExpertsPerLane = PER_LANE;
     const int lane = threadIdx.x & 31;
     float v[kMaxExpertsPerLane];
     float mx = -INFINITY;
@@ -138,6 +152,16 @@ __device__ __forceinline__ void warp_softmax_topk(const float *logits, int exper
     }
     if (renormalize && picked_sum > 0.f)
         out_w /= picked_sum;
+}
+
+__device__ __forceinline__ void warp_softmax_topk(const float *logits, int experts, int top_k,
+                                                  int renormalize, int &out_id, float &out_w) {
+    if (experts <= 128)
+        warp_softmax_topk_n<4>(logits, experts, top_k, renormalize, out_id, out_w);
+    else if (experts <= 256)
+        warp_softmax_topk_n<8>(logits, experts, top_k, renormalize, out_id, out_w);
+    else
+        warp_softmax_topk_n<kMaxExpertsPerLane>(logits, experts, top_k, renormalize, out_id, out_w);
 }
 
 }  // namespace ab::moe

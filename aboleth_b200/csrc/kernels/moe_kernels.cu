@@ -69,10 +69,17 @@ struct DispatchParams {
     int *expert_pos;               // [world*capacity, k]
     int *expert_counts;            // [experts]
     float *expert_scales;          // [world*capacity, cols]   (fp8 only)
+    unsigned long long *trace;     // optional [8]: %globaltimer stamps of CTA 0 and of the last CTA
 };
 
 __device__ __forceinline__ int meta_words(const EpGeometry &g) {
     return 2 + 2 * g.top_k + (g.value_fp8 ? g.hidden / g.scale_group : 0);
+}
+
+// Phase stamps for the tracing buffer: slot i <- %globaltimer (ns).
+__device__ __forceinline__ void stamp(unsigned long long *trace, int slot, bool who) {
+    if (trace != nullptr && who)
+        trace[slot] = aboleth::detail::globaltimer_ns();
 }
 
 // Thread 0 of every CTA calls this after a CTA barrier.  Returns true in the
@@ -165,42 +172,44 @@ __device__ __forceinline__ void send_token_by_warp(const DispatchParams &p, int 
     }
     const unsigned live = __ballot_sync(0xffffffffu, slot >= 0);
 
-    // ---- payload: two 512-element steps in flight ----
+    // ---- payload: four 512-element steps (128 bytes per lane) in flight ----
     const std::uint32_t *xrow = p.x + static_cast<std::size_t>(t) * (g.hidden / 2);
     const int chunks = g.hidden / 16;
     const int lanes_per_group = g.scale_group / 16;
-    for (int base = 0; base < chunks; base += 64) {
-        uint4 a[2], b[2];
-        bool ok[2];
+    constexpr int kDepth = 4;
+    for (int base = 0; base < chunks; base += 32 * kDepth) {
+        uint4 a[kDepth], b[kDepth];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kDepth; ++u) {
             const int c = base + u * 32 + lane;
-            ok[u] = c < chunks;
             a[u] = make_uint4(0, 0, 0, 0);
             b[u] = a[u];
-            if (ok[u]) {
+            if (c < chunks) {
                 a[u] = aboleth::detail::ld_stream16(xrow + c * 8);
                 b[u] = aboleth::detail::ld_stream16(xrow + c * 8 + 4);
             }
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kDepth; ++u) {
             const int c = base + u * 32 + lane;
+            const bool ok = c < chunks;
+            if (base + u * 32 >= chunks)
+                break;
             if (g.value_fp8) {
                 const float amax = group_max(amax16(a[u], b[u]), lanes_per_group);
                 const float scale = quant_scale(amax, g.amax_floor, g.round_scale);
                 const uint4 q = quant16(a[u], b[u], scale);
-                if (ok[u] && c % lanes_per_group == 0)
+                if (ok && c % lanes_per_group == 0)
                     ws.scale[c / lanes_per_group] = scale;
                 for (unsigned m = live; m; m &= m - 1) {
                     const std::uint64_t row = shfl_u64(my_row, __ffs(m) - 1);
-                    if (ok[u])
+                    if (ok)
                         aboleth::detail::st_stream16(reinterpret_cast<void *>(row + c * 16), q);
                 }
             } else {
                 for (unsigned m = live; m; m &= m - 1) {
                     const std::uint64_t row = shfl_u64(my_row, __ffs(m) - 1);
-                    if (ok[u]) {
+                    if (ok) {
                         aboleth::detail::st_stream16(reinterpret_cast<void *>(row + c * 32), a[u]);
                         aboleth::detail::st_stream16(reinterpret_cast<void *>(row + c * 32 + 16), b[u]);
                     }
@@ -245,7 +254,7 @@ __device__ __forceinline__ void send_token_by_warp(const DispatchParams &p, int 
     }
 }
 
-__global__ void __launch_bounds__(kThreads) ep_dispatch_kernel(DispatchParams p) {
+__global__ void __launch_bounds__(kThreads, 4) ep_dispatch_kernel(DispatchParams p) {
     const EpGeometry &g = p.g;
     __shared__ int s_id[kMaxTopK];
     __shared__ float s_w[kMaxTopK];
@@ -264,6 +273,8 @@ __global__ void __launch_bounds__(kThreads) ep_dispatch_kernel(DispatchParams p)
     const int cols = g.value_fp8 ? g.hidden / g.scale_group : 0;
     const int words = meta_words(g);
     const int row_bytes = g.value_fp8 ? g.hidden : g.hidden * 2;
+    const bool tracer = blockIdx.x == 0 && tid == 0;
+    stamp(p.trace, 0, tracer);
 
     if ((p.phases & kPhaseSend) && p.by_warp) {
         __shared__ WarpScratch scratch[kThreads / 32];
@@ -387,9 +398,12 @@ __global__ void __launch_bounds__(kThreads) ep_dispatch_kernel(DispatchParams p)
 
         // ---- publication: the last CTA writes counts and one flag per peer ----
         __syncthreads();
+        stamp(p.trace, 1, tracer);
         if (tid == 0)
             s_flag = arrive_last(p.done + 0) ? 1 : 0;
         __syncthreads();
+        stamp(p.trace, 2, tracer);
+        stamp(p.trace, 5, s_flag && tid == 0);
         if (s_flag && tid < g.world) {
             const unsigned long long n = ab::min64(
                 aboleth::detail::ld_relaxed_sys(reinterpret_cast<const std::uint64_t *>(p.send_counts + tid)),
@@ -407,6 +421,7 @@ __global__ void __launch_bounds__(kThreads) ep_dispatch_kernel(DispatchParams p)
     if (p.phases & kPhaseRecv) {
         if (!wait_all_peers(p.flags, g.world, epoch, p.status, &s_flag, 0x1000))
             return;
+        stamp(p.trace, 3, tracer);
         // One warp per received record.
         const int warps = gridDim.x * (kThreads / 32);
         const int total = g.world * g.capacity;
@@ -451,6 +466,7 @@ __global__ void __launch_bounds__(kThreads) ep_dispatch_kernel(DispatchParams p)
                     p.expert_scales[static_cast<std::size_t>(row) * cols + c] =
                         __int_as_float(meta[2 + 2 * g.top_k + c]);
         }
+        stamp(p.trace, 4, tracer);
     }
 }
 
@@ -475,6 +491,7 @@ struct CombineParams {
     int *expert_counts;                 // zeroed at the end (self-cleaning)
     unsigned long long *epoch;
     unsigned long long *status;
+    unsigned long long *trace;          // optional [8]
 };
 
 __device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4 &y, float w) {
@@ -593,6 +610,8 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
     const std::uint64_t epoch = *p.epoch;
     const int vecs = g.hidden / 8;  // 16-byte vectors per bf16 row
     const int words = meta_words(g);
+    const bool tracer = blockIdx.x == 0 && tid == 0;
+    stamp(p.trace, 0, tracer);
 
     if ((p.phases & kPhaseSend) && p.by_warp) {
         const int warps = gridDim.x * (kThreads / 32);
@@ -656,9 +675,11 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
                 __syncthreads();
         }
         __syncthreads();
+        stamp(p.trace, 1, tracer);
         if (tid == 0)
             s_flag = arrive_last(p.done + 1) ? 1 : 0;
         __syncthreads();
+        stamp(p.trace, 2, tracer);
         if (s_flag && tid < g.world) {
             std::uint64_t *flag = reinterpret_cast<std::uint64_t *>(p.peer_return_flags[tid]) + g.rank;
             aboleth::detail::st_release_sys(flag, epoch);
@@ -670,6 +691,7 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
     if (p.phases & kPhaseRecv) {
         if (!wait_all_peers(p.return_flags, g.world, epoch, p.status, &s_flag, 0x2000))
             return;
+        stamp(p.trace, 3, tracer);
         if (p.by_warp) {
             const int warps = gridDim.x * (kThreads / 32);
             for (int t = blockIdx.x * (kThreads / 32) + (tid >> 5); t < p.num_tokens; t += warps)
@@ -700,6 +722,7 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
         // Close the layer: the last CTA clears the expert counters and
         // advances the epoch for the next dispatch.
         __syncthreads();
+        stamp(p.trace, 4, tracer);
         if (tid == 0)
             s_flag = arrive_last(p.done + 2) ? 1 : 0;
         __syncthreads();
@@ -974,6 +997,7 @@ AB_EXPORT int ab_ep_dispatch(const int *ints, float amax_floor, const std::uint6
     p.expert_pos = reinterpret_cast<int *>(ptrs[i++]);
     p.expert_counts = reinterpret_cast<int *>(ptrs[i++]);
     p.expert_scales = reinterpret_cast<float *>(ptrs[i++]);
+    p.trace = reinterpret_cast<unsigned long long *>(ptrs[i++]);
     ep_dispatch_kernel<<<resident_grid(ep_dispatch_kernel, grid), kThreads, 0, stream>>>(p);
     return ab::launch_result("ep_dispatch");
 }
@@ -1009,6 +1033,7 @@ AB_EXPORT int ab_ep_combine(const int *ints, float amax_floor, const std::uint64
     p.expert_counts = reinterpret_cast<int *>(ptrs[i++]);
     p.epoch = reinterpret_cast<unsigned long long *>(ptrs[i++]);
     p.status = reinterpret_cast<unsigned long long *>(ptrs[i++]);
+    p.trace = reinterpret_cast<unsigned long long *>(ptrs[i++]);
     ep_combine_kernel<<<resident_grid(ep_combine_kernel, grid), kThreads, 0, stream>>>(p);
     return ab::launch_result("ep_combine");
 }

@@ -127,6 +127,8 @@ class NativeMoESlot:
         self.grid = int(grid) if grid else 0
         self.by_warp: Optional[bool] = None
         self.by_warp_threshold = 512
+        # Optional device trace: %globaltimer stamps (ns) of kernel phases, see trace().
+        self.trace_buffer: Optional[torch.Tensor] = None
         self._ints = (ctypes.c_int * 16)()
         self._ptrs = (ctypes.c_uint64 * 32)()
         self._table = None
@@ -193,7 +195,7 @@ class NativeMoESlot:
                     self.status, t["recv_payload"], t["recv_meta"], t["recv_counts"],
                     t["dispatch_flags"], self.recv_meta, self.recv_counts, self.dispatch_flags,
                     self.expert_ids, self.expert_weights, self.expert_pos, self.expert_counts,
-                    self.expert_scales]
+                    self.expert_scales, self.trace_buffer]
         call("ab_ep_dispatch", self._geometry(n, routing, renormalize, phases),
              ctypes.c_float(s.quant_amax_floor), self._fill(pointers), self.grid, stream_ptr())
         self._last_tokens = n
@@ -223,10 +225,22 @@ class NativeMoESlot:
         pointers = [y, self.expert_ids, self.expert_pos, self.expert_weights, expert_offsets,
                     self.recv_meta, self.recv_counts, t["returned"], t["return_flags"],
                     self.return_flags, self.returned, self.source_slots, out, self.done,
-                    self.expert_counts, self.epoch, self.status]
+                    self.expert_counts, self.epoch, self.status, self.trace_buffer]
         call("ab_ep_combine", self._geometry(n, 0, False, phases, int(expert_offsets is not None)),
              ctypes.c_float(s.quant_amax_floor), self._fill(pointers), self.grid, stream_ptr())
         return out[:n]
+
+    def enable_trace(self) -> None:
+        """Record phase stamps of the next kernels (CTA 0 and the publishing CTA)."""
+        self.trace_buffer = torch.zeros(8, dtype=torch.int64, device=self.device)
+
+    def trace(self) -> dict:
+        """Phase durations (us) of the last traced kernel: send, publish, wait, finish."""
+        t = self.trace_buffer.tolist()
+        us = lambda a, b: (t[b] - t[a]) / 1e3 if t[a] and t[b] else None  # noqa: E731
+        return {"send_us": us(0, 1), "publish_us": us(1, 2), "wait_us": us(2, 3),
+                "finish_us": us(3, 4), "total_us": us(0, 4),
+                "publisher_at_us": us(0, 5) if t[5] else None}
 
     def reset(self) -> None:
         """Clear per-layer counters (only needed when a dispatch is not followed by a combine)."""
