@@ -367,7 +367,10 @@ void verify_submit(const Op &op, const Scope &scope) {
         if (cmd->kind == "post_nop" && i + 1 != op.operands.size())
             fail(op, "post_nop may only be the last command of a submission");
         const std::string after = cmd->get("after");
-        if (!segment_open) {
+        if (op.has("publicationsOrdered")) {
+            // order-publications moved payload ahead of the (chained) signals; the
+            // per-segment chain rule was checked before that rewrite.
+        } else if (!segment_open) {
             if (!after.empty() && in_batch.count(after))
                 fail(op, "the first command of a segment depends on a command in the batch");
         } else if (after != previous) {

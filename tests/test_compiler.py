@@ -1,0 +1,229 @@
+"""Tier-2 specializer: pass behaviour, emitted-code facts and golden files (no GPU).
+
+The golden check is the compile-only configuration: the all-to-all program for
+world 2, rank 0, 4096 int8 bytes per peer, lowered through the whole pipeline,
+with batch count, fence kind and flag writes asserted.
+"""
+import json
+import os
+import subprocess
+from pathlib import Path
+
+import pytest
+
+from aboleth_b200.compiler import (OPTIMIZATIONS, CompileError, ProgramBuilder, build_artifact,
+                                   compilation, compile_program, enabled_optimizations, pipeline_key,
+                                   programs)
+from aboleth_b200.compiler.driver import _affine
+from aboleth_b200.compiler.goldens import all_files
+
+GOLDENS = Path(__file__).parent / "goldens"
+
+
+def _compile(builder, backend="p2p", **kw):
+    kw.setdefault("rank", 0)
+    kw.setdefault("world_size", 2)
+    with compilation(backend, **kw):
+        return compile_program(builder)
+
+
+def test_goldens_are_current():
+    files = all_files()
+    assert len(files) > 100
+    stale = [n for n, text in files.items()
+             if not (GOLDENS / n).exists() or (GOLDENS / n).read_text() != text]
+    assert not stale, f"regenerate with python -m aboleth_b200.compiler.goldens --write tests/goldens: {stale[:5]}"
+
+
+def test_alltoall_p2p_golden_facts():
+    c = _compile(programs.alltoall(4096))
+    f = c.facts
+    assert f["batches"] == 1 and f["commands"] == 2
+    assert f["fences"] == ["bar.sync", "st.release.sys", "ld.acquire.sys"]  # no membar.sys before the signal
+    assert f["system_fences"] == 0 and f["barriers"] == 1
+    assert f["flag_writes"] == ["release.sys:epoch"] and f["flag_reads"] == ["acquire.sys>=epoch"]
+    assert f["completion"] == "vacuous" and f["strong_signals"] == 1 and f["weak_signals"] == 0
+    assert f["exclusive_issuers"] == 0  # pid + (pid >= RANK) is not proven injective
+    assert "submit %t4 %s6 batch=2" in c.ir and "mode=P2PRelease" in c.ir
+    assert "t2::put_p2p<512>" in c.cuda  # smallest power of two covering 4096 bytes
+    assert "fence_acq_rel_sys" not in c.cuda and c.cuda.count("st_release_sys") == 1
+
+
+def test_alltoall_proxy_one_reservation_two_commands():
+    f = _compile(programs.alltoall(4096), "proxy").facts
+    assert (f["reservations"], f["commands"], f["ready_stores"], f["completion_waits"]) == (1, 2, 1, 1)
+    assert f["flag_writes"] == ["strong:epoch"]
+
+
+def test_put_without_signal_gets_barrier_and_system_fence():
+    b = ProgramBuilder("lonely", args=[("src", "ptr"), ("ep", "table"), ("tab", "table")])
+    e = b.endpoint("ep", 1)
+    t = b.put(e, b.remote("tab", 1), b.local("src"), bytes=8192)
+    b.wait(t)
+    f = _compile(b).facts
+    assert f["fences"] == ["bar.sync", "membar.sys"] and f["system_fences"] == 1
+
+
+def test_standalone_signal_is_weak_and_switch_controls_it():
+    b = ProgramBuilder("ack", args=[("ep", "table"), ("tab", "table")])
+    e = b.endpoint("ep", 1)
+    b.signal(e, b.remote("tab", 1), epoch=7)
+    assert _compile(b).facts["weak_signals"] == 1
+    assert _compile(b, passes="-plan-publication").facts["strong_signals"] == 1
+
+
+def test_valid_extent_trimming_and_switch():
+    b = ProgramBuilder("trim", args=[("src", "ptr"), ("ep", "table"), ("tab", "table"), ("n", "i64")])
+    e = b.endpoint("ep", 1)
+    src = b.local("src", valid=("n", 64, 128), at=256)
+    t = b.put(e, b.remote("tab", 1), src, bytes=8192)
+    b.wait(t)
+    on = _compile(b)
+    assert "ab_valid_bytes(8192,n,64,128,256)" in on.ir and on.facts["trimmed_puts"] == 1
+    off = _compile(b, passes="-valid-extents")
+    assert "ab_checked_bytes(8192,n,64,128,256)" in off.ir and off.facts["trimmed_puts"] == 0
+
+
+def test_inline_forwarding_requires_exact_tiling():
+    def program(widths, mention_again=False):
+        b = ProgramBuilder("hdr", args=[("stage", "ptr"), ("ep", "table"), ("tab", "table"), ("v", "i64")])
+        e = b.endpoint("ep", 1)
+        offset = 0
+        for w in widths:
+            b.store("stage", offset=offset, width=w, value="v")
+            offset += w // 8
+        if mention_again:
+            b.store("stage", offset=64, width=32, value="v")
+        t = b.put(e, b.remote("tab", 1), b.local("stage"), bytes=12)
+        b.signal(e, b.remote("tab", 1, offset=64), epoch=1, after=t)
+        return b
+
+    good = _compile(program([32, 32, 32]))
+    assert good.passes["forward-inline-payloads"] == 1 and "post_inline" in good.ir and "store stage" not in good.ir
+    assert good.facts["inline_puts"] == 1 and good.facts["cooperative_puts"] == 0
+    assert _compile(program([32, 32]))  .passes["forward-inline-payloads"] == 0   # hole at the end
+    assert _compile(program([32, 32, 32], True)).passes["forward-inline-payloads"] == 0  # extra store to the base
+    assert _compile(program([32, 32, 32]), passes="-forward-inline-payloads").passes["forward-inline-payloads"] == 0
+    assert _compile(program([32, 32, 32]), "proxy").passes["forward-inline-payloads"] == 0  # only p2p, rdma, ionic
+
+
+def test_planned_wait_interval_respects_reuse_policy_and_queue():
+    def k(c):
+        import re
+        return int(re.search(r"interval=(\d+)", c.ir).group(1))
+
+    prog = programs.stream("pipelined", 1, 256, reuse=32)
+    assert k(_compile(prog, "rdma")) == 16                       # transport preference 16
+    assert k(_compile(prog, "proxy")) == 8                       # proxy prefers 8
+    assert k(_compile(prog, "rdma", completion_interval=4)) == 4
+    assert k(_compile(prog, "rdma", queue_capacity=9)) == 4      # (9-1)/2 commands
+    assert k(_compile(prog, "rdma", passes="-completion-planning")) == 1
+    assert k(_compile(programs.stream("pipelined", 1, 256, reuse=6), "rdma")) == 4  # bit_floor(6)
+
+
+def test_coalescing_and_ordering_only_on_queue_transports():
+    prog = programs.stream("chains", 4, 256)
+    rdma = _compile(prog, "rdma")
+    assert rdma.facts["batches"] == 1 and rdma.facts["reservations"] == 1 and rdma.facts["commands"] == 8
+    assert rdma.passes["coalesce-submissions"] == 3 and rdma.passes["order-publications"] == 1
+    assert rdma.ir.count("ordering_point") == 1 and rdma.ir.count("chained=") == 3
+    off = _compile(prog, "rdma", passes="-coalesce-submissions")
+    assert off.facts["batches"] == 4 and off.facts["reservations"] == 4
+    p2p = _compile(prog, "p2p")
+    assert p2p.facts["batches"] == 4 and p2p.passes["coalesce-submissions"] == 0  # no-op by design
+
+
+def test_elide_epochs_skips_kernels_that_wait_on_peers():
+    prog = programs.stream("pipelined", 2, 256, reuse=4)
+    assert _compile(prog, "rdma").facts["elided_signals"] == 2
+    b = programs.stream("pipelined", 2, 256, reuse=4)
+    b.wait_signal("payload", 1)
+    assert _compile(b, "rdma").facts["elided_signals"] == 0
+
+
+def test_defer_announcement_is_opt_in():
+    prog = programs.stream("pipelined", 1, 256, reuse=4)
+    assert "deferredAnnouncement" not in _compile(prog, "rdma").ir
+    assert "deferredAnnouncement" in _compile(prog, "rdma", passes="+defer-announcement").ir
+
+
+def test_producer_barrier_placed_once_per_dirty_region():
+    c = _compile(programs.fp8_dispatch())
+    assert c.facts["producer_barriers"] == 1 and c.ir.count("producerBarrier") == 1
+    assert c.facts["batches"] == 1 and c.facts["commands"] == 6 and c.facts["inline_puts"] == 1
+    assert c.facts["exclusive_issuers"] == 1          # endpoint index is the program id
+    q = _compile(programs.fp8_dispatch(), "rdma", queue_capacity=64)
+    assert q.facts["reservations"] == 1 and "planned=iteration" in q.ir
+
+
+def test_issuer_analysis_patterns():
+    def known(expr):
+        return json.loads(_affine(expr))
+
+    assert known("pid")["known"] and known("pid")["scale"] == 1
+    assert known("pid + 3")["scale"] == 1 and known("2*pid + base")["scale"] == 2
+    assert known("(pid + 1) % 8") == {"known": True, "scale": 1, "modular": True, "modulus": 8}
+    assert not known("pid + (pid >= RANK)")["known"]
+    assert not known("pid * stride")["known"]       # an unknown uniform factor may be zero
+    assert not known("pid / 2")["known"]
+    assert known("lane*4 + 3")["scale"] == 0          # uniform only: not injective
+
+
+def test_verifier_diagnostics():
+    bad_width = "program p backend=p2p\n%e = endpoint t 0\n%r = remote t 0\n%x = put_inline %e %r values=v:12\n"
+    with pytest.raises(CompileError, match="width 12 is not one of 8, 16, 24, 32, 64"):
+        compile_program(bad_width)
+    too_big = "program p backend=p2p\n%e = endpoint t 0\n%r = remote t 0\n%x = put_inline %e %r values=" + \
+        ",".join(["v:64"] * 122) + "\n"
+    with pytest.raises(CompileError, match="exceeds the 972-byte limit"):
+        compile_program(too_big)
+    with pytest.raises(CompileError, match="after=%nope is not defined"):
+        compile_program("program p backend=p2p\n%e = endpoint t 0\n%r = remote t 0\n%s = signal %e %r epoch=1 after=%nope\n")
+    with pytest.raises(CompileError, match="belongs to another endpoint"):
+        compile_program("program p backend=p2p\n%e = endpoint t 0\n%f = endpoint t 1\n%r = remote t 0\n%l = local a\n"
+                        "%t = put %e %r %l bytes=8\n%s = signal %f %r epoch=1 after=%t\n")
+    with pytest.raises(CompileError, match="has no wait_group"):
+        compile_program("program p backend=p2p\n%e = endpoint t 0\n%g = begin_group %e\n")
+    with pytest.raises(CompileError, match="written for transport 'gin'"):
+        compile_program("program p backend=gin\n")
+    with pytest.raises(ValueError, match="unknown transport 'gin'"):
+        compilation("gin").__enter__()
+    with pytest.raises(CompileError, match="written for transport 'rdma'"):
+        compile_program("program p backend=rdma\n")
+
+
+def test_passes_grammar_and_key_coverage(monkeypatch):
+    assert enabled_optimizations("none") == frozenset()
+    assert enabled_optimizations("all") == frozenset(OPTIMIZATIONS)
+    assert "elide-epochs" not in enabled_optimizations("-elide-epochs")
+    assert "defer-announcement" in enabled_optimizations("default,+defer-announcement")
+    with pytest.raises(ValueError, match="not \\+name or -name"):
+        enabled_optimizations("elide-epochs")
+    monkeypatch.setenv("ABOLETH_PASSES", "-plan-publication")
+    assert "plan-publication" not in enabled_optimizations()
+    monkeypatch.delenv("ABOLETH_PASSES")
+    # Every option and every switch moves the artefact key.
+    text = programs.alltoall(4096).text()
+    base = compilation("p2p").__enter__()
+    keys = {pipeline_key(text, base)}
+    from dataclasses import replace
+    for change in (dict(backend="proxy"), dict(queue_capacity=64), dict(completion_interval=2),
+                   dict(strict_registrations=True), dict(gpu_resident_queues=True), dict(inline_bytes=16),
+                   dict(p2p_copy="scalar"), dict(endpoint_profile="seed"), dict(plan_hash="abc"),
+                   dict(coop_min=512), dict(coop_elements=1024), dict(arch="sm_100")):
+        keys.add(pipeline_key(text, replace(base, **change)))
+    for name in OPTIMIZATIONS:
+        flipped = base.passes ^ {name}
+        keys.add(pipeline_key(text, replace(base, passes=frozenset(flipped))))
+    assert len(keys) == 1 + 12 + len(OPTIMIZATIONS)
+
+
+def test_emitted_kernels_compile_for_sm_100a(tmp_path, monkeypatch):
+    monkeypatch.setenv("ABOLETH_CACHE_DIR", str(tmp_path))
+    for backend in ("p2p", "rdma"):
+        with compilation(backend, rank=0, world_size=2):
+            art = build_artifact(compile_program(programs.stream("fused", 8, 1024)))
+        assert art.cubin.exists() and art.cubin_bytes > 0 and art.spill_bytes == 0
+        assert art.manifest()["n_regs"] > 0
+    again = build_artifact(_compile(programs.stream("fused", 8, 1024), "rdma"))
+    assert again.cubin == art.cubin  # cache hit under the same key
