@@ -33,6 +33,7 @@ struct PlainPolicy {
         t.rows_valid = min(BM, m - tm * BM);
         t.cols_valid = min(BN, n - tn * BN);
         t.tag = 0;
+        t.a_sel = 0;
         return true;
     }
     __device__ __forceinline__ bool ready(const Tile &) const { return true; }
@@ -42,6 +43,7 @@ struct PlainPolicy {
                              t.cols_valid - col0);
     }
     __device__ __forceinline__ void tile_done(const Tile &) const {}
+    __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
 };
 
 struct GroupedPolicy {
@@ -73,6 +75,7 @@ struct GroupedPolicy {
         t.rows_valid = min(BM, counts[e] - tm * BM);
         t.cols_valid = min(BN, n - tn * BN);
         t.tag = e;
+        t.a_sel = 0;
         return true;
     }
     __device__ __forceinline__ bool ready(const Tile &) const { return true; }
@@ -82,6 +85,7 @@ struct GroupedPolicy {
                              t.cols_valid - col0);
     }
     __device__ __forceinline__ void tile_done(const Tile &) const {}
+    __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
 };
 
 template <typename Policy>

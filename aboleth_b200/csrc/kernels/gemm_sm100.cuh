@@ -147,6 +147,7 @@ struct Tile {
     int rows_valid;  // output rows of this tile that exist (<= BM)
     int cols_valid;  // output columns that exist (<= BN)
     int tag;         // policy-defined (expert, source rank, ...)
+    int a_sel;       // 0: first A tensor map, 1: the alternate one
 };
 
 // Policy concept:
@@ -155,10 +156,15 @@ struct Tile {
 //   __device__ void store(const Tile &t, int row, int col0, const float (&v)[32], bool row_ok)
 //   __device__ void tile_done(const Tile &t)              - called by ONE epilogue thread after the
 //                                                           whole tile was stored (CTA-wide ordered)
+//   __device__ void finish(int thread, int nthreads, status) - epilogue warps, after the last tile
+// `map_a_alt` is the tensor map used by tiles with a_sel == 1 (pass map_a when unused).
 template <typename Policy>
 __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap *map_a,
                                               const CUtensorMap *map_b,
-                                              unsigned long long *status) {
+                                              unsigned long long *status,
+                                              const CUtensorMap *map_a_alt = nullptr) {
+    if (map_a_alt == nullptr)
+        map_a_alt = map_a;
     extern __shared__ std::uint8_t smem_raw[];
     __shared__ SharedState st;
     std::uint8_t *tiles = reinterpret_cast<std::uint8_t *>(
@@ -207,7 +213,7 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
                     }
                     std::uint8_t *sa = tiles + stage * kStageBytes;
                     mbar_expect_tx(&st.full[stage], kStageBytes);
-                    tma_load_2d(sa, map_a, kb * BK, t.a_row, &st.full[stage]);
+                    tma_load_2d(sa, t.a_sel ? map_a_alt : map_a, kb * BK, t.a_row, &st.full[stage]);
                     tma_load_2d(sa + kStageBytesA, map_b, kb * BK, t.b_row, &st.full[stage]);
                     if (++stage == kStages) {
                         stage = 0;
@@ -292,6 +298,8 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
             if (warp == 2 && lane == 0)
                 policy.tile_done(t);
         }
+        if (!st.abort)
+            policy.finish((warp - 2) * 32 + lane, kEpilogueWarps * 32, status);
     }
 
     // ---------------- teardown ----------------
