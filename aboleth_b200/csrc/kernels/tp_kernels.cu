@@ -1,0 +1,293 @@
+// Tensor-parallel GEMMs fused with their collective, one launch each.
+//
+// ALL-GATHER -> GEMM   C[world*Ml, Nl] = gather_ranks(A_local[Ml, K]) * B_local[Nl, K]^T
+//   `push_ctas` CTAs first store this rank's A shard, 128-row chunk by chunk,
+//   into every peer's gathered-A staging over NVLink and publish each chunk
+//   with one release flag; then they join the others in the persistent tcgen05
+//   main loop.  The TMA producer of a tile whose rows came from rank s waits
+//   (bounded) on the chunk's flag and then loads the tile from LOCAL staging -
+//   a remote tile crosses NVLink once, TMA never touches peer memory, nothing
+//   is multicast.  Tiles of the rank's own rows read A_local through a second
+//   tensor map and start at once; remote sources follow in arrival order.
+//
+// GEMM -> REDUCE-SCATTER   out[Ml, N] = sum_ranks(A_local[world*Ml, Kl] * B_local[N, Kl]^T)[own rows]
+//   The epilogue converts each fp32 accumulator tile from TMEM to bf16 and
+//   stores it straight into the OWNER rank's partial buffer (peer stores), then
+//   publishes the tile with one release flag.  Tiles owned by peers are computed
+//   first.  When a CTA has no GEMM tiles left its epilogue warps reduce owned
+//   tiles: wait for the tile's flag from every rank, sum the partials in fp32.
+//
+// No reference kernel exists for these; the baseline is NCCL all-gather /
+// reduce-scatter around a library GEMM.
+#include "gemm_sm100.cuh"
+
+namespace {
+
+using namespace ab::gemm;
+using aboleth::Status;
+
+constexpr int kPhaseProduce = 1;  // AG: push shard.  RS: GEMM + partial stores.
+constexpr int kPhaseConsume = 2;  // AG: GEMM.        RS: reduction of owned tiles.
+
+// ---- all-gather -> GEMM -----------------------------------------------------------------
+
+struct AgGemmPolicy {
+    __nv_bfloat16 *c;
+    const std::uint64_t *flags;       // local: [world * chunks] epochs
+    unsigned long long *status;
+    std::uint64_t epoch;
+    int rank, world, m_local, n, k, ldc, phases;
+    int tiles_n, chunks;              // chunks = m_local / BM (row blocks per rank)
+
+    __device__ __forceinline__ bool next(int it, Tile &t) const {
+        if (!(phases & kPhaseConsume))
+            return false;
+        const int idx = blockIdx.x + it * gridDim.x;
+        const int per_src = chunks * tiles_n;
+        if (idx >= world * per_src)
+            return false;
+        // Source order: own rows first, then rank-1, rank-2, ... (the order in which
+        // peers' pushes arrive, since every rank pushes to rank+1 first).
+        const int order = idx / per_src, local = idx - order * per_src;
+        const int src = (rank - order + world) % world;
+        const int chunk = local / tiles_n, tn = local - chunk * tiles_n;
+        t.a_sel = src == rank ? 1 : 0;
+        t.a_row = src == rank ? chunk * BM : src * m_local + chunk * BM;
+        t.b_row = tn * BN;
+        t.k_blocks = (k + BK - 1) / BK;
+        t.c_row = src * m_local + chunk * BM;
+        t.c_col = tn * BN;
+        t.rows_valid = min(BM, m_local - chunk * BM);
+        t.cols_valid = min(BN, n - tn * BN);
+        t.tag = src * chunks + chunk;
+        return true;
+    }
+    __device__ __forceinline__ bool ready(const Tile &t) const {
+        if (t.a_sel)
+            return true;
+        return aboleth::wait_signal_status(flags + t.tag, epoch) == Status::Ok;
+    }
+    __device__ __forceinline__ void store(const Tile &t, int row, int col0, const float (&v)[32],
+                                          bool row_ok) const {
+        if (row_ok)
+            store_row32_bf16(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col0, v,
+                             t.cols_valid - col0);
+    }
+    __device__ __forceinline__ void tile_done(const Tile &) const {}
+    __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
+};
+
+struct AgPush {
+    const std::uint8_t *a_local;          // [m_local, k] bf16
+    const std::uint64_t *peer_staging;    // [world] address of each peer's gathered-A buffer
+    const std::uint64_t *peer_flags;      // [world] address of each peer's flag array
+    int push_ctas;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap map_staging,
+               const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_local, AgGemmPolicy params, AgPush push) {
+    AgGemmPolicy policy = params;
+    if ((policy.phases & kPhaseProduce) && static_cast<int>(blockIdx.x) < push.push_ctas) {
+        // Work items (peer, chunk), nearest peer first; one CTA per item.
+        const int items = (policy.world - 1) * policy.chunks;
+        const std::size_t chunk_bytes = static_cast<std::size_t>(BM) * policy.k * 2;
+        for (int item = blockIdx.x; item < items; item += push.push_ctas) {
+            const int hop = item / policy.chunks + 1, chunk = item - (hop - 1) * policy.chunks;
+            const int peer = (policy.rank + hop) % policy.world;
+            const int rows = min(BM, policy.m_local - chunk * BM);
+            const std::size_t bytes = static_cast<std::size_t>(rows) * policy.k * 2;
+            std::uint8_t *dst = reinterpret_cast<std::uint8_t *>(push.peer_staging[peer]) +
+                                (static_cast<std::size_t>(policy.rank) * policy.m_local) * policy.k * 2 +
+                                chunk * chunk_bytes;
+            aboleth::detail::copy_strided(dst, push.a_local + chunk * chunk_bytes, bytes, threadIdx.x,
+                                          blockDim.x);
+            std::uint64_t *flag = reinterpret_cast<std::uint64_t *>(push.peer_flags[peer]) +
+                                  policy.rank * policy.chunks + chunk;
+            aboleth::signal_block(aboleth::RemoteRegion{reinterpret_cast<std::uint64_t>(flag), 0},
+                                  policy.epoch);
+            __syncthreads();
+        }
+    }
+    gemm_mainloop(policy, &map_staging, &map_b, policy.status, &map_local);
+}
+
+// ---- GEMM -> reduce-scatter -----------------------------------------------------------------
+
+struct GemmRsPolicy {
+    const std::uint64_t *peer_partials;  // [world] address of each rank's partial buffer
+    const std::uint64_t *peer_flags;     // [world] address of each rank's flag array
+    const __nv_bfloat16 *partials;       // local: [world, m_local, n]
+    const std::uint64_t *flags;          // local: [world * tiles_local]
+    __nv_bfloat16 *out;                  // [m_local, n]
+    unsigned long long *status;
+    std::uint64_t epoch;
+    int rank, world, m_local, n, k, phases;
+    int tiles_n, chunks;                 // tiles per owner = chunks * tiles_n
+
+    __device__ __forceinline__ bool next(int it, Tile &t) const {
+        if (!(phases & kPhaseProduce))
+            return false;
+        const int idx = blockIdx.x + it * gridDim.x;
+        const int per_owner = chunks * tiles_n;
+        if (idx >= world * per_owner)
+            return false;
+        // Owners in the order rank+1, rank+2, ..., rank: peers get their partials early.
+        const int order = idx / per_owner, local = idx - order * per_owner;
+        const int owner = (rank + 1 + order) % world;
+        const int chunk = local / tiles_n, tn = local - chunk * tiles_n;
+        t.a_sel = 0;
+        t.a_row = owner * m_local + chunk * BM;
+        t.b_row = tn * BN;
+        t.k_blocks = (k + BK - 1) / BK;
+        t.c_row = chunk * BM;  // row inside the owner's block
+        t.c_col = tn * BN;
+        t.rows_valid = min(BM, m_local - chunk * BM);
+        t.cols_valid = min(BN, n - tn * BN);
+        t.tag = owner * 65536 + local;  // owner and tile index inside the owner's block
+        return true;
+    }
+    __device__ __forceinline__ bool ready(const Tile &) const { return true; }
+    __device__ __forceinline__ void store(const Tile &t, int row, int col0, const float (&v)[32],
+                                          bool row_ok) const {
+        if (!row_ok)
+            return;
+        const int owner = t.tag >> 16;
+        __nv_bfloat16 *base = reinterpret_cast<__nv_bfloat16 *>(peer_partials[owner]) +
+                              static_cast<std::size_t>(rank) * m_local * n;
+        store_row32_bf16(base + static_cast<std::size_t>(t.c_row + row) * n + t.c_col + col0, v,
+                         t.cols_valid - col0);
+    }
+    // One thread, after all four epilogue warps stored the tile (bar.sync): publish it.
+    __device__ __forceinline__ void tile_done(const Tile &t) const {
+        const int owner = t.tag >> 16, local = t.tag & 0xffff;
+        std::uint64_t *flag = reinterpret_cast<std::uint64_t *>(peer_flags[owner]) +
+                              rank * (chunks * tiles_n) + local;
+        aboleth::detail::fence_acq_rel_sys();
+        aboleth::detail::st_relaxed_sys(flag, epoch);
+    }
+    // Reduction of owned tiles by the 128 epilogue threads of every CTA.
+    __device__ __forceinline__ void finish(int thread, int nthreads, unsigned long long *st) const {
+        if (!(phases & kPhaseConsume))
+            return;
+        const int per_owner = chunks * tiles_n;
+        for (int tile = blockIdx.x; tile < per_owner; tile += gridDim.x) {
+            const int chunk = tile / tiles_n, tn = tile - chunk * tiles_n;
+            // Threads 0..world-1 wait for one source each; the named barrier publishes it.
+            bool ok = true;
+            if (thread < world)
+                ok = aboleth::wait_signal_status(flags + thread * per_owner + tile, epoch) == Status::Ok;
+            if (!ok)
+                ab::set_status(st, Status::Timeout, 0x4000 + thread);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int rows = min(BM, m_local - chunk * BM), cols = min(BN, n - tn * BN);
+            const int vec_per_row = cols / 8;
+            for (int i = thread; i < rows * vec_per_row; i += nthreads) {
+                const int r = i / vec_per_row, v = i - r * vec_per_row;
+                const std::size_t off = static_cast<std::size_t>(chunk * BM + r) * n + tn * BN + v * 8;
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                for (int s = 0; s < world; ++s) {
+                    const uint4 y = aboleth::detail::ld_stream16(
+                        partials + static_cast<std::size_t>(s) * m_local * n + off);
+                    const std::uint32_t w[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        acc[2 * q] += __uint_as_float(w[q] << 16);
+                        acc[2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u);
+                    }
+                }
+                uint4 o;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[0], acc[1]);
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(acc[2], acc[3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[4], acc[5]);
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(acc[6], acc[7]);
+                o.x = *reinterpret_cast<std::uint32_t *>(&p0);
+                o.y = *reinterpret_cast<std::uint32_t *>(&p1);
+                o.z = *reinterpret_cast<std::uint32_t *>(&p2);
+                o.w = *reinterpret_cast<std::uint32_t *>(&p3);
+                *reinterpret_cast<uint4 *>(out + off) = o;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+    }
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               GemmRsPolicy params) {
+    GemmRsPolicy policy = params;
+    gemm_mainloop(policy, &map_a, &map_b, policy.status);
+}
+
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    }
+    return sms;
+}
+
+}  // namespace
+
+// a_local [m_local, k]; staging [world*m_local, k] (this rank's gathered-A buffer, peers write it);
+// b [n, k]; c [world*m_local, n].  m_local must be a multiple of 128.  peer_staging / peer_flags:
+// device int64 [world] address tables; flags: local int64 [world * m_local/128].
+AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const void *b, void *c,
+                              const std::uint64_t *peer_staging, const std::uint64_t *peer_flags,
+                              const std::uint64_t *flags, unsigned long long *status,
+                              std::uint64_t epoch, int rank, int world, int m_local, int n, int k,
+                              int push_ctas, int phases, cudaStream_t stream) {
+    if (world < 1 || m_local < BM || m_local % BM || n < 8 || n % 8 || k < 8 || k % 8 || rank < 0 ||
+        rank >= world)
+        return -1;
+    CUtensorMap map_staging, map_b, map_local;
+    if (!make_map_bf16(&map_staging, staging, static_cast<std::uint64_t>(world) * m_local, k, k, BM) ||
+        !make_map_bf16(&map_b, b, n, k, k, BN) || !make_map_bf16(&map_local, a_local, m_local, k, k, BM))
+        return -2;
+    static bool configured =
+        cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) ==
+        cudaSuccess;
+    if (!configured)
+        return -3;
+    AgGemmPolicy p{static_cast<__nv_bfloat16 *>(c), flags, status, epoch, rank, world, m_local, n, k, n,
+                   phases, (n + BN - 1) / BN, m_local / BM};
+    if (push_ctas < 1)
+        push_ctas = 32;
+    if (push_ctas > sm_count())
+        push_ctas = sm_count();
+    AgPush push{static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, push_ctas};
+    ag_gemm_kernel<<<sm_count(), kThreads, kSmemBytes, stream>>>(map_staging, map_b, map_local, p, push);
+    return ab::launch_result("ag_gemm_bf16");
+}
+
+// a [world*m_local, k_local]; b [n, k_local]; partials: local [world, m_local, n] (peers write it);
+// out [m_local, n].  m_local multiple of 128, n multiple of 8 and tiles per owner < 65536.
+AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials, void *out,
+                              const std::uint64_t *peer_partials, const std::uint64_t *peer_flags,
+                              const std::uint64_t *flags, unsigned long long *status,
+                              std::uint64_t epoch, int rank, int world, int m_local, int n, int k,
+                              int phases, cudaStream_t stream) {
+    if (world < 1 || m_local < BM || m_local % BM || n < 8 || n % 8 || k < 8 || k % 8 || rank < 0 ||
+        rank >= world)
+        return -1;
+    const int tiles_n = (n + BN - 1) / BN, chunks = m_local / BM;
+    if (tiles_n * chunks >= 65536)
+        return -1;
+    CUtensorMap map_a, map_b;
+    if (!make_map_bf16(&map_a, a, static_cast<std::uint64_t>(world) * m_local, k, k, BM) ||
+        !make_map_bf16(&map_b, b, n, k, k, BN))
+        return -2;
+    static bool configured =
+        cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) ==
+        cudaSuccess;
+    if (!configured)
+        return -3;
+    GemmRsPolicy p{peer_partials, peer_flags, static_cast<const __nv_bfloat16 *>(partials), flags,
+                   static_cast<__nv_bfloat16 *>(out), status, epoch, rank, world, m_local, n, k, phases,
+                   tiles_n, chunks};
+    gemm_rs_kernel<<<sm_count(), kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+    return ab::launch_result("gemm_rs_bf16");
+}

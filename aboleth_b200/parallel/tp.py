@@ -1,0 +1,210 @@
+"""Tensor parallelism: GEMMs fused with their collective over NVLink peer memory.
+
+``AllGatherGemm``       ``C[world*Ml, Nl] = all_gather(A_local) @ B_local.T`` in one launch
+``GemmReduceScatter``   ``out[Ml, N] = reduce_scatter(A_local @ B_local.T)`` in one launch
+
+Kernels: csrc/kernels/tp_kernels.cu (tcgen05 / TMEM main loop, TMA from local memory
+only, peer stores and release flags for the collective half).  Each object owns two
+sets of peer-visible buffers and alternates between them, so a rank may run one call
+ahead of its slowest peer; any collective between two calls keeps ranks that close.
+
+``LocalTpGroup`` runs several ranks on ONE device by launching every rank's producing
+half before any rank's consuming half (tests, single-GPU development).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from ..ops._kernels import _I, _U64, _VP, call, declare, ptr, stream_ptr
+from ..world import World
+
+declare("ab_ag_gemm_bf16", [_VP] * 8 + [_U64] + [_I] * 7 + [_VP])
+declare("ab_gemm_rs_bf16", [_VP] * 8 + [_U64] + [_I] * 6 + [_VP])
+
+PRODUCE, CONSUME = 1, 2
+BM = 128
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class _Buffers:
+    """Two alternating (data, flags) sets carved from one arena."""
+
+    def __init__(self, arena: torch.Tensor, data_bytes: int, flag_count: int):
+        self.data_bytes, self.flag_count = data_bytes, flag_count
+        stride = _align(data_bytes) + _align(flag_count * 8)
+        self.offsets = [(i * stride, i * stride + _align(data_bytes)) for i in range(2)]
+        self.arena = arena
+
+    @staticmethod
+    def nbytes(data_bytes: int, flag_count: int) -> int:
+        return 2 * (_align(data_bytes) + _align(flag_count * 8))
+
+    def data(self, i: int) -> torch.Tensor:
+        start = self.offsets[i][0]
+        return self.arena[start:start + self.data_bytes]
+
+    def flags(self, i: int) -> torch.Tensor:
+        start = self.offsets[i][1]
+        return self.arena[start:start + self.flag_count * 8].view(torch.int64)
+
+
+def _exchange(world: World, buffers: _Buffers, tag: str):
+    registration = world.register(buffers.arena, network=False)
+    regions = []
+    for i in range(2):
+        regions.append(world.region(f"data{i}", registration, offset=buffers.offsets[i][0],
+                                    length=buffers.data_bytes))
+        regions.append(world.region(f"flags{i}", registration, offset=buffers.offsets[i][1],
+                                    length=buffers.flag_count * 8))
+    table = world.exchange_regions(regions, tag=tag)
+    return [(table.addresses(f"data{i}"), table.addresses(f"flags{i}")) for i in range(2)], table
+
+
+class AllGatherGemm:
+    """Column-parallel linear layer whose input is sharded by rows across ranks."""
+
+    def __init__(self, rank: int, world_size: int, m_local: int, k: int, buffers: _Buffers,
+                 tables, *, push_ctas: int = 32):
+        if m_local % BM:
+            raise ValueError("rows per rank must be a multiple of 128")
+        self.rank, self.world_size, self.m_local, self.k = rank, world_size, m_local, k
+        self.buffers, self.tables, self.push_ctas = buffers, tables, push_ctas
+        self.status = torch.zeros(2, dtype=torch.int64, device=buffers.arena.device)
+        self.epoch = 0
+
+    @staticmethod
+    def arena_bytes(world_size: int, m_local: int, k: int) -> int:
+        return _Buffers.nbytes(world_size * m_local * k * 2, world_size * (m_local // BM))
+
+    @classmethod
+    def create(cls, world: World, m_local: int, k: int, *, tag: str = "ag_gemm", **kw) -> "AllGatherGemm":
+        n = world.world_size
+        arena = world.runtime.allocate(cls.arena_bytes(n, m_local, k))
+        buffers = _Buffers(arena, n * m_local * k * 2, n * (m_local // BM))
+        tables, table = _exchange(world, buffers, tag)
+        obj = cls(world.rank, n, m_local, k, buffers, tables, **kw)
+        obj._table = table
+        return obj
+
+    def __call__(self, a_local: torch.Tensor, b_local: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 *, phases: int = PRODUCE | CONSUME, advance: bool = True) -> torch.Tensor:
+        """``a_local`` bf16 ``[m_local, k]``, ``b_local`` bf16 ``[n_local, k]`` ->
+        bf16 ``[world*m_local, n_local]`` (rows of rank r at ``r*m_local``)."""
+        assert a_local.dtype == b_local.dtype == torch.bfloat16
+        assert a_local.shape == (self.m_local, self.k) and b_local.shape[1] == self.k
+        assert a_local.is_contiguous() and b_local.is_contiguous()
+        n = b_local.shape[0]
+        if out is None:
+            out = torch.empty(self.world_size * self.m_local, n, dtype=torch.bfloat16,
+                              device=a_local.device)
+        if advance and (phases & PRODUCE):
+            self.epoch += 1
+        which = self.epoch & 1
+        peer_data, peer_flags = self.tables[which]
+        call("ab_ag_gemm_bf16", ptr(a_local), ptr(self.buffers.data(which)), ptr(b_local), ptr(out),
+             ptr(peer_data), ptr(peer_flags), ptr(self.buffers.flags(which)), ptr(self.status),
+             (self.epoch + 1) // 2, self.rank, self.world_size, self.m_local, n, self.k,
+             self.push_ctas, phases, stream_ptr())
+        return out
+
+    def check(self) -> None:
+        status = self.status.tolist()
+        if status[0]:
+            raise RuntimeError(f"all-gather GEMM wait gave up (status {status[0]}, detail {status[1]:#x})")
+
+
+class GemmReduceScatter:
+    """Row-parallel linear layer whose output is reduced and scattered by rows."""
+
+    def __init__(self, rank: int, world_size: int, m_local: int, n: int, buffers: _Buffers, tables):
+        if m_local % BM or n % 8:
+            raise ValueError("rows per rank must be a multiple of 128 and n a multiple of 8")
+        self.rank, self.world_size, self.m_local, self.n = rank, world_size, m_local, n
+        self.buffers, self.tables = buffers, tables
+        self.status = torch.zeros(2, dtype=torch.int64, device=buffers.arena.device)
+        self.epoch = 0
+
+    @staticmethod
+    def _tiles(m_local: int, n: int) -> int:
+        return (m_local // BM) * ((n + 255) // 256)
+
+    @staticmethod
+    def arena_bytes(world_size: int, m_local: int, n: int) -> int:
+        return _Buffers.nbytes(world_size * m_local * n * 2,
+                               world_size * GemmReduceScatter._tiles(m_local, n))
+
+    @classmethod
+    def create(cls, world: World, m_local: int, n: int, *, tag: str = "gemm_rs") -> "GemmReduceScatter":
+        w = world.world_size
+        arena = world.runtime.allocate(cls.arena_bytes(w, m_local, n))
+        buffers = _Buffers(arena, w * m_local * n * 2, w * cls._tiles(m_local, n))
+        tables, table = _exchange(world, buffers, tag)
+        obj = cls(world.rank, w, m_local, n, buffers, tables)
+        obj._table = table
+        return obj
+
+    def __call__(self, a: torch.Tensor, b_local: torch.Tensor, out: Optional[torch.Tensor] = None, *,
+                 phases: int = PRODUCE | CONSUME, advance: bool = True) -> torch.Tensor:
+        """``a`` bf16 ``[world*m_local, k_local]``, ``b_local`` bf16 ``[n, k_local]`` ->
+        bf16 ``[m_local, n]``: this rank's rows of the sum over ranks."""
+        assert a.dtype == b_local.dtype == torch.bfloat16 and a.is_contiguous() and b_local.is_contiguous()
+        assert a.shape[0] == self.world_size * self.m_local and b_local.shape == (self.n, a.shape[1])
+        if out is None:
+            out = torch.empty(self.m_local, self.n, dtype=torch.bfloat16, device=a.device)
+        if advance and (phases & PRODUCE):
+            self.epoch += 1
+        which = self.epoch & 1
+        peer_data, peer_flags = self.tables[which]
+        call("ab_gemm_rs_bf16", ptr(a), ptr(b_local), ptr(self.buffers.data(which)), ptr(out),
+             ptr(peer_data), ptr(peer_flags), ptr(self.buffers.flags(which)), ptr(self.status),
+             (self.epoch + 1) // 2, self.rank, self.world_size, self.m_local, self.n, a.shape[1],
+             phases, stream_ptr())
+        return out
+
+    def check(self) -> None:
+        status = self.status.tolist()
+        if status[0]:
+            raise RuntimeError(f"GEMM reduce-scatter wait gave up (status {status[0]}, detail {status[1]:#x})")
+
+
+class LocalTpGroup:
+    """Emulates ``world_size`` tensor-parallel ranks on one device in one process."""
+
+    def __init__(self, world_size: int, m_local: int, k_or_n_ag: int, n_rs: int, device="cuda:0"):
+        device = torch.device(device)
+        self.world_size = world_size
+
+        def build(kind, data_bytes, flag_count, make):
+            arenas = [torch.zeros(_Buffers.nbytes(data_bytes, flag_count), dtype=torch.uint8, device=device)
+                      for _ in range(world_size)]
+            bufs = [_Buffers(a, data_bytes, flag_count) for a in arenas]
+            tables = [(torch.tensor([b.data(i).data_ptr() for b in bufs], dtype=torch.int64, device=device),
+                       torch.tensor([b.flags(i).data_ptr() for b in bufs], dtype=torch.int64, device=device))
+                      for i in range(2)]
+            return [make(r, bufs[r], tables) for r in range(world_size)]
+
+        k = k_or_n_ag
+        self.ag = build("ag", world_size * m_local * k * 2, world_size * (m_local // BM),
+                        lambda r, b, t: AllGatherGemm(r, world_size, m_local, k, b, t))
+        self.rs = build("rs", world_size * m_local * n_rs * 2,
+                        world_size * GemmReduceScatter._tiles(m_local, n_rs),
+                        lambda r, b, t: GemmReduceScatter(r, world_size, m_local, n_rs, b, t))
+
+    def ag_gemm(self, a_shards: Sequence[torch.Tensor], b_shards: Sequence[torch.Tensor]) -> list[torch.Tensor]:
+        outs = [None] * self.world_size
+        for r, op in enumerate(self.ag):
+            outs[r] = op(a_shards[r], b_shards[r], phases=PRODUCE)
+        return [op(a_shards[r], b_shards[r], outs[r], phases=CONSUME, advance=False)
+                for r, op in enumerate(self.ag)]
+
+    def gemm_rs(self, a_parts: Sequence[torch.Tensor], b_shards: Sequence[torch.Tensor]) -> list[torch.Tensor]:
+        outs = [None] * self.world_size
+        for r, op in enumerate(self.rs):
+            outs[r] = op(a_parts[r], b_shards[r], phases=PRODUCE)
+        return [op(a_parts[r], b_shards[r], outs[r], phases=CONSUME, advance=False)
+                for r, op in enumerate(self.rs)]
