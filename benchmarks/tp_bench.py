@@ -1,0 +1,126 @@
+#!/usr/bin/env python
+"""Fused tensor-parallel GEMM collectives at the Llama-3-70B MLP shapes, against
+NCCL all-gather / reduce-scatter around torch.matmul (cuBLAS).
+
+    torchrun --nproc-per-node 8 benchmarks/tp_bench.py --out out.json
+
+all-gather -> GEMM : M = 8192 tokens (M / world per rank), K = 8192, N = 28672 / world
+GEMM -> reduce-scatter : M = 8192, K = 28672 / world, N = 8192
+Weights N(0, 0.02), activations N(0, 1), bf16.  Roofline per kernel = the slower of
+FLOPs / measured cuBLAS peak and NVLink bytes / 770 GB/s.
+"""
+import argparse
+
+from common import emit, setup, teardown
+
+import torch
+import torch.distributed as dist
+
+from aboleth_b200.bench_support import NVLINK_GBS, L2Flusher, device_max, measured_peaks, sync_ranks
+from aboleth_b200.ops import gemm_bf16
+from aboleth_b200.parallel import AllGatherGemm, GemmReduceScatter
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=8192)
+    ap.add_argument("--ffn", type=int, default=28672)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--push-ctas", type=int, default=32)
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    ab, world, distributed = setup()
+    w, rank, dev = world.world_size, world.rank, world.torch_device
+    m_local = args.tokens // w
+    g = torch.Generator(device=dev).manual_seed(rank)
+    flush = L2Flusher(dev)
+    peaks = measured_peaks()
+    rows = []
+
+    def timed(fn):
+        times = []
+        for it in range(args.steps + 3):
+            flush()
+            sync_ranks(distributed)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(200_000)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                times.append(device_max(a.elapsed_time(b), distributed))
+        times.sort()
+        return times[len(times) // 2] * 1e3  # median, us
+
+    def roof(flops, nvlink_bytes):
+        t_flop = flops / (peaks["bf16_tflops"] * 1e12) * 1e6
+        t_link = nvlink_bytes / (NVLINK_GBS * 1e9) * 1e6
+        return max(t_flop, t_link), t_flop, t_link
+
+    # ---- plain GEMM for context ----
+    a_full = torch.randn(args.tokens, args.hidden, generator=g, device=dev).to(torch.bfloat16)
+    b_col = (torch.randn(args.ffn // w, args.hidden, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    out = torch.empty(args.tokens, args.ffn // w, dtype=torch.bfloat16, device=dev)
+    flops = 2.0 * args.tokens * args.hidden * (args.ffn // w)
+    t_ours = timed(lambda: gemm_bf16(a_full, b_col, out))
+    t_lib = timed(lambda: torch.matmul(a_full, b_col.t(), out=out))
+    rows.append({"op": "gemm (no collective)", "ours_us": t_ours, "cublas_us": t_lib,
+                 "ours_tflops": flops / t_ours / 1e6, "cublas_tflops": flops / t_lib / 1e6,
+                 "frac_of_measured_peak": flops / t_ours / 1e6 / peaks["bf16_tflops"]})
+
+    # ---- all-gather -> GEMM ----
+    a_local = a_full[rank * m_local:(rank + 1) * m_local].contiguous()
+    fused = AllGatherGemm.create(world, m_local, args.hidden, push_ctas=args.push_ctas)
+    t_fused = timed(lambda: fused(a_local, b_col, out))
+    fused.check()
+    gathered = torch.empty_like(a_full)
+
+    def baseline_ag():
+        if distributed:
+            dist.all_gather_into_tensor(gathered, a_local)
+        else:
+            gathered.copy_(a_full)
+        torch.matmul(gathered, b_col.t(), out=out)
+    t_base = timed(baseline_ag)
+    link = (w - 1) * m_local * args.hidden * 2
+    bound, t_flop, t_link = roof(flops, link)
+    rows.append({"op": "all-gather -> GEMM", "m": args.tokens, "k": args.hidden, "n": args.ffn // w,
+                 "fused_us": t_fused, "nccl_plus_cublas_us": t_base, "speedup": t_base / t_fused,
+                 "roof_us": bound, "roof_flops_us": t_flop, "roof_nvlink_us": t_link,
+                 "frac_of_roof": bound / t_fused})
+
+    # ---- GEMM -> reduce-scatter ----
+    k_local = args.ffn // w
+    a_row = torch.randn(args.tokens, k_local, generator=g, device=dev).to(torch.bfloat16)
+    b_row = (torch.randn(args.hidden, k_local, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    rs = GemmReduceScatter.create(world, m_local, args.hidden)
+    out_rs = torch.empty(m_local, args.hidden, dtype=torch.bfloat16, device=dev)
+    t_fused = timed(lambda: rs(a_row, b_row, out_rs))
+    rs.check()
+    partial = torch.empty(args.tokens, args.hidden, dtype=torch.bfloat16, device=dev)
+
+    def baseline_rs():
+        torch.matmul(a_row, b_row.t(), out=partial)
+        if distributed:
+            dist.reduce_scatter_tensor(out_rs, partial)
+        else:
+            out_rs.copy_(partial[:m_local])
+    t_base = timed(baseline_rs)
+    flops = 2.0 * args.tokens * k_local * args.hidden
+    link = (w - 1) * m_local * args.hidden * 2
+    bound, t_flop, t_link = roof(flops, link)
+    rows.append({"op": "GEMM -> reduce-scatter", "m": args.tokens, "k": k_local, "n": args.hidden,
+                 "fused_us": t_fused, "nccl_plus_cublas_us": t_base, "speedup": t_base / t_fused,
+                 "roof_us": bound, "roof_flops_us": t_flop, "roof_nvlink_us": t_link,
+                 "frac_of_roof": bound / t_fused})
+    emit({"bench": "tp fused collectives", "n_gpus": w, "dtype": "bf16", "peaks": peaks, "rows": rows,
+          "methodology": "L2 flushed before every timed launch; CUDA events after a busy-wait kernel; "
+                         "median of steps; max over ranks"}, args.out)
+    teardown(world, distributed)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
