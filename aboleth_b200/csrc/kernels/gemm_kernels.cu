@@ -9,6 +9,8 @@
 // offsets stay on the device (no host round trip), and a CTA finds its tiles by
 // walking the expert list.  The reference has no GEMM; the baseline for these
 // kernels is cuBLAS through torch.matmul.
+#include <algorithm>
+
 #include "gemm_sm100.cuh"
 
 namespace {
@@ -19,12 +21,21 @@ struct PlainPolicy {
     __nv_bfloat16 *c;
     int m, n, k, ldc;
     int tiles_n, tiles_total;
+    int group_n;  // tile columns per raster group: their B panels stay resident in L2
 
+    // Tiles are visited group by group: all row tiles of `group_n` tile columns
+    // before the next group, column fastest inside a group.  B panels of one group
+    // (group_n * 256 * K * 2 bytes) fit the L2, A streams once per group.
     __device__ __forceinline__ bool next(int it, Tile &t) const {
         const int idx = blockIdx.x + it * gridDim.x;
         if (idx >= tiles_total)
             return false;
-        const int tm = idx / tiles_n, tn = idx - tm * tiles_n;
+        const int tiles_m = tiles_total / tiles_n;
+        const int per_group = group_n * tiles_m;
+        const int group = idx / per_group;
+        const int width = min(group_n, tiles_n - group * group_n);
+        const int local = idx - group * per_group;
+        const int tm = local / width, tn = group * group_n + (local - tm * width);
         t.a_row = tm * BM;
         t.b_row = tn * BN;
         t.k_blocks = (k + BK - 1) / BK;
@@ -129,8 +140,11 @@ AB_EXPORT int ab_gemm_bf16(const void *a, const void *b, void *c, int m, int n, 
     static bool configured = configure(gemm_tcgen05_kernel<PlainPolicy>);
     if (!configured)
         return -3;
-    PlainPolicy p{static_cast<__nv_bfloat16 *>(c), m, n, k, ldc, (n + BN - 1) / BN, 0};
+    PlainPolicy p{static_cast<__nv_bfloat16 *>(c), m, n, k, ldc, (n + BN - 1) / BN, 0, 0};
     p.tiles_total = ((m + BM - 1) / BM) * p.tiles_n;
+    // About 48 MiB of B per raster group.
+    const long long column_bytes = static_cast<long long>(BN) * k * 2;
+    p.group_n = static_cast<int>(std::max(1LL, std::min<long long>(p.tiles_n, (48LL << 20) / column_bytes)));
     const int grid = p.tiles_total < sm_count() ? p.tiles_total : sm_count();
     gemm_tcgen05_kernel<PlainPolicy><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p, status);
     return ab::launch_result("gemm_bf16");
