@@ -2,7 +2,7 @@
 """All-to-all and put/signal-chain microbenchmarks over NVLink peer memory, with an
 NCCL baseline (grouped send/recv through ``all_to_all_single``).
 
-    torchrun --nproc-per-node N benchmarks/comm_bench.py --min 1024 --max 268435456 --out out.json
+    torchrun --nproc-per-node N benchmarks/comm_bench.py --min-bytes 1024 --max-bytes 268435456 --out out.json
 
 Per-peer message sizes are powers of two; the payload is seeded uniform-random
 bytes that the receiver regenerates and checks on the device.  Bus bandwidth is
@@ -24,8 +24,8 @@ from aboleth_b200.ops import alltoall, check_payload, fill_payload
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--min", type=int, default=1024)
-    ap.add_argument("--max", type=int, default=1 << 26)
+    ap.add_argument("--min-bytes", dest="min", type=int, default=1024)
+    ap.add_argument("--max-bytes", dest="max", type=int, default=1 << 26)
     ap.add_argument("--rounds", type=int, default=20)
     ap.add_argument("--chains", default="1,8,64")
     ap.add_argument("--max-lanes", type=int, default=32)
