@@ -45,7 +45,9 @@ def _nvcc() -> str:
 def _digest(paths: list[Path], flags: list[str]) -> str:
     h = hashlib.sha256()
     for flag in flags:
-        h.update(flag.encode())
+        # Paths under the package are hashed relative to it: a copy of the tree at
+        # another location must not look like a source change.
+        h.update(flag.replace(str(_ROOT), "<pkg>").encode())
     headers = sorted(_INCLUDE.rglob("*.h")) + sorted(_INCLUDE.rglob("*.cuh")) + sorted(
         _CSRC.rglob("*.cuh")) + sorted(_CSRC.rglob("*.h")) + sorted(_CSRC.rglob("*.hpp"))
     for path in list(paths) + headers:
@@ -103,6 +105,16 @@ def build(name: str, *, force: bool = False, verbose: bool = False) -> Path:
     digest = _digest(sources, target["compile"] + target["link"])
     if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
         return out
+    import fcntl
+    with open(_LIB / f"{name}.lock", "w") as lock:
+        # Ranks started together build once: the others wait here and then see the stamp.
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
+            return out
+        return _build_locked(name, target, sources, out, stamp, digest, verbose)
+
+
+def _build_locked(name, target, sources, out, stamp, digest, verbose) -> Path:
     objdir = _LIB / f"obj_{name}"
     objdir.mkdir(exist_ok=True)
     logs: list[str] = []

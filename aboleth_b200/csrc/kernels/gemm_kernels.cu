@@ -17,6 +17,9 @@ namespace {
 
 using namespace ab::gemm;
 
+constexpr int kPlainHalves = 2;
+constexpr int kPlainRows = BM * kPlainHalves;
+
 struct PlainPolicy {
     __nv_bfloat16 *c;
     int m, n, k, ldc;
@@ -36,12 +39,12 @@ struct PlainPolicy {
         const int width = min(group_n, tiles_n - group * group_n);
         const int local = idx - group * per_group;
         const int tm = local / width, tn = group * group_n + (local - tm * width);
-        t.a_row = tm * BM;
+        t.a_row = tm * kPlainRows;
         t.b_row = tn * BN;
         t.k_blocks = (k + BK - 1) / BK;
-        t.c_row = tm * BM;
+        t.c_row = tm * kPlainRows;
         t.c_col = tn * BN;
-        t.rows_valid = min(BM, m - tm * BM);
+        t.rows_valid = min(kPlainRows, m - tm * kPlainRows);
         t.cols_valid = min(BN, n - tn * BN);
         t.tag = 0;
         t.a_sel = 0;
@@ -99,13 +102,13 @@ struct GroupedPolicy {
     __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
 };
 
-template <typename Policy>
+template <int HALVES, typename Policy>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_b, Policy params,
                     unsigned long long *status) {
     Policy policy = params;
-    gemm_mainloop(policy, &map_a, &map_b, status);
+    gemm_mainloop<HALVES>(policy, &map_a, &map_b, status);
 }
 
 int sm_count() {
@@ -119,8 +122,8 @@ int sm_count() {
 }
 
 template <typename Kernel>
-bool configure(Kernel kernel) {
-    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) ==
+bool configure(Kernel kernel, unsigned smem_bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) ==
            cudaSuccess;
 }
 
@@ -135,18 +138,19 @@ AB_EXPORT int ab_gemm_bf16(const void *a, const void *b, void *c, int m, int n, 
          reinterpret_cast<std::uintptr_t>(c)) & 15)
         return -1;
     CUtensorMap map_a, map_b;
-    if (!make_map_bf16(&map_a, a, m, k, lda, BM) || !make_map_bf16(&map_b, b, n, k, ldb, BN))
+    if (!make_map_bf16(&map_a, a, m, k, lda, kPlainRows) || !make_map_bf16(&map_b, b, n, k, ldb, BN))
         return -2;
-    static bool configured = configure(gemm_tcgen05_kernel<PlainPolicy>);
+    constexpr unsigned smem = Geometry<kPlainHalves>::kSmemBytes;
+    static bool configured = configure(gemm_tcgen05_kernel<kPlainHalves, PlainPolicy>, smem);
     if (!configured)
         return -3;
     PlainPolicy p{static_cast<__nv_bfloat16 *>(c), m, n, k, ldc, (n + BN - 1) / BN, 0, 0};
-    p.tiles_total = ((m + BM - 1) / BM) * p.tiles_n;
+    p.tiles_total = ((m + kPlainRows - 1) / kPlainRows) * p.tiles_n;
     // About 48 MiB of B per raster group.
     const long long column_bytes = static_cast<long long>(BN) * k * 2;
     p.group_n = static_cast<int>(std::max(1LL, std::min<long long>(p.tiles_n, (48LL << 20) / column_bytes)));
     const int grid = p.tiles_total < sm_count() ? p.tiles_total : sm_count();
-    gemm_tcgen05_kernel<PlainPolicy><<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p, status);
+    gemm_tcgen05_kernel<kPlainHalves, PlainPolicy><<<grid, kThreads, smem, stream>>>(map_a, map_b, p, status);
     return ab::launch_result("gemm_bf16");
 }
 
@@ -163,12 +167,12 @@ AB_EXPORT int ab_grouped_gemm_bf16(const void *a, const void *w, void *c, const 
     if (!make_map_bf16(&map_a, a, total_rows, k, k, BM) ||
         !make_map_bf16(&map_b, w, static_cast<std::uint64_t>(experts) * n, k, k, BN))
         return -2;
-    static bool configured = configure(gemm_tcgen05_kernel<GroupedPolicy>);
+    constexpr unsigned smem = Geometry<1>::kSmemBytes;
+    static bool configured = configure(gemm_tcgen05_kernel<1, GroupedPolicy>, smem);
     if (!configured)
         return -3;
     GroupedPolicy p{static_cast<__nv_bfloat16 *>(c), counts, offsets, experts, n, k, n,
                     (n + BN - 1) / BN, 0, 0};
-    gemm_tcgen05_kernel<GroupedPolicy><<<sm_count(), kThreads, kSmemBytes, stream>>>(map_a, map_b, p,
-                                                                                    status);
+    gemm_tcgen05_kernel<1, GroupedPolicy><<<sm_count(), kThreads, smem, stream>>>(map_a, map_b, p, status);
     return ab::launch_result("grouped_gemm_bf16");
 }

@@ -28,14 +28,10 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;   // 64 bf16 = 128 bytes = one swizzle atom row
 constexpr int UMMA_K = 16;
-constexpr int kStages = 4;
+constexpr int kStages = 4;  // upper bound over configurations (barrier array size)
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarps = 4;
-constexpr unsigned kStageBytesA = BM * BK * 2;
-constexpr unsigned kStageBytesB = BN * BK * 2;
-constexpr unsigned kStageBytes = kStageBytesA + kStageBytesB;
 constexpr unsigned kTmemCols = 512;
-constexpr unsigned kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
 
 struct SharedState {
     std::uint64_t full[kStages];
@@ -144,7 +140,7 @@ struct Tile {
     int k_blocks;    // K / BK
     int c_row;       // first output row
     int c_col;       // first output column
-    int rows_valid;  // output rows of this tile that exist (<= BM)
+    int rows_valid;  // output rows of this tile that exist (<= 128 * HALVES)
     int cols_valid;  // output columns that exist (<= BN)
     int tag;         // policy-defined (expert, source rank, ...)
     int a_sel;       // 0: first A tensor map, 1: the alternate one
@@ -158,11 +154,29 @@ struct Tile {
 //                                                           whole tile was stored (CTA-wide ordered)
 //   __device__ void finish(int thread, int nthreads, status) - epilogue warps, after the last tile
 // `map_a_alt` is the tensor map used by tiles with a_sel == 1 (pass map_a when unused).
-template <typename Policy>
+// Geometry of one configuration.  HALVES = 1: 128 x 256 tiles, the two 256-column
+// halves of TMEM double-buffer the accumulator (epilogue of tile i overlaps the main
+// loop of tile i+1), 4 stages of 48 KiB.  HALVES = 2: 256 x 256 tiles - two 128-row
+// MMAs per K step share one B tile, which cuts shared-memory fill traffic per FLOP by
+// a third - each TMEM half holds one 128-row accumulator, the epilogue drains half 0
+// first so the next tile's first MMAs can start while half 1 drains; 3 stages of 64 KiB.
+template <int HALVES>
+struct Geometry {
+    static constexpr int kRows = BM * HALVES;
+    static constexpr int kStages = HALVES == 1 ? 4 : 3;
+    static constexpr unsigned kBytesA = kRows * BK * 2;
+    static constexpr unsigned kBytesB = BN * BK * 2;
+    static constexpr unsigned kStageBytes = kBytesA + kBytesB;
+    static constexpr unsigned kSmemBytes = kStages * kStageBytes + 1024;
+};
+
+template <int HALVES, typename Policy>
 __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap *map_a,
                                               const CUtensorMap *map_b,
                                               unsigned long long *status,
                                               const CUtensorMap *map_a_alt = nullptr) {
+    using G = Geometry<HALVES>;
+    constexpr int kStagesG = G::kStages;
     if (map_a_alt == nullptr)
         map_a_alt = map_a;
     extern __shared__ std::uint8_t smem_raw[];
@@ -173,7 +187,7 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kStagesG; ++s) {
             mbar_init(&st.full[s], 1);
             mbar_init(&st.empty[s], 1);
         }
@@ -193,6 +207,10 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
     tc_fence_after();
     const std::uint32_t tmem_base = st.tmem_base;
 
+    // Accumulator slot (TMEM half) and barrier parity of half `h` of tile `it`.
+    auto slot_of = [](int it, int h) { return HALVES == 1 ? (it & 1) : h; };
+    auto use_of = [](int it) -> unsigned { return HALVES == 1 ? ((it >> 1) & 1) : (it & 1); };
+
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
@@ -211,11 +229,11 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
                         set_status(status, aboleth::Status::Timeout, 0x3100 + stage);
                         break;
                     }
-                    std::uint8_t *sa = tiles + stage * kStageBytes;
-                    mbar_expect_tx(&st.full[stage], kStageBytes);
+                    std::uint8_t *sa = tiles + stage * G::kStageBytes;
+                    mbar_expect_tx(&st.full[stage], G::kStageBytes);
                     tma_load_2d(sa, t.a_sel ? map_a_alt : map_a, kb * BK, t.a_row, &st.full[stage]);
-                    tma_load_2d(sa + kStageBytesA, map_b, kb * BK, t.b_row, &st.full[stage]);
-                    if (++stage == kStages) {
+                    tma_load_2d(sa + G::kBytesA, map_b, kb * BK, t.b_row, &st.full[stage]);
+                    if (++stage == kStagesG) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -230,15 +248,7 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
             unsigned phase = 0;
             Tile t;
             for (int it = 0; !st.abort && policy.next(it, t); ++it) {
-                const int buf = it & 1;
-                const unsigned use = (it >> 1) & 1;
-                if (!mbar_wait(&st.tmem_empty[buf], use ^ 1)) {
-                    st.abort = 1;
-                    set_status(status, aboleth::Status::Timeout, 0x3200 + buf);
-                    break;
-                }
-                tc_fence_after();
-                const std::uint32_t d = tmem_base + buf * BN;
+                const unsigned use = use_of(it);
                 for (int kb = 0; kb < t.k_blocks && !st.abort; ++kb) {
                     if (!mbar_wait(&st.full[stage], phase)) {
                         st.abort = 1;
@@ -246,22 +256,38 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
                         break;
                     }
                     tc_fence_after();
-                    const std::uint32_t sa = smem_u32(tiles + stage * kStageBytes);
-                    const std::uint64_t da = smem_desc_sw128(sa);
-                    const std::uint64_t db = smem_desc_sw128(sa + kStageBytesA);
+                    const std::uint32_t sa = smem_u32(tiles + stage * G::kStageBytes);
+                    const std::uint64_t db = smem_desc_sw128(sa + G::kBytesA);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // 16 bf16 = 32 bytes further along K inside the swizzle atom.
-                        umma_bf16(d, da + (k * UMMA_K * 2 >> 4), db + (k * UMMA_K * 2 >> 4), idesc,
-                                  (kb | k) != 0);
+                    for (int h = 0; h < HALVES; ++h) {
+                        const int slot = slot_of(it, h);
+                        if (kb == 0) {
+                            // The accumulator must have been drained by the epilogue.
+                            if (!mbar_wait(&st.tmem_empty[slot], use ^ 1)) {
+                                st.abort = 1;
+                                set_status(status, aboleth::Status::Timeout, 0x3200 + slot);
+                                break;
+                            }
+                            tc_fence_after();
+                        }
+                        const std::uint32_t d = tmem_base + slot * BN;
+                        const std::uint64_t da = smem_desc_sw128(sa + h * (BM * BK * 2));
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            // 16 bf16 = 32 bytes further along K inside the swizzle atom.
+                            umma_bf16(d, da + (k * UMMA_K * 2 >> 4), db + (k * UMMA_K * 2 >> 4), idesc,
+                                      (kb | k) != 0);
+                        }
                     }
                     umma_commit(&st.empty[stage]);  // stage reusable once these MMAs read it
-                    if (++stage == kStages) {
+                    if (++stage == kStagesG) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
-                umma_commit(&st.tmem_full[buf]);  // accumulator complete
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h)
+                    umma_commit(&st.tmem_full[slot_of(it, h)]);  // accumulators complete
             }
         }
     } else {
@@ -269,30 +295,33 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
         const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31
         Tile t;
         for (int it = 0; !st.abort && policy.next(it, t); ++it) {
-            const int buf = it & 1;
-            const unsigned use = (it >> 1) & 1;
-            if (!mbar_wait(&st.tmem_full[buf], use)) {
-                st.abort = 1;
-                set_status(status, aboleth::Status::Timeout, 0x3400 + buf);
-                break;
-            }
-            tc_fence_after();
-            const int row = quarter * 32 + lane;
-            const bool row_ok = row < t.rows_valid;
-            const std::uint32_t taddr = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) +
-                                        buf * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                if (c * 32 >= t.cols_valid)
+            const unsigned use = use_of(it);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+                const int slot = slot_of(it, h);
+                if (!mbar_wait(&st.tmem_full[slot], use)) {
+                    st.abort = 1;
+                    set_status(status, aboleth::Status::Timeout, 0x3400 + slot);
                     break;
-                float v[32];
-                tmem_ld32(taddr + c * 32, v);
-                policy.store(t, row, c * 32, v, row_ok);
+                }
+                tc_fence_after();
+                const int row = h * BM + quarter * 32 + lane;
+                const bool row_ok = row < t.rows_valid;
+                const std::uint32_t taddr = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) +
+                                            slot * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    if (c * 32 >= t.cols_valid)
+                        break;
+                    float v[32];
+                    tmem_ld32(taddr + c * 32, v);
+                    policy.store(t, row, c * 32, v, row_ok);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&st.tmem_empty[slot]);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(&st.tmem_empty[buf]);
             // Tile-complete hook: needs all four epilogue warps' stores.
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (warp == 2 && lane == 0)

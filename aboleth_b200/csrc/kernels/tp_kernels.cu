@@ -1,7 +1,7 @@
 // Tensor-parallel GEMMs fused with their collective, one launch each.
 //
 // ALL-GATHER -> GEMM   C[world*Ml, Nl] = gather_ranks(A_local[Ml, K]) * B_local[Nl, K]^T
-//   `push_ctas` CTAs first store this rank's A shard, 128-row chunk by chunk,
+//   `push_ctas` CTAs first store this rank's A shard, 256-row chunk by chunk,
 //   into every peer's gathered-A staging over NVLink and publish each chunk
 //   with one release flag; then they join the others in the persistent tcgen05
 //   main loop.  The TMA producer of a tile whose rows came from rank s waits
@@ -26,6 +26,10 @@ namespace {
 using namespace ab::gemm;
 using aboleth::Status;
 
+constexpr int kHalves = 2;          // 256-row tiles
+constexpr int kRows = BM * kHalves;  // rows per chunk / tile
+constexpr unsigned kSmem = Geometry<kHalves>::kSmemBytes;
+
 constexpr int kPhaseProduce = 1;  // AG: push shard.  RS: GEMM + partial stores.
 constexpr int kPhaseConsume = 2;  // AG: GEMM.        RS: reduction of owned tiles.
 
@@ -37,7 +41,7 @@ struct AgGemmPolicy {
     unsigned long long *status;
     std::uint64_t epoch;
     int rank, world, m_local, n, k, ldc, phases;
-    int tiles_n, chunks;              // chunks = m_local / BM (row blocks per rank)
+    int tiles_n, chunks;              // chunks = m_local / 256 (row blocks per rank)
 
     __device__ __forceinline__ bool next(int it, Tile &t) const {
         if (!(phases & kPhaseConsume))
@@ -52,12 +56,12 @@ struct AgGemmPolicy {
         const int src = (rank - order + world) % world;
         const int chunk = local / tiles_n, tn = local - chunk * tiles_n;
         t.a_sel = src == rank ? 1 : 0;
-        t.a_row = src == rank ? chunk * BM : src * m_local + chunk * BM;
+        t.a_row = src == rank ? chunk * kRows : src * m_local + chunk * kRows;
         t.b_row = tn * BN;
         t.k_blocks = (k + BK - 1) / BK;
-        t.c_row = src * m_local + chunk * BM;
+        t.c_row = src * m_local + chunk * kRows;
         t.c_col = tn * BN;
-        t.rows_valid = min(BM, m_local - chunk * BM);
+        t.rows_valid = min(kRows, m_local - chunk * kRows);
         t.cols_valid = min(BN, n - tn * BN);
         t.tag = src * chunks + chunk;
         return true;
@@ -92,11 +96,11 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_staging,
     if ((policy.phases & kPhaseProduce) && static_cast<int>(blockIdx.x) < push.push_ctas) {
         // Work items (peer, chunk), nearest peer first; one CTA per item.
         const int items = (policy.world - 1) * policy.chunks;
-        const std::size_t chunk_bytes = static_cast<std::size_t>(BM) * policy.k * 2;
+        const std::size_t chunk_bytes = static_cast<std::size_t>(kRows) * policy.k * 2;
         for (int item = blockIdx.x; item < items; item += push.push_ctas) {
             const int hop = item / policy.chunks + 1, chunk = item - (hop - 1) * policy.chunks;
             const int peer = (policy.rank + hop) % policy.world;
-            const int rows = min(BM, policy.m_local - chunk * BM);
+            const int rows = min(kRows, policy.m_local - chunk * kRows);
             const std::size_t bytes = static_cast<std::size_t>(rows) * policy.k * 2;
             std::uint8_t *dst = reinterpret_cast<std::uint8_t *>(push.peer_staging[peer]) +
                                 (static_cast<std::size_t>(policy.rank) * policy.m_local) * policy.k * 2 +
@@ -110,7 +114,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_staging,
             __syncthreads();
         }
     }
-    gemm_mainloop(policy, &map_staging, &map_b, policy.status, &map_local);
+    gemm_mainloop<kHalves>(policy, &map_staging, &map_b, policy.status, &map_local);
 }
 
 // ---- GEMM -> reduce-scatter -----------------------------------------------------------------
@@ -138,12 +142,12 @@ struct GemmRsPolicy {
         const int owner = (rank + 1 + order) % world;
         const int chunk = local / tiles_n, tn = local - chunk * tiles_n;
         t.a_sel = 0;
-        t.a_row = owner * m_local + chunk * BM;
+        t.a_row = owner * m_local + chunk * kRows;
         t.b_row = tn * BN;
         t.k_blocks = (k + BK - 1) / BK;
-        t.c_row = chunk * BM;  // row inside the owner's block
+        t.c_row = chunk * kRows;  // row inside the owner's block
         t.c_col = tn * BN;
-        t.rows_valid = min(BM, m_local - chunk * BM);
+        t.rows_valid = min(kRows, m_local - chunk * kRows);
         t.cols_valid = min(BN, n - tn * BN);
         t.tag = owner * 65536 + local;  // owner and tile index inside the owner's block
         return true;
@@ -181,11 +185,11 @@ struct GemmRsPolicy {
             if (!ok)
                 ab::set_status(st, Status::Timeout, 0x4000 + thread);
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            const int rows = min(BM, m_local - chunk * BM), cols = min(BN, n - tn * BN);
+            const int rows = min(kRows, m_local - chunk * kRows), cols = min(BN, n - tn * BN);
             const int vec_per_row = cols / 8;
             for (int i = thread; i < rows * vec_per_row; i += nthreads) {
                 const int r = i / vec_per_row, v = i - r * vec_per_row;
-                const std::size_t off = static_cast<std::size_t>(chunk * BM + r) * n + tn * BN + v * 8;
+                const std::size_t off = static_cast<std::size_t>(chunk * kRows + r) * n + tn * BN + v * 8;
                 float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                 for (int s = 0; s < world; ++s) {
                     const uint4 y = aboleth::detail::ld_stream16(
@@ -217,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                GemmRsPolicy params) {
     GemmRsPolicy policy = params;
-    gemm_mainloop(policy, &map_a, &map_b, policy.status);
+    gemm_mainloop<kHalves>(policy, &map_a, &map_b, policy.status);
 }
 
 int sm_count() {
@@ -233,61 +237,61 @@ int sm_count() {
 }  // namespace
 
 // a_local [m_local, k]; staging [world*m_local, k] (this rank's gathered-A buffer, peers write it);
-// b [n, k]; c [world*m_local, n].  m_local must be a multiple of 128.  peer_staging / peer_flags:
-// device int64 [world] address tables; flags: local int64 [world * m_local/128].
+// b [n, k]; c [world*m_local, n].  m_local must be a multiple of 256.  peer_staging / peer_flags:
+// device int64 [world] address tables; flags: local int64 [world * m_local/256].
 AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const void *b, void *c,
                               const std::uint64_t *peer_staging, const std::uint64_t *peer_flags,
                               const std::uint64_t *flags, unsigned long long *status,
                               std::uint64_t epoch, int rank, int world, int m_local, int n, int k,
                               int push_ctas, int phases, cudaStream_t stream) {
-    if (world < 1 || m_local < BM || m_local % BM || n < 8 || n % 8 || k < 8 || k % 8 || rank < 0 ||
+    if (world < 1 || m_local < kRows || m_local % kRows || n < 8 || n % 8 || k < 8 || k % 8 || rank < 0 ||
         rank >= world)
         return -1;
     CUtensorMap map_staging, map_b, map_local;
-    if (!make_map_bf16(&map_staging, staging, static_cast<std::uint64_t>(world) * m_local, k, k, BM) ||
-        !make_map_bf16(&map_b, b, n, k, k, BN) || !make_map_bf16(&map_local, a_local, m_local, k, k, BM))
+    if (!make_map_bf16(&map_staging, staging, static_cast<std::uint64_t>(world) * m_local, k, k, kRows) ||
+        !make_map_bf16(&map_b, b, n, k, k, BN) || !make_map_bf16(&map_local, a_local, m_local, k, k, kRows))
         return -2;
     static bool configured =
-        cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) ==
+        cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) ==
         cudaSuccess;
     if (!configured)
         return -3;
     AgGemmPolicy p{static_cast<__nv_bfloat16 *>(c), flags, status, epoch, rank, world, m_local, n, k, n,
-                   phases, (n + BN - 1) / BN, m_local / BM};
+                   phases, (n + BN - 1) / BN, m_local / kRows};
     if (push_ctas < 1)
         push_ctas = 32;
     if (push_ctas > sm_count())
         push_ctas = sm_count();
     AgPush push{static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, push_ctas};
-    ag_gemm_kernel<<<sm_count(), kThreads, kSmemBytes, stream>>>(map_staging, map_b, map_local, p, push);
+    ag_gemm_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_staging, map_b, map_local, p, push);
     return ab::launch_result("ag_gemm_bf16");
 }
 
 // a [world*m_local, k_local]; b [n, k_local]; partials: local [world, m_local, n] (peers write it);
-// out [m_local, n].  m_local multiple of 128, n multiple of 8 and tiles per owner < 65536.
+// out [m_local, n].  m_local multiple of 256, n multiple of 8 and tiles per owner < 65536.
 AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials, void *out,
                               const std::uint64_t *peer_partials, const std::uint64_t *peer_flags,
                               const std::uint64_t *flags, unsigned long long *status,
                               std::uint64_t epoch, int rank, int world, int m_local, int n, int k,
                               int phases, cudaStream_t stream) {
-    if (world < 1 || m_local < BM || m_local % BM || n < 8 || n % 8 || k < 8 || k % 8 || rank < 0 ||
+    if (world < 1 || m_local < kRows || m_local % kRows || n < 8 || n % 8 || k < 8 || k % 8 || rank < 0 ||
         rank >= world)
         return -1;
-    const int tiles_n = (n + BN - 1) / BN, chunks = m_local / BM;
+    const int tiles_n = (n + BN - 1) / BN, chunks = m_local / kRows;
     if (tiles_n * chunks >= 65536)
         return -1;
     CUtensorMap map_a, map_b;
-    if (!make_map_bf16(&map_a, a, static_cast<std::uint64_t>(world) * m_local, k, k, BM) ||
+    if (!make_map_bf16(&map_a, a, static_cast<std::uint64_t>(world) * m_local, k, k, kRows) ||
         !make_map_bf16(&map_b, b, n, k, k, BN))
         return -2;
     static bool configured =
-        cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) ==
+        cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) ==
         cudaSuccess;
     if (!configured)
         return -3;
     GemmRsPolicy p{peer_partials, peer_flags, static_cast<const __nv_bfloat16 *>(partials), flags,
                    static_cast<__nv_bfloat16 *>(out), status, epoch, rank, world, m_local, n, k, phases,
                    tiles_n, chunks};
-    gemm_rs_kernel<<<sm_count(), kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+    gemm_rs_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_a, map_b, p);
     return ab::launch_result("gemm_rs_bf16");
 }

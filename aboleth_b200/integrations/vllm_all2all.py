@@ -1,0 +1,107 @@
+"""``--all2all-backend aboleth`` for a vLLM-style engine: manager and prepare/finalize.
+
+The reference ships this as a patch against one vLLM commit
+(integrations/vllm/0001-aboleth-all2all-backend.patch:96-136,751-955).  Here the same
+two classes are plain Python over this package's runtime, usable by the in-repo
+serving model (``aboleth_b200.models.mixtral``) and registrable with an installed
+vLLM whose ``FusedMoEPrepareAndFinalize`` interface matches (``register_with_vllm``).
+Constraints are the reference's: expert parallel == data parallel >= 2 (1 is allowed
+here for single-GPU runs), tensor parallel 1.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..bootstrap import TorchDistributedBootstrap
+from ..moe.family import uniform_token_bound
+from ..world import World
+from .compiled_vllm import AbolethMoERuntimeManager, ModularMoERuntime, PreparedExperts
+
+
+class AbolethAll2AllManager:
+    """Owns the World and the MoE runtime manager of one engine process."""
+
+    def __init__(self, cpu_group=None, *, tp_size: int = 1, device: Optional[int] = None,
+                 world: Optional[World] = None):
+        if tp_size != 1:
+            raise ValueError("the aboleth all2all backend requires tensor parallel size 1")
+        self.cpu_group = cpu_group
+        if world is None:
+            import torch.distributed as dist
+            if cpu_group is not None:
+                bootstrap = TorchDistributedBootstrap(cpu_group)
+                rank, size = bootstrap.rank, bootstrap.world_size
+            elif dist.is_available() and dist.is_initialized():
+                raise ValueError("pass the engine's CPU (gloo) group as cpu_group")
+            else:
+                bootstrap, rank, size = None, 0, 1
+            world = World(rank, size, device=device, bootstrap=bootstrap)
+            world.connect_all("auto", remote_transport="proxy")
+        self.world = world
+        self.runtime = AbolethMoERuntimeManager(world=world, internode=False)
+
+    def get_handle(self, kwargs: dict, **options):
+        return self.runtime.get_handle(kwargs, **options)
+
+    def destroy(self) -> None:
+        self.runtime.close()
+        self.world.close()
+
+
+class AbolethPrepareAndFinalize:
+    """Dispatch before the experts, combine after them; one instance per MoE layer."""
+
+    def __init__(self, manager: AbolethAll2AllManager, layer_facts: dict, *, num_slots: int = 1,
+                 placement_strategy: str = "linear", layer_name: str = ""):
+        self.manager = manager
+        self.num_experts = layer_facts["num_experts"]
+        self.slot = 0
+        family = manager.get_handle(layer_facts, num_slots=num_slots,
+                                    placement_strategy=placement_strategy)
+        self.runtime = ModularMoERuntime(family, layer_name=layer_name, slot_provider=lambda: self.slot)
+
+    def _wave_uniform_tokens(self, tokens: int) -> int:
+        """Every rank must select the same shape variant: agree on the maximum token count."""
+        if not self.runtime.has_decode_sibling:
+            return tokens
+        return uniform_token_bound(tokens, self.manager.cpu_group)
+
+    def prepare(self, a1: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor, *,
+                quantized_input: bool = False, apply_router_weight_on_input: bool = False) -> PreparedExperts:
+        return self.runtime.prepare(
+            a1, topk_weights, topk_ids, num_experts=self.num_experts, expert_map=True,
+            apply_router_weight_on_input=apply_router_weight_on_input,
+            required_tokens=self._wave_uniform_tokens(a1.shape[0]), quantized_input=quantized_input,
+            defer_input_quant=False)
+
+    def finalize(self, output: torch.Tensor, fused_expert_output: torch.Tensor,
+                 expert_offsets: Optional[torch.Tensor] = None) -> None:
+        self.runtime.finalize(output, fused_expert_output, expert_offsets)
+
+    # Dual-batch overlap: the two halves of a layer are separate calls, so an engine can
+    # interleave another micro-batch (another slot) between them.
+    def prepare_async(self, *args, slot: int = 0, **kwargs):
+        self.slot = slot
+        prepared = self.prepare(*args, **kwargs)
+        return lambda: prepared
+
+    def finalize_async(self, output, fused_expert_output, *, slot: int = 0, **kwargs):
+        self.slot = slot
+        self.finalize(output, fused_expert_output, **kwargs)
+        return lambda: None
+
+
+def register_with_vllm() -> bool:
+    """Expose the backend name to an installed vLLM if its registry can be found.
+    Returns False (and changes nothing) when vLLM is absent or its layout differs."""
+    try:
+        from vllm.distributed.device_communicators import all2all  # type: ignore
+    except Exception:  # noqa: BLE001
+        return False
+    registry = getattr(all2all, "ALL2ALL_BACKENDS", None)
+    if isinstance(registry, dict):
+        registry["aboleth"] = AbolethAll2AllManager
+        return True
+    return False

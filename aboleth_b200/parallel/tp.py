@@ -24,7 +24,7 @@ declare("ab_ag_gemm_bf16", [_VP] * 8 + [_U64] + [_I] * 7 + [_VP])
 declare("ab_gemm_rs_bf16", [_VP] * 8 + [_U64] + [_I] * 6 + [_VP])
 
 PRODUCE, CONSUME = 1, 2
-BM = 128
+BM = 256  # rows per tile / chunk of the fused kernels
 
 
 def _align(n: int, a: int = 256) -> int:
@@ -71,7 +71,7 @@ class AllGatherGemm:
     def __init__(self, rank: int, world_size: int, m_local: int, k: int, buffers: _Buffers,
                  tables, *, push_ctas: int = 32):
         if m_local % BM:
-            raise ValueError("rows per rank must be a multiple of 128")
+            raise ValueError("rows per rank must be a multiple of 256")
         self.rank, self.world_size, self.m_local, self.k = rank, world_size, m_local, k
         self.buffers, self.tables, self.push_ctas = buffers, tables, push_ctas
         self.status = torch.zeros(2, dtype=torch.int64, device=buffers.arena.device)
@@ -123,7 +123,7 @@ class GemmReduceScatter:
 
     def __init__(self, rank: int, world_size: int, m_local: int, n: int, buffers: _Buffers, tables):
         if m_local % BM or n % 8:
-            raise ValueError("rows per rank must be a multiple of 128 and n a multiple of 8")
+            raise ValueError("rows per rank must be a multiple of 256 and n a multiple of 8")
         self.rank, self.world_size, self.m_local, self.n = rank, world_size, m_local, n
         self.buffers, self.tables = buffers, tables
         self.status = torch.zeros(2, dtype=torch.int64, device=buffers.arena.device)
