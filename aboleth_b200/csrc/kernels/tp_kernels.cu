@@ -1,10 +1,10 @@
 // Tensor-parallel GEMMs fused with their collective, one launch each.
 //
 // ALL-GATHER -> GEMM   C[world*Ml, Nl] = gather_ranks(A_local[Ml, K]) * B_local[Nl, K]^T
-//   `push_ctas` CTAs first store this rank's A shard, 256-row chunk by chunk,
-//   into every peer's gathered-A staging over NVLink and publish each chunk
-//   with one release flag; then they join the others in the persistent tcgen05
-//   main loop.  The TMA producer of a tile whose rows came from rank s waits
+//   Every CTA first stores its share of this rank's A shard into every peer's
+//   gathered-A staging over NVLink; the CTA that completes a 256-row chunk for a
+//   peer publishes it with one release flag; then all CTAs run the persistent
+//   tcgen05 main loop.  The TMA producer of a tile whose rows came from rank s waits
 //   (bounded) on the chunk's flag and then loads the tile from LOCAL staging -
 //   a remote tile crosses NVLink once, TMA never touches peer memory, nothing
 //   is multicast.  Tiles of the rank's own rows read A_local through a second
@@ -19,6 +19,8 @@
 //
 // No reference kernel exists for these; the baseline is NCCL all-gather /
 // reduce-scatter around a library GEMM.
+#include <algorithm>
+
 #include "gemm_sm100.cuh"
 
 namespace {
@@ -85,7 +87,8 @@ struct AgPush {
     const std::uint8_t *a_local;          // [m_local, k] bf16
     const std::uint64_t *peer_staging;    // [world] address of each peer's gathered-A buffer
     const std::uint64_t *peer_flags;      // [world] address of each peer's flag array
-    int push_ctas;
+    unsigned *arrivals;                   // local scratch [world * chunks], zero between calls
+    int parts;                            // CTAs that share one (peer, chunk)
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -93,24 +96,39 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_staging,
                const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_local, AgGemmPolicy params, AgPush push) {
     AgGemmPolicy policy = params;
-    if ((policy.phases & kPhaseProduce) && static_cast<int>(blockIdx.x) < push.push_ctas) {
-        // Work items (peer, chunk), nearest peer first; one CTA per item.
-        const int items = (policy.world - 1) * policy.chunks;
-        const std::size_t chunk_bytes = static_cast<std::size_t>(kRows) * policy.k * 2;
-        for (int item = blockIdx.x; item < items; item += push.push_ctas) {
-            const int hop = item / policy.chunks + 1, chunk = item - (hop - 1) * policy.chunks;
+    if (policy.phases & kPhaseProduce) {
+        // Every CTA pushes its share first (a few hundred KiB), so that no CTA starts its
+        // GEMM tiles much later than the others.  Work item = (peer, chunk, part), nearest
+        // peer first; the part that arrives last on (peer, chunk) publishes the chunk.
+        __shared__ int last;
+        const int items = (policy.world - 1) * policy.chunks * push.parts;
+        const std::size_t row_bytes = static_cast<std::size_t>(policy.k) * 2;
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const int part = item % push.parts;
+            const int pc = item / push.parts;
+            const int hop = pc / policy.chunks + 1, chunk = pc - (hop - 1) * policy.chunks;
             const int peer = (policy.rank + hop) % policy.world;
             const int rows = min(kRows, policy.m_local - chunk * kRows);
-            const std::size_t bytes = static_cast<std::size_t>(rows) * policy.k * 2;
+            const int per = (rows + push.parts - 1) / push.parts;
+            const int r0 = min(part * per, rows), r1 = min(r0 + per, rows);
+            const std::size_t offset = (static_cast<std::size_t>(chunk) * kRows + r0) * row_bytes;
             std::uint8_t *dst = reinterpret_cast<std::uint8_t *>(push.peer_staging[peer]) +
-                                (static_cast<std::size_t>(policy.rank) * policy.m_local) * policy.k * 2 +
-                                chunk * chunk_bytes;
-            aboleth::detail::copy_strided(dst, push.a_local + chunk * chunk_bytes, bytes, threadIdx.x,
+                                static_cast<std::size_t>(policy.rank) * policy.m_local * row_bytes + offset;
+            aboleth::detail::copy_strided(dst, push.a_local + offset, (r1 - r0) * row_bytes, threadIdx.x,
                                           blockDim.x);
-            std::uint64_t *flag = reinterpret_cast<std::uint64_t *>(push.peer_flags[peer]) +
-                                  policy.rank * policy.chunks + chunk;
-            aboleth::signal_block(aboleth::RemoteRegion{reinterpret_cast<std::uint64_t>(flag), 0},
-                                  policy.epoch);
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                aboleth::detail::fence_acq_rel_sys();
+                unsigned *counter = push.arrivals + peer * policy.chunks + chunk;
+                last = atomicAdd(counter, 1u) == static_cast<unsigned>(push.parts) - 1;
+                if (last) {
+                    *counter = 0;  // self-cleaning
+                    aboleth::detail::fence_acq_rel_sys();
+                    std::uint64_t *flag = reinterpret_cast<std::uint64_t *>(push.peer_flags[peer]) +
+                                          policy.rank * policy.chunks + chunk;
+                    aboleth::detail::st_release_sys(flag, policy.epoch);
+                }
+            }
             __syncthreads();
         }
     }
@@ -187,30 +205,43 @@ struct GemmRsPolicy {
             asm volatile("bar.sync 1, 128;" ::: "memory");
             const int rows = min(kRows, m_local - chunk * kRows), cols = min(BN, n - tn * BN);
             const int vec_per_row = cols / 8;
-            for (int i = thread; i < rows * vec_per_row; i += nthreads) {
-                const int r = i / vec_per_row, v = i - r * vec_per_row;
-                const std::size_t off = static_cast<std::size_t>(chunk * kRows + r) * n + tn * BN + v * 8;
-                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            // Two 16-byte vectors per thread and per source in flight.
+            for (int i = thread; i < rows * vec_per_row; i += 2 * nthreads) {
+                const int i2 = i + nthreads;
+                const bool two = i2 < rows * vec_per_row;
+                const int ra = i / vec_per_row, va = i - ra * vec_per_row;
+                const int rb = two ? i2 / vec_per_row : ra, vb = two ? i2 - rb * vec_per_row : va;
+                const std::size_t offa = static_cast<std::size_t>(chunk * kRows + ra) * n + tn * BN + va * 8;
+                const std::size_t offb = static_cast<std::size_t>(chunk * kRows + rb) * n + tn * BN + vb * 8;
+                float acc[2][8] = {};
                 for (int s = 0; s < world; ++s) {
-                    const uint4 y = aboleth::detail::ld_stream16(
-                        partials + static_cast<std::size_t>(s) * m_local * n + off);
-                    const std::uint32_t w[4] = {y.x, y.y, y.z, y.w};
+                    const __nv_bfloat16 *base = partials + static_cast<std::size_t>(s) * m_local * n;
+                    const uint4 ya = aboleth::detail::ld_stream16(base + offa);
+                    const uint4 yb = aboleth::detail::ld_stream16(base + offb);
+                    const std::uint32_t wa[4] = {ya.x, ya.y, ya.z, ya.w}, wb[4] = {yb.x, yb.y, yb.z, yb.w};
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        acc[2 * q] += __uint_as_float(w[q] << 16);
-                        acc[2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u);
+                        acc[0][2 * q] += __uint_as_float(wa[q] << 16);
+                        acc[0][2 * q + 1] += __uint_as_float(wa[q] & 0xffff0000u);
+                        acc[1][2 * q] += __uint_as_float(wb[q] << 16);
+                        acc[1][2 * q + 1] += __uint_as_float(wb[q] & 0xffff0000u);
                     }
                 }
-                uint4 o;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[0], acc[1]);
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(acc[2], acc[3]);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[4], acc[5]);
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(acc[6], acc[7]);
-                o.x = *reinterpret_cast<std::uint32_t *>(&p0);
-                o.y = *reinterpret_cast<std::uint32_t *>(&p1);
-                o.z = *reinterpret_cast<std::uint32_t *>(&p2);
-                o.w = *reinterpret_cast<std::uint32_t *>(&p3);
-                *reinterpret_cast<uint4 *>(out + off) = o;
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (u == 1 && !two)
+                        break;
+                    uint4 o;
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[u][0], acc[u][1]);
+                    __nv_bfloat162 p1 = __floats2bfloat162_rn(acc[u][2], acc[u][3]);
+                    __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[u][4], acc[u][5]);
+                    __nv_bfloat162 p3 = __floats2bfloat162_rn(acc[u][6], acc[u][7]);
+                    o.x = *reinterpret_cast<std::uint32_t *>(&p0);
+                    o.y = *reinterpret_cast<std::uint32_t *>(&p1);
+                    o.z = *reinterpret_cast<std::uint32_t *>(&p2);
+                    o.w = *reinterpret_cast<std::uint32_t *>(&p3);
+                    *reinterpret_cast<uint4 *>(out + (u ? offb : offa)) = o;
+                }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
@@ -242,8 +273,8 @@ int sm_count() {
 AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const void *b, void *c,
                               const std::uint64_t *peer_staging, const std::uint64_t *peer_flags,
                               const std::uint64_t *flags, unsigned long long *status,
-                              std::uint64_t epoch, int rank, int world, int m_local, int n, int k,
-                              int push_ctas, int phases, cudaStream_t stream) {
+                              unsigned *arrivals, std::uint64_t epoch, int rank, int world, int m_local,
+                              int n, int k, int parts, int phases, cudaStream_t stream) {
     if (world < 1 || m_local < kRows || m_local % kRows || n < 8 || n % 8 || k < 8 || k % 8 || rank < 0 ||
         rank >= world)
         return -1;
@@ -258,11 +289,10 @@ AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const vo
         return -3;
     AgGemmPolicy p{static_cast<__nv_bfloat16 *>(c), flags, status, epoch, rank, world, m_local, n, k, n,
                    phases, (n + BN - 1) / BN, m_local / kRows};
-    if (push_ctas < 1)
-        push_ctas = 32;
-    if (push_ctas > sm_count())
-        push_ctas = sm_count();
-    AgPush push{static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, push_ctas};
+    const int pairs = (world - 1) * (m_local / kRows);
+    if (parts < 1)  // about one work item per CTA
+        parts = pairs > 0 ? std::max(1, sm_count() / pairs) : 1;
+    AgPush push{static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, arrivals, parts};
     ag_gemm_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_staging, map_b, map_local, p, push);
     return ab::launch_result("ag_gemm_bf16");
 }

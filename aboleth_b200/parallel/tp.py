@@ -20,7 +20,7 @@ import torch
 from ..ops._kernels import _I, _U64, _VP, call, declare, ptr, stream_ptr
 from ..world import World
 
-declare("ab_ag_gemm_bf16", [_VP] * 8 + [_U64] + [_I] * 7 + [_VP])
+declare("ab_ag_gemm_bf16", [_VP] * 9 + [_U64] + [_I] * 7 + [_VP])
 declare("ab_gemm_rs_bf16", [_VP] * 8 + [_U64] + [_I] * 6 + [_VP])
 
 PRODUCE, CONSUME = 1, 2
@@ -69,12 +69,15 @@ class AllGatherGemm:
     """Column-parallel linear layer whose input is sharded by rows across ranks."""
 
     def __init__(self, rank: int, world_size: int, m_local: int, k: int, buffers: _Buffers,
-                 tables, *, push_ctas: int = 32):
+                 tables, *, push_parts: int = 0):
         if m_local % BM:
             raise ValueError("rows per rank must be a multiple of 256")
         self.rank, self.world_size, self.m_local, self.k = rank, world_size, m_local, k
-        self.buffers, self.tables, self.push_ctas = buffers, tables, push_ctas
+        self.buffers, self.tables, self.push_parts = buffers, tables, push_parts  # 0: one item per CTA
         self.status = torch.zeros(2, dtype=torch.int64, device=buffers.arena.device)
+        # Sender-side arrival counters of the push, one per (peer, chunk); the kernel resets them.
+        self.arrivals = torch.zeros(world_size * (m_local // BM), dtype=torch.int32,
+                                    device=buffers.arena.device)
         self.epoch = 0
 
     @staticmethod
@@ -108,8 +111,8 @@ class AllGatherGemm:
         peer_data, peer_flags = self.tables[which]
         call("ab_ag_gemm_bf16", ptr(a_local), ptr(self.buffers.data(which)), ptr(b_local), ptr(out),
              ptr(peer_data), ptr(peer_flags), ptr(self.buffers.flags(which)), ptr(self.status),
-             (self.epoch + 1) // 2, self.rank, self.world_size, self.m_local, n, self.k,
-             self.push_ctas, phases, stream_ptr())
+             ptr(self.arrivals), (self.epoch + 1) // 2, self.rank, self.world_size, self.m_local, n,
+             self.k, self.push_parts, phases, stream_ptr())
         return out
 
     def check(self) -> None:

@@ -18,6 +18,8 @@ from __future__ import annotations
 import argparse
 import json
 import os
+
+os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
 import statistics
 import sys
 import threading

@@ -27,7 +27,7 @@ def main() -> int:
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--ffn", type=int, default=28672)
     ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--push-ctas", type=int, default=32)
+    ap.add_argument("--push-parts", type=int, default=0, help="CTAs per (peer, chunk) of the push; 0 = auto")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     ab, world, distributed = setup()
@@ -72,7 +72,7 @@ def main() -> int:
 
     # ---- all-gather -> GEMM ----
     a_local = a_full[rank * m_local:(rank + 1) * m_local].contiguous()
-    fused = AllGatherGemm.create(world, m_local, args.hidden, push_ctas=args.push_ctas)
+    fused = AllGatherGemm.create(world, m_local, args.hidden, push_parts=args.push_parts)
     t_fused = timed(lambda: fused(a_local, b_col, out))
     fused.check()
     gathered = torch.empty_like(a_full)

@@ -1,0 +1,58 @@
+"""The public names a user of the reference package expects exist (no GPU)."""
+import aboleth_b200 as ab
+
+EXPECTED = """AllocationHandle AllocationProvider Artifact AutoTransportPolicy Bootstrap CapacityContract
+CommunicationDataflow CommunicationRegion CommunicationStage CompiledPattern CompiledPatternPlan CompiledPhase
+DeviceLibrary Endpoint EndpointTable ExecutionContract ExecutionDecision ExecutionFallback FragmentArtifact
+GENERIC_KV_TARGET_PROFILE H200_NVLINK_KV_TARGET_PROFILE KVCacheLayoutContract KVRuntimeOverrides KVTargetProfile
+KernelBinding LocalBuffer LocalEndpoint LocalRegion OpaqueCapabilities OpaqueStage P2PRealizationProfile
+PaddingSemantics Pattern PeerRegionTable PhaseBinding PhaseResources PhaseSchedule PipeBootstrap
+PipeBootstrapCoordinator RegionEffect RegionRequirement RankControl RegisteredBuffer RemoteBuffer RemoteHandle
+Runtime RuntimeGuard SimplifiedCommunicationDataflow StandaloneKernel TcpStoreBootstrap TorchDistributedBootstrap
+Transport TransportPhase TransportPlan Workset World compilation compile_execution_plan compile_phase
+connection_info_from_bytes connection_transport device_library plan_transport select_kv_target_profile
+simplify_communication_dataflow""".split()
+
+
+def test_reference_names_exist():
+    missing = [name for name in EXPECTED if not hasattr(ab, name)]
+    assert not missing, missing
+
+
+def test_subpackages_import():
+    import aboleth_b200.compiler  # noqa: F401
+    import aboleth_b200.integrations  # noqa: F401
+    import aboleth_b200.kv  # noqa: F401
+    import aboleth_b200.models  # noqa: F401
+    import aboleth_b200.moe  # noqa: F401
+    import aboleth_b200.records  # noqa: F401
+    from aboleth_b200.device_library import cached_device_library
+    from aboleth_b200.integrations import AbolethAll2AllManager, AbolethPrepareAndFinalize  # noqa: F401
+    from aboleth_b200.moe import MoESpec, NativeMoEFamily, NativeMoESlot, compile_moe_plan  # noqa: F401
+    assert callable(cached_device_library)
+
+
+def test_device_library_package(tmp_path, monkeypatch):
+    import json
+    import subprocess
+
+    monkeypatch.setenv("ABOLETH_CACHE_DIR", str(tmp_path))
+    lib = ab.device_library(transports=["p2p", "rdma"])
+    manifest = json.loads(lib.manifest.read_text())
+    assert manifest["abi"] == 2 and manifest["served_by_host_proxy"] == ["rdma"] and manifest["bounded_waits"]
+    assert "put_many_signal" in manifest["operations"] and lib.header.exists()
+    assert ab.device_library(transports=["p2p", "rdma"]).digest == lib.digest  # cache hit
+    # A client kernel written against the facade compiles for sm_100a with the published flags.
+    src = tmp_path / "client.cu"
+    src.write_text('#include "aboleth/device.cuh"\n'
+                   '__global__ void k(const std::uint64_t* eps, unsigned long long* st, '
+                   'unsigned long long dst, unsigned long long src, unsigned long long flag) {\n'
+                   '  aboleth::DeviceContext ctx{eps, nullptr, st};\n'
+                   '  aboleth::put(ctx, 1, aboleth::RemoteRegion{dst, 0}, aboleth::LocalRegion{src, 0}, 256);\n'
+                   '  aboleth::put_inline(ctx, 1, aboleth::RemoteRegion{dst + 256, 0}, 7);\n'
+                   '  aboleth::signal(ctx, 1, aboleth::RemoteRegion{flag, 0}, 1);\n'
+                   '  aboleth::quiet(ctx, 1);\n'
+                   '  aboleth::wait_signal(ctx, (const std::uint64_t*)flag, 1);\n}\n')
+    subprocess.run(["nvcc", *lib.nvcc_flags(), "-c", str(src), "-o", str(tmp_path / "client.o")], check=True)
+    special = ab.device_library(transports=["p2p"], specialize="p2p")
+    assert "ABOLETH_TIER1_SPECIALIZED" in special.header.read_text()
