@@ -47,10 +47,17 @@ def _rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight
 
 
+_ROPE_INV: dict = {}
+
+
 def _rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
     # x: [B, heads, S, D]; positions: [B, S]
     d = x.shape[-1]
-    inv = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
+    key = (d, theta, x.device)
+    inv = _ROPE_INV.get(key)
+    if inv is None:
+        inv = _ROPE_INV[key] = 1.0 / (theta ** (torch.arange(0, d, 2, device=x.device,
+                                                                 dtype=torch.float32) / d))
     ang = positions[:, None, :, None].float() * inv
     cos, sin = ang.cos(), ang.sin()
     x1, x2 = x[..., 0::2].float(), x[..., 1::2].float()
@@ -143,6 +150,15 @@ class MixtralEP:
         self.kv[index, 0, :b, :, start:start + s] = k
         self.kv[index, 1, :b, :, start:start + s] = v
         keys, values = self.kv[index, 0, :b, :, : start + s], self.kv[index, 1, :b, :, : start + s]
+        if s == 1:
+            # Decode: one query per head.  Batched matmuls over the cache slice; the library's fused
+            # attention takes a slow generic path for a strided cache with grouped heads.
+            group = c.heads // c.kv_heads
+            qg = q.reshape(b, c.kv_heads, group, c.head_dim)
+            scores = torch.matmul(qg, keys.transpose(-1, -2)).float() * (c.head_dim ** -0.5)
+            out = torch.matmul(torch.softmax(scores, -1).to(values.dtype), values)
+            out = out.reshape(b, 1, c.heads * c.head_dim)
+            return out @ layer["wo"].t()
         out = F.scaled_dot_product_attention(q, keys, values, is_causal=(s > 1 and start == 0),
                                              enable_gqa=True)
         return out.transpose(1, 2).reshape(b, s, c.heads * c.head_dim) @ layer["wo"].t()

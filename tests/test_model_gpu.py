@@ -33,3 +33,9 @@ def test_moe_layer_and_generate_tiny():
         assert out.shape == (4, 5) and int(out.min()) >= 0 and int(out.max()) < 128
         # greedy decoding is deterministic
         assert torch.equal(out, model.generate(prompts, 5))
+        # the decode attention path agrees with a prefill that includes the same position
+        full = model.forward(prompts, 0)
+        model.forward(prompts[:, :15].contiguous(), 0)
+        step = model.forward(prompts[:, 15:16].contiguous(), 15)
+        torch.cuda.synchronize()
+        assert ((full - step).norm() / full.norm()).item() < 3e-2
