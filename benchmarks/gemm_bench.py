@@ -1,0 +1,100 @@
+#!/usr/bin/env python
+"""bf16 GEMM on one GPU: the tcgen05 kernels of this package against cuBLAS (torch.matmul).
+
+    python benchmarks/gemm_bench.py                      # dense C = A @ B^T over the TP / FFN shapes
+    python benchmarks/gemm_bench.py --shape 4096 4096 4096 --steps 3 --no-library   # small case for a profiler
+    python benchmarks/gemm_bench.py --grouped            # grouped (per-expert) GEMM, Mixtral expert shapes
+
+Each timed launch is preceded by an L2 flush; times are medians of CUDA-event brackets.
+Fractions are of the measured cuBLAS bf16 burst throughput recorded for this pool.
+"""
+import argparse
+import json
+
+from common import emit
+
+import torch
+
+from aboleth_b200.bench_support import L2Flusher, measured_peaks
+from aboleth_b200.ops import check_gemm_status, gemm_bf16, grouped_gemm_bf16
+
+DENSE = [(8192, 3584, 8192), (8192, 8192, 3584), (8192, 28672, 8192), (8192, 8192, 8192), (4096, 4096, 4096)]
+
+
+def timed(fn, flush, steps):
+    ts = []
+    for i in range(steps + 3):
+        flush()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(200000)  # the host gets ahead, so launch latency stays outside the bracket
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--grouped", action="store_true")
+    ap.add_argument("--no-library", action="store_true", help="skip the cuBLAS arm (profiler runs)")
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    flush = L2Flusher("cuda")
+    peak = measured_peaks().get("bf16_tflops", 1590.0)
+    rows = []
+    if args.grouped:
+        experts, n, k = 8, 28672, 4096
+        for per_expert in (512, 2048, 8192):
+            total = experts * per_expert
+            x = torch.randn(total, k, device="cuda").to(torch.bfloat16)
+            w = (torch.randn(experts, n, k, device="cuda") * 0.02).to(torch.bfloat16)
+            counts = torch.full((experts,), per_expert, dtype=torch.int32, device="cuda")
+            offsets = (torch.arange(experts, device="cuda", dtype=torch.int32) * per_expert).contiguous()
+            y = torch.empty(total, n, dtype=torch.bfloat16, device="cuda")
+            ms = timed(lambda: grouped_gemm_bf16(x, w, counts, offsets, y), flush, args.steps)
+            check_gemm_status("cuda")
+            flops = 2.0 * total * n * k
+            row = {"experts": experts, "rows_per_expert": per_expert, "n": n, "k": k, "ours_us": ms * 1e3,
+                   "ours_tflops": flops / ms / 1e9, "ours_frac_of_measured": flops / ms / 1e9 / peak}
+            if not args.no_library:
+                def library():
+                    for e in range(experts):
+                        torch.matmul(x[e * per_expert:(e + 1) * per_expert], w[e].t(),
+                                     out=y[e * per_expert:(e + 1) * per_expert])
+                ms2 = timed(library, flush, args.steps)
+                row.update(cublas_loop_us=ms2 * 1e3, cublas_loop_tflops=flops / ms2 / 1e9)
+            rows.append(row)
+            del x, w, y
+    else:
+        for m, n, k in ([tuple(args.shape)] if args.shape else DENSE):
+            a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+            b = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+            c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            ms = timed(lambda: gemm_bf16(a, b, c), flush, args.steps)
+            check_gemm_status("cuda")
+            flops = 2.0 * m * n * k
+            row = {"m": m, "n": n, "k": k, "ours_us": ms * 1e3, "ours_tflops": flops / ms / 1e9,
+                   "ours_frac_of_measured": flops / ms / 1e9 / peak}
+            if not args.no_library:
+                ref = torch.matmul(a, b.t())
+                row["rel_err_vs_cublas"] = ((c.float() - ref.float()).norm() / ref.float().norm()).item()
+                ms2 = timed(lambda: torch.matmul(a, b.t(), out=c), flush, args.steps)
+                row.update(cublas_us=ms2 * 1e3, cublas_tflops=flops / ms2 / 1e9)
+            rows.append(row)
+            del a, b, c
+    emit({"bench": "grouped gemm bf16" if args.grouped else "gemm bf16", "n_gpus": 1, "dtype": "bf16",
+          "l2": "flushed before every timed launch", "peak_bf16_tflops_measured": peak, "rows": rows},
+         args.out)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
