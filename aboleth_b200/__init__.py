@@ -34,7 +34,11 @@ TransportPlan = dict
 
 from . import moe, ops, parallel  # noqa: E402,F401
 from .kv import (GENERIC_KV_TARGET_PROFILE, H200_NVLINK_KV_TARGET_PROFILE,  # noqa: E402
-                 CompiledKVTransferManager, KVCacheLayoutContract, KVRuntimeOverrides, KVTargetProfile,
+                 CompiledKVTransferManager, KVPoolLayout, KVRuntimeOverrides, KVTargetProfile,
                  select_kv_target_profile)
+
+from .patterns import (CompiledKVCacheMigrationPlan, KVCacheLayoutContract,  # noqa: E402
+                       KVCacheMigrationSpec, KVCachePhysicalization, MoEPatternSpec,
+                       build_kv_cache_migration_pattern, build_moe_pattern, compile_kv_cache_migration)
 
 __version__ = "0.1.0"

@@ -283,7 +283,23 @@ class TcpStoreBootstrap:
         return gathered
 
     def barrier(self, tag: str = "barrier") -> None:
-        self.all_gather(tag, b"")
+        """All ranks arrive; rank 0 (the store's host) returns last.
+
+        After the gather every other rank acknowledges that it has read all keys, and rank 0
+        waits for those acknowledgements: when ``barrier`` returns on rank 0 no peer still
+        needs the store, so rank 0 may drop it.
+        """
+        sequence = self._sequence
+        self.all_gather(tag, b"\x01")
+        if self.rank != 0:
+            self._store.set(self._key(sequence, tag + ".read", self.rank), b"\x01")
+            return
+        for peer in range(1, self.world_size):
+            try:
+                self._store.get(self._key(sequence, tag + ".read", peer))
+            except Exception as error:
+                raise TimeoutError(
+                    f"rank 0 did not see rank {peer} leave bootstrap {tag}") from error
 
     def close(self) -> None:
         self._store = None

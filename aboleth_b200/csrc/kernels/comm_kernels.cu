@@ -244,6 +244,28 @@ __global__ void tier1_exercise_kernel(Tier1Params p) {
     }
 }
 
+// ---- endpoint probe -----------------------------------------------------------------
+// One CTA per lane.  Per iteration: the CTA copies the lane's slice to the partner and
+// publishes one epoch in the lane's flag there; "sender completed" on peer memory is the
+// release store itself, so there is nothing further to wait for.  Nothing here waits on
+// another rank.  (Role of the reference's probe kernel, python/aboleth/endpoint_probe.py:32-45.)
+__global__ void __launch_bounds__(1024) probe_send_kernel(const std::uint8_t *payload,
+                                                          std::uint64_t peer_receive,
+                                                          std::uint64_t peer_flags,
+                                                          const std::uint64_t *starts,
+                                                          std::uint64_t chunk, int iterations) {
+    const int lane = blockIdx.x;
+    const std::uint64_t offset = chunk * lane;
+    const std::uint64_t first = starts[lane];
+    const aboleth::RemoteRegion dst{peer_receive + offset, 0};
+    const aboleth::LocalRegion src{reinterpret_cast<std::uint64_t>(payload) + offset, 0};
+    const aboleth::RemoteRegion flag{peer_flags + 8ull * lane, 0};
+    for (int i = 0; i < iterations; ++i) {
+        aboleth::put_block(dst, src, chunk);
+        aboleth::signal_block(flag, first + i + 1);
+    }
+}
+
 }  // namespace
 
 AB_EXPORT int ab_alltoall(const void *send, const std::uint64_t *peer_recv,
@@ -323,4 +345,18 @@ AB_EXPORT int ab_tier1_exercise(const std::uint64_t *endpoints, unsigned long lo
                   epoch, wait_epoch, timeout_ns, bytes, peer, pieces};
     tier1_exercise_kernel<<<1, 32, 0, stream>>>(p);
     return ab::launch_result("tier1_exercise");
+}
+
+// payload: local bytes; peer_receive / peer_flags: the partner's mapped addresses; starts: device
+// u64 [lanes] with every lane's current epoch.  chunk must be a multiple of 16.
+AB_EXPORT int ab_probe_send(const void *payload, std::uint64_t peer_receive, std::uint64_t peer_flags,
+                            const std::uint64_t *starts, std::uint64_t chunk, int lanes, int warps,
+                            int iterations, cudaStream_t stream) {
+    if (lanes < 1 || lanes > 1024 || warps < 1 || warps > 32 || iterations < 0 || chunk % 16 ||
+        (reinterpret_cast<std::uintptr_t>(payload) | peer_receive) % 16)
+        return -1;
+    probe_send_kernel<<<lanes, warps * 32, 0, stream>>>(static_cast<const std::uint8_t *>(payload),
+                                                        peer_receive, peer_flags, starts, chunk,
+                                                        iterations);
+    return ab::launch_result("probe_send");
 }

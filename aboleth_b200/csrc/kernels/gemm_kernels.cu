@@ -21,6 +21,7 @@ constexpr int kPlainHalves = 2;
 constexpr int kPlainRows = BM * kPlainHalves;
 
 struct PlainPolicy {
+    static constexpr bool kBackground = false, kDrainedHook = false;
     __nv_bfloat16 *c;
     int m, n, k, ldc;
     int tiles_n, tiles_total;
@@ -60,17 +61,26 @@ struct PlainPolicy {
     __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
 };
 
+template <int HALVES>
 struct GroupedPolicy {
+    static constexpr int kRows = BM * HALVES;
+    static constexpr bool kBackground = false, kDrainedHook = false;
     __nv_bfloat16 *c;
     const int *counts, *offsets;
     int experts, n, k, ldc, tiles_n;
+    int group_n;  // tile columns per raster group (their weight panels stay in L2)
     // cursor (per thread): expert `e` starts at linear tile `base`
     int e, base;
 
+    // Inside one expert the tiles are visited like the plain GEMM's: all row tiles of
+    // `group_n` tile columns before the next group, column fastest, so an expert's weight
+    // panels are read from DRAM once however many row tiles it has.
     __device__ __forceinline__ bool next(int it, Tile &t) {
         const int idx = blockIdx.x + it * gridDim.x;
+        int tiles_m = 0;
         while (e < experts) {
-            const int tiles_e = ((counts[e] + BM - 1) / BM) * tiles_n;
+            tiles_m = (counts[e] + kRows - 1) / kRows;
+            const int tiles_e = tiles_m * tiles_n;
             if (idx < base + tiles_e)
                 break;
             base += tiles_e;
@@ -79,14 +89,18 @@ struct GroupedPolicy {
         if (e >= experts)
             return false;
         const int local = idx - base;
-        const int tm = local / tiles_n, tn = local - tm * tiles_n;
-        const int row0 = offsets[e] + tm * BM;
+        const int per_group = group_n * tiles_m;
+        const int group = local / per_group;
+        const int width = min(group_n, tiles_n - group * group_n);
+        const int in_group = local - group * per_group;
+        const int tm = in_group / width, tn = group * group_n + (in_group - tm * width);
+        const int row0 = offsets[e] + tm * kRows;
         t.a_row = row0;
         t.b_row = e * n + tn * BN;
         t.k_blocks = (k + BK - 1) / BK;
         t.c_row = row0;
         t.c_col = tn * BN;
-        t.rows_valid = min(BM, counts[e] - tm * BM);
+        t.rows_valid = min(kRows, counts[e] - tm * kRows);
         t.cols_valid = min(BN, n - tn * BN);
         t.tag = e;
         t.a_sel = 0;
@@ -127,6 +141,27 @@ bool configure(Kernel kernel, unsigned smem_bytes) {
            cudaSuccess;
 }
 
+template <int HALVES>
+int launch_grouped(const void *a, const void *w, void *c, const int *counts, const int *offsets,
+                   int experts, int total_rows, int n, int k, unsigned long long *status,
+                   cudaStream_t stream) {
+    using Policy = GroupedPolicy<HALVES>;
+    CUtensorMap map_a, map_b;
+    if (!make_map_bf16(&map_a, a, total_rows, k, k, Policy::kRows) ||
+        !make_map_bf16(&map_b, w, static_cast<std::uint64_t>(experts) * n, k, k, BN))
+        return -2;
+    constexpr unsigned smem = Geometry<HALVES>::kSmemBytes;
+    static bool configured = configure(gemm_tcgen05_kernel<HALVES, Policy>, smem);
+    if (!configured)
+        return -3;
+    const int tiles_n = (n + BN - 1) / BN;
+    const long long column_bytes = static_cast<long long>(BN) * k * 2;
+    const int group_n = static_cast<int>(std::max(1LL, std::min<long long>(tiles_n, (48LL << 20) / column_bytes)));
+    Policy p{static_cast<__nv_bfloat16 *>(c), counts, offsets, experts, n, k, n, tiles_n, group_n, 0, 0};
+    gemm_tcgen05_kernel<HALVES, Policy><<<sm_count(), kThreads, smem, stream>>>(map_a, map_b, p, status);
+    return ab::launch_result("grouped_gemm_bf16");
+}
+
 }  // namespace
 
 // C[M,N] = A[M,K] * B[N,K]^T, all bf16 row-major, lda/ldb/ldc in elements.
@@ -163,16 +198,8 @@ AB_EXPORT int ab_grouped_gemm_bf16(const void *a, const void *w, void *c, const 
         (reinterpret_cast<std::uintptr_t>(a) | reinterpret_cast<std::uintptr_t>(w) |
          reinterpret_cast<std::uintptr_t>(c)) & 15)
         return -1;
-    CUtensorMap map_a, map_b;
-    if (!make_map_bf16(&map_a, a, total_rows, k, k, BM) ||
-        !make_map_bf16(&map_b, w, static_cast<std::uint64_t>(experts) * n, k, k, BN))
-        return -2;
-    constexpr unsigned smem = Geometry<1>::kSmemBytes;
-    static bool configured = configure(gemm_tcgen05_kernel<1, GroupedPolicy>, smem);
-    if (!configured)
-        return -3;
-    GroupedPolicy p{static_cast<__nv_bfloat16 *>(c), counts, offsets, experts, n, k, n,
-                    (n + BN - 1) / BN, 0, 0};
-    gemm_tcgen05_kernel<1, GroupedPolicy><<<sm_count(), kThreads, smem, stream>>>(map_a, map_b, p, status);
-    return ab::launch_result("grouped_gemm_bf16");
+    // 256-row tiles once the experts are big enough on average to fill them.
+    if (total_rows / experts >= 512)
+        return launch_grouped<2>(a, w, c, counts, offsets, experts, total_rows, n, k, status, stream);
+    return launch_grouped<1>(a, w, c, counts, offsets, experts, total_rows, n, k, status, stream);
 }

@@ -40,6 +40,7 @@ struct SharedState {
     std::uint64_t tmem_empty[2];
     std::uint32_t tmem_base;
     volatile int abort;
+    volatile int epi_ready;  // epilogue warps: shared outcome of one accumulator poll
 };
 
 // ---- tcgen05 wrappers --------------------------------------------------------------
@@ -153,6 +154,13 @@ struct Tile {
 //   __device__ void tile_done(const Tile &t)              - called by ONE epilogue thread after the
 //                                                           whole tile was stored (CTA-wide ordered)
 //   __device__ void finish(int thread, int nthreads, status) - epilogue warps, after the last tile
+//   static constexpr bool kBackground  - if true: bool background(int thread, int nthreads) is called by
+//                                        all 128 epilogue threads together while they would otherwise
+//                                        wait for an accumulator, and after the last tile until it
+//                                        returns false (no item left); it may use `bar.sync 1, 128`
+//   static constexpr bool kDrainedHook - if true: void drained(const Tile &, int thread, int nthreads) is
+//                                        called by all 128 epilogue threads after a tile was stored and
+//                                        its accumulator released, before tile_done
 // `map_a_alt` is the tensor map used by tiles with a_sel == 1 (pass map_a when unused).
 // Geometry of one configuration.  HALVES = 1: 128 x 256 tiles, the two 256-column
 // halves of TMEM double-buffer the accumulator (epilogue of tile i overlaps the main
@@ -293,12 +301,28 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
     } else {
         // ---------------- epilogue (warps 2..5) ----------------
         const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31
+        const int epi_thread = (warp - 2) * 32 + lane;
+        constexpr int kEpiThreads = kEpilogueWarps * 32;
         Tile t;
         for (int it = 0; !st.abort && policy.next(it, t); ++it) {
             const unsigned use = use_of(it);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) {
                 const int slot = slot_of(it, h);
+                if constexpr (Policy::kBackground) {
+                    // While the accumulator is not ready the four warps run the policy's
+                    // background items (communication).  One thread polls; the decision is
+                    // shared through a named barrier because an item contains barriers.
+                    for (;;) {
+                        if (epi_thread == 0)
+                            st.epi_ready = mbar_try_wait(&st.tmem_full[slot], use) ? 1 : 0;
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        const int ready_now = st.epi_ready;
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (ready_now || !policy.background(epi_thread, kEpiThreads))
+                            break;
+                    }
+                }
                 if (!mbar_wait(&st.tmem_full[slot], use)) {
                     st.abort = 1;
                     set_status(status, aboleth::Status::Timeout, 0x3400 + slot);
@@ -322,13 +346,22 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
                 if (lane == 0)
                     mbar_arrive(&st.tmem_empty[slot]);
             }
-            // Tile-complete hook: needs all four epilogue warps' stores.
+            // Tile-complete hooks: they need all four epilogue warps' stores.  The accumulator
+            // is already released, so whatever `drained` does overlaps the next main loop.
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            if constexpr (Policy::kDrainedHook) {
+                policy.drained(t, epi_thread, kEpiThreads);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
             if (warp == 2 && lane == 0)
                 policy.tile_done(t);
         }
+        if constexpr (Policy::kBackground) {
+            while (!st.abort && policy.background(epi_thread, kEpiThreads)) {
+            }
+        }
         if (!st.abort)
-            policy.finish((warp - 2) * 32 + lane, kEpilogueWarps * 32, status);
+            policy.finish(epi_thread, kEpiThreads, status);
     }
 
     // ---------------- teardown ----------------

@@ -613,26 +613,31 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
     const bool tracer = blockIdx.x == 0 && tid == 0;
     stamp(p.trace, 0, tracer);
 
+    // Records are visited round-robin over the source ranks, starting at rank + 1: at any moment
+    // the CTAs of one rank write to every peer, and no two ranks start on the same peer.  (Walking
+    // source 0, then source 1, ... makes all ranks converge on one receiver at a time.)
+    int most = 0;
+    for (int src = 0; src < g.world; ++src)
+        most = max(most, static_cast<int>(ab::min64(p.recv_counts[src], g.capacity)));
+    const int spread = most * g.world;
     if ((p.phases & kPhaseSend) && p.by_warp) {
         const int warps = gridDim.x * (kThreads / 32);
         const int gw = blockIdx.x * (kThreads / 32) + (tid >> 5);
-        for (int src = 0; src < g.world; ++src) {
-            const int count = static_cast<int>(ab::min64(p.recv_counts[src], g.capacity));
-            for (int slot = gw; slot < count; slot += warps)
+        for (int i = gw; i < spread; i += warps) {
+            const int slot = i / g.world;
+            const int src = (g.rank + 1 + (i - slot * g.world)) % g.world;
+            if (static_cast<unsigned long long>(slot) < p.recv_counts[src])
                 return_row_by_warp(p, src * g.capacity + slot, src, slot);
         }
     }
     if (p.phases & kPhaseSend) {
-        const int total = p.by_warp ? 0 : g.world * g.capacity;
-        for (int row = blockIdx.x; row < total; row += gridDim.x) {
-            const int src = row / g.capacity;
-            const int slot = row - src * g.capacity;
-            if (static_cast<unsigned long long>(slot) >= p.recv_counts[src]) {
-                // Skip the rest of this source's segment in one step.
-                const int next = (src + 1) * g.capacity;
-                row += ((next - row - 1) / static_cast<int>(gridDim.x)) * gridDim.x;
-                continue;
-            }
+        const int total = p.by_warp ? 0 : spread;
+        for (int i = blockIdx.x; i < total; i += gridDim.x) {
+            const int slot = i / g.world;
+            const int src = (g.rank + 1 + (i - slot * g.world)) % g.world;
+            if (static_cast<unsigned long long>(slot) >= p.recv_counts[src])
+                continue;  // the same for every thread of the CTA
+            const int row = src * g.capacity + slot;
             int n = 1;
             if (p.weighted) {
                 n = p.recv_meta[static_cast<std::size_t>(row) * words + 1];

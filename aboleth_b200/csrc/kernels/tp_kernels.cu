@@ -1,21 +1,26 @@
 // Tensor-parallel GEMMs fused with their collective, one launch each.
 //
 // ALL-GATHER -> GEMM   C[world*Ml, Nl] = gather_ranks(A_local[Ml, K]) * B_local[Nl, K]^T
-//   Every CTA first stores its share of this rank's A shard into every peer's
-//   gathered-A staging over NVLink; the CTA that completes a 256-row chunk for a
-//   peer publishes it with one release flag; then all CTAs run the persistent
-//   tcgen05 main loop.  The TMA producer of a tile whose rows came from rank s waits
+//   The four epilogue warps of every CTA store the CTA's share of this rank's A shard
+//   into every peer's gathered-A staging over NVLink, in 64 KiB items, whenever they
+//   would otherwise wait for an accumulator - so the push runs under the tensor-core
+//   main loop of the rank's own rows.  The item that completes a 256-row chunk for a
+//   peer publishes it with one release flag.  The TMA producer of a tile whose rows came from rank s waits
 //   (bounded) on the chunk's flag and then loads the tile from LOCAL staging -
 //   a remote tile crosses NVLink once, TMA never touches peer memory, nothing
 //   is multicast.  Tiles of the rank's own rows read A_local through a second
 //   tensor map and start at once; remote sources follow in arrival order.
 //
 // GEMM -> REDUCE-SCATTER   out[Ml, N] = sum_ranks(A_local[world*Ml, Kl] * B_local[N, Kl]^T)[own rows]
-//   The epilogue converts each fp32 accumulator tile from TMEM to bf16 and
-//   stores it straight into the OWNER rank's partial buffer (peer stores), then
-//   publishes the tile with one release flag.  Tiles owned by peers are computed
-//   first.  When a CTA has no GEMM tiles left its epilogue warps reduce owned
-//   tiles: wait for the tile's flag from every rank, sum the partials in fp32.
+//   The epilogue converts each fp32 accumulator tile from TMEM to bf16 into a per-CTA
+//   staging tile in local memory (L2-resident) and releases the accumulator; while the
+//   next tile's main loop runs, the same four warps copy the staged tile into the OWNER
+//   rank's partial buffer with row-contiguous 512-byte peer stores and publish it with
+//   one release flag.  (Storing straight from the TMEM registers - 16 bytes per lane,
+//   every lane another row - reached a quarter of the link rate and stalled the
+//   accumulator.)  Tiles owned by peers are computed first.  When a CTA has no GEMM
+//   tiles left its epilogue warps reduce owned tiles: wait for the tile's flag from
+//   every rank, sum the partials in fp32.
 //
 // No reference kernel exists for these; the baseline is NCCL all-gather /
 // reduce-scatter around a library GEMM.
@@ -38,12 +43,20 @@ constexpr int kPhaseConsume = 2;  // AG: GEMM.        RS: reduction of owned til
 // ---- all-gather -> GEMM -----------------------------------------------------------------
 
 struct AgGemmPolicy {
+    static constexpr bool kBackground = true, kDrainedHook = false;
     __nv_bfloat16 *c;
     const std::uint64_t *flags;       // local: [world * chunks] epochs
     unsigned long long *status;
     std::uint64_t epoch;
     int rank, world, m_local, n, k, ldc, phases;
     int tiles_n, chunks;              // chunks = m_local / 256 (row blocks per rank)
+    // push of this rank's shard (background work of the epilogue warps)
+    const std::uint8_t *a_local;          // [m_local, k] bf16
+    const std::uint64_t *peer_staging;    // [world] address of each peer's gathered-A buffer
+    const std::uint64_t *peer_flags;      // [world] address of each peer's flag array
+    unsigned *arrivals;                   // local scratch [world * chunks], zero between calls
+    int parts;                            // items that share one (peer, chunk)
+    int pushed;                           // items this CTA has pushed so far (same in every thread)
 
     __device__ __forceinline__ bool next(int it, Tile &t) const {
         if (!(phases & kPhaseConsume))
@@ -81,68 +94,62 @@ struct AgGemmPolicy {
     }
     __device__ __forceinline__ void tile_done(const Tile &) const {}
     __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
-};
 
-struct AgPush {
-    const std::uint8_t *a_local;          // [m_local, k] bf16
-    const std::uint64_t *peer_staging;    // [world] address of each peer's gathered-A buffer
-    const std::uint64_t *peer_flags;      // [world] address of each peer's flag array
-    unsigned *arrivals;                   // local scratch [world * chunks], zero between calls
-    int parts;                            // CTAs that share one (peer, chunk)
+    // One push item = (peer, chunk, part), nearest peer first; the item that arrives last on
+    // (peer, chunk) publishes the chunk.  Called by the 128 epilogue threads together.
+    __device__ __forceinline__ bool background(int thread, int nthreads) {
+        if (!(phases & kPhaseProduce))
+            return false;
+        const int item = blockIdx.x + pushed * gridDim.x;
+        if (item >= (world - 1) * chunks * parts)
+            return false;
+        ++pushed;
+        const std::size_t row_bytes = static_cast<std::size_t>(k) * 2;
+        const int part = item % parts;
+        const int pc = item / parts;
+        const int hop = pc / chunks + 1, chunk = pc - (hop - 1) * chunks;
+        const int peer = (rank + hop) % world;
+        const int rows = min(kRows, m_local - chunk * kRows);
+        const int per = (rows + parts - 1) / parts;
+        const int r0 = min(part * per, rows), r1 = min(r0 + per, rows);
+        const std::size_t offset = (static_cast<std::size_t>(chunk) * kRows + r0) * row_bytes;
+        std::uint8_t *dst = reinterpret_cast<std::uint8_t *>(peer_staging[peer]) +
+                            static_cast<std::size_t>(rank) * m_local * row_bytes + offset;
+        aboleth::detail::copy_strided(dst, a_local + offset, (r1 - r0) * row_bytes, thread, nthreads);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (thread == 0) {
+            aboleth::detail::fence_acq_rel_sys();
+            unsigned *counter = arrivals + peer * chunks + chunk;
+            if (atomicAdd(counter, 1u) == static_cast<unsigned>(parts) - 1) {
+                *counter = 0;  // self-cleaning
+                aboleth::detail::fence_acq_rel_sys();
+                std::uint64_t *flag = reinterpret_cast<std::uint64_t *>(peer_flags[peer]) +
+                                      rank * chunks + chunk;
+                aboleth::detail::st_release_sys(flag, epoch);
+            }
+        }
+        return true;
+    }
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap map_staging,
                const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_local, AgGemmPolicy params, AgPush push) {
+               const __grid_constant__ CUtensorMap map_local, AgGemmPolicy params) {
     AgGemmPolicy policy = params;
-    if (policy.phases & kPhaseProduce) {
-        // Every CTA pushes its share first (a few hundred KiB), so that no CTA starts its
-        // GEMM tiles much later than the others.  Work item = (peer, chunk, part), nearest
-        // peer first; the part that arrives last on (peer, chunk) publishes the chunk.
-        __shared__ int last;
-        const int items = (policy.world - 1) * policy.chunks * push.parts;
-        const std::size_t row_bytes = static_cast<std::size_t>(policy.k) * 2;
-        for (int item = blockIdx.x; item < items; item += gridDim.x) {
-            const int part = item % push.parts;
-            const int pc = item / push.parts;
-            const int hop = pc / policy.chunks + 1, chunk = pc - (hop - 1) * policy.chunks;
-            const int peer = (policy.rank + hop) % policy.world;
-            const int rows = min(kRows, policy.m_local - chunk * kRows);
-            const int per = (rows + push.parts - 1) / push.parts;
-            const int r0 = min(part * per, rows), r1 = min(r0 + per, rows);
-            const std::size_t offset = (static_cast<std::size_t>(chunk) * kRows + r0) * row_bytes;
-            std::uint8_t *dst = reinterpret_cast<std::uint8_t *>(push.peer_staging[peer]) +
-                                static_cast<std::size_t>(policy.rank) * policy.m_local * row_bytes + offset;
-            aboleth::detail::copy_strided(dst, push.a_local + offset, (r1 - r0) * row_bytes, threadIdx.x,
-                                          blockDim.x);
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                aboleth::detail::fence_acq_rel_sys();
-                unsigned *counter = push.arrivals + peer * policy.chunks + chunk;
-                last = atomicAdd(counter, 1u) == static_cast<unsigned>(push.parts) - 1;
-                if (last) {
-                    *counter = 0;  // self-cleaning
-                    aboleth::detail::fence_acq_rel_sys();
-                    std::uint64_t *flag = reinterpret_cast<std::uint64_t *>(push.peer_flags[peer]) +
-                                          policy.rank * policy.chunks + chunk;
-                    aboleth::detail::st_release_sys(flag, policy.epoch);
-                }
-            }
-            __syncthreads();
-        }
-    }
     gemm_mainloop<kHalves>(policy, &map_staging, &map_b, policy.status, &map_local);
 }
 
 // ---- GEMM -> reduce-scatter -----------------------------------------------------------------
 
 struct GemmRsPolicy {
+    static constexpr bool kBackground = false, kDrainedHook = true;
     const std::uint64_t *peer_partials;  // [world] address of each rank's partial buffer
     const std::uint64_t *peer_flags;     // [world] address of each rank's flag array
     const __nv_bfloat16 *partials;       // local: [world, m_local, n]
     const std::uint64_t *flags;          // local: [world * tiles_local]
     __nv_bfloat16 *out;                  // [m_local, n]
+    __nv_bfloat16 *stage;                // local: [gridDim.x, 256, 256] staging tiles
     unsigned long long *status;
     std::uint64_t epoch;
     int rank, world, m_local, n, k, phases;
@@ -176,10 +183,48 @@ struct GemmRsPolicy {
         if (!row_ok)
             return;
         const int owner = t.tag >> 16;
-        __nv_bfloat16 *base = reinterpret_cast<__nv_bfloat16 *>(peer_partials[owner]) +
-                              static_cast<std::size_t>(rank) * m_local * n;
-        store_row32_bf16(base + static_cast<std::size_t>(t.c_row + row) * n + t.c_col + col0, v,
-                         t.cols_valid - col0);
+        if (owner == rank) {  // own tile: straight into this rank's slot of the local partials
+            __nv_bfloat16 *base = const_cast<__nv_bfloat16 *>(partials) +
+                                  static_cast<std::size_t>(rank) * m_local * n;
+            store_row32_bf16(base + static_cast<std::size_t>(t.c_row + row) * n + t.c_col + col0, v,
+                             t.cols_valid - col0);
+        } else {
+            store_row32_bf16(stage + static_cast<std::size_t>(blockIdx.x) * (kRows * BN) + row * BN + col0, v,
+                             t.cols_valid - col0);
+        }
+    }
+    // The accumulator is free again: copy the staged tile to its owner, one 512-byte row per
+    // warp instruction, eight rows' worth of loads in flight per thread.
+    __device__ __forceinline__ void drained(const Tile &t, int thread, int nthreads) const {
+        const int owner = t.tag >> 16;
+        if (owner == rank)
+            return;
+        const __nv_bfloat16 *src = stage + static_cast<std::size_t>(blockIdx.x) * (kRows * BN);
+        __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(peer_partials[owner]) +
+                             static_cast<std::size_t>(rank) * m_local * n +
+                             static_cast<std::size_t>(t.c_row) * n + t.c_col;
+        const int vpr = t.cols_valid / 8;  // 16-byte vectors per row
+        const int total = t.rows_valid * vpr;
+        constexpr int kInFlight = 8;
+        for (int i0 = thread; i0 < total; i0 += kInFlight * nthreads) {
+            uint4 v[kInFlight];
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                const int i = i0 + u * nthreads;
+                if (i < total) {
+                    const int r = i / vpr, c = i - r * vpr;
+                    v[u] = aboleth::detail::ld_stream16(src + r * BN + c * 8);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                const int i = i0 + u * nthreads;
+                if (i < total) {
+                    const int r = i / vpr, c = i - r * vpr;
+                    aboleth::detail::st_stream16(dst + static_cast<std::size_t>(r) * n + c * 8, v[u]);
+                }
+            }
+        }
     }
     // One thread, after all four epilogue warps stored the tile (bar.sync): publish it.
     __device__ __forceinline__ void tile_done(const Tile &t) const {
@@ -287,25 +332,33 @@ AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const vo
         cudaSuccess;
     if (!configured)
         return -3;
+    const int chunks = m_local / kRows;
+    if (parts < 1) {  // items of about 64 KiB: short enough to slot in between accumulator polls
+        const long long chunk_bytes = static_cast<long long>(kRows) * k * 2;
+        parts = static_cast<int>(std::min<long long>(kRows, std::max<long long>(1, chunk_bytes / 65536)));
+    }
+    parts = std::min(parts, kRows);
     AgGemmPolicy p{static_cast<__nv_bfloat16 *>(c), flags, status, epoch, rank, world, m_local, n, k, n,
-                   phases, (n + BN - 1) / BN, m_local / kRows};
-    const int pairs = (world - 1) * (m_local / kRows);
-    if (parts < 1)  // about one work item per CTA
-        parts = pairs > 0 ? std::max(1, sm_count() / pairs) : 1;
-    AgPush push{static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, arrivals, parts};
-    ag_gemm_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_staging, map_b, map_local, p, push);
+                   phases, (n + BN - 1) / BN, chunks,
+                   static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, arrivals, parts, 0};
+    ag_gemm_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_staging, map_b, map_local, p);
     return ab::launch_result("ag_gemm_bf16");
 }
 
 // a [world*m_local, k_local]; b [n, k_local]; partials: local [world, m_local, n] (peers write it);
-// out [m_local, n].  m_local multiple of 256, n multiple of 8 and tiles per owner < 65536.
-AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials, void *out,
+// out [m_local, n]; stage: local scratch of ab_gemm_rs_stage_bytes() bytes (staging tiles, one per CTA).
+// m_local multiple of 256, n multiple of 8 and tiles per owner < 65536.
+AB_EXPORT long long ab_gemm_rs_stage_bytes() {
+    return static_cast<long long>(sm_count()) * kRows * BN * 2;
+}
+
+AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials, void *out, void *stage,
                               const std::uint64_t *peer_partials, const std::uint64_t *peer_flags,
                               const std::uint64_t *flags, unsigned long long *status,
                               std::uint64_t epoch, int rank, int world, int m_local, int n, int k,
                               int phases, cudaStream_t stream) {
     if (world < 1 || m_local < kRows || m_local % kRows || n < 8 || n % 8 || k < 8 || k % 8 || rank < 0 ||
-        rank >= world)
+        rank >= world || stage == nullptr)
         return -1;
     const int tiles_n = (n + BN - 1) / BN, chunks = m_local / kRows;
     if (tiles_n * chunks >= 65536)
@@ -320,8 +373,8 @@ AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials
     if (!configured)
         return -3;
     GemmRsPolicy p{peer_partials, peer_flags, static_cast<const __nv_bfloat16 *>(partials), flags,
-                   static_cast<__nv_bfloat16 *>(out), status, epoch, rank, world, m_local, n, k, phases,
-                   tiles_n, chunks};
+                   static_cast<__nv_bfloat16 *>(out), static_cast<__nv_bfloat16 *>(stage), status, epoch, rank,
+                   world, m_local, n, k, phases, tiles_n, chunks};
     gemm_rs_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_a, map_b, p);
     return ab::launch_result("gemm_rs_bf16");
 }

@@ -10,6 +10,8 @@ here for single-GPU runs), tensor parallel 1.
 """
 from __future__ import annotations
 
+import contextlib
+
 from typing import Optional
 
 import torch
@@ -58,6 +60,7 @@ class AbolethPrepareAndFinalize:
         self.manager = manager
         self.num_experts = layer_facts["num_experts"]
         self.slot = 0
+        self._wave_bound: Optional[int] = None
         family = manager.get_handle(layer_facts, num_slots=num_slots,
                                     placement_strategy=placement_strategy)
         self.runtime = ModularMoERuntime(family, layer_name=layer_name, slot_provider=lambda: self.slot)
@@ -66,7 +69,26 @@ class AbolethPrepareAndFinalize:
         """Every rank must select the same shape variant: agree on the maximum token count."""
         if not self.runtime.has_decode_sibling:
             return tokens
+        if self._wave_bound is not None:
+            return max(tokens, self._wave_bound)
         return uniform_token_bound(tokens, self.manager.cpu_group)
+
+    @contextlib.contextmanager
+    def wave(self, tokens: int):
+        """One forward pass: agree on the token bound once (one host all-reduce) instead of in every
+        layer.  An engine that already knows the maximum over the data-parallel ranks installs it with
+        :meth:`set_wave_bound` instead and pays no host collective at all."""
+        previous = self._wave_bound
+        self._wave_bound = (uniform_token_bound(tokens, self.manager.cpu_group)
+                            if self.runtime.has_decode_sibling else tokens)
+        try:
+            yield self._wave_bound
+        finally:
+            self._wave_bound = previous
+
+    def set_wave_bound(self, bound: Optional[int]) -> None:
+        """Install (or clear, with ``None``) a token bound every rank already agrees on."""
+        self._wave_bound = bound
 
     def prepare(self, a1: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor, *,
                 quantized_input: bool = False, apply_router_weight_on_input: bool = False) -> PreparedExperts:

@@ -22,7 +22,7 @@ from .profile import KVTargetProfile, select_kv_target_profile
 
 
 @dataclass(frozen=True)
-class KVCacheLayoutContract:
+class KVPoolLayout:
     layers: int
     blocks: int            # pages in this rank's pool, per layer
     page_bytes: int
@@ -39,7 +39,7 @@ class KVCacheLayoutContract:
 
 
 class CompiledKVTransferManager:
-    def __init__(self, world: World, layout: KVCacheLayoutContract, *,
+    def __init__(self, world: World, layout: KVPoolLayout, *,
                  profile: Optional[KVTargetProfile] = None, tag: str = "kv"):
         self.world, self.layout = world, layout
         name = torch.cuda.get_device_name(world.device) if not world.runtime._cpu else ""

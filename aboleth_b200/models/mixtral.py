@@ -169,10 +169,12 @@ class MixtralEP:
         b, s = token_ids.shape
         positions = torch.arange(start, start + s, device=self.device).expand(b, s)
         x = self.embed[token_ids]
-        for index, layer in enumerate(self.layers):
-            x = x + self.attention(_rms_norm(x, layer["attn_norm"], c.rms_eps), layer, index, positions, start)
-            h = _rms_norm(x, layer["ffn_norm"], c.rms_eps).reshape(b * s, c.hidden).contiguous()
-            x = x + self.moe_layer(h, layer).view(b, s, c.hidden)
+        with self.moe.wave(b * s):  # one agreement on the shape variant per forward, not per layer
+            for index, layer in enumerate(self.layers):
+                x = x + self.attention(_rms_norm(x, layer["attn_norm"], c.rms_eps), layer, index,
+                                       positions, start)
+                h = _rms_norm(x, layer["ffn_norm"], c.rms_eps).reshape(b * s, c.hidden).contiguous()
+                x = x + self.moe_layer(h, layer).view(b, s, c.hidden)
         x = _rms_norm(x[:, -1], self.final_norm, c.rms_eps)
         return (x @ self.lm_head.t()).float()
 

@@ -13,15 +13,16 @@ half before any rank's consuming half (tests, single-GPU development).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional, Sequence
 
 import torch
 
-from ..ops._kernels import _I, _U64, _VP, call, declare, ptr, stream_ptr
+from ..ops._kernels import _I, _U64, _VP, call, declare, lib, ptr, stream_ptr
 from ..world import World
 
 declare("ab_ag_gemm_bf16", [_VP] * 9 + [_U64] + [_I] * 7 + [_VP])
-declare("ab_gemm_rs_bf16", [_VP] * 8 + [_U64] + [_I] * 6 + [_VP])
+declare("ab_gemm_rs_bf16", [_VP] * 9 + [_U64] + [_I] * 6 + [_VP])
 
 PRODUCE, CONSUME = 1, 2
 BM = 256  # rows per tile / chunk of the fused kernels
@@ -73,7 +74,7 @@ class AllGatherGemm:
         if m_local % BM:
             raise ValueError("rows per rank must be a multiple of 256")
         self.rank, self.world_size, self.m_local, self.k = rank, world_size, m_local, k
-        self.buffers, self.tables, self.push_parts = buffers, tables, push_parts  # 0: one item per CTA
+        self.buffers, self.tables, self.push_parts = buffers, tables, push_parts  # 0: items of ~64 KiB
         self.status = torch.zeros(2, dtype=torch.int64, device=buffers.arena.device)
         # Sender-side arrival counters of the push, one per (peer, chunk); the kernel resets them.
         self.arrivals = torch.zeros(world_size * (m_local // BM), dtype=torch.int32,
@@ -130,6 +131,13 @@ class GemmReduceScatter:
         self.rank, self.world_size, self.m_local, self.n = rank, world_size, m_local, n
         self.buffers, self.tables = buffers, tables
         self.status = torch.zeros(2, dtype=torch.int64, device=buffers.arena.device)
+        # One 256x256 bf16 staging tile per CTA: the epilogue parks a tile here (it stays in L2) and
+        # pushes it to its owner while the next tile's main loop runs.
+        with torch.cuda.device(buffers.arena.device):
+            query = lib().ab_gemm_rs_stage_bytes
+            query.restype, query.argtypes = ctypes.c_longlong, []
+            stage_bytes = int(query())
+        self.stage = torch.empty(stage_bytes, dtype=torch.uint8, device=buffers.arena.device)
         self.epoch = 0
 
     @staticmethod
@@ -164,7 +172,7 @@ class GemmReduceScatter:
         which = self.epoch & 1
         peer_data, peer_flags = self.tables[which]
         call("ab_gemm_rs_bf16", ptr(a), ptr(b_local), ptr(self.buffers.data(which)), ptr(out),
-             ptr(peer_data), ptr(peer_flags), ptr(self.buffers.flags(which)), ptr(self.status),
+             ptr(self.stage), ptr(peer_data), ptr(peer_flags), ptr(self.buffers.flags(which)), ptr(self.status),
              (self.epoch + 1) // 2, self.rank, self.world_size, self.m_local, self.n, a.shape[1],
              phases, stream_ptr())
         return out

@@ -320,6 +320,10 @@ class Pattern(CommunicationDataflow):
     def copy_each(self, name: str, workset: Workset, dst: str) -> str:
         return self.copy(name, workset.region, dst)
 
+    def copy_each_from(self, name: str, src: str, dst: str) -> str:
+        """Copy every received record of ``src`` into ``dst`` (the materialising copy after a transfer)."""
+        return self.copy(name, src, dst)
+
     def opaque_compute(self, name: str, reads: Sequence[str], writes: str, *,
                        capabilities: OpaqueCapabilities = OpaqueCapabilities(),
                        kernel: Optional[str] = None) -> str:

@@ -54,3 +54,27 @@ def test_grouped_gemm_matches_loop_of_matmuls():
             assert _rel_err(out[lo:lo + cnt], want) < 5e-3
         pad = out[lo + cnt:lo + int(padded[e])]
         assert bool((pad == 7.0).all())  # rows outside the expert are never written
+
+
+def test_grouped_gemm_large_experts_use_wide_tiles():
+    """Averages of >= 512 rows per expert take the 256-row tile path; ragged counts, many columns."""
+    from aboleth_b200.ops import check_gemm_status, grouped_gemm_bf16
+
+    experts, n, k = 4, 1288, 256  # 6 tile columns, the last one partial
+    counts = torch.tensor([700, 0, 1031, 517], dtype=torch.int32, device="cuda")
+    padded = (counts + 7) // 8 * 8
+    offsets = (torch.cumsum(padded, 0) - padded).to(torch.int32)
+    rows = int(padded.sum())
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = torch.randn(rows, k, generator=g, device="cuda").to(torch.bfloat16)
+    w = torch.randn(experts, n, k, generator=g, device="cuda").to(torch.bfloat16)
+    out = torch.full((rows, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    grouped_gemm_bf16(a, w, counts, offsets, out)
+    torch.cuda.synchronize()
+    check_gemm_status("cuda")
+    for e in range(experts):
+        lo, cnt = int(offsets[e]), int(counts[e])
+        if cnt:
+            want = a[lo:lo + cnt].float() @ w[e].float().t()
+            assert _rel_err(out[lo:lo + cnt], want) < 5e-3
+        assert bool((out[lo + cnt:lo + int(padded[e])] == 7.0).all())

@@ -16,12 +16,12 @@ def test_canonical_runs():
 
 def test_push_pages_publish_readiness_and_lifecycle():
     import aboleth_b200 as ab
-    from aboleth_b200.kv import CompiledKVTransferManager, KVCacheLayoutContract, TransferState
+    from aboleth_b200.kv import CompiledKVTransferManager, KVPoolLayout, TransferState
 
     torch.cuda.set_device(0)
     with ab.World(0, 1, device=0) as world:
         world.connect_all("p2p")
-        layout = KVCacheLayoutContract(layers=6, blocks=32, page_bytes=4096, slots=2, slot_pages=8)
+        layout = KVPoolLayout(layers=6, blocks=32, page_bytes=4096, slots=2, slot_pages=8)
         kv = CompiledKVTransferManager(world, layout)
         g = torch.Generator(device="cuda").manual_seed(0)
         kv.pool.copy_(torch.randint(0, 255, kv.pool.shape, generator=g, device="cuda", dtype=torch.uint8))
