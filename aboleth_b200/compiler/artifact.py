@@ -116,3 +116,97 @@ class LoadedKernel:
                                                      for v in values])
         self._check(self._cuda.cuLaunchKernel(self._function, grid, 1, 1, threads, 1, 1, shared_bytes,
                                               ctypes.c_void_p(stream), pointers, None), "cuLaunchKernel")
+
+
+# ---- artifact forms of a bound transport program -------------------------------------------------
+
+@dataclass(frozen=True)
+class FragmentArtifact:
+    """Device code of one transport program, ready to be included into a client kernel.
+
+    ``source`` declares ``__device__ void <symbol>(<slots...>, unsigned long long *ab_status)``;
+    ``call`` renders the invocation for given slot expressions.  ``facts`` are the pipeline's
+    facts for this transport (batches, fences, flag writes)."""
+
+    name: str
+    symbol: str
+    artifact: str
+    source: str
+    parameters: tuple[tuple[str, str], ...]
+    facts: dict
+    key: str
+
+    def call(self, status: str = "nullptr", **slots: str) -> str:
+        missing = [n for n, _ in self.parameters if n not in slots]
+        if missing:
+            raise ValueError(f"fragment {self.name!r}: missing slots {missing}")
+        return f"{self.symbol}({', '.join(slots[n] for n, _ in self.parameters)}, {status});"
+
+
+@dataclass(frozen=True)
+class StandaloneKernel:
+    """A transport program compiled to its own cubin."""
+
+    name: str
+    artifact: Artifact
+    parameters: tuple[tuple[str, str], ...]
+    facts: dict
+
+    def load(self) -> LoadedKernel:
+        return LoadedKernel(self.artifact)
+
+
+def _parameters(cuda: str, name: str) -> tuple[tuple[str, str], ...]:
+    header = re.search(r"__global__ void " + re.escape(name) + r"\(([^)]*)\)", cuda)
+    if header is None:
+        raise RuntimeError(f"emitted source has no kernel named {name}")
+    out = []
+    for item in header.group(1).split(","):
+        item = item.strip()
+        if not item or item.endswith("ab_status"):
+            continue
+        ctype, _, ident = item.rpartition(" ")
+        out.append((ident.lstrip("*"), ctype + ("*" if ident.startswith("*") else "")))
+    return tuple(out)
+
+
+def compile_fragment_artifact(binding, *, reuse: int = 1, threads: int = 32,
+                              options=None) -> FragmentArtifact:
+    """Specialise a :class:`TransportProgramBinding` for the current compilation and return it as
+    device code: the emitted kernel body with a ``__device__`` signature instead of an entry point."""
+    from .driver import compile_program
+
+    compiled = compile_program(binding.to_builder(reuse=reuse, threads=threads), options)
+    if compiled.cuda is None:
+        raise ValueError("the pipeline was stopped before the lowering; nothing to bind")
+    symbol = compiled.name + "_fragment"
+    source = compiled.cuda.replace(f'extern "C" __global__ void {compiled.name}(',
+                                   f"__device__ __forceinline__ void {symbol}(", 1)
+    if source == compiled.cuda:
+        raise RuntimeError("emitted source has no entry point to rebind")
+    return FragmentArtifact(binding.name, symbol, binding.artifact, source,
+                            _parameters(compiled.cuda, compiled.name), compiled.facts, compiled.key)
+
+
+def realize_bindable_epilogue(binding, **kwargs) -> FragmentArtifact:
+    """The fragment of a binding declared ``bindable_epilogue``: the client calls it as the last
+    statement of its kernel, after a CTA barrier if several threads produced the source."""
+    if binding.artifact != "bindable_epilogue":
+        raise ValueError(f"binding {binding.name!r} is declared {binding.artifact!r}, not bindable_epilogue")
+    if binding.reductions:
+        raise ValueError("a bindable epilogue cannot carry reductions: they belong to the consumer kernel")
+    return compile_fragment_artifact(binding, **kwargs)
+
+
+def realize_standalone_kernel(binding, *, reuse: int = 1, threads: int = 32, options=None,
+                              force: bool = False) -> StandaloneKernel:
+    """Compile a binding declared ``standalone_kernel`` to a cubin of its own (nvcc, sm_100a)."""
+    from .driver import compile_program
+
+    if binding.artifact != "standalone_kernel":
+        raise ValueError(f"binding {binding.name!r} is declared {binding.artifact!r}, not standalone_kernel")
+    if binding.reductions:
+        raise ValueError("a standalone transport kernel cannot carry reductions")
+    compiled = compile_program(binding.to_builder(reuse=reuse, threads=threads), options)
+    artifact = build_artifact(compiled, force=force)
+    return StandaloneKernel(binding.name, artifact, _parameters(compiled.cuda, compiled.name), compiled.facts)

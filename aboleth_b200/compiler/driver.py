@@ -123,3 +123,12 @@ def _affine(expr: str) -> str:
 
 def include_dir() -> Path:
     return Path(_native.__file__).resolve().parent / "include"
+
+
+def install_compiler() -> None:
+    """Make the specializer ready: build (if stale) and load the native pass library.
+
+    The reference hooks its passes into another compiler's stage list
+    (python/aboleth/compiler.py:470-471); here the pipeline is this package's own native
+    library, so installing means having it built and loaded.  Idempotent."""
+    _lib()

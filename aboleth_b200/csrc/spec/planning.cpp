@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <limits>
 
 #include "aboleth/abi/transport_plan.h"
 #include "ir.hpp"
@@ -402,6 +403,264 @@ void plan_transport(const Program &p, Json &j) {
     j.end_array();
 }
 
+// ---- plan-transport-program ---------------------------------------------------------------------
+//
+// An ordered list of phases (transfers) and kernels with the memory each one reads and
+// writes.  An access is an arithmetic walk over one allocation:
+//   allocation, generation, offset, length, stride, period, count [, unknown]
+// iteration i touches [offset + (i*stride mod period), +length).  From the overlaps the
+// planner derives, per phase: how many iterations pass before the source is touched again
+// (reuse distance), the completion interval that lifetime, the queue and the policy allow,
+// the first later operation that overwrites the source (completion deadline) and the first
+// that reads the destination (publication deadline), wrapping once when the program is
+// cyclic; per kernel: who consumes its output last, who overwrites it first, and whether the
+// output buffer may be pooled.  (reference: compiler/lib/Transforms/PlanTransport.cpp:61-198
+// for the walk, 203-316 for the interval, 318-422 deadlines, 424-563 output lifetimes.)
+
+struct Walk {
+    long long allocation = 0, generation = 0, offset = 0, length = 0, stride = 0, period = 0, count = 1;
+    bool unknown = false;
+};
+
+bool interval_at(const Walk &w, long long iteration, long long &begin, long long &end) {
+    if (w.unknown || iteration < 0 || iteration >= w.count)
+        return false;
+    if (w.stride != 0 && iteration > (std::numeric_limits<long long>::max() - w.offset) / std::max(w.stride, 1LL))
+        return false;
+    long long displacement = iteration * w.stride;
+    if (w.period > 0)
+        displacement %= w.period;
+    begin = w.offset + displacement;
+    if (w.length > std::numeric_limits<long long>::max() - begin)
+        return false;
+    end = begin + w.length;
+    return true;
+}
+
+bool walks_overlap_at(const Walk &a, long long ia, const Walk &b, long long ib) {
+    if (a.unknown || b.unknown)
+        return true;
+    if (a.allocation != b.allocation || a.generation != b.generation)
+        return false;
+    long long a0, a1, b0, b1;
+    if (!interval_at(a, ia, a0, a1) || !interval_at(b, ib, b0, b1))
+        return true;  // cannot be bounded: assume they meet
+    return a0 < b1 && b0 < a1;
+}
+
+bool any_overlap(const std::vector<Walk> &first, const std::vector<Walk> &second) {
+    for (const Walk &a : first)
+        for (const Walk &b : second)
+            for (long long i = 0; i < std::max(a.count, 1LL); ++i)
+                for (long long k = 0; k < std::max(b.count, 1LL); ++k)
+                    if (walks_overlap_at(a, i, b, k))
+                        return true;
+    return false;
+}
+
+struct Step {
+    const Op *op;
+    bool is_phase;
+    std::string name;
+    std::vector<Walk> reads, writes;
+    bool unknown_access = false;
+};
+
+Step read_step(const Op &op) {
+    Step s{&op, op.kind == "phase", op.get("name"), {}, {}, false};
+    if (s.name.empty())
+        throw Error(op.kind + " needs a name");
+    for (const Op &access : op.body) {
+        if (access.kind != "read" && access.kind != "write")
+            throw Error(op.kind + " " + s.name + ": unknown access '" + access.kind + "'");
+        Walk w;
+        w.allocation = num(access, "allocation");
+        w.generation = num(access, "generation");
+        w.offset = num(access, "offset");
+        w.length = num(access, "length");
+        w.stride = num(access, "stride");
+        w.period = num(access, "period");
+        w.count = num(access, "count", 1);
+        w.unknown = num(access, "unknown", 0) != 0;
+        if (w.length < 0 || w.count < 1 || w.period < 0)
+            throw Error(op.kind + " " + s.name + ": access needs length >= 0, count >= 1, period >= 0");
+        s.unknown_access = s.unknown_access || w.unknown;
+        (access.kind == "read" ? s.reads : s.writes).push_back(w);
+    }
+    return s;
+}
+
+void plan_transport_program(const Program &p, Json &j) {
+    using namespace aboleth::abi;
+    const bool cyclic = to_integer(p.get("cyclic", "0")) != 0;
+    std::vector<Step> steps;
+    for (const Op &op : p.body)
+        if (op.kind == "phase" || op.kind == "kernel")
+            steps.push_back(read_step(op));
+    for (std::size_t i = 0; i < steps.size(); ++i)
+        for (std::size_t k = i + 1; k < steps.size(); ++k)
+            if (steps[i].name == steps[k].name)
+                throw Error("operation name '" + steps[i].name + "' is used twice");
+
+    // First operation after `index` (wrapping once when cyclic) for which `test` holds.
+    auto first_after = [&](std::size_t index, auto test, std::string &name, long long &delta) {
+        name = "program_end";
+        delta = 0;
+        for (std::size_t k = index + 1; k < steps.size(); ++k)
+            if (test(steps[k])) {
+                name = steps[k].name;
+                return;
+            }
+        if (!cyclic)
+            return;
+        for (std::size_t k = 0; k <= index; ++k)
+            if (test(steps[k])) {
+                name = steps[k].name;
+                delta = 1;
+                return;
+            }
+    };
+
+    j.key("cyclic").value(cyclic);
+    j.key("phases").begin_array();
+    for (std::size_t index = 0; index < steps.size(); ++index) {
+        const Step &s = steps[index];
+        if (!s.is_phase)
+            continue;
+        const Op &phase = *s.op;
+        const long long commands = num(phase, "commands", 1), iterations = num(phase, "iterations", 1),
+                        payload = num(phase, "payload_bytes", 0);
+        if (commands <= 0 || iterations <= 0 || payload < 0)
+            throw Error("phase " + s.name + " has invalid transport planning facts");
+        // Reuse distance: the smallest d such that iteration i and i + d touch the same source bytes.
+        long long reuse = s.reads.empty() ? 1 : iterations;
+        for (const Walk &read : s.reads) {
+            if (read.count != iterations)
+                throw Error("phase " + s.name + ": read effect count must equal iterations");
+            long long mine = iterations;
+            for (long long d = 1; d < iterations && mine == iterations; ++d)
+                for (long long i = 0; i + d < iterations; ++i)
+                    if (walks_overlap_at(read, i, read, i + d)) {
+                        mine = d;
+                        break;
+                    }
+            reuse = std::min(reuse, mine);
+        }
+        const std::vector<std::string> transports = list(phase.get("transports"));
+        const std::vector<std::string> capacities = list(phase.get("capacities"));
+        const std::vector<std::string> peer_intervals = list(phase.get("intervals"));
+        if (transports.size() != capacities.size())
+            throw Error("phase " + s.name + " requires one endpoint capacity per peer transport");
+        if (!peer_intervals.empty() && peer_intervals.size() != transports.size())
+            throw Error("phase " + s.name + " requires one completion interval per peer transport");
+        const bool explicit_interval = phase.has("interval");
+        const long long tiny = num(phase, "tiny", 4096);
+        long long policy = iterations, capacity_limit = iterations;
+        bool queued = false;
+        for (std::size_t t = 0; t < transports.size(); ++t) {
+            const TransportCaps *caps = lookup_transport_caps(transports[t].c_str());
+            if (caps == nullptr)
+                throw Error("unknown peer transport '" + transports[t] + "'");
+            if (!explicit_interval) {
+                const long long configured = peer_intervals.empty() ? 0 : to_integer(peer_intervals[t]);
+                const long long preferred =
+                    configured > 0 ? configured
+                    : (payload <= tiny || caps->load_store_addressable) ? iterations
+                    : caps->default_completion_interval > 0
+                        ? static_cast<long long>(caps->default_completion_interval) : iterations;
+                policy = std::min(policy, std::min(preferred, iterations));
+            }
+            if (caps->queue_capacity_limited) {
+                queued = true;
+                const long long capacity = to_integer(capacities[t]);
+                if (capacity < commands)
+                    throw Error("phase " + s.name + ": endpoint capacity cannot hold one iteration");
+                capacity_limit = std::min(capacity_limit,
+                                          std::min(std::max(1LL, (capacity - 1) / commands), iterations));
+            }
+        }
+        const long long legal = std::min(reuse, capacity_limit);
+        long long interval;
+        if (explicit_interval) {
+            interval = num(phase, "interval");
+            if (interval < 1 || interval > legal)
+                throw Error("phase " + s.name + ": explicit completion interval exceeds region lifetime "
+                            "or endpoint capacity");
+        } else {
+            if (transports.empty())
+                throw Error("phase " + s.name + ": automatic completion planning requires endpoint capabilities");
+            interval = std::min(legal, policy);
+        }
+        std::string completion_before, publication_before;
+        long long completion_delta = 0, publication_delta = 0;
+        first_after(index, [&](const Step &later) { return any_overlap(s.reads, later.writes); },
+                    completion_before, completion_delta);
+        first_after(index, [&](const Step &later) { return any_overlap(later.reads, s.writes); },
+                    publication_before, publication_delta);
+        j.begin_object();
+        j.key("name").value(s.name);
+        j.key("resolvedCompletionInterval").value(interval);
+        j.key("reuseDistance").value(reuse);
+        j.key("completionBefore").value(completion_before);
+        j.key("completionIterationDelta").value(completion_delta);
+        j.key("publicationBefore").value(publication_before);
+        j.key("publicationIterationDelta").value(publication_delta);
+        j.key("requiresFinalDrain").value(queued && interval > 1);
+        j.end_object();
+    }
+    j.end_array();
+
+    j.key("kernels").begin_array();
+    for (std::size_t index = 0; index < steps.size(); ++index) {
+        const Step &s = steps[index];
+        if (s.is_phase)
+            continue;
+        const Op &kernel = *s.op;
+        j.begin_object();
+        j.key("name").value(s.name);
+        j.key("opaque").value(num(kernel, "opaque", 0) != 0);
+        bool reusable = false;
+        std::string last_consumer = "none", reuse_before = "program_end";
+        long long consumer_delta = 0, reuse_delta = 0;
+        if (!s.writes.empty() && !s.unknown_access) {
+            bool unknown_interference = false;
+            auto inspect = [&](const Step &later, long long delta) {
+                if (later.unknown_access) {
+                    unknown_interference = true;
+                    return;
+                }
+                if (any_overlap(later.reads, s.writes)) {
+                    last_consumer = later.name;
+                    consumer_delta = delta;
+                }
+                if (any_overlap(s.writes, later.writes)) {
+                    reuse_before = later.name;
+                    reuse_delta = delta;
+                }
+            };
+            for (std::size_t k = index + 1; k < steps.size() && reuse_before == "program_end"; ++k)
+                inspect(steps[k], 0);
+            if (reuse_before == "program_end" && cyclic)
+                for (std::size_t k = 0; k <= index && reuse_before == "program_end"; ++k)
+                    inspect(steps[k], 1);
+            const bool asynchronous = num(kernel, "asynchronous", 0) != 0;
+            const bool async_ok = !asynchronous || num(kernel, "event_ordered", 0) != 0;
+            reusable = !unknown_interference && async_ok && last_consumer != "none" &&
+                       reuse_before != "program_end" && consumer_delta <= reuse_delta;
+            if (reusable) {
+                j.key("outputLastConsumer").value(last_consumer);
+                j.key("outputLastConsumerIterationDelta").value(consumer_delta);
+                j.key("outputReuseBefore").value(reuse_before);
+                j.key("outputReuseIterationDelta").value(reuse_delta);
+                j.key("outputPoolDepth").value(asynchronous ? std::max(num(kernel, "max_inflight", 1), 1LL) : 1LL);
+            }
+        }
+        j.key("outputReusable").value(reusable);
+        j.end_object();
+    }
+    j.end_array();
+}
+
 // ---- simplify-communication-dataflow --------------------------------------------------------------
 
 void simplify_dataflow(const Program &p, Json &j) {
@@ -557,6 +816,8 @@ std::string run_planner(const std::string &kind, const std::string &request) {
         plan_storage(program, j);
     else if (kind == "plan-transport")
         plan_transport(program, j);
+    else if (kind == "plan-transport-program")
+        plan_transport_program(program, j);
     else if (kind == "simplify-dataflow")
         simplify_dataflow(program, j);
     else

@@ -109,6 +109,35 @@ class ExecutionContract:
         return ExecutionDecision(self.fallback.value, actual_items, "fixed capacity not proven")
 
 
+@dataclass(frozen=True)
+class CompiledExecutionPlan:
+    """Compiled phases plus the contract they may run under."""
+
+    phases: tuple
+    contract: ExecutionContract
+
+    def __post_init__(self) -> None:
+        names = tuple(phase.name for phase in self.phases)
+        if not names:
+            raise ValueError("compiled execution plan requires at least one phase")
+        if len(names) != len(set(names)):
+            raise ValueError("compiled execution phase names must be unique")
+
+    def phase(self, name: str):
+        for phase in self.phases:
+            if phase.name == name:
+                return phase
+        raise KeyError(f"compiled execution has no phase {name!r}")
+
+    def resolve(self, actual_items: int, **kwargs) -> ExecutionDecision:
+        return self.contract.resolve(actual_items, **kwargs)
+
+    def describe(self) -> dict:
+        return {"contract": self.contract.describe(),
+                "phases": [phase.manifest() if hasattr(phase, "manifest") else {"name": phase.name}
+                           for phase in self.phases]}
+
+
 def compile_execution_plan(contract: ExecutionContract, variants: tuple[int, ...]) -> dict:
     """Which compiled capacities a contract may use, smallest first."""
     usable = tuple(v for v in sorted(variants) if v <= contract.capacity.max_items) or \

@@ -13,7 +13,7 @@ from .records import await_records, send_records
 
 
 @dataclass(frozen=True)
-class PhaseBinding:
+class PhaseLaunch:
     name: str
     sender_grid: tuple[int, int]
     receiver_grid: tuple[int, int]
@@ -26,7 +26,7 @@ class PhaseBinding:
 class CompiledPhase:
     name: str
     schedule: PhaseSchedule
-    binding: PhaseBinding
+    binding: PhaseLaunch
     sender: CompiledProgram
     receiver: CompiledProgram
     completion_interval: int
@@ -54,7 +54,7 @@ def compile_phase(plan: CompiledPatternPlan, name: str, *, rank: int, capacity: 
         ready_stride=launch.ready_stride, threads=32 * launch.sender_warps))
     receiver = compile_program(await_records(ready_stride=launch.ready_stride,
                                              lanes_per_program=launch.receiver_lanes_per_program))
-    binding = PhaseBinding(name, launch.sender_grid, launch.receiver_grid, 32 * launch.sender_warps,
+    binding = PhaseLaunch(name, launch.sender_grid, launch.receiver_grid, 32 * launch.sender_warps,
                            launch.ready_stride, launch.signal_slots)
     return CompiledPhase(name, schedule, binding, sender, receiver,
                          plan.completion_interval_for(name.replace(".", "_")))

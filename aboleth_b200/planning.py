@@ -130,6 +130,16 @@ class TransportPhase:
     policy_interval: Optional[int] = None
     strict_registrations: bool = False
     exclusive: bool = False
+    # Program-level planning (plan_transport_program): what the phase reads and writes per
+    # iteration, and the queues it goes through.
+    iterations: int = 1
+    peer_transports: tuple[str, ...] = ()
+    peer_capacities: tuple[int, ...] = ()
+    completion_intervals: tuple[int, ...] = ()
+    explicit_interval: Optional[int] = None
+    tiny_payload_bytes: int = 4096
+    reads: tuple["RegionAccess", ...] = ()
+    writes: tuple["RegionAccess", ...] = ()
 
 
 def plan_transport(peers: Mapping[int, str], phases: Sequence[TransportPhase]) -> dict:
@@ -218,3 +228,122 @@ def simplify_communication_dataflow(dataflow: CommunicationDataflow) -> Simplifi
     result = run_planner("simplify-dataflow", dataflow.to_request())
     return SimplifiedCommunicationDataflow(tuple(result["operations"]), tuple(result["removed"]),
                                            result["aliases"], tuple(result["unallocated_regions"]))
+
+
+# ---- program-level transport planning -----------------------------------------------------------
+
+@dataclass(frozen=True)
+class RegionAccess:
+    """An arithmetic walk over one allocation: iteration ``i`` touches
+    ``[offset + (i * stride mod period), + length)``; ``unknown`` overlaps everything."""
+
+    allocation: int
+    generation: int = 0
+    offset: int = 0
+    length: int = 0
+    stride: int = 0
+    period: int = 0
+    count: int = 1
+    unknown: bool = False
+
+    def to_request(self, kind: str) -> str:
+        return (f"  {kind} allocation={self.allocation} generation={self.generation} offset={self.offset} "
+                f"length={self.length} stride={self.stride} period={self.period} count={self.count} "
+                f"unknown={int(self.unknown)}")
+
+
+@dataclass(frozen=True)
+class TransportKernel:
+    """A compute step between phases.  ``opaque``: the client compiles it, nothing may be placed inside."""
+
+    name: str
+    reads: tuple[RegionAccess, ...] = ()
+    writes: tuple[RegionAccess, ...] = ()
+    asynchronous: bool = False
+    max_inflight: int = 1
+    event_ordered: bool = False
+    opaque: bool = False
+
+
+@dataclass(frozen=True)
+class TransportPlan:
+    completion_interval: int
+    reuse_distance: int
+    completion_before: str
+    completion_iteration_delta: int
+    publication_before: str
+    publication_iteration_delta: int
+    requires_final_drain: bool = False
+
+
+@dataclass(frozen=True)
+class OutputLifetimePlan:
+    last_consumer: str
+    last_consumer_iteration_delta: int
+    reuse_before: str
+    reuse_iteration_delta: int
+    pool_depth: int
+
+
+def _program_request(operations: Sequence[object], cyclic: bool) -> str:
+    lines = [f"program plan cyclic={int(cyclic)} enable={_enable()}"]
+    for op in operations:
+        if isinstance(op, TransportPhase):
+            transports = op.peer_transports or (op.backend,)
+            capacities = op.peer_capacities or (op.queue_capacity,) * len(transports)
+            head = (f"phase name={op.name} commands={op.commands} iterations={op.iterations} "
+                    f"payload_bytes={op.payload_bytes} tiny={op.tiny_payload_bytes} "
+                    f"transports={','.join(transports)} capacities={','.join(map(str, capacities))}")
+            if op.completion_intervals:
+                head += f" intervals={','.join(map(str, op.completion_intervals))}"
+            if op.explicit_interval is not None:
+                head += f" interval={op.explicit_interval}"
+        elif isinstance(op, TransportKernel):
+            head = (f"kernel name={op.name} asynchronous={int(op.asynchronous)} max_inflight={op.max_inflight} "
+                    f"event_ordered={int(op.event_ordered)} opaque={int(op.opaque)}")
+        else:
+            raise TypeError("a transport program is made of TransportPhase and TransportKernel")
+        lines.append(head + " {")
+        lines += [a.to_request("read") for a in op.reads] + [a.to_request("write") for a in op.writes]
+        lines.append("}")
+    return "\n".join(lines) + "\n"
+
+
+def plan_transport_facts(operations: Sequence[object], cyclic: bool = False) -> dict:
+    """The native planner's facts for one ordered program of phases and kernels (read-only)."""
+    return run_planner("plan-transport-program", _program_request(tuple(operations), cyclic))
+
+
+def plan_transport_program(operations: Sequence[object], cyclic: bool = False) -> dict[str, TransportPlan]:
+    facts = plan_transport_facts(operations, cyclic)
+    plans = {p["name"]: TransportPlan(p["resolvedCompletionInterval"], p["reuseDistance"],
+                                      p["completionBefore"], p["completionIterationDelta"],
+                                      p["publicationBefore"], p["publicationIterationDelta"],
+                                      p["requiresFinalDrain"]) for p in facts["phases"]}
+    expected = {op.name for op in operations if isinstance(op, TransportPhase)}
+    if set(plans) != expected:
+        raise RuntimeError("transport planner omitted a phase")
+    return plans
+
+
+def plan_output_lifetimes(operations: Sequence[object], cyclic: bool = False) -> dict[str, OutputLifetimePlan]:
+    """Kernels whose output buffer may be pooled: last consumer, first overwriter, pool depth."""
+    facts = plan_transport_facts(operations, cyclic)
+    return {k["name"]: OutputLifetimePlan(k["outputLastConsumer"], k["outputLastConsumerIterationDelta"],
+                                          k["outputReuseBefore"], k["outputReuseIterationDelta"],
+                                          k["outputPoolDepth"])
+            for k in facts["kernels"] if k.get("outputReusable")}
+
+
+@dataclass(frozen=True)
+class CommunicationDataflowOperation:
+    """Typed view of one entry of ``CommunicationDataflow.operations``."""
+
+    kind: str
+    name: str
+    attributes: Mapping[str, object] = field(default_factory=dict)
+
+    @classmethod
+    def from_dict(cls, record: Mapping[str, object]) -> "CommunicationDataflowOperation":
+        return cls(str(record["kind"]), str(record["name"]),
+                   {k: v for k, v in record.items() if k not in ("kind", "name")})

@@ -27,7 +27,7 @@ import threading
 from dataclasses import dataclass
 from enum import Enum, IntEnum
 from multiprocessing import shared_memory
-from typing import Optional
+from typing import Mapping, Optional
 
 import torch
 
@@ -663,6 +663,108 @@ class EndpointTable:
             return self._endpoints[peer]
         except KeyError as error:
             raise KeyError(f"no endpoint to rank {peer}") from error
+
+
+class EndpointPair:
+    """Both ends of one connection inside a single process (one runtime per end)."""
+
+    def __init__(self, transport: Transport, first: "Runtime", second: "Runtime",
+                 ids: tuple[int, int]):
+        self._transport = Transport(transport)
+        a = first.create_local_endpoint(self._transport)
+        b = second.create_local_endpoint(self._transport)
+        try:
+            if self._transport == Transport.P2P:
+                a.connect_p2p(ids[1], second.device_index)
+                b.connect_p2p(ids[0], first.device_index)
+            else:
+                info_a, info_b = a.connection_info, b.connection_info
+                a.connect(ids[1], info_b)
+                b.connect(ids[0], info_a)
+        except Exception:
+            a.close()
+            b.close()
+            raise
+        self.ids = ids
+        self.endpoints = (a, b)
+        self._closed = False
+
+    @property
+    def transport(self) -> Transport:
+        return self._transport
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        for endpoint in reversed(self.endpoints):
+            endpoint.close()
+        self._closed = True
+
+
+class EndpointMesh:
+    """Every pair of a set of same-process participants connected, with one table per participant.
+
+    ``runtimes`` maps a participant id (a device ordinal, or any small integer for CPU
+    runtimes) to its :class:`Runtime`.  Reference: python/aboleth/runtime.py:1020-1165 (pair),
+    1168-1231 (mesh); there the runtime is per process and spans devices, here it is per device.
+    """
+
+    def __init__(self, runtimes: Mapping[int, "Runtime"], transport: Transport = Transport.P2P):
+        self._runtimes = dict(runtimes)
+        ids = sorted(self._runtimes)
+        if len(ids) < 2:
+            raise ValueError("an endpoint mesh needs at least two participants")
+        self._pairs: list[EndpointPair] = []
+        endpoints: dict[int, dict[int, LocalEndpoint]] = {i: {} for i in ids}
+        try:
+            for n, first in enumerate(ids):
+                for second in ids[n + 1:]:
+                    pair = EndpointPair(transport, self._runtimes[first], self._runtimes[second],
+                                        (first, second))
+                    self._pairs.append(pair)
+                    endpoints[first][second], endpoints[second][first] = pair.endpoints
+        except Exception:
+            for pair in reversed(self._pairs):
+                pair.close()
+            raise
+        size = max(ids) + 1
+        self.tables = {i: EndpointTable(self._runtimes[i].torch_device, endpoints[i], size) for i in ids}
+        self._closed = False
+
+    def _ensure_open(self) -> None:
+        if self._closed:
+            raise RuntimeError("Aboleth endpoint mesh is closed")
+
+    def runtime(self, participant: int) -> "Runtime":
+        return self._runtimes[participant]
+
+    def endpoint(self, participant: int, peer: int) -> LocalEndpoint:
+        self._ensure_open()
+        return self.tables[participant].endpoint(peer)
+
+    @property
+    def pairs(self) -> tuple[EndpointPair, ...]:
+        self._ensure_open()
+        return tuple(self._pairs)
+
+    def close(self) -> None:
+        if self._closed:
+            return
+        for pair in reversed(self._pairs):
+            pair.close()
+        self._closed = True
+
+    def __enter__(self) -> "EndpointMesh":
+        self._ensure_open()
+        return self
+
+    def __exit__(self, exc_type, exc_value, traceback) -> None:
+        try:
+            self.close()
+        except Exception as cleanup_error:  # keep the original error first
+            if exc_value is None:
+                raise
+            exc_value.add_note(f"Aboleth endpoint-mesh cleanup also failed: {cleanup_error}")
 
 
 class Runtime:

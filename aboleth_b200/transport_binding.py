@@ -1,0 +1,278 @@
+"""Binding a planned communication attachment to the slots of a client kernel.
+
+A *transport program* is the communication of one attachment (one or more logical
+transfers that share a publication) written against named scalar slots: the endpoint, and
+for every region pair a remote pointer/key, a local pointer/key, a byte count and a
+predicate; for the publication a remote and a local flag address with their keys and the
+iteration counters.  The client kernel supplies values for the slots at its insertion
+point.  ``TransportProgramBinding.to_builder()`` turns a binding into a Tier-2 program
+(predicated puts chained into one strong signal, then a planned wait), which the pass
+pipeline specialises per transport like any other program.
+
+Data model after the reference (python/aboleth/transport_binding.py:16-265; the program
+records of python/aboleth/pattern.py); slot types are i1 / i32 / i64.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+from .compiler.language import ProgramBuilder
+
+ARTIFACT_KINDS = ("inline_fragment", "bindable_epilogue", "standalone_kernel")
+_CUDA_TYPES = {"i1": "i32", "i32": "i32", "i64": "u64"}
+
+
+@dataclass(frozen=True)
+class BoundScalar:
+    name: str
+    mlir_type: str
+
+    def __post_init__(self):
+        if not self.name:
+            raise ValueError("bound scalar requires a name")
+        if self.mlir_type not in ("i1", "i32", "i64"):
+            raise ValueError("bound scalar type must be i1, i32, or i64")
+
+
+@dataclass(frozen=True)
+class RegionSide:
+    pointer: BoundScalar
+    key: BoundScalar
+
+    def __post_init__(self):
+        if self.pointer.mlir_type != "i64":
+            raise ValueError("region pointers must use i64 slots")
+        if self.key.mlir_type != "i32":
+            raise ValueError("region keys must use i32 slots")
+
+
+@dataclass(frozen=True)
+class RegionBinding:
+    remote: RegionSide
+    local: RegionSide
+    byte_count: BoundScalar
+    predicate: BoundScalar
+    max_bytes: int
+    operations: tuple[str, ...] = ()
+
+    def __post_init__(self):
+        if self.byte_count.mlir_type != "i32":
+            raise ValueError("region byte count must use an i32 slot")
+        if self.predicate.mlir_type != "i1":
+            raise ValueError("region predicate must use an i1 slot")
+        if self.max_bytes <= 0:
+            raise ValueError("region max bytes must be positive")
+
+    def slots(self) -> tuple[BoundScalar, ...]:
+        return (self.remote.pointer, self.local.pointer, self.byte_count, self.local.key,
+                self.remote.key, self.predicate)
+
+
+_REGION_ROLES = ("remote pointer", "local pointer", "byte count", "local key", "remote key", "predicate")
+
+
+@dataclass(frozen=True)
+class PublicationBinding:
+    remote: RegionSide
+    local: RegionSide
+    iteration: BoundScalar
+    iterations: BoundScalar
+
+    def __post_init__(self):
+        if self.iteration.mlir_type != "i32" or self.iterations.mlir_type != "i32":
+            raise ValueError("publication iteration slots must use i32")
+
+    def slots(self) -> tuple[BoundScalar, ...]:
+        return (self.remote.pointer, self.local.pointer, self.local.key, self.remote.key,
+                self.iteration, self.iterations)
+
+
+_PUBLICATION_ROLES = ("remote pointer", "local pointer", "local key", "remote key", "iteration", "iterations")
+
+
+@dataclass(frozen=True)
+class KernelTransportArgument:
+    name: str
+    mlir_type: str
+
+
+@dataclass(frozen=True)
+class KernelTransportTransfer:
+    operations: tuple[str, ...]
+    destination: str
+    source: str
+    byte_count: str
+    source_key: str
+    destination_key: str
+    predicate: str
+    max_bytes: int
+
+
+@dataclass(frozen=True)
+class KernelTransportSignal:
+    destination: str
+    source: str
+    source_key: str
+    destination_key: str
+    iteration: str
+    iterations: str
+
+
+@dataclass(frozen=True)
+class KernelTransportReduction:
+    """A reduction the client kernel applies while it consumes the received rows."""
+
+    operation: str
+    sources: tuple[str, ...]
+    destination: str
+    combiner: str = "add"
+
+    def __post_init__(self):
+        if not self.operation or not self.sources or not self.destination:
+            raise ValueError("a transport reduction names an operation, sources and a destination")
+
+
+@dataclass(frozen=True)
+class KernelTransportTransform:
+    """A transform the packing kernel applies while it produces the source (e.g. fp8 quantisation)."""
+
+    operation: str
+    name: str
+    role: str = "values"
+
+
+@dataclass(frozen=True)
+class KernelTransportProgram:
+    name: str
+    operations: tuple[str, ...]
+    kernel: str
+    insertion_point: str
+    arguments: tuple[KernelTransportArgument, ...]
+    transfers: tuple[KernelTransportTransfer, ...]
+    signal: Optional[KernelTransportSignal]
+    artifact: str = "inline_fragment"
+    reductions: tuple[KernelTransportReduction, ...] = ()
+    transforms: tuple[KernelTransportTransform, ...] = ()
+    program_id: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class TransportProgramBinding:
+    name: str
+    operations: tuple[str, ...]
+    kernel: str
+    insertion_point: str
+    endpoint: BoundScalar
+    regions: tuple[RegionBinding, ...]
+    publication: PublicationBinding
+    artifact: str = "inline_fragment"
+    reductions: tuple[KernelTransportReduction, ...] = ()
+    transforms: tuple[KernelTransportTransform, ...] = ()
+
+    def __post_init__(self):
+        if not self.name or not self.kernel or not self.insertion_point:
+            raise ValueError("transport binding requires name, kernel, and insertion point")
+        if self.artifact not in ARTIFACT_KINDS:
+            raise ValueError(f"unknown artifact kind {self.artifact!r}; expected one of "
+                             + ", ".join(ARTIFACT_KINDS))
+        if self.endpoint.mlir_type != "i64":
+            raise ValueError("transport endpoint must use an i64 slot")
+        if not self.operations or not self.regions:
+            raise ValueError("transport binding requires operations and regions")
+        realized = tuple(op for region in self.regions for op in region.operations)
+        if len(realized) != len(set(realized)) or set(realized) != set(self.operations):
+            raise ValueError("transport binding must realize each logical operation once")
+
+    def slots(self) -> tuple[BoundScalar, ...]:
+        """The bound scalars in invocation order.  One name is one role: the same name under
+        two roles is refused (the second role would be issued through the first one's storage)."""
+        candidates = [("endpoint", self.endpoint)]
+        for index, region in enumerate(self.regions):
+            candidates += [(f"region {index} {role}", slot) for role, slot in zip(_REGION_ROLES, region.slots())]
+        candidates += [(f"publication {role}", slot)
+                       for role, slot in zip(_PUBLICATION_ROLES, self.publication.slots())]
+        result, roles = [], {}
+        for role, slot in candidates:
+            previous = roles.get(slot.name)
+            if previous is None:
+                roles[slot.name] = (role, slot.mlir_type)
+                result.append(slot)
+            elif previous != (role, slot.mlir_type):
+                raise ValueError(f"transport binding {self.name!r} binds slot {slot.name!r} to two roles: "
+                                 f"the {previous[0]} ({previous[1]}) and the {role} ({slot.mlir_type})")
+        return tuple(result)
+
+    def to_program(self, program_id: Optional[int] = None) -> KernelTransportProgram:
+        return KernelTransportProgram(
+            name=self.name, operations=self.operations, kernel=self.kernel,
+            insertion_point=self.insertion_point,
+            arguments=tuple(KernelTransportArgument(s.name, s.mlir_type) for s in self.slots()),
+            transfers=tuple(KernelTransportTransfer(
+                operations=r.operations, destination=r.remote.pointer.name, source=r.local.pointer.name,
+                byte_count=r.byte_count.name, source_key=r.local.key.name,
+                destination_key=r.remote.key.name, predicate=r.predicate.name, max_bytes=r.max_bytes)
+                for r in self.regions),
+            signal=KernelTransportSignal(
+                destination=self.publication.remote.pointer.name, source=self.publication.local.pointer.name,
+                source_key=self.publication.local.key.name, destination_key=self.publication.remote.key.name,
+                iteration=self.publication.iteration.name, iterations=self.publication.iterations.name),
+            artifact=self.artifact, reductions=self.reductions, transforms=self.transforms,
+            program_id=program_id)
+
+    def to_builder(self, *, reuse: int = 1, threads: int = 32) -> ProgramBuilder:
+        """The attachment as a Tier-2 program whose arguments are the slots, in slot order.
+
+        Every region becomes one predicated put; the puts are chained, the last one carries
+        the strong signal (epoch = iteration + 1), and a planned wait with ``reuse`` lets the
+        completion pass pick the interval."""
+        args = [(s.name, _CUDA_TYPES[s.mlir_type]) for s in self.slots()]
+        b = ProgramBuilder(_symbol(self.name), args=args, threads=threads)
+        # The endpoint slot carries the handle itself: a one-entry table at the argument's address.
+        endpoint = b.endpoint(f"(&{self.endpoint.name})", 0)
+        token = None
+        for region in self.regions:
+            dst = b.remote_at(region.remote.pointer.name, key=region.remote.key.name)
+            src = b.local(region.local.pointer.name, key=region.local.key.name)
+            token = b.put(endpoint, dst, src, bytes=region.byte_count.name, after=token,
+                          predicate=region.predicate.name)
+        flag = b.remote_at(self.publication.remote.pointer.name, key=self.publication.remote.key.name)
+        ready = b.signal(endpoint, flag, epoch=f"{self.publication.iteration.name} + 1", after=token)
+        b.wait(ready, iteration=self.publication.iteration.name, reuse=reuse,
+               final=f"{self.publication.iteration.name} + 1 == {self.publication.iterations.name}")
+        return b
+
+
+def _symbol(name: str) -> str:
+    stem = "".join(c if c.isalnum() else "_" for c in name)
+    return ("t_" + stem) if not stem[:1].isalpha() else stem
+
+
+@dataclass(frozen=True)
+class InvokeManifest:
+    program_id: int
+    arguments: tuple[KernelTransportArgument, ...]
+    transfers: tuple[KernelTransportTransfer, ...]
+    signal: Optional[KernelTransportSignal]
+
+    @property
+    def slot_names(self) -> tuple[str, ...]:
+        return tuple(a.name for a in self.arguments)
+
+
+def invoke_manifest(program: KernelTransportProgram) -> InvokeManifest:
+    if program.program_id is None:
+        raise ValueError("transport program is not bound")
+    return InvokeManifest(program.program_id, program.arguments, program.transfers, program.signal)
+
+
+def invoke_transport_program(manifest: InvokeManifest, symbol: str, **slots: str) -> str:
+    """The call a CUDA client writes at its insertion point: every slot of the manifest must be
+    given exactly once (as a C++ expression); returns ``symbol(expr, ...);`` in slot order."""
+    missing = [n for n in manifest.slot_names if n not in slots]
+    extra = [n for n in slots if n not in manifest.slot_names]
+    if missing or extra:
+        raise ValueError(f"transport program {manifest.program_id}: missing slots {missing}, unknown slots {extra}")
+    casts = {"i64": "static_cast<std::uint64_t>", "i32": "static_cast<int>", "i1": "static_cast<int>"}
+    values = ", ".join(f"{casts[a.mlir_type]}({slots[a.name]})" for a in manifest.arguments)
+    return f"{symbol}({values});"

@@ -1,17 +1,22 @@
 """The public names a user of the reference package expects exist (no GPU)."""
 import aboleth_b200 as ab
 
-EXPECTED = """AllocationHandle AllocationProvider Artifact AutoTransportPolicy Bootstrap CapacityContract
-CommunicationDataflow CommunicationRegion CommunicationStage CompiledPattern CompiledPatternPlan CompiledPhase
-DeviceLibrary Endpoint EndpointTable ExecutionContract ExecutionDecision ExecutionFallback FragmentArtifact
-GENERIC_KV_TARGET_PROFILE H200_NVLINK_KV_TARGET_PROFILE KVCacheLayoutContract KVRuntimeOverrides KVTargetProfile
-KernelBinding LocalBuffer LocalEndpoint LocalRegion OpaqueCapabilities OpaqueStage P2PRealizationProfile
-PaddingSemantics Pattern PeerRegionTable PhaseBinding PhaseResources PhaseSchedule PipeBootstrap
-PipeBootstrapCoordinator RegionEffect RegionRequirement RankControl RegisteredBuffer RemoteBuffer RemoteHandle
-Runtime RuntimeGuard SimplifiedCommunicationDataflow StandaloneKernel TcpStoreBootstrap TorchDistributedBootstrap
-Transport TransportPhase TransportPlan Workset World compilation compile_execution_plan compile_phase
-connection_info_from_bytes connection_transport device_library plan_transport select_kv_target_profile
-simplify_communication_dataflow""".split()
+EXPECTED = """AllocationHandle AllocationProvider Artifact AutoTransportPolicy Bootstrap CapacityContract CommunicationDataflow
+CommunicationDataflowOperation CommunicationRegion CommunicationStage CompiledExecutionPlan CompiledKVCacheMigrationPlan
+CompiledPattern CompiledPatternPlan CompiledPhase DeviceLibrary Endpoint EndpointMesh EndpointPair EndpointTable
+ExecutionContract ExecutionDecision ExecutionFallback FragmentArtifact GENERIC_KV_TARGET_PROFILE
+H200_NVLINK_KV_TARGET_PROFILE InvokeManifest KVCacheLayoutContract KVCacheMigrationSpec KVCachePhysicalization
+KVRuntimeOverrides KVTargetProfile KernelBinding KernelTransportReduction LocalBuffer LocalEndpoint LocalRegion
+MoEPatternSpec OpaqueCapabilities OpaqueStage OutputLifetimePlan P2PRealizationProfile PaddingSemantics Pattern
+PeerRegionTable PhaseBinding PhaseResources PhaseSchedule PhysicalizedPattern PipeBootstrap PipeBootstrapCoordinator
+RegionEffect RegionRequirement RankControl RegisteredBuffer RemoteBuffer RemoteHandle Runtime RuntimeGuard
+RuntimeBindings RuntimeBufferBinding SimplifiedCommunicationDataflow StandaloneKernel TcpStoreBootstrap
+TorchDistributedBootstrap Transport TransportKernel TransportPhase TransportPlan Workset World
+build_kv_cache_migration_pattern build_moe_pattern compilation compile_execution_plan compile_fragment_artifact
+compile_kv_cache_migration compile_phase connection_info_from_bytes connection_transport device_library drain
+install_compiler invoke_transport_program physicalize_pattern plan_output_lifetimes plan_transport
+plan_transport_facts plan_transport_program planned_wait put realize_bindable_epilogue realize_standalone_kernel
+select_kv_target_profile signal simplify_communication_dataflow token token_type wait wait_signal""".split()
 
 
 def test_reference_names_exist():
