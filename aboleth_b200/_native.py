@@ -68,10 +68,12 @@ def _targets() -> dict[str, dict]:
     host = sorted((_CSRC / "host").glob("*.cu")) + sorted((_CSRC / "host").glob("*.cpp"))
     spec = sorted((_CSRC / "spec").glob("*.cpp"))
     common = ["-O3", "-std=c++17", f"-I{_INCLUDE}", "-Xcompiler", "-fPIC"]
+    # Extra preprocessor definitions for the kernels, e.g. ABOLETH_KERNEL_DEFINES=AB_GEMM_TRACE.
+    defines = [f"-D{d}" for d in os.environ.get("ABOLETH_KERNEL_DEFINES", "").split(",") if d]
     return {
         "kernels": {
             "sources": kernels,
-            "compile": [_nvcc(), *_ARCH, "-lineinfo", *common, f"-I{_CSRC / 'kernels'}",
+            "compile": [_nvcc(), *_ARCH, "-lineinfo", *common, *defines, f"-I{_CSRC / 'kernels'}",
                         "-Xptxas", "-v", "-c"],
             "link": [_nvcc(), *_ARCH, "-shared", "-Xcompiler", "-fPIC"],
         },

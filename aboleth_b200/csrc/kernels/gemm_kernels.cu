@@ -10,8 +10,9 @@
 // walking the expert list.  The reference has no GEMM; the baseline for these
 // kernels is cuBLAS through torch.matmul.
 #include <algorithm>
+#include <cstdlib>
 
-#include "gemm_sm100.cuh"
+#include "gemm_pair_sm100.cuh"
 
 namespace {
 
@@ -26,12 +27,14 @@ struct PlainPolicy {
     int m, n, k, ldc;
     int tiles_n, tiles_total;
     int group_n;  // tile columns per raster group: their B panels stay resident in L2
+    int pair;     // 1: two CTAs share a tile (worker = CTA pair), 0: one CTA per tile
+    int rows;     // rows of C per tile
 
     // Tiles are visited group by group: all row tiles of `group_n` tile columns
     // before the next group, column fastest inside a group.  B panels of one group
     // (group_n * 256 * K * 2 bytes) fit the L2, A streams once per group.
     __device__ __forceinline__ bool next(int it, Tile &t) const {
-        const int idx = blockIdx.x + it * gridDim.x;
+        const int idx = (blockIdx.x >> pair) + it * (gridDim.x >> pair);
         if (idx >= tiles_total)
             return false;
         const int tiles_m = tiles_total / tiles_n;
@@ -40,22 +43,20 @@ struct PlainPolicy {
         const int width = min(group_n, tiles_n - group * group_n);
         const int local = idx - group * per_group;
         const int tm = local / width, tn = group * group_n + (local - tm * width);
-        t.a_row = tm * kPlainRows;
+        t.a_row = tm * rows;
         t.b_row = tn * BN;
         t.k_blocks = (k + BK - 1) / BK;
-        t.c_row = tm * kPlainRows;
+        t.c_row = tm * rows;
         t.c_col = tn * BN;
-        t.rows_valid = min(kPlainRows, m - tm * kPlainRows);
+        t.rows_valid = min(rows, m - tm * rows);
         t.cols_valid = min(BN, n - tn * BN);
         t.tag = 0;
         t.a_sel = 0;
         return true;
     }
     __device__ __forceinline__ bool ready(const Tile &) const { return true; }
-    __device__ __forceinline__ void store(const Tile &t, int row, int col0, const float (&v)[32], bool row_ok) const {
-        if (row_ok)
-            store_row32_bf16(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col0, v,
-                             t.cols_valid - col0);
+    __device__ __forceinline__ void store16(const Tile &t, int row, int col, const uint4 &v) const {
+        *reinterpret_cast<uint4 *>(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col) = v;
     }
     __device__ __forceinline__ void tile_done(const Tile &) const {}
     __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
@@ -107,10 +108,8 @@ struct GroupedPolicy {
         return true;
     }
     __device__ __forceinline__ bool ready(const Tile &) const { return true; }
-    __device__ __forceinline__ void store(const Tile &t, int row, int col0, const float (&v)[32], bool row_ok) const {
-        if (row_ok)
-            store_row32_bf16(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col0, v,
-                             t.cols_valid - col0);
+    __device__ __forceinline__ void store16(const Tile &t, int row, int col, const uint4 &v) const {
+        *reinterpret_cast<uint4 *>(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col) = v;
     }
     __device__ __forceinline__ void tile_done(const Tile &) const {}
     __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
@@ -125,6 +124,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     gemm_mainloop<HALVES>(policy, &map_a, &map_b, status);
 }
 
+template <int MH, typename Policy>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 Policy params, unsigned long long *status) {
+    Policy policy = params;
+    pair::gemm_mainloop_pair<MH>(policy, &map_a, &map_b, status);
+}
+
 int sm_count() {
     static int sms = 0;
     if (sms == 0) {
@@ -133,6 +140,41 @@ int sm_count() {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     }
     return sms;
+}
+
+// ABOLETH_GEMM_PAIR: 0 = single-CTA kernels (256 x 256 tile per CTA), 1 = CTA pairs with 256 x 256
+// tiles, 2 (default) = CTA pairs with 512 x 256 tiles.
+int gemm_pair_mode() {
+    static const int mode = [] {
+        const char *v = std::getenv("ABOLETH_GEMM_PAIR");
+        return v == nullptr ? 2 : std::atoi(v);
+    }();
+    return mode;
+}
+
+// How many 2-CTA clusters of `kernel` the device can hold at the same time.
+template <typename Kernel>
+int resident_pairs(Kernel kernel, unsigned smem_bytes) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(2 * sm_count());
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    if (const char *v = std::getenv("ABOLETH_GEMM_PAIR_TRACE"))
+        if (v[0] == '1')
+            fprintf(stderr, "aboleth_b200: %d CTA pairs resident (%d SMs)\n", clusters, sm_count());
+    return clusters;
 }
 
 template <typename Kernel>
@@ -162,6 +204,30 @@ int launch_grouped(const void *a, const void *w, void *c, const int *counts, con
     return ab::launch_result("grouped_gemm_bf16");
 }
 
+template <int MH>
+int launch_pair(const void *a, const void *b, PlainPolicy p, int lda, int ldb, unsigned long long *status,
+                cudaStream_t stream) {
+    using G = pair::PairGeometry<MH>;
+    CUtensorMap map_a, map_b;
+    // Each CTA of a pair loads MH * 128 rows of A and 128 rows of B per K step.
+    if (!make_map_bf16(&map_a, a, p.m, p.k, lda, G::kRowsPerCta) || !make_map_bf16(&map_b, b, p.n, p.k, ldb, BN / 2))
+        return -2;
+    static bool configured = configure(gemm_pair_kernel<MH, PlainPolicy>, G::kSmemBytes);
+    if (!configured)
+        return -3;
+    // A persistent kernel must not launch more clusters than can be resident at once: the
+    // surplus would start only after a resident one has finished all of its tiles.
+    static const int resident = resident_pairs(gemm_pair_kernel<MH, PlainPolicy>, G::kSmemBytes);
+    if (resident < 1)
+        return -3;
+    p.pair = 1;
+    p.rows = G::kTileRows;
+    p.tiles_total = ((p.m + p.rows - 1) / p.rows) * p.tiles_n;
+    const int pairs = std::min(p.tiles_total, resident);
+    gemm_pair_kernel<MH, PlainPolicy><<<2 * pairs, kThreads, G::kSmemBytes, stream>>>(map_a, map_b, p, status);
+    return ab::launch_result("gemm_bf16 (CTA pairs)");
+}
+
 }  // namespace
 
 // C[M,N] = A[M,K] * B[N,K]^T, all bf16 row-major, lda/ldb/ldc in elements.
@@ -172,6 +238,15 @@ AB_EXPORT int ab_gemm_bf16(const void *a, const void *b, void *c, int m, int n, 
         (reinterpret_cast<std::uintptr_t>(a) | reinterpret_cast<std::uintptr_t>(b) |
          reinterpret_cast<std::uintptr_t>(c)) & 15)
         return -1;
+    PlainPolicy p{static_cast<__nv_bfloat16 *>(c), m, n, k, ldc, (n + BN - 1) / BN, 0, 0, 0, kPlainRows};
+    // About 48 MiB of B per raster group.
+    const long long column_bytes = static_cast<long long>(BN) * k * 2;
+    p.group_n = static_cast<int>(std::max(1LL, std::min<long long>(p.tiles_n, (48LL << 20) / column_bytes)));
+    if (gemm_pair_mode() == 2)
+        return launch_pair<2>(a, b, p, lda, ldb, status, stream);
+    if (gemm_pair_mode() == 1)
+        return launch_pair<1>(a, b, p, lda, ldb, status, stream);
+    p.tiles_total = ((m + kPlainRows - 1) / kPlainRows) * p.tiles_n;
     CUtensorMap map_a, map_b;
     if (!make_map_bf16(&map_a, a, m, k, lda, kPlainRows) || !make_map_bf16(&map_b, b, n, k, ldb, BN))
         return -2;
@@ -179,11 +254,6 @@ AB_EXPORT int ab_gemm_bf16(const void *a, const void *b, void *c, int m, int n, 
     static bool configured = configure(gemm_tcgen05_kernel<kPlainHalves, PlainPolicy>, smem);
     if (!configured)
         return -3;
-    PlainPolicy p{static_cast<__nv_bfloat16 *>(c), m, n, k, ldc, (n + BN - 1) / BN, 0, 0};
-    p.tiles_total = ((m + kPlainRows - 1) / kPlainRows) * p.tiles_n;
-    // About 48 MiB of B per raster group.
-    const long long column_bytes = static_cast<long long>(BN) * k * 2;
-    p.group_n = static_cast<int>(std::max(1LL, std::min<long long>(p.tiles_n, (48LL << 20) / column_bytes)));
     const int grid = p.tiles_total < sm_count() ? p.tiles_total : sm_count();
     gemm_tcgen05_kernel<kPlainHalves, PlainPolicy><<<grid, kThreads, smem, stream>>>(map_a, map_b, p, status);
     return ab::launch_result("gemm_bf16");

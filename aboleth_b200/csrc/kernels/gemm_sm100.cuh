@@ -32,6 +32,10 @@ constexpr int kStages = 4;  // upper bound over configurations (barrier array si
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarps = 4;
 constexpr unsigned kTmemCols = 512;
+// Per epilogue warp: 32 rows x 128 bf16 columns, through which an accumulator is transposed so
+// that the stores to C are row-contiguous (two 256-byte row pieces per warp instruction).
+constexpr unsigned kEpilogueWarpStageBytes = 32 * 128 * 2;
+constexpr unsigned kEpilogueStageBytes = kEpilogueWarps * kEpilogueWarpStageBytes;
 
 struct SharedState {
     std::uint64_t full[kStages];
@@ -133,6 +137,53 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
+// ---- epilogue: one 128-row accumulator block, one warp's 32 rows ----------------------------
+//
+// TMEM -> registers (32 lanes x 32 columns at a time) -> bf16 -> this warp's staging in shared
+// memory (row r at r*256 bytes, its sixteen 16-byte units XOR-swizzled with r & 15, which keeps
+// both directions free of bank conflicts) -> `policy.store16`, 16 lanes per row.
+__device__ __forceinline__ uint4 pack8_bf16(const float *v) {
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]);
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]);
+    __nv_bfloat162 p3 = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 o;
+    o.x = *reinterpret_cast<std::uint32_t *>(&p0);
+    o.y = *reinterpret_cast<std::uint32_t *>(&p1);
+    o.z = *reinterpret_cast<std::uint32_t *>(&p2);
+    o.w = *reinterpret_cast<std::uint32_t *>(&p3);
+    return o;
+}
+
+template <typename Policy, typename TileT>
+__device__ __forceinline__ void drain_rows32(Policy &policy, const TileT &t, std::uint32_t taddr,
+                                             int row_base, uint4 *stage, int lane) {
+#pragma unroll 1
+    for (int g = 0; g < BN / 128; ++g) {
+        if (g * 128 >= t.cols_valid)
+            break;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            float v[32];
+            tmem_ld32(taddr + g * 128 + c * 32, v);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                stage[lane * 16 + ((c * 4 + q) ^ (lane & 15))] = pack8_bf16(v + q * 8);
+        }
+        __syncwarp();
+#pragma unroll 4
+        for (int j = 0; j < 16; ++j) {
+            const int idx = j * 32 + lane;
+            const int r = idx >> 4, unit = idx & 15;
+            const uint4 value = stage[r * 16 + (unit ^ (r & 15))];
+            const int row = row_base + r, col = g * 128 + unit * 8;
+            if (row < t.rows_valid && col < t.cols_valid)
+                policy.store16(t, row, col, value);
+        }
+        __syncwarp();
+    }
+}
+
 // ---- tile description handed out by a policy -------------------------------------------
 
 struct Tile {
@@ -150,7 +201,11 @@ struct Tile {
 // Policy concept:
 //   __device__ bool next(int iteration, Tile &t)          - tile `iteration` of this CTA, false when done
 //   __device__ bool ready(const Tile &t)                  - producer-side gate before loading A (bounded)
-//   __device__ void store(const Tile &t, int row, int col0, const float (&v)[32], bool row_ok)
+//   __device__ void store16(const Tile &t, int row, int col, const uint4 &v)
+//                                                         - eight bf16 of tile row `row` at tile columns
+//                                                           col..col+7 (col a multiple of 8); only called
+//                                                           for rows and columns that exist; consecutive
+//                                                           lanes get consecutive 16-byte pieces of a row
 //   __device__ void tile_done(const Tile &t)              - called by ONE epilogue thread after the
 //                                                           whole tile was stored (CTA-wide ordered)
 //   __device__ void finish(int thread, int nthreads, status) - epilogue warps, after the last tile
@@ -175,7 +230,7 @@ struct Geometry {
     static constexpr unsigned kBytesA = kRows * BK * 2;
     static constexpr unsigned kBytesB = BN * BK * 2;
     static constexpr unsigned kStageBytes = kBytesA + kBytesB;
-    static constexpr unsigned kSmemBytes = kStages * kStageBytes + 1024;
+    static constexpr unsigned kSmemBytes = kStages * kStageBytes + kEpilogueStageBytes + 1024;
 };
 
 template <int HALVES, typename Policy>
@@ -303,6 +358,8 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
         const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31
         const int epi_thread = (warp - 2) * 32 + lane;
         constexpr int kEpiThreads = kEpilogueWarps * 32;
+        uint4 *epi_stage = reinterpret_cast<uint4 *>(tiles + kStagesG * G::kStageBytes +
+                                                     (warp - 2) * kEpilogueWarpStageBytes);
         Tile t;
         for (int it = 0; !st.abort && policy.next(it, t); ++it) {
             const unsigned use = use_of(it);
@@ -329,18 +386,9 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
                     break;
                 }
                 tc_fence_after();
-                const int row = h * BM + quarter * 32 + lane;
-                const bool row_ok = row < t.rows_valid;
                 const std::uint32_t taddr = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) +
                                             slot * BN;
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    if (c * 32 >= t.cols_valid)
-                        break;
-                    float v[32];
-                    tmem_ld32(taddr + c * 32, v);
-                    policy.store(t, row, c * 32, v, row_ok);
-                }
+                drain_rows32(policy, t, taddr, h * BM + quarter * 32, epi_stage, lane);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0)

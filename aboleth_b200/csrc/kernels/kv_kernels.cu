@@ -73,3 +73,14 @@ AB_EXPORT int ab_kv_wait(const std::uint64_t *cells, int count, std::uint64_t ep
     kv_wait_kernel<<<(count + 127) / 128, 128, 0, stream>>>(cells, count, epoch, timeout_ns, status);
     return ab::launch_result("kv_wait");
 }
+
+// Copy-engine path for few, large runs: one asynchronous copy per run (addresses may be peer
+// mappings; unified addressing picks the direction).
+AB_EXPORT int ab_memcpy_async(void *dst, const void *src, std::uint64_t bytes, cudaStream_t stream) {
+    const cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, stream);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "aboleth_b200: asynchronous copy failed: %s\n", cudaGetErrorString(e));
+        return static_cast<int>(e);
+    }
+    return 0;
+}

@@ -86,11 +86,8 @@ struct AgGemmPolicy {
             return true;
         return aboleth::wait_signal_status(flags + t.tag, epoch) == Status::Ok;
     }
-    __device__ __forceinline__ void store(const Tile &t, int row, int col0, const float (&v)[32],
-                                          bool row_ok) const {
-        if (row_ok)
-            store_row32_bf16(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col0, v,
-                             t.cols_valid - col0);
+    __device__ __forceinline__ void store16(const Tile &t, int row, int col, const uint4 &v) const {
+        *reinterpret_cast<uint4 *>(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col) = v;
     }
     __device__ __forceinline__ void tile_done(const Tile &) const {}
     __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
@@ -178,19 +175,15 @@ struct GemmRsPolicy {
         return true;
     }
     __device__ __forceinline__ bool ready(const Tile &) const { return true; }
-    __device__ __forceinline__ void store(const Tile &t, int row, int col0, const float (&v)[32],
-                                          bool row_ok) const {
-        if (!row_ok)
-            return;
+    __device__ __forceinline__ void store16(const Tile &t, int row, int col, const uint4 &v) const {
         const int owner = t.tag >> 16;
         if (owner == rank) {  // own tile: straight into this rank's slot of the local partials
             __nv_bfloat16 *base = const_cast<__nv_bfloat16 *>(partials) +
                                   static_cast<std::size_t>(rank) * m_local * n;
-            store_row32_bf16(base + static_cast<std::size_t>(t.c_row + row) * n + t.c_col + col0, v,
-                             t.cols_valid - col0);
+            *reinterpret_cast<uint4 *>(base + static_cast<std::size_t>(t.c_row + row) * n + t.c_col + col) = v;
         } else {
-            store_row32_bf16(stage + static_cast<std::size_t>(blockIdx.x) * (kRows * BN) + row * BN + col0, v,
-                             t.cols_valid - col0);
+            *reinterpret_cast<uint4 *>(stage + static_cast<std::size_t>(blockIdx.x) * (kRows * BN) + row * BN +
+                                       col) = v;
         }
     }
     // The accumulator is free again: copy the staged tile to its owner, one 512-byte row per

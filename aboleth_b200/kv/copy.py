@@ -10,6 +10,7 @@ from ..ops._kernels import _I, _U64, _VP, call, declare, ptr, stream_ptr
 
 declare("ab_kv_push", [_VP, _VP, _I, _U64, _I, _I, _VP, _VP])
 declare("ab_kv_wait", [_VP, _I, _U64, _U64, _VP, _VP])
+declare("ab_memcpy_async", [_VP, _VP, _U64, _VP])
 
 
 def canonicalize_block_runs(src_blocks: Sequence[int], dst_blocks: Sequence[int]) -> list[tuple[int, int, int]]:
@@ -40,3 +41,8 @@ def push(batches: torch.Tensor, arrivals: torch.Tensor, count: int, epoch: int, 
 def wait_ready(cells: torch.Tensor, epoch: int, status: torch.Tensor, *, timeout_ns: int = 2_000_000_000) -> None:
     """Enqueue a bounded device-side wait for every int64 readiness cell in ``cells``."""
     call("ab_kv_wait", ptr(cells), cells.numel(), epoch, timeout_ns, ptr(status), stream_ptr())
+
+
+def cuda_memcpy_async(dst: int, src: int, nbytes: int, stream: int) -> None:
+    """One copy-engine transfer between two device addresses (either may be a peer mapping)."""
+    call("ab_memcpy_async", dst, src, nbytes, stream)

@@ -14,15 +14,16 @@ _status: dict[torch.device, torch.Tensor] = {}
 
 
 def gemm_status(device) -> torch.Tensor:
-    """int64[2] status words shared by the GEMM launches on ``device`` (0 = ok)."""
+    """int64 status words shared by the GEMM launches on ``device`` (word 0: status, 0 = ok; word 1: detail;
+    words 2..15: cycle counters the kernels fill when built with ``-DAB_GEMM_TRACE``)."""
     device = torch.device(device)
     if device not in _status:
-        _status[device] = torch.zeros(2, dtype=torch.int64, device=device)
+        _status[device] = torch.zeros(16, dtype=torch.int64, device=device)
     return _status[device]
 
 
 def check_gemm_status(device) -> None:
-    status = gemm_status(device).tolist()
+    status = gemm_status(device)[:2].tolist()
     if status[0]:
         raise RuntimeError(f"GEMM kernel gave up waiting (status {status[0]}, detail {status[1]:#x})")
 

@@ -22,8 +22,7 @@ class ExpertParallelLayer:
         self.world, self.spec = world, spec
         self.slot = NativeMoESlot.create(world, spec, tag=tag, grid=grid)
         self._host_result = torch.zeros(4, dtype=torch.int64).pin_memory()
-        self._staging_x: Optional[torch.Tensor] = None
-        self._staging_logits: Optional[torch.Tensor] = None
+        self._staging: Optional[list] = None
 
     def standin_experts(self, result: DispatchResult, y: torch.Tensor) -> None:
         """The benchmark's expert stage, ``f_e(x) = x * (1 + (e mod 7)/8)``, gate-weighted."""
@@ -48,17 +47,47 @@ class ExpertParallelLayer:
         return self.slot.combine(y, expert_offsets=offsets, out=out)
 
     def forward_from_host(self, tokens_host: torch.Tensor, logits_host: torch.Tensor,
-                          experts: Optional[ExpertFn] = None) -> torch.Tensor:
+                          experts: Optional[ExpertFn] = None, *,
+                          prefetch: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
         """Same, from pinned host tensors; returns a pinned int64[4] summary
-        (status, detail, overflow, output checksum bits) after the stream drained."""
-        if self._staging_x is None or self._staging_x.shape != tokens_host.shape:
-            dev = self.world.torch_device
-            self._staging_x = torch.empty_like(tokens_host, device=dev)
-            self._staging_logits = torch.empty_like(logits_host, device=dev)
+        (status, detail, overflow, output checksum bits).  The caller synchronises the
+        stream before reading it.
+
+        ``prefetch=(tokens, logits)`` names the inputs of the NEXT call: their host-to-device
+        copy is enqueued on a side stream before this call's kernels, so it runs under them
+        (two staging buffers alternate).  The next call must then pass those same tensors.
+        """
+        dev = self.world.torch_device
+        if self._staging is None or self._staging[0][0].shape != tokens_host.shape:
+            self._staging = [(torch.empty_like(tokens_host, device=dev),
+                              torch.empty_like(logits_host, device=dev)) for _ in range(2)]
             self._summary = torch.zeros(4, dtype=torch.int64, device=dev)
-        self._staging_x.copy_(tokens_host, non_blocking=True)
-        self._staging_logits.copy_(logits_host, non_blocking=True)
-        out = self.forward(self._staging_x, self._staging_logits, experts)
+            self._copy_stream = torch.cuda.Stream(device=dev)
+            self._copied = [torch.cuda.Event() for _ in range(2)]
+            self._consumed = [None, None]
+            self._current, self._prefetched = 0, None
+        main = torch.cuda.current_stream()
+        cur = self._current
+        x_dev, l_dev = self._staging[cur]
+        if self._prefetched == (tokens_host.data_ptr(), logits_host.data_ptr()):
+            main.wait_event(self._copied[cur])          # copied by the previous call's prefetch
+        else:
+            x_dev.copy_(tokens_host, non_blocking=True)
+            l_dev.copy_(logits_host, non_blocking=True)
+        self._prefetched = None
+        if prefetch is not None:
+            nxt = cur ^ 1
+            if self._consumed[nxt] is not None:
+                self._copy_stream.wait_event(self._consumed[nxt])  # its last reader has finished
+            with torch.cuda.stream(self._copy_stream):
+                self._staging[nxt][0].copy_(prefetch[0], non_blocking=True)
+                self._staging[nxt][1].copy_(prefetch[1], non_blocking=True)
+                self._copied[nxt].record(self._copy_stream)
+            self._prefetched = (prefetch[0].data_ptr(), prefetch[1].data_ptr())
+        out = self.forward(x_dev, l_dev, experts)
+        self._consumed[cur] = torch.cuda.Event()
+        self._consumed[cur].record(main)
+        self._current = cur ^ 1
         self._summary[:2].copy_(self.slot.status)
         self._summary[2:3].copy_(self.slot.overflow)
         self._summary[3:4].copy_(out.view(torch.int16).to(torch.int64).sum().view(1))
@@ -68,8 +97,8 @@ class ExpertParallelLayer:
     @property
     def h2d_bytes(self) -> int:
         s = self.spec
-        return 0 if self._staging_x is None else (
-            self._staging_x.numel() * 2 + self._staging_logits.numel() * 4)
+        return 0 if self._staging is None else (
+            self._staging[0][0].numel() * 2 + self._staging[0][1].numel() * 4)
 
     def check(self) -> None:
         self.slot.check()

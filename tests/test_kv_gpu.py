@@ -51,3 +51,51 @@ def test_push_pages_publish_readiness_and_lifecycle():
         kvcopy.wait_ready(kv.ready[0, 0, 0:1], 99, kv.status, timeout_ns=20_000_000)
         torch.cuda.synchronize()
         assert kv.status.tolist()[0] == 1 and kv.poll("c", source=0) == TransferState.FAILED
+
+
+def test_engine_pull_runtime_on_one_device():
+    """The decode side pulls remapped blocks of every layer; here both 'ranks' are one device, so the
+    peer table is stood in by the local addresses (the kernels only see addresses)."""
+    import aboleth_b200 as ab
+    from aboleth_b200.integrations import VLLMKVPeerRuntime
+
+    torch.cuda.set_device(0)
+
+    class _Table:
+        def __init__(self, caches):
+            self.caches = caches
+
+        def addresses(self, name):
+            return [self.caches[name[3:]].data_ptr()] * 2
+
+        def close(self):
+            pass
+
+    with ab.World(0, 1, device=0) as world:
+        world.connect_all("p2p")
+        runtime = VLLMKVPeerRuntime(rank=0, world_size=2, device=0, world=world)
+        g = torch.Generator(device="cuda").manual_seed(5)
+        layers = {f"layer{i}": torch.randint(0, 255, (64, 2, 16, 128), generator=g, device="cuda",
+                                             dtype=torch.uint8) for i in range(6)}
+        remote = {k: v.clone() for k, v in layers.items()}      # what the prefill rank holds
+        world.exchange_regions = lambda regions, tag="": _Table(remote)
+        runtime.register_kv_caches(layers, consumer_order=tuple(layers))
+        assert runtime.plan.physicalization.direct_destination
+        local_ids, remote_ids = [40, 41, 42, 7, 8, 60], [3, 4, 5, 20, 21, 9]
+        before = {k: v.clone() for k, v in layers.items()}
+        ticket = runtime.start_layered_pull_blocks(local_block_ids=local_ids, remote_block_ids=remote_ids,
+                                                   remote_rank=1)
+        assert set(ticket.layer_events) == set(layers)
+        ticket.completion.synchronize()
+        runtime.check()
+        assert runtime.last_run_count == 3 and "generated_p2p" in runtime.last_physicalization
+        for name, cache in layers.items():
+            assert torch.equal(cache[local_ids], remote[name][remote_ids])
+            untouched = [b for b in range(64) if b not in local_ids]
+            assert torch.equal(cache[untouched], before[name][untouched])
+        us = runtime.pull_blocks(local_block_ids=[0, 1], remote_block_ids=[62, 63], remote_rank=1)
+        assert us > 0 and torch.equal(layers["layer3"][0:2], remote["layer3"][62:64])
+        with pytest.raises(ValueError, match="outside the registered cache"):
+            runtime.start_pull_blocks(local_block_ids=[64], remote_block_ids=[0], remote_rank=1)
+        with pytest.raises(ValueError, match="other rank"):
+            runtime.start_pull_blocks(local_block_ids=[1], remote_block_ids=[0], remote_rank=0)
