@@ -9,6 +9,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import json
+import os
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Optional, Union
@@ -98,9 +99,27 @@ def compile_program(program: Union[str, ProgramBuilder], options: Optional[Compi
         backend=opts.backend, rank=opts.rank, world_size=opts.world_size)
     result = _call(_lib().ab200_spec_compile, text, opts.to_native())
     name = text.split()[1] if text.startswith("program") else "program"
-    return CompiledProgram(name=name, ir=result["ir"], cuda=result.get("cuda"),
-                           facts=result.get("facts", {}), passes=result.get("passes", {}),
-                           key=pipeline_key(text, opts), options=opts, source=text)
+    compiled = CompiledProgram(name=name, ir=result["ir"], cuda=result.get("cuda"),
+                               facts=result.get("facts", {}), passes=result.get("passes", {}),
+                               key=pipeline_key(text, opts), options=opts, source=text)
+    _dump(compiled)
+    return compiled
+
+
+def _dump(compiled: CompiledProgram) -> None:
+    """``ABOLETH_DUMP_SCHEDULED_IR=<dir>`` writes, per compilation, the input program, the IR after the
+    last pass that ran, the emitted CUDA C++ and the facts (the reference dumps its post-schedule IR the
+    same way, python/aboleth/compiler.py:399-404)."""
+    root = os.environ.get("ABOLETH_DUMP_SCHEDULED_IR")
+    if not root:
+        return
+    out = Path(root) / f"{compiled.name}-{compiled.options.backend}-{compiled.key[:12]}"
+    out.mkdir(parents=True, exist_ok=True)
+    (out / "program.txt").write_text(compiled.source)
+    (out / "scheduled.ir").write_text(compiled.ir)
+    if compiled.cuda is not None:
+        (out / "kernel.cu").write_text(compiled.cuda)
+    (out / "facts.json").write_text(json.dumps({"facts": compiled.facts, "passes": compiled.passes}, indent=1))
 
 
 def run_planner(kind: str, request: str) -> dict:

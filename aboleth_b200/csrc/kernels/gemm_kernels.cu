@@ -22,13 +22,15 @@ constexpr int kPlainHalves = 2;
 constexpr int kPlainRows = BM * kPlainHalves;
 
 struct PlainPolicy {
-    static constexpr bool kBackground = false, kDrainedHook = false;
+    static constexpr bool kBackground = false, kDrainedHook = false, kScaled = true;
     __nv_bfloat16 *c;
     int m, n, k, ldc;
     int tiles_n, tiles_total;
     int group_n;  // tile columns per raster group: their B panels stay resident in L2
     int pair;     // 1: two CTAs share a tile (worker = CTA pair), 0: one CTA per tile
     int rows;     // rows of C per tile
+    int bk;       // elements of K per stage (64 for bf16, 128 for e4m3)
+    float alpha;  // factor applied to the accumulator before rounding
 
     // Tiles are visited group by group: all row tiles of `group_n` tile columns
     // before the next group, column fastest inside a group.  B panels of one group
@@ -45,7 +47,7 @@ struct PlainPolicy {
         const int tm = local / width, tn = group * group_n + (local - tm * width);
         t.a_row = tm * rows;
         t.b_row = tn * BN;
-        t.k_blocks = (k + BK - 1) / BK;
+        t.k_blocks = (k + bk - 1) / bk;
         t.c_row = tm * rows;
         t.c_col = tn * BN;
         t.rows_valid = min(rows, m - tm * rows);
@@ -65,7 +67,7 @@ struct PlainPolicy {
 template <int HALVES>
 struct GroupedPolicy {
     static constexpr int kRows = BM * HALVES;
-    static constexpr bool kBackground = false, kDrainedHook = false;
+    static constexpr bool kBackground = false, kDrainedHook = false, kScaled = false;
     __nv_bfloat16 *c;
     const int *counts, *offsets;
     int experts, n, k, ldc, tiles_n;
@@ -124,12 +126,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     gemm_mainloop<HALVES>(policy, &map_a, &map_b, status);
 }
 
-template <int MH, typename Policy>
+template <int MH, typename Op, typename Policy>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  Policy params, unsigned long long *status) {
     Policy policy = params;
-    pair::gemm_mainloop_pair<MH>(policy, &map_a, &map_b, status);
+    pair::gemm_mainloop_pair<MH, Op>(policy, &map_a, &map_b, status);
 }
 
 int sm_count() {
@@ -204,28 +206,32 @@ int launch_grouped(const void *a, const void *w, void *c, const int *counts, con
     return ab::launch_result("grouped_gemm_bf16");
 }
 
-template <int MH>
+template <int MH, typename Op>
 int launch_pair(const void *a, const void *b, PlainPolicy p, int lda, int ldb, unsigned long long *status,
                 cudaStream_t stream) {
     using G = pair::PairGeometry<MH>;
     CUtensorMap map_a, map_b;
     // Each CTA of a pair loads MH * 128 rows of A and 128 rows of B per K step.
-    if (!make_map_bf16(&map_a, a, p.m, p.k, lda, G::kRowsPerCta) || !make_map_bf16(&map_b, b, p.n, p.k, ldb, BN / 2))
+    const bool mapped = Op::kBK == 64
+        ? make_map_bf16(&map_a, a, p.m, p.k, lda, G::kRowsPerCta) && make_map_bf16(&map_b, b, p.n, p.k, ldb, BN / 2)
+        : make_map_e4m3(&map_a, a, p.m, p.k, lda, G::kRowsPerCta) && make_map_e4m3(&map_b, b, p.n, p.k, ldb, BN / 2);
+    if (!mapped)
         return -2;
-    static bool configured = configure(gemm_pair_kernel<MH, PlainPolicy>, G::kSmemBytes);
+    static bool configured = configure(gemm_pair_kernel<MH, Op, PlainPolicy>, G::kSmemBytes);
     if (!configured)
         return -3;
     // A persistent kernel must not launch more clusters than can be resident at once: the
     // surplus would start only after a resident one has finished all of its tiles.
-    static const int resident = resident_pairs(gemm_pair_kernel<MH, PlainPolicy>, G::kSmemBytes);
+    static const int resident = resident_pairs(gemm_pair_kernel<MH, Op, PlainPolicy>, G::kSmemBytes);
     if (resident < 1)
         return -3;
     p.pair = 1;
     p.rows = G::kTileRows;
+    p.bk = Op::kBK;
     p.tiles_total = ((p.m + p.rows - 1) / p.rows) * p.tiles_n;
     const int pairs = std::min(p.tiles_total, resident);
-    gemm_pair_kernel<MH, PlainPolicy><<<2 * pairs, kThreads, G::kSmemBytes, stream>>>(map_a, map_b, p, status);
-    return ab::launch_result("gemm_bf16 (CTA pairs)");
+    gemm_pair_kernel<MH, Op, PlainPolicy><<<2 * pairs, kThreads, G::kSmemBytes, stream>>>(map_a, map_b, p, status);
+    return ab::launch_result(Op::kBK == 64 ? "gemm_bf16 (CTA pairs)" : "gemm_e4m3 (CTA pairs)");
 }
 
 }  // namespace
@@ -238,14 +244,14 @@ AB_EXPORT int ab_gemm_bf16(const void *a, const void *b, void *c, int m, int n, 
         (reinterpret_cast<std::uintptr_t>(a) | reinterpret_cast<std::uintptr_t>(b) |
          reinterpret_cast<std::uintptr_t>(c)) & 15)
         return -1;
-    PlainPolicy p{static_cast<__nv_bfloat16 *>(c), m, n, k, ldc, (n + BN - 1) / BN, 0, 0, 0, kPlainRows};
+    PlainPolicy p{static_cast<__nv_bfloat16 *>(c), m, n, k, ldc, (n + BN - 1) / BN, 0, 0, 0, kPlainRows, BK, 1.0f};
     // About 48 MiB of B per raster group.
     const long long column_bytes = static_cast<long long>(BN) * k * 2;
     p.group_n = static_cast<int>(std::max(1LL, std::min<long long>(p.tiles_n, (48LL << 20) / column_bytes)));
     if (gemm_pair_mode() == 2)
-        return launch_pair<2>(a, b, p, lda, ldb, status, stream);
+        return launch_pair<2, OpBf16>(a, b, p, lda, ldb, status, stream);
     if (gemm_pair_mode() == 1)
-        return launch_pair<1>(a, b, p, lda, ldb, status, stream);
+        return launch_pair<1, OpBf16>(a, b, p, lda, ldb, status, stream);
     p.tiles_total = ((m + kPlainRows - 1) / kPlainRows) * p.tiles_n;
     CUtensorMap map_a, map_b;
     if (!make_map_bf16(&map_a, a, m, k, lda, kPlainRows) || !make_map_bf16(&map_b, b, n, k, ldb, BN))
@@ -257,6 +263,22 @@ AB_EXPORT int ab_gemm_bf16(const void *a, const void *b, void *c, int m, int n, 
     const int grid = p.tiles_total < sm_count() ? p.tiles_total : sm_count();
     gemm_tcgen05_kernel<kPlainHalves, PlainPolicy><<<grid, kThreads, smem, stream>>>(map_a, map_b, p, status);
     return ab::launch_result("gemm_bf16");
+}
+
+// C[M,N] (bf16) = alpha * A[M,K] * B[N,K]^T with A and B in e4m3 (one byte per element), row-major,
+// lda/ldb in elements (= bytes), ldc in bf16 elements.  K, lda and ldb must be multiples of 16.
+// `alpha` carries the product of the two per-tensor scales.  CTA-pair main loop, kind::f8f6f4.
+AB_EXPORT int ab_gemm_e4m3(const void *a, const void *b, void *c, int m, int n, int k, int lda, int ldb,
+                           int ldc, float alpha, unsigned long long *status, cudaStream_t stream) {
+    if (m < 1 || n < 1 || k < 1 || k % 16 || lda % 16 || ldb % 16 || ldc % 8 ||
+        (reinterpret_cast<std::uintptr_t>(a) | reinterpret_cast<std::uintptr_t>(b) |
+         reinterpret_cast<std::uintptr_t>(c)) & 15)
+        return -1;
+    PlainPolicy p{static_cast<__nv_bfloat16 *>(c), m, n, k, ldc, (n + BN - 1) / BN, 0, 0, 0, kPlainRows,
+                  OpE4m3::kBK, alpha};
+    const long long column_bytes = static_cast<long long>(BN) * k;
+    p.group_n = static_cast<int>(std::max(1LL, std::min<long long>(p.tiles_n, (48LL << 20) / column_bytes)));
+    return launch_pair<2, OpE4m3>(a, b, p, lda, ldb, status, stream);
 }
 
 // Grouped GEMM over `experts` problems that share N and K.  a: [total_rows, K],

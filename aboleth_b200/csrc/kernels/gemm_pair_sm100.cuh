@@ -86,15 +86,24 @@ __device__ __forceinline__ void pair_tmem_dealloc(std::uint32_t base, unsigned c
                  : "memory");
 }
 
-__device__ __forceinline__ void pair_umma_bf16(std::uint32_t d_tmem, std::uint64_t a_desc,
-                                               std::uint64_t b_desc, std::uint32_t idesc,
-                                               std::uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
+template <typename Op>
+__device__ __forceinline__ void pair_umma(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
+                                          std::uint32_t idesc, std::uint32_t accumulate) {
+    if constexpr (Op::kBK == 64) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
 }
 
 // One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair once
@@ -159,9 +168,9 @@ __device__ __forceinline__ bool pair_wait(std::uint64_t *bar, unsigned parity) {
 
 // Policy concept: the one of gemm_mainloop, with tiles of PairGeometry<MH>::kTileRows rows.
 // `policy.next` must hand the SAME tile to both CTAs of a pair (index tiles by blockIdx.x / 2
-// out of gridDim.x / 2).  Rows passed to `store` are rows of the tile.  map_a boxes are
-// (MH * 128) x 64, map_b boxes 128 x 64.
-template <int MH, typename Policy>
+// out of gridDim.x / 2).  Rows passed to `store16` are rows of the tile.  map_a boxes are
+// (MH * 128) rows x 128 bytes, map_b boxes 128 rows x 128 bytes; `Op` selects bf16 or e4m3 operands.
+template <int MH, typename Op, typename Policy>
 __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtensorMap *map_a,
                                                    const CUtensorMap *map_b, unsigned long long *status,
                                                    const CUtensorMap *map_a_alt = nullptr) {
@@ -238,9 +247,9 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
                     // (A cluster-scope release arrive per K step cost ~1400 cycles and starved the pipe.)
                     if (leader)
                         mbar_expect_tx(&st.full[stage], 2 * G::kStageBytes);
-                    pair_tma_load_2d(sa, t.a_sel ? map_a_alt : map_a, kb * BK,
+                    pair_tma_load_2d(sa, t.a_sel ? map_a_alt : map_a, kb * Op::kBK,
                                      t.a_row + static_cast<int>(rank) * G::kRowsPerCta, full_in_leader);
-                    pair_tma_load_2d(sa + G::kBytesA, map_b, kb * BK, t.b_row + static_cast<int>(rank) * (BN / 2),
+                    pair_tma_load_2d(sa + G::kBytesA, map_b, kb * Op::kBK, t.b_row + static_cast<int>(rank) * (BN / 2),
                                      full_in_leader);
                     if (++stage == kStagesG) {
                         stage = 0;
@@ -258,7 +267,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader only) ----------------
         if (lane == 0 && leader) {
-            constexpr std::uint32_t idesc = idesc_bf16(2 * BM, BN);
+            constexpr std::uint32_t idesc = Op::idesc(2 * BM, BN);
             int stage = 0;
             unsigned phase = 0;
             Tile t;
@@ -305,9 +314,8 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
                         const std::uint32_t d = tmem_base + slot * BN;
                         const std::uint64_t da = smem_desc_sw128(sa + h * (BM * BK * 2));
 #pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k)
-                            pair_umma_bf16(d, da + (k * UMMA_K * 2 >> 4), db + (k * UMMA_K * 2 >> 4), idesc,
-                                           (kb | k) != 0);
+                        for (int k = 0; k < 4; ++k)  // four MMAs per stage, 32 bytes of K each
+                            pair_umma<Op>(d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
                     }
                     pair_umma_commit(&st.empty[stage]);  // frees the stage in both CTAs
                     if (++stage == kStagesG) {

@@ -122,6 +122,25 @@ __device__ __forceinline__ std::uint64_t smem_desc_sw128(std::uint32_t smem_addr
            (static_cast<std::uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// Instruction descriptor, kind::f8f6f4 with e4m3 A and B (format code 0), fp32 accumulate, K-major.
+__host__ __device__ constexpr std::uint32_t idesc_e4m3(int m, int n) {
+    return (1u << 4) | (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(m >> 4) << 24);
+}
+
+// Operand kinds of the main loops.  Both fill a 128-byte swizzle row per K step (64 bf16 or
+// 128 e4m3) and advance the shared-memory descriptors by 32 bytes per MMA, so the loops differ
+// only in the K extent of a step, the instruction kind and its descriptor.
+struct OpBf16 {
+    static constexpr int kBK = 64;  // elements of K per stage
+    static constexpr const char *kName = "bf16";
+    __host__ __device__ static constexpr std::uint32_t idesc(int m, int n) { return idesc_bf16(m, n); }
+};
+struct OpE4m3 {
+    static constexpr int kBK = 128;
+    static constexpr const char *kName = "e4m3";
+    __host__ __device__ static constexpr std::uint32_t idesc(int m, int n) { return idesc_e4m3(m, n); }
+};
+
 // ---- TMA (tiled, no multicast) --------------------------------------------------------
 
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y,
@@ -166,6 +185,12 @@ __device__ __forceinline__ void drain_rows32(Policy &policy, const TileT &t, std
         for (int c = 0; c < 4; ++c) {
             float v[32];
             tmem_ld32(taddr + g * 128 + c * 32, v);
+            if constexpr (Policy::kScaled) {
+                const float alpha = policy.alpha;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    v[i] *= alpha;
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q)
                 stage[lane * 16 + ((c * 4 + q) ^ (lane & 15))] = pack8_bf16(v + q * 8);
@@ -209,6 +234,8 @@ struct Tile {
 //   __device__ void tile_done(const Tile &t)              - called by ONE epilogue thread after the
 //                                                           whole tile was stored (CTA-wide ordered)
 //   __device__ void finish(int thread, int nthreads, status) - epilogue warps, after the last tile
+//   static constexpr bool kScaled      - if true: the accumulator is multiplied by `float alpha` (a policy
+//                                        member) before it is rounded to bf16
 //   static constexpr bool kBackground  - if true: bool background(int thread, int nthreads) is called by
 //                                        all 128 epilogue threads together while they would otherwise
 //                                        wait for an accumulator, and after the last tile until it
@@ -461,6 +488,24 @@ inline bool make_map_bf16(CUtensorMap *map, const void *base, std::uint64_t rows
                            strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS)
+        fprintf(stderr, "aboleth_b200: cuTensorMapEncodeTiled failed with CUresult %d\n", static_cast<int>(rc));
+    return rc == CUDA_SUCCESS;
+}
+
+// e4m3 [rows, cols] row-major with `ld` bytes between rows; box = box_rows x 128 columns.
+inline bool make_map_e4m3(CUtensorMap *map, const void *base, std::uint64_t rows, std::uint64_t cols,
+                          std::uint64_t ld, unsigned box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr)
+        return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld};
+    const cuuint32_t box[2] = {128u, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box,
+                           elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS)
         fprintf(stderr, "aboleth_b200: cuTensorMapEncodeTiled failed with CUresult %d\n", static_cast<int>(rc));
     return rc == CUDA_SUCCESS;

@@ -43,7 +43,7 @@ constexpr int kPhaseConsume = 2;  // AG: GEMM.        RS: reduction of owned til
 // ---- all-gather -> GEMM -----------------------------------------------------------------
 
 struct AgGemmPolicy {
-    static constexpr bool kBackground = true, kDrainedHook = false;
+    static constexpr bool kBackground = true, kDrainedHook = false, kScaled = false;
     __nv_bfloat16 *c;
     const std::uint64_t *flags;       // local: [world * chunks] epochs
     unsigned long long *status;
@@ -140,7 +140,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_staging,
 // ---- GEMM -> reduce-scatter -----------------------------------------------------------------
 
 struct GemmRsPolicy {
-    static constexpr bool kBackground = false, kDrainedHook = true;
+    static constexpr bool kBackground = false, kDrainedHook = true, kScaled = false;
     const std::uint64_t *peer_partials;  // [world] address of each rank's partial buffer
     const std::uint64_t *peer_flags;     // [world] address of each rank's flag array
     const __nv_bfloat16 *partials;       // local: [world, m_local, n]

@@ -1,14 +1,17 @@
-"""bf16 GEMMs on tcgen05 / TMEM / TMA (kernels: csrc/kernels/gemm_kernels.cu)."""
+"""bf16 and e4m3 GEMMs on tcgen05 / TMEM / TMA (kernels: csrc/kernels/gemm_kernels.cu)."""
 from __future__ import annotations
 
 from typing import Optional
 
 import torch
 
+import ctypes
+
 from ._kernels import _I, _VP, call, declare, ptr, stream_ptr
 
 declare("ab_gemm_bf16", [_VP, _VP, _VP] + [_I] * 6 + [_VP, _VP])
 declare("ab_grouped_gemm_bf16", [_VP] * 5 + [_I] * 4 + [_VP, _VP])
+declare("ab_gemm_e4m3", [_VP, _VP, _VP] + [_I] * 6 + [ctypes.c_float, _VP, _VP])
 
 _status: dict[torch.device, torch.Tensor] = {}
 
@@ -17,6 +20,8 @@ def gemm_status(device) -> torch.Tensor:
     """int64 status words shared by the GEMM launches on ``device`` (word 0: status, 0 = ok; word 1: detail;
     words 2..15: cycle counters the kernels fill when built with ``-DAB_GEMM_TRACE``)."""
     device = torch.device(device)
+    if device.type == "cuda" and device.index is None:  # "cuda" means the current device
+        device = torch.device("cuda", torch.cuda.current_device())
     if device not in _status:
         _status[device] = torch.zeros(16, dtype=torch.int64, device=device)
     return _status[device]
@@ -39,6 +44,23 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
     assert out.stride(1) == 1 and out.shape == (m, n)
     call("ab_gemm_bf16", ptr(a), ptr(b), ptr(out), m, n, k, a.stride(0), b.stride(0), out.stride(0),
          ptr(gemm_status(a.device)), stream_ptr())
+    return out
+
+
+def gemm_e4m3(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *,
+              alpha: float = 1.0) -> torch.Tensor:
+    """``out[M, N] = alpha * a[M, K] @ b[N, K].T`` for ``torch.float8_e4m3fn`` operands (per-tensor
+    scaling: pass the product of the two dequantisation scales as ``alpha``); bf16 output, fp32
+    accumulation in tensor memory, ``kind::f8f6f4`` on CTA pairs."""
+    assert a.dtype == b.dtype == torch.float8_e4m3fn and a.is_cuda and a.dim() == b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1 and a.shape[1] == b.shape[1]
+    m, k = a.shape
+    n = b.shape[0]
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (m, n)
+    call("ab_gemm_e4m3", ptr(a), ptr(b), ptr(out), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+         float(alpha), ptr(gemm_status(a.device)), stream_ptr())
     return out
 
 

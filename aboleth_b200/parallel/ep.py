@@ -12,6 +12,7 @@ import torch
 
 from ..moe import DispatchResult, MoESpec, NativeMoESlot
 from ..ops import standin_expert
+from ..utils import host_range
 from ..world import World
 
 ExpertFn = Callable[[DispatchResult, torch.Tensor], Optional[torch.Tensor]]
@@ -41,10 +42,13 @@ class ExpertParallelLayer:
         it wrote ``y`` in expert-contiguous order and wants the combine kernel to apply
         the gates.
         """
-        result = self.slot.dispatch(tokens, logits=logits, renormalize=renormalize)
+        with host_range("ep.dispatch"):
+            result = self.slot.dispatch(tokens, logits=logits, renormalize=renormalize)
         y = self.slot.expert_output
-        offsets = (experts or self.standin_experts)(result, y)
-        return self.slot.combine(y, expert_offsets=offsets, out=out)
+        with host_range("ep.experts"):
+            offsets = (experts or self.standin_experts)(result, y)
+        with host_range("ep.combine"):
+            return self.slot.combine(y, expert_offsets=offsets, out=out)
 
     def forward_from_host(self, tokens_host: torch.Tensor, logits_host: torch.Tensor,
                           experts: Optional[ExpertFn] = None, *,

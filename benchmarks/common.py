@@ -42,18 +42,7 @@ def teardown(world, distributed: bool) -> None:
         dist.destroy_process_group()
 
 
-def provenance() -> dict:
-    def git(*args):
-        try:
-            return subprocess.run(["git", *args], capture_output=True, text=True, timeout=5,
-                                  cwd=Path(__file__).resolve().parent.parent).stdout.strip()
-        except Exception:  # noqa: BLE001
-            return ""
-    return {"time": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()), "host": platform.node(),
-            "git": git("rev-parse", "--short", "HEAD"), "torch": torch.__version__,
-            "cuda": torch.version.cuda, "gpu": torch.cuda.get_device_name(0),
-            "nccl": ".".join(map(str, torch.cuda.nccl.version())),
-            "env": {k: v for k, v in os.environ.items() if k.startswith(("ABOLETH_", "NCCL_"))}}
+from aboleth_b200.utils import provenance  # noqa: E402,F401
 
 
 def emit(record: dict, out: str | None) -> None:

@@ -4,6 +4,7 @@
     python benchmarks/gemm_bench.py                      # dense C = A @ B^T over the TP / FFN shapes
     python benchmarks/gemm_bench.py --shape 4096 4096 4096 --steps 3 --no-library   # small case for a profiler
     python benchmarks/gemm_bench.py --grouped            # grouped (per-expert) GEMM, Mixtral expert shapes
+    python benchmarks/gemm_bench.py --fp8                # e4m3 operands, against torch._scaled_mm (cuBLASLt)
 
 Each timed launch is preceded by an L2 flush; times are medians of CUDA-event brackets.
 Fractions are of the measured cuBLAS bf16 burst throughput recorded for this pool.
@@ -43,6 +44,7 @@ def main() -> int:
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--grouped", action="store_true")
+    ap.add_argument("--fp8", action="store_true", help="e4m3 operands (per-tensor scale), against torch._scaled_mm")
     ap.add_argument("--no-library", action="store_true", help="skip the cuBLAS arm (profiler runs)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
@@ -73,6 +75,26 @@ def main() -> int:
                 row.update(cublas_loop_us=ms2 * 1e3, cublas_loop_tflops=flops / ms2 / 1e9)
             rows.append(row)
             del x, w, y
+    elif args.fp8:
+        from aboleth_b200.ops import gemm_e4m3
+
+        one = torch.ones((), device="cuda")
+        for m, n, k in ([tuple(args.shape)] if args.shape else DENSE):
+            a = torch.randn(m, k, device="cuda").to(torch.float8_e4m3fn)
+            b = (torch.randn(n, k, device="cuda")).to(torch.float8_e4m3fn)
+            c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            ms = timed(lambda: gemm_e4m3(a, b, c), flush, args.steps)
+            check_gemm_status("cuda:0")
+            flops = 2.0 * m * n * k
+            row = {"m": m, "n": n, "k": k, "dtype": "e4m3", "ours_us": ms * 1e3, "ours_tflops": flops / ms / 1e9}
+            if not args.no_library:
+                ref = torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+                row["rel_err_vs_cublaslt"] = ((c.float() - ref.float()).norm() / ref.float().norm()).item()
+                ms2 = timed(lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one,
+                                                     out_dtype=torch.bfloat16), flush, args.steps)
+                row.update(cublaslt_us=ms2 * 1e3, cublaslt_tflops=flops / ms2 / 1e9)
+            rows.append(row)
+            del a, b, c
     else:
         for m, n, k in ([tuple(args.shape)] if args.shape else DENSE):
             a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
@@ -90,7 +112,8 @@ def main() -> int:
                 row.update(cublas_us=ms2 * 1e3, cublas_tflops=flops / ms2 / 1e9)
             rows.append(row)
             del a, b, c
-    emit({"bench": "grouped gemm bf16" if args.grouped else "gemm bf16", "n_gpus": 1, "dtype": "bf16",
+    emit({"bench": "grouped gemm bf16" if args.grouped else "gemm e4m3" if args.fp8 else "gemm bf16", "n_gpus": 1,
+          "dtype": "e4m3" if args.fp8 else "bf16",
           "l2": "flushed before every timed launch", "peak_bf16_tflops_measured": peak, "rows": rows},
          args.out)
     return 0

@@ -227,3 +227,28 @@ def test_emitted_kernels_compile_for_sm_100a(tmp_path, monkeypatch):
         assert art.manifest()["n_regs"] > 0
     again = build_artifact(_compile(programs.stream("fused", 8, 1024), "rdma"))
     assert again.cubin == art.cubin  # cache hit under the same key
+
+
+def test_scheduled_ir_dump_and_utils(tmp_path, monkeypatch):
+    """ABOLETH_DUMP_SCHEDULED_IR writes program, scheduled IR, emitted source and facts per compilation."""
+    import json
+
+    from aboleth_b200.compiler import compilation, compile_program
+    from aboleth_b200.compiler.programs import alltoall
+    from aboleth_b200.utils import host_range, provenance, ranges_enabled
+
+    monkeypatch.setenv("ABOLETH_DUMP_SCHEDULED_IR", str(tmp_path))
+    with compilation("proxy", rank=1, world_size=4, queue_capacity=64):
+        compiled = compile_program(alltoall())
+    (folder,) = list(tmp_path.iterdir())
+    assert folder.name.startswith("alltoall-proxy-")
+    assert {p.name for p in folder.iterdir()} == {"program.txt", "scheduled.ir", "kernel.cu", "facts.json"}
+    assert json.loads((folder / "facts.json").read_text())["facts"] == compiled.facts
+    assert (folder / "kernel.cu").read_text() == compiled.cuda
+    record = provenance()
+    assert {"time", "host", "git", "torch", "env"} <= set(record)
+    assert "ABOLETH_DUMP_SCHEDULED_IR" in record["env"]
+    monkeypatch.delenv("ABOLETH_NVTX", raising=False)
+    assert not ranges_enabled()
+    with host_range("noop"):
+        pass

@@ -78,3 +78,25 @@ def test_grouped_gemm_large_experts_use_wide_tiles():
             want = a[lo:lo + cnt].float() @ w[e].float().t()
             assert _rel_err(out[lo:lo + cnt], want) < 5e-3
         assert bool((out[lo + cnt:lo + int(padded[e])] == 7.0).all())
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 256, 256), (1000, 520, 384), (4096, 4096, 2048)])
+def test_gemm_e4m3_matches_fp32(m, n, k):
+    """e4m3 x e4m3 products are exact in fp32, so only the accumulation order and the final bf16
+    rounding separate the kernel from an fp32 matmul of the dequantised operands."""
+    from aboleth_b200.ops import check_gemm_status, gemm_e4m3
+
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g, device="cuda").to(torch.float8_e4m3fn)
+    b = torch.randn(n, k, generator=g, device="cuda").to(torch.float8_e4m3fn)
+    out = gemm_e4m3(a, b, alpha=0.5)
+    torch.cuda.synchronize()
+    check_gemm_status(a.device)
+    want = 0.5 * (a.float() @ b.float().t())
+    assert _rel_err(out, want) < 5e-3
+    # small integers: every partial sum is exact
+    ai = torch.randint(-2, 3, (m, k), generator=g, device="cuda").float().to(torch.float8_e4m3fn)
+    bi = torch.randint(-2, 3, (n, k), generator=g, device="cuda").float().to(torch.float8_e4m3fn)
+    got = gemm_e4m3(ai, bi).float()
+    torch.cuda.synchronize()
+    assert torch.equal(got, (ai.float() @ bi.float().t()).to(torch.bfloat16).float())
