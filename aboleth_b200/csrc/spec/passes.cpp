@@ -68,7 +68,7 @@ bool contains_if(const Block &ops, const std::function<bool(const Op &)> &pred) 
 // Pure ops, bindings, loads and stores, and structured control flow made of
 // those may be crossed; other chains' commands too.
 bool crossable(const Op &op) {
-    static const std::set<std::string> plain = {"endpoint", "local", "remote", "let", "load",
+    static const std::set<std::string> plain = {"endpoint", "local", "remote", "remote_at", "let", "load",
                                                 "store", "tensor_store", "compute"};
     if (plain.count(op.kind) || is_command(op) || is_posted(op))
         return true;

@@ -178,6 +178,73 @@ class MixtralEP:
         x = _rms_norm(x[:, -1], self.final_norm, c.rms_eps)
         return (x @ self.lm_head.t()).float()
 
+    # -- decode step as a CUDA graph ------------------------------------------------------------
+    def _attention_static(self, x: torch.Tensor, layer: dict, index: int) -> torch.Tensor:
+        """One-token attention whose position is a DEVICE scalar (``self._g_pos``): the new key and
+        value are scattered into the cache with ``index_copy_`` and the scores run over the whole
+        cache under a mask, so the launch sequence does not depend on the position."""
+        c = self.config
+        b = x.shape[0]
+        positions = self._g_pos.expand(b, 1)
+        qkv = x @ layer["wqkv"].t()
+        q, k, v = qkv.split([c.heads * c.head_dim, c.kv_heads * c.head_dim, c.kv_heads * c.head_dim], -1)
+        q = _rope(q.view(b, 1, c.heads, c.head_dim).transpose(1, 2), positions, c.rope_theta)
+        k = _rope(k.view(b, 1, c.kv_heads, c.head_dim).transpose(1, 2), positions, c.rope_theta)
+        v = v.view(b, 1, c.kv_heads, c.head_dim).transpose(1, 2)
+        self.kv[index, 0, :b].index_copy_(2, self._g_pos, k)
+        self.kv[index, 1, :b].index_copy_(2, self._g_pos, v)
+        keys, values = self.kv[index, 0, :b], self.kv[index, 1, :b]          # [b, kv, max_seq, d]
+        group = c.heads // c.kv_heads
+        qg = q.reshape(b, c.kv_heads, group, c.head_dim)
+        scores = torch.matmul(qg, keys.transpose(-1, -2)).float() * (c.head_dim ** -0.5)
+        scores = scores.masked_fill(self._g_steps > self._g_pos, float("-inf"))
+        out = torch.matmul(torch.softmax(scores, -1).to(values.dtype), values)
+        return out.reshape(b, 1, c.heads * c.head_dim) @ layer["wo"].t()
+
+    def _decode_static(self) -> torch.Tensor:
+        c = self.config
+        b = self._g_tokens.shape[0]
+        x = self.embed[self._g_tokens]
+        for index, layer in enumerate(self.layers):
+            x = x + self._attention_static(_rms_norm(x, layer["attn_norm"], c.rms_eps), layer, index)
+            h = _rms_norm(x, layer["ffn_norm"], c.rms_eps).reshape(b, c.hidden).contiguous()
+            x = x + self.moe_layer(h, layer).view(b, 1, c.hidden)
+        x = _rms_norm(x[:, -1], self.final_norm, c.rms_eps)
+        return (x @ self.lm_head.t()).float()
+
+    @torch.no_grad()
+    def enable_decode_graph(self, batch: Optional[int] = None) -> None:
+        """Capture one decode step (all layers: attention, router, fused dispatch, grouped expert
+        GEMMs, fused combine) into a CUDA graph.  Every rank must call this at the same point: the
+        warm-up and the capture run the MoE collectives.  Afterwards :meth:`decode` replays the graph;
+        the token ids and the position travel through device tensors."""
+        b = self.max_batch if batch is None else int(batch)
+        self._g_tokens = torch.zeros(b, 1, dtype=torch.int64, device=self.device)
+        self._g_pos = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self._g_steps = torch.arange(self.config.max_seq, device=self.device)
+        self.moe.set_wave_bound(self.max_batch)  # decode: every rank has at most max_batch tokens
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):  # first-use initialisation of the launchers must not be captured
+                self._decode_static()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._g_logits = self._decode_static()
+        self.moe.set_wave_bound(None)
+
+    @torch.no_grad()
+    def decode(self, token_ids: torch.Tensor, position: int) -> torch.Tensor:
+        """One decode step for ``token_ids`` int64 ``[B, 1]`` at ``position``; logits ``[B, vocab]``."""
+        if getattr(self, "_graph", None) is None or token_ids.shape != self._g_tokens.shape:
+            return self.forward(token_ids, position)
+        self._g_tokens.copy_(token_ids)
+        self._g_pos.fill_(position)
+        self._graph.replay()
+        return self._g_logits
+
     @torch.no_grad()
     def generate(self, prompts: torch.Tensor, new_tokens: int) -> torch.Tensor:
         """Greedy decoding: prefill the prompts, then ``new_tokens`` single-token steps."""
@@ -187,7 +254,7 @@ class MixtralEP:
         for i in range(new_tokens):
             out[:, i] = nxt
             if i + 1 < new_tokens:
-                nxt = self.forward(nxt[:, None], s + i).argmax(-1)
+                nxt = self.decode(nxt[:, None], s + i).argmax(-1)
         return out
 
     def check(self) -> None:

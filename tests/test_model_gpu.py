@@ -39,3 +39,29 @@ def test_moe_layer_and_generate_tiny():
         step = model.forward(prompts[:, 15:16].contiguous(), 15)
         torch.cuda.synchronize()
         assert ((full - step).norm() / full.norm()).item() < 3e-2
+
+
+def test_decode_graph_replays_the_eager_step():
+    import aboleth_b200 as ab
+    from aboleth_b200.models import MixtralConfig, MixtralEP
+
+    cfg = MixtralConfig(layers=2, hidden=256, experts=4, top_k=2, ffn=512, heads=4, kv_heads=2,
+                        vocab=128, max_seq=64)
+    with ab.World(0, 1, device=0) as world:
+        world.connect_all("p2p")
+        model = MixtralEP(cfg, world, max_batch=4, max_prompt=16, seed=3)
+        g = torch.Generator(device="cuda").manual_seed(2)
+        prompts = torch.randint(0, 128, (4, 16), generator=g, device="cuda")
+        with torch.no_grad():
+            eager = model.generate(prompts, 6)
+            model.enable_decode_graph()
+            # the capture ran decode steps at position 0 of the cache: prefill again, then replay
+            graphed = model.generate(prompts, 6)
+            first = model.forward(prompts, 0).argmax(-1)
+            a = model.forward(first[:, None], 16).clone()
+            model.forward(prompts, 0)
+            b = model.decode(first[:, None], 16).clone()
+        torch.cuda.synchronize()
+        model.check()
+        assert torch.equal(eager, graphed)
+        assert ((a - b).norm() / a.norm()).item() < 2e-2

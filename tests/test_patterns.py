@@ -188,3 +188,44 @@ def test_endpoint_mesh_on_cpu_runtimes():
     finally:
         for r in runtimes.values():
             r.close()
+
+
+def test_tier1_operations_as_programs():
+    """What each Tier-1 call costs per transport: one reservation / doorbell per call on the ring,
+    one release store and no fence per signalled chain on peer memory."""
+    from aboleth_b200.tier1 import PROGRAMS, tier1_facts, tier1_program
+
+    assert {"put", "put_inline24", "signal", "put_signal", "put_many_8", "put_many_32_signal",
+            "put_many_8_flush", "quiet", "wait_signal"} <= set(PROGRAMS)
+    p2p, ring = tier1_facts("p2p"), tier1_facts("proxy")
+    chain = p2p["put_many_8_signal"]
+    assert (chain["batches"], chain["commands"], chain["strong_signals"], chain["system_fences"]) == (1, 9, 1, 0)
+    assert p2p["put_many_32_flush"]["system_fences"] == 1 and p2p["put"]["system_fences"] == 1
+    assert p2p["quiet"]["completion_waits"] == 0                      # vacuous on peer memory
+    assert p2p["put_inline24"]["inline_puts"] == 1
+    queued = ring["put_many_8_signal"]
+    assert (queued["batches"], queued["reservations"], queued["commands"], queued["completion_waits"]) == (1, 1, 9, 1)
+    assert ring["quiet"]["completion_waits"] == 1
+    assert "unsupported" in ring["put_inline24"] and ring["put_inline64"]["inline_puts"] == 1
+    with pytest.raises(KeyError, match="unknown Tier-1 operation"):
+        tier1_program("put_many_7")
+
+
+def test_planned_fragments_compile_per_transport():
+    from aboleth_b200 import planned_phase as pp
+
+    with ab.compilation("p2p"):
+        put = pp.compile_planned_put_artifact(max_bytes=4096, cta_exclusive=True)
+        drain = pp.compile_planned_drain_artifact()
+    assert [n for n, _ in put.parameters] == [n for n, _ in pp.PUT_SLOTS]
+    assert "__device__ __forceinline__ void phase_put_fragment(" in put.source and put.facts["completion"] == "vacuous"
+    assert drain.facts["completion_waits"] == 0
+    with ab.compilation("proxy", queue_capacity=64):
+        put = pp.compile_planned_put_artifact(max_bytes=4096)
+        drain = pp.compile_planned_drain_artifact()
+        fence = pp.compile_planned_fence_artifact(artifact=ab.Artifact.INLINE_FRAGMENT)
+        publish = pp.compile_planned_publish_artifact()
+    assert put.facts["reservations"] == 1 and drain.facts["completion_waits"] == 1
+    assert fence.artifact == "inline_fragment" and [n for n, _ in publish.parameters] == ["endpoint", "only_if_advanced"]
+    with pytest.raises(ValueError, match="max_bytes must be positive"):
+        pp.planned_put_program(max_bytes=0)
