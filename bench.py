@@ -31,7 +31,7 @@ METRIC = "EP dispatch+combine tokens/s (DeepSeek-V3 shape, fp8 1x128 dispatch, b
 
 def reference_arm(args) -> int:
     """The reference cannot run here: say why in one line and exit 0."""
-    reason = ("installed from /root/reference into baseline/_ref (pure-Python wheel), but "
+    reason = ("the reference installs into baseline/_ref (pure-Python wheel), but "
               "`import aboleth` raises ImportError: compiler plugin libAbolethPlugin.so is not "
               "built; building it needs third_party/triton (empty submodule) built with "
               "TRITON_EXT_ENABLED=1 plus a pinned LLVM download, impossible offline")

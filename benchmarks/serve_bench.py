@@ -24,6 +24,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--generate", type=int, default=256)
+    ap.add_argument("--graph", action="store_true", help="replay the decode step as a CUDA graph")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     ab, world, distributed = setup()
@@ -40,10 +41,12 @@ def main() -> int:
     prompts = torch.randint(0, cfg.vocab, (local_batch, args.prompt), generator=g,
                             device=world.torch_device)
     with torch.no_grad():
+        if args.graph:
+            model.enable_decode_graph()
         # Warm-up at the timed shapes: library kernel selection for a new shape costs far more than a step.
         nxt = model.forward(prompts, 0).argmax(-1)
         for i in range(3):
-            nxt = model.forward(nxt[:, None], args.prompt + i).argmax(-1)
+            nxt = model.decode(nxt[:, None], args.prompt + i).argmax(-1)
         torch.cuda.synchronize()
         model.check()
         sync_ranks(distributed)
@@ -52,7 +55,7 @@ def main() -> int:
         nxt = model.forward(prompts, 0).argmax(-1)
         ev[1].record()
         for i in range(args.generate - 1):
-            nxt = model.forward(nxt[:, None], args.prompt + i).argmax(-1)
+            nxt = model.decode(nxt[:, None], args.prompt + i).argmax(-1)
         ev[2].record()
         torch.cuda.synchronize()
     model.check()
@@ -62,7 +65,8 @@ def main() -> int:
     emit({"bench": "mixtral-style EP serving", "n_gpus": w, "dtype": "bf16",
           "config": {"layers": args.layers, "hidden": cfg.hidden, "experts": cfg.experts, "top_k": cfg.top_k,
                      "ffn": cfg.ffn, "heads": cfg.heads, "kv_heads": cfg.kv_heads, "batch": args.batch,
-                     "prompt": args.prompt, "generate": args.generate, "parallelism": f"ep{w} dp{w} tp1"},
+                     "prompt": args.prompt, "generate": args.generate, "parallelism": f"ep{w} dp{w} tp1",
+                     "decode": "cuda graph" if args.graph else "eager"},
           "request_latency_ms": total, "time_to_first_token_ms": ttft,
           "decode_ms_per_token": decode / max(args.generate - 1, 1),
           "generated_tokens_per_s": args.batch * args.generate / (total * 1e-3),

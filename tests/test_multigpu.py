@@ -114,3 +114,66 @@ def test_peer_that_never_sends_times_out_with_status_1():
     assert kind == "ok", value
     _, status = value
     assert status[0] == 1 and status[1] == 0x1000 + 1  # dispatch wait on rank 1 gave up
+
+
+def _kv_pull_rank(rank, world_size):
+    """Rank 0 plays the prefill engine (its caches hold the data), rank 1 pulls remapped blocks."""
+    ab, boot, world = _setup(rank, world_size)
+    from aboleth_b200.integrations import VLLMKVPeerRuntime
+
+    runtime = VLLMKVPeerRuntime(rank=rank, world_size=2, device=rank, world=world)
+    g = torch.Generator(device="cuda").manual_seed(7)  # same seed: rank 1 knows what rank 0 holds
+    reference = {f"layer{i}": torch.randint(0, 255, (32, 2, 8, 128), generator=g, device="cuda",
+                                            dtype=torch.uint8) for i in range(5)}
+    caches = {k: (v.clone() if rank == 0 else torch.zeros_like(v)) for k, v in reference.items()}
+    runtime.register_kv_caches(caches, consumer_order=tuple(caches))
+    boot.barrier("registered")
+    local_ids, remote_ids = [20, 21, 22, 3], [4, 5, 6, 30]
+    ok = True
+    if rank == 1:
+        ticket = runtime.start_layered_pull_blocks(local_block_ids=local_ids, remote_block_ids=remote_ids,
+                                                   remote_rank=0)
+        ticket.completion.synchronize()
+        runtime.check()
+        for name, cache in caches.items():
+            ok = ok and bool(torch.equal(cache[local_ids], reference[name][remote_ids]))
+            rest = [b for b in range(32) if b not in local_ids]
+            ok = ok and int(cache[rest].max().item()) == 0
+    boot.barrier("pulled")   # rank 0 keeps its caches mapped until rank 1 has read them
+    out = (ok, runtime.last_run_count, runtime.last_physicalization)
+    runtime.close()
+    world.close()
+    return out
+
+
+def test_kv_pull_between_two_engines():
+    results = run_ranks(_kv_pull_rank, 2, timeout=180)
+    for rank in range(2):
+        kind, value = results[rank]
+        assert kind == "ok", value
+    ok, runs, physical = results[1][1]
+    assert ok and runs == 2 and physical.endswith("generated_p2p")
+
+
+def _probe_rank(rank, world_size):
+    ab, boot, world = _setup(rank, world_size)
+    from aboleth_b200.endpoint_probe import calibrate
+
+    profile, result = calibrate(world, fit_bytes=(65536, 1 << 20, 4 << 20), holdout_bytes=(8 << 20,),
+                                lanes=(1, 4, 16), warps=(1, 8), trials=2, tag="probe")
+    out = (None if profile is None else (profile.max_lanes, profile.sender_warps), result.get("reason"),
+           result["world"]["senders"] if "world" in result else 0)
+    boot.barrier("probed")
+    world.close()
+    return out
+
+
+def test_endpoint_probe_two_gpus():
+    results = run_ranks(_probe_rank, 2, timeout=180)
+    for rank in range(2):
+        kind, value = results[rank]
+        assert kind == "ok", value
+        profile, reason, senders = value
+        assert reason is None and senders == 2
+        assert profile is None or profile[0] in (4, 16)
+    assert results[0][1] == results[1][1]  # the fit uses world rates: every rank derives the same profile
