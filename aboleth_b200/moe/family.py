@@ -52,9 +52,13 @@ class NativeMoEFamily:
 
     def local_counts(self, expert_counts: torch.Tensor) -> torch.Tensor:
         """Counts of the experts this rank owns, in local expert order."""
-        any_slot = next(iter(self._slots.values()))
-        mine = [e for e, o in enumerate(any_slot.owners_list) if o == self.world.rank]
-        return expert_counts[torch.tensor(mine, device=expert_counts.device)]
+        index = getattr(self, "_local_experts", None)
+        if index is None or index.device != expert_counts.device:
+            any_slot = next(iter(self._slots.values()))
+            mine = [e for e, o in enumerate(any_slot.owners_list) if o == self.world.rank]
+            # Built once: a host-to-device copy per layer is both slow and illegal under graph capture.
+            index = self._local_experts = torch.tensor(mine, device=expert_counts.device)
+        return expert_counts[index]
 
     def manifest(self) -> dict:
         return {"variants": [v.capacity for v in self.family.variants], "slots": self.slots,
