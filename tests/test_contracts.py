@@ -1,0 +1,107 @@
+"""Execution contracts, KV lifecycle and profiles, record programs, compiled phases (CPU only)."""
+import pytest
+
+import aboleth_b200 as ab
+from aboleth_b200.execution import (CapacityContract, ExecutionContract, ExecutionFallback, PaddingSemantics,
+                                    RankControl, RuntimeGuard, compile_execution_plan)
+
+
+def _contract(**over):
+    args = dict(capacity=CapacityContract(64, True, PaddingSemantics.DEAD, True),
+                rank_control=RankControl.LOCKSTEP,
+                guards=(RuntimeGuard("count_within_capacity", ExecutionFallback.ERROR),
+                        RuntimeGuard("contiguous", ExecutionFallback.EAGER)),
+                fallback=ExecutionFallback.EXACT_AGREEMENT)
+    args.update(over)
+    return ExecutionContract(**args)
+
+
+def test_fixed_capacity_needs_every_proof():
+    contract = _contract()
+    assert contract.fixed_capacity_legal
+    decision = contract.resolve(10)
+    assert (decision.mode, decision.capacity) == ("fixed_capacity", 64)
+    # any missing proof falls back, with the live item count
+    for change in (dict(rank_control=RankControl.DYNAMIC),
+                   dict(capacity=CapacityContract(64, True, PaddingSemantics.PRESERVED, True)),
+                   dict(capacity=CapacityContract(64, False, PaddingSemantics.DEAD, True)),
+                   dict(capacity=CapacityContract(64, True, PaddingSemantics.DEAD, False))):
+        weaker = _contract(**change)
+        assert not weaker.fixed_capacity_legal
+        assert weaker.resolve(10).mode == "exact_agreement" and weaker.resolve(10).capacity == 10
+    assert contract.resolve(10, graph_stable_addresses=False).mode == "exact_agreement"
+    assert contract.resolve(10, failed_guards=("contiguous",)).mode == "eager"
+    with pytest.raises(RuntimeError, match="guard 'count_within_capacity' failed"):
+        contract.resolve(10, failed_guards=("count_within_capacity",))
+    with pytest.raises(ValueError, match="outside the contract"):
+        contract.resolve(65)
+    with pytest.raises(RuntimeError, match="forbids a fallback"):
+        _contract(rank_control=RankControl.DYNAMIC, fallback=ExecutionFallback.ERROR).resolve(1)
+    with pytest.raises(ValueError, match="must be unique"):
+        _contract(guards=(RuntimeGuard("a", ExecutionFallback.EAGER), RuntimeGuard("a", ExecutionFallback.EAGER)))
+    plan = compile_execution_plan(contract, (8, 256, 64))
+    assert plan["variants"] == (8, 64) and plan["mode"] == "fixed_capacity"
+    described = contract.describe()
+    assert described["capacity"]["padding"] == "dead" and described["fixed_capacity_legal"]
+    compiled = ab.CompiledExecutionPlan((type("P", (), {"name": "a"})(),), contract)
+    assert compiled.phase("a").name == "a" and compiled.resolve(3).mode == "fixed_capacity"
+    with pytest.raises(ValueError, match="at least one phase"):
+        ab.CompiledExecutionPlan((), contract)
+
+
+def test_kv_lifecycle_and_profiles():
+    from aboleth_b200.kv import TransferState
+    from aboleth_b200.kv.lifecycle import TransferLedger
+
+    ledger = TransferLedger(2)
+    a, b = ledger.admit("a", 4), ledger.admit("b", 4)
+    assert (a.slot, a.epoch, b.slot, b.epoch) == (0, 1, 1, 2) and ledger.admit("c", 4) is None
+    with pytest.raises(RuntimeError, match="already in flight"):
+        ledger.admit("a", 4)
+    a.move(TransferState.TRANSFERRING)
+    a.move(TransferState.READY)
+    with pytest.raises(RuntimeError, match="not allowed"):
+        a.move(TransferState.FAILED)          # a ready transfer can only be consumed or aborted
+    a.move(TransferState.CONSUMED)
+    assert a.terminal and a.history == [TransferState.ADMITTED, TransferState.TRANSFERRING, TransferState.READY]
+    c = ledger.admit("c", 4)
+    assert c.slot == 0 and c.epoch == 3       # the freed slot, a fresh epoch
+    b.move(TransferState.FAILED, error="status 1")
+    assert b.error == "status 1" and [r.request_id for r in ledger.live()] == ["c"]
+    assert ledger.admit("a", 4).slot == 1     # a finished request id may come back
+
+    assert ab.select_kv_target_profile("NVIDIA B200").name == "b200-nvlink"
+    assert ab.select_kv_target_profile("NVIDIA H200").name == "h200-nvlink"
+    assert ab.select_kv_target_profile("something else") is ab.GENERIC_KV_TARGET_PROFILE
+    tuned = ab.select_kv_target_profile("NVIDIA H200", overrides=ab.KVRuntimeOverrides(copy_workers=4))
+    assert tuned.copy_workers == 4 and tuned.copy_engine_threshold == ab.H200_NVLINK_KV_TARGET_PROFILE.copy_engine_threshold
+    assert ab.GENERIC_KV_TARGET_PROFILE.copy_engine_threshold is None
+
+
+def test_record_programs_and_compiled_phase():
+    from aboleth_b200.compiler import compile_program
+    from aboleth_b200.records import await_records, send_records
+
+    send = send_records(rank=1, peer_extent=4, capacity=64, width_bytes=512, meta_width_words=12, lanes=4,
+                        row_quotient=16, row_remainder=0, reuse=8, ready_stride=8)
+    with ab.compilation("proxy", rank=1, world_size=4, queue_capacity=64):
+        queued = compile_program(send)
+        waiting = compile_program(await_records(ready_stride=8, lanes_per_program=4))
+    # payload + metadata + count + signal travel under one reservation; dead padding is trimmed
+    assert queued.facts["reservations"] == 1 and queued.facts["strong_signals"] == 1
+    assert queued.facts["trimmed_puts"] >= 2 and queued.facts["completion"] == "poll"
+    assert waiting.facts["flag_reads"] and waiting.facts["commands"] == 0
+    with ab.compilation("p2p", rank=1, world_size=4):
+        direct = compile_program(send)
+    assert direct.facts["reservations"] == 0 and direct.facts["fences"].count("st.release.sys") == 1
+
+    pattern = ab.build_moe_pattern(ab.MoEPatternSpec(max_tokens=64, hidden=512, top_k=4, num_ranks=4)).compile()
+    plan = pattern.compile_plan(ab.PhaseResources(peers={0: "p2p", 2: "p2p", 3: "p2p"}))
+    with ab.compilation("p2p", rank=1, world_size=4):
+        phase = ab.compile_phase(plan, "return.values", rank=1, capacity=64, width_bytes=1024)
+    manifest = phase.manifest()
+    assert manifest["strategy"] == "parallel_copy" and manifest["publication"] == "fused_kernel"
+    assert manifest["sender_facts"]["strong_signals"] == 1 and manifest["completion_interval"] == 0
+    assert phase.binding.sender_threads % 32 == 0 and phase.binding.sender_grid[0] >= 1
+    with pytest.raises(KeyError):
+        ab.compile_phase(plan, "no.such.phase", rank=1, capacity=64, width_bytes=1024)
