@@ -290,7 +290,7 @@ class TcpStoreBootstrap:
         needs the store, so rank 0 may drop it.
         """
         sequence = self._sequence
-        self.all_gather(tag, b"\x01")
+        self.all_gather(tag, b"")
         if self.rank != 0:
             self._store.set(self._key(sequence, tag + ".read", self.rank), b"\x01")
             return

@@ -61,3 +61,30 @@ def test_device_library_package(tmp_path, monkeypatch):
     subprocess.run(["nvcc", *lib.nvcc_flags(), "-c", str(src), "-o", str(tmp_path / "client.o")], check=True)
     special = ab.device_library(transports=["p2p"], specialize="p2p")
     assert "ABOLETH_TIER1_SPECIALIZED" in special.header.read_text()
+
+
+def test_device_library_archive_links_into_a_client(tmp_path, monkeypatch):
+    """The static archive exports aboleth_tier1_<op>_<transport>; a client that only declares the
+    symbols compiles with -rdc=true and links against it (device link included)."""
+    import json
+    import subprocess
+
+    monkeypatch.setenv("ABOLETH_CACHE_DIR", str(tmp_path))
+    lib = ab.device_library(transports=["p2p", "rdma"], archive=True)
+    manifest = json.loads(lib.manifest.read_text())
+    assert lib.archive is not None and lib.archive.exists() and not manifest["header_only"]
+    assert "aboleth_tier1_put_signal_p2p" in manifest["symbols"] and "aboleth_tier1_quiet_rdma" in manifest["symbols"]
+    assert ab.device_library(transports=["p2p", "rdma"], archive=True).archive == lib.archive  # cache hit
+    src = tmp_path / "client.cu"
+    src.write_text('extern "C" __device__ unsigned long long aboleth_tier1_put_signal_p2p(unsigned long long, unsigned, '
+                   'unsigned long long, unsigned, unsigned long long, unsigned, unsigned, unsigned long long, unsigned, '
+                   'unsigned long long);\n'
+                   'extern "C" __device__ unsigned long long aboleth_tier1_wait_signal(unsigned long long, '
+                   'unsigned long long, unsigned long long);\n'
+                   '__global__ void k(unsigned long long eps, unsigned long long dst, unsigned long long src, '
+                   'unsigned long long flag, unsigned long long *status) {\n'
+                   '  status[0] = aboleth_tier1_put_signal_p2p(eps, 1, dst, 0, src, 0, 256, flag, 0, 1);\n'
+                   '  status[1] = aboleth_tier1_wait_signal(flag, 1, 1000000);\n}\n'
+                   'int main() { return 0; }\n')
+    subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-rdc=true", str(src),
+                    f"-L{lib.archive.parent}", "-laboleth_tier1", "-o", str(tmp_path / "client")], check=True)
