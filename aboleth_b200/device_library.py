@@ -29,7 +29,7 @@ import subprocess
 from . import abi
 from .compiler.driver import include_dir
 
-OPERATIONS = ("open", "put", "put_warp", "put_block", "put_inline", "signal", "signal_block",
+OPERATIONS = ("open", "put", "put_warp", "put_block", "put_inline", "put_inline_small", "signal", "signal_block",
               "put_signal", "put_many", "put_many_signal", "put_many_flush", "quiet", "wait_signal",
               "wait_signal_status")
 SERVED = ("p2p", "proxy")
@@ -161,6 +161,11 @@ def generate_device_library(out: Path, *, transports: Sequence[str] = ("p2p",),
                  % (specialize, abi.KIND_BITS[specialize]))
         header.write_text(header.read_text().replace("#define ABOLETH_TIER1_ABI 2",
                                                      "#define ABOLETH_TIER1_ABI 2" + guard))
+    lanes = int(options.get("endpoints_per_peer", 1))
+    if lanes != 1:
+        header.write_text(header.read_text().replace(
+            "#ifndef ABOLETH_TIER1_ENDPOINTS_PER_PEER",
+            f"#define ABOLETH_TIER1_ENDPOINTS_PER_PEER {lanes}\n#ifndef ABOLETH_TIER1_ENDPOINTS_PER_PEER", 1))
     built = _build_archive(out, inc, list(transports)) if archive else None
     manifest = out / "manifest.json"
     manifest.write_text(json.dumps({

@@ -47,6 +47,11 @@
 #define ABOLETH_TIER1_HAS_PROXY 1
 #define ABOLETH_TIER1_HAS_RDMA 0
 #define ABOLETH_TIER1_BOUNDED_WAITS 1
+#define ABOLETH_TIER1_SMALL_INLINE 1
+#ifndef ABOLETH_TIER1_ENDPOINTS_PER_PEER
+// Endpoints (lanes) per peer in the handle table: entry peer * N + blockIdx.x % N is used.
+#define ABOLETH_TIER1_ENDPOINTS_PER_PEER 1
+#endif
 
 namespace aboleth {
 
@@ -182,8 +187,13 @@ __device__ __forceinline__ void copy_strided(
 
 namespace aboleth {
 
+inline constexpr int kEndpointsPerPeer = ABOLETH_TIER1_ENDPOINTS_PER_PEER;
+
+// The handle table is peer-major with kEndpointsPerPeer entries per peer; a CTA uses the
+// entry its block index selects, so CTAs spread over a peer's endpoints.
 __device__ __forceinline__ PeerRef open(const DeviceContext &ctx, int peer) {
-    const std::uint64_t raw = ctx.endpoints[peer];
+    const int slot = kEndpointsPerPeer == 1 ? 0 : static_cast<int>(blockIdx.x % kEndpointsPerPeer);
+    const std::uint64_t raw = ctx.endpoints[peer * kEndpointsPerPeer + slot];
     return PeerRef{raw & ~abi::kKindMask, static_cast<std::uint32_t>(raw & abi::kKindMask)};
 }
 
@@ -257,6 +267,22 @@ __device__ __forceinline__ void put_inline(
 __device__ __forceinline__ void put_inline(
     const DeviceContext &ctx, int peer, const RemoteRegion &dst, std::uint64_t value) {
     put_inline(ctx, open(ctx, peer), dst, value);
+}
+
+// The low `bytes` (1, 2, 3, 4 or 8) of `value`, little endian.  Peer memory takes any of
+// them as plain stores; the ring carries only whole 8-byte values.
+__device__ __forceinline__ void put_inline_small(
+    const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
+    std::uint64_t value, int bytes) {
+    if (bytes == 8) {
+        put_inline(ctx, ref, dst, value);
+    } else if (ref.kind == abi::kKindP2P && bytes >= 1 && bytes <= 4) {
+        volatile std::uint8_t *out = reinterpret_cast<volatile std::uint8_t *>(dst.address);
+        for (int i = 0; i < bytes; ++i)
+            out[i] = static_cast<std::uint8_t>(value >> (8 * i));
+    } else {
+        detail::record(ctx, Status::Malformed);
+    }
 }
 
 // Strong publication: a peer that observes `epoch` in `flag` observes every
@@ -401,6 +427,32 @@ __device__ __forceinline__ void signal_block(const RemoteRegion &flag, std::uint
         detail::fence_acq_rel_sys();
         detail::st_relaxed_sys(reinterpret_cast<std::uint64_t *>(flag.address), epoch);
     }
+}
+
+// ---- compile-time peer forms ---------------------------------------------------------------
+
+template <int Peer>
+__device__ __forceinline__ void put(const DeviceContext &ctx, const RemoteRegion &dst,
+                                    const LocalRegion &src, std::uint32_t bytes) {
+    put(ctx, open(ctx, Peer), dst, src, bytes);
+}
+
+template <int Peer>
+__device__ __forceinline__ void signal(const DeviceContext &ctx, const RemoteRegion &flag,
+                                       std::uint64_t epoch) {
+    signal(ctx, open(ctx, Peer), flag, epoch);
+}
+
+template <int Peer>
+__device__ __forceinline__ void put_signal(const DeviceContext &ctx, const RemoteRegion &dst,
+                                           const LocalRegion &src, std::uint32_t bytes,
+                                           const RemoteRegion &flag, std::uint64_t epoch) {
+    put_signal(ctx, open(ctx, Peer), dst, src, bytes, flag, epoch);
+}
+
+template <int Peer>
+__device__ __forceinline__ void quiet(const DeviceContext &ctx) {
+    quiet(ctx, open(ctx, Peer));
 }
 
 }  // namespace aboleth

@@ -88,3 +88,23 @@ def test_device_library_archive_links_into_a_client(tmp_path, monkeypatch):
                    'int main() { return 0; }\n')
     subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-rdc=true", str(src),
                     f"-L{lib.archive.parent}", "-laboleth_tier1", "-o", str(tmp_path / "client")], check=True)
+
+
+def test_device_library_lanes_and_compile_time_peers(tmp_path, monkeypatch):
+    import subprocess
+
+    monkeypatch.setenv("ABOLETH_CACHE_DIR", str(tmp_path))
+    lib = ab.device_library(transports=["p2p"], endpoints_per_peer=4)
+    text = lib.header.read_text()
+    assert "#define ABOLETH_TIER1_ENDPOINTS_PER_PEER 4" in text and "#define ABOLETH_TIER1_SMALL_INLINE 1" in text
+    src = tmp_path / "lanes.cu"
+    src.write_text('#include "aboleth/device.cuh"\n'
+                   'static_assert(aboleth::kEndpointsPerPeer == 4, "lanes");\n'
+                   '__global__ void k(const std::uint64_t* eps, unsigned long long* st, unsigned long long dst, '
+                   'unsigned long long src, unsigned long long flag) {\n'
+                   '  aboleth::DeviceContext ctx{eps, nullptr, st};\n'
+                   '  aboleth::put_signal<1>(ctx, aboleth::RemoteRegion{dst, 0}, aboleth::LocalRegion{src, 0}, 64, '
+                   'aboleth::RemoteRegion{flag, 0}, 1);\n'
+                   '  aboleth::put_inline_small(ctx, aboleth::open(ctx, 2), aboleth::RemoteRegion{dst, 0}, 0x010203, 3);\n'
+                   '  aboleth::quiet<1>(ctx);\n}\n')
+    subprocess.run(["nvcc", *lib.nvcc_flags(), "-c", str(src), "-o", str(tmp_path / "lanes.o")], check=True)
