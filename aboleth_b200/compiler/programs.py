@@ -95,3 +95,48 @@ def fp8_dispatch(chunks: int = 4, rows: int = 16, cols: int = 128, slots: int = 
     s = b.signal(e, b.remote("flag_table", peer, offset="RANK*8"), epoch="iteration + 1", after=count)
     b.wait(s, iteration="iteration", reuse=slots)
     return b
+
+
+_LADDER_ARGS = [("payload", "ptr"), ("endpoints", "table"), ("remote_table", "table"), ("my_flag", "ptr"),
+                ("rounds", "i64"), ("epoch0", "i64")]
+
+
+def pingpong(nbytes: int, *, chain: int = 1, leader: bool = True, threads: int = 32) -> ProgramBuilder:
+    """Latency ladder (reference: experiments/bench/tier2.py ``_pingpong``): per round the leader
+    sends ``chain`` puts closed by ONE signal and waits for the echo; the follower waits first and
+    echoes.  Payload at offset 0 of the peer's region, its flag right after the payload."""
+    b = ProgramBuilder("pingpong_leader" if leader else "pingpong_follower", args=_LADDER_ARGS,
+                       threads=threads, grid=1)
+    e = b.endpoint("endpoints", 1)
+    piece = max(nbytes // chain, 8)
+    with b.for_range("round", 0, "rounds"):
+        if not leader:
+            b.wait_signal("my_flag", "epoch0 + round + 1")
+        previous = None
+        for c in range(chain):
+            previous = b.put(e, b.remote("remote_table", 1, offset=c * piece), b.local(f"payload + {c * piece}"),
+                             bytes=piece, after=previous)
+        s = b.signal(e, b.remote("remote_table", 1, offset=chain * piece), epoch="epoch0 + round + 1",
+                     after=previous)
+        b.wait(s)
+        if leader:
+            b.wait_signal("my_flag", "epoch0 + round + 1")
+    return b
+
+
+def windowed(nbytes: int, *, window: int = 16, reuse: int = 4, threads: int = 32) -> ProgramBuilder:
+    """Bandwidth ladder (``_windowed``): ``window`` independent puts per round and one completion
+    for the round (planned over ``reuse`` buffers), a drain at the end.  One program per CTA; CTA
+    ``pid`` owns the span ``pid * window * nbytes`` of both buffers."""
+    b = ProgramBuilder("windowed", args=[("payload", "ptr"), ("endpoints", "table"), ("remote_table", "table"),
+                                         ("rounds", "i64")], threads=threads)
+    e = b.endpoint("endpoints", 1)
+    span = window * nbytes
+    with b.for_range("round", 0, "rounds"):
+        previous = None
+        for k in range(window):
+            previous = b.put(e, b.remote("remote_table", 1, offset=f"pid*{span} + {k * nbytes}"),
+                             b.local(f"payload + pid*{span} + {k * nbytes}"), bytes=nbytes, after=previous)
+        b.wait(previous, iteration="round", reuse=reuse, final="round == rounds - 1")
+    b.drain(e)
+    return b

@@ -252,3 +252,20 @@ def test_scheduled_ir_dump_and_utils(tmp_path, monkeypatch):
     assert not ranges_enabled()
     with host_range("noop"):
         pass
+
+
+def test_ladder_programs_batch_as_the_benchmarks_expect():
+    from aboleth_b200.compiler import compilation, compile_program
+    from aboleth_b200.compiler.programs import pingpong, windowed
+
+    with compilation("p2p", rank=0, world_size=2):
+        lead = compile_program(pingpong(4096, chain=4)).facts
+        echo = compile_program(pingpong(4096, leader=False)).facts
+        window = compile_program(windowed(65536, window=8)).facts
+    # a chain is one batch closed by one release; a window without a signal ends in one system fence
+    assert (lead["batches"], lead["commands"], lead["strong_signals"], lead["system_fences"]) == (1, 5, 1, 0)
+    assert echo["flag_reads"] == lead["flag_reads"] == ["acquire.sys>=(epoch0 + round + 1)"]
+    assert (window["batches"], window["commands"], window["system_fences"]) == (1, 8, 1)
+    with compilation("proxy", rank=0, world_size=2, queue_capacity=64):
+        queued = compile_program(windowed(65536, window=8)).facts
+    assert queued["reservations"] == 1 and queued["completion"] == "poll"
