@@ -25,7 +25,20 @@ CASES = {
     "stream_chains_4": lambda: programs.stream("chains", 4, 256),
     "stream_pipelined_4": lambda: programs.stream("pipelined", 4, 256, reuse=4),
     "fp8_dispatch": lambda: programs.fp8_dispatch(),
+    "pingpong_leader_chain4": lambda: programs.pingpong(4096, chain=4),
+    "pingpong_follower": lambda: programs.pingpong(4096, leader=False),
+    "windowed_8": lambda: programs.windowed(65536, window=8),
+    "tier1_put_many_8_signal": lambda: _tier1("put_many_8_signal"),
+    "tier1_put_inline64": lambda: _tier1("put_inline64"),
 }
+
+
+def _tier1(name: str):
+    from ..tier1 import tier1_program
+
+    return tier1_program(name)
+
+
 BACKENDS = ("p2p", "proxy", "rdma", "efa")
 VARIANTS = {"default": "default", "none": "none"}
 
