@@ -23,6 +23,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--flush", action="store_true")
+    ap.add_argument("--out", default=None)
     args = ap.parse_args()
 
     import torch
@@ -39,7 +40,11 @@ def main() -> int:
             layer.step()
         layer.check()
         out = layer.phase_times(steps=args.steps, distributed=False, flush=args.flush)
-        print(json.dumps({k: out[k] for k in ("dispatch_us", "combine_us", "tokens_per_rank")}))
+        line = json.dumps({k: out[k] for k in ("dispatch_us", "combine_us", "tokens_per_rank")})
+        print(line)
+        if args.out:
+            Path(args.out).parent.mkdir(parents=True, exist_ok=True)
+            Path(args.out).write_text(line + "\n")
     return 0
 
 
