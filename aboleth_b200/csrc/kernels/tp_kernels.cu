@@ -18,9 +18,10 @@
 //   rank's partial buffer with row-contiguous 512-byte peer stores and publish it with
 //   one release flag.  (Storing straight from the TMEM registers - 16 bytes per lane,
 //   every lane another row - reached a quarter of the link rate and stalled the
-//   accumulator.)  Tiles owned by peers are computed first.  When a CTA has no GEMM
-//   tiles left its epilogue warps reduce owned tiles: wait for the tile's flag from
-//   every rank, sum the partials in fp32.
+//   accumulator.)  Every rank computes tile j of all owners before tile j + 1 of any, so
+//   an owner's tile is complete on all ranks early; whenever the epilogue warps would wait
+//   for an accumulator they reduce the next owned tile whose partials have all arrived
+//   (fp32 sum), and after the last GEMM tile they finish the rest with bounded waits.
 //
 // No reference kernel exists for these; the baseline is NCCL all-gather /
 // reduce-scatter around a library GEMM.
@@ -140,7 +141,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_staging,
 // ---- GEMM -> reduce-scatter -----------------------------------------------------------------
 
 struct GemmRsPolicy {
-    static constexpr bool kBackground = false, kDrainedHook = true, kScaled = false;
+    static constexpr bool kBackground = true, kDrainedHook = true, kScaled = false;
     const std::uint64_t *peer_partials;  // [world] address of each rank's partial buffer
     const std::uint64_t *peer_flags;     // [world] address of each rank's flag array
     const __nv_bfloat16 *partials;       // local: [world, m_local, n]
@@ -151,6 +152,7 @@ struct GemmRsPolicy {
     std::uint64_t epoch;
     int rank, world, m_local, n, k, phases;
     int tiles_n, chunks;                 // tiles per owner = chunks * tiles_n
+    int reduced;                         // owned tiles this CTA has reduced so far (same in every thread)
 
     __device__ __forceinline__ bool next(int it, Tile &t) const {
         if (!(phases & kPhaseProduce))
@@ -159,8 +161,10 @@ struct GemmRsPolicy {
         const int per_owner = chunks * tiles_n;
         if (idx >= world * per_owner)
             return false;
-        // Owners in the order rank+1, rank+2, ..., rank: peers get their partials early.
-        const int order = idx / per_owner, local = idx - order * per_owner;
+        // Tile j of every owner is computed before tile j + 1 of any owner, owners in the order
+        // rank+1, rank+2, ..., rank: all partials of an owner's tile j exist after about (j + 1) * world
+        // tile times everywhere, so the owner can reduce tile j while the GEMM is still running.
+        const int local = idx / world, order = idx - local * world;
         const int owner = (rank + 1 + order) % world;
         const int chunk = local / tiles_n, tn = local - chunk * tiles_n;
         t.a_sel = 0;
@@ -227,13 +231,75 @@ struct GemmRsPolicy {
         aboleth::detail::fence_acq_rel_sys();
         aboleth::detail::st_relaxed_sys(flag, epoch);
     }
-    // Reduction of owned tiles by the 128 epilogue threads of every CTA.
-    __device__ __forceinline__ void finish(int thread, int nthreads, unsigned long long *st) const {
+    // Sum the partials of owned tile `tile` over the ranks (fp32) into `out`.  All 128 epilogue threads.
+    __device__ __forceinline__ void reduce_tile(int tile, int thread, int nthreads) const {
+        const int chunk = tile / tiles_n, tn = tile - chunk * tiles_n;
+        const int rows = min(kRows, m_local - chunk * kRows), cols = min(BN, n - tn * BN);
+        const int vec_per_row = cols / 8;
+        // Two 16-byte vectors per thread and per source in flight.
+        for (int i = thread; i < rows * vec_per_row; i += 2 * nthreads) {
+            const int i2 = i + nthreads;
+            const bool two = i2 < rows * vec_per_row;
+            const int ra = i / vec_per_row, va = i - ra * vec_per_row;
+            const int rb = two ? i2 / vec_per_row : ra, vb = two ? i2 - rb * vec_per_row : va;
+            const std::size_t offa = static_cast<std::size_t>(chunk * kRows + ra) * n + tn * BN + va * 8;
+            const std::size_t offb = static_cast<std::size_t>(chunk * kRows + rb) * n + tn * BN + vb * 8;
+            float acc[2][8] = {};
+            for (int s = 0; s < world; ++s) {
+                const __nv_bfloat16 *base = partials + static_cast<std::size_t>(s) * m_local * n;
+                const uint4 ya = aboleth::detail::ld_stream16(base + offa);
+                const uint4 yb = aboleth::detail::ld_stream16(base + offb);
+                const std::uint32_t wa[4] = {ya.x, ya.y, ya.z, ya.w}, wb[4] = {yb.x, yb.y, yb.z, yb.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    acc[0][2 * q] += __uint_as_float(wa[q] << 16);
+                    acc[0][2 * q + 1] += __uint_as_float(wa[q] & 0xffff0000u);
+                    acc[1][2 * q] += __uint_as_float(wb[q] << 16);
+                    acc[1][2 * q + 1] += __uint_as_float(wb[q] & 0xffff0000u);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (u == 1 && !two)
+                    break;
+                *reinterpret_cast<uint4 *>(out + (u ? offb : offa)) = pack8_bf16(acc[u]);
+            }
+        }
+    }
+
+    // Background work of the epilogue warps: reduce the next owned tile if every rank's partial of it
+    // has already arrived (checked without waiting).  Returns false when there is nothing to do now.
+    __device__ __forceinline__ bool background(int thread, int nthreads) {
+        if (!(phases & kPhaseConsume))
+            return false;
+        const int per_owner = chunks * tiles_n;
+        const int tile = blockIdx.x + reduced * gridDim.x;
+        if (tile >= per_owner)
+            return false;
+        __shared__ int missing;
+        if (thread == 0)
+            missing = 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (thread < world &&
+            aboleth::detail::ld_acquire_sys(flags + thread * per_owner + tile) < epoch)
+            missing = 1;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool arrived = missing == 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // `missing` is rewritten by the next call
+        if (!arrived)
+            return false;
+        reduce_tile(tile, thread, nthreads);
+        ++reduced;
+        return true;
+    }
+
+    // After the last GEMM tile: the owned tiles that were not reduced in the background, with
+    // (bounded) waits for the partials that are still on their way.
+    __device__ __forceinline__ void finish(int thread, int nthreads, unsigned long long *st) {
         if (!(phases & kPhaseConsume))
             return;
         const int per_owner = chunks * tiles_n;
-        for (int tile = blockIdx.x; tile < per_owner; tile += gridDim.x) {
-            const int chunk = tile / tiles_n, tn = tile - chunk * tiles_n;
+        for (int tile = blockIdx.x + reduced * gridDim.x; tile < per_owner; tile += gridDim.x) {
             // Threads 0..world-1 wait for one source each; the named barrier publishes it.
             bool ok = true;
             if (thread < world)
@@ -241,46 +307,7 @@ struct GemmRsPolicy {
             if (!ok)
                 ab::set_status(st, Status::Timeout, 0x4000 + thread);
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            const int rows = min(kRows, m_local - chunk * kRows), cols = min(BN, n - tn * BN);
-            const int vec_per_row = cols / 8;
-            // Two 16-byte vectors per thread and per source in flight.
-            for (int i = thread; i < rows * vec_per_row; i += 2 * nthreads) {
-                const int i2 = i + nthreads;
-                const bool two = i2 < rows * vec_per_row;
-                const int ra = i / vec_per_row, va = i - ra * vec_per_row;
-                const int rb = two ? i2 / vec_per_row : ra, vb = two ? i2 - rb * vec_per_row : va;
-                const std::size_t offa = static_cast<std::size_t>(chunk * kRows + ra) * n + tn * BN + va * 8;
-                const std::size_t offb = static_cast<std::size_t>(chunk * kRows + rb) * n + tn * BN + vb * 8;
-                float acc[2][8] = {};
-                for (int s = 0; s < world; ++s) {
-                    const __nv_bfloat16 *base = partials + static_cast<std::size_t>(s) * m_local * n;
-                    const uint4 ya = aboleth::detail::ld_stream16(base + offa);
-                    const uint4 yb = aboleth::detail::ld_stream16(base + offb);
-                    const std::uint32_t wa[4] = {ya.x, ya.y, ya.z, ya.w}, wb[4] = {yb.x, yb.y, yb.z, yb.w};
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        acc[0][2 * q] += __uint_as_float(wa[q] << 16);
-                        acc[0][2 * q + 1] += __uint_as_float(wa[q] & 0xffff0000u);
-                        acc[1][2 * q] += __uint_as_float(wb[q] << 16);
-                        acc[1][2 * q + 1] += __uint_as_float(wb[q] & 0xffff0000u);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    if (u == 1 && !two)
-                        break;
-                    uint4 o;
-                    __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[u][0], acc[u][1]);
-                    __nv_bfloat162 p1 = __floats2bfloat162_rn(acc[u][2], acc[u][3]);
-                    __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[u][4], acc[u][5]);
-                    __nv_bfloat162 p3 = __floats2bfloat162_rn(acc[u][6], acc[u][7]);
-                    o.x = *reinterpret_cast<std::uint32_t *>(&p0);
-                    o.y = *reinterpret_cast<std::uint32_t *>(&p1);
-                    o.z = *reinterpret_cast<std::uint32_t *>(&p2);
-                    o.w = *reinterpret_cast<std::uint32_t *>(&p3);
-                    *reinterpret_cast<uint4 *>(out + (u ? offb : offa)) = o;
-                }
-            }
+            reduce_tile(tile, thread, nthreads);
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
     }
@@ -367,7 +394,7 @@ AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials
         return -3;
     GemmRsPolicy p{peer_partials, peer_flags, static_cast<const __nv_bfloat16 *>(partials), flags,
                    static_cast<__nv_bfloat16 *>(out), static_cast<__nv_bfloat16 *>(stage), status, epoch, rank,
-                   world, m_local, n, k, phases, tiles_n, chunks};
+                   world, m_local, n, k, phases, tiles_n, chunks, 0};
     gemm_rs_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_a, map_b, p);
     return ab::launch_result("gemm_rs_bf16");
 }
