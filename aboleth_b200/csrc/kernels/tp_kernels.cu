@@ -38,6 +38,18 @@ constexpr int kHalves = 2;          // 256-row tiles
 constexpr int kRows = BM * kHalves;  // rows per chunk / tile
 constexpr unsigned kSmem = Geometry<kHalves>::kSmemBytes;
 
+// Position `pos` inside one rank's block of chunks x tiles_n tiles -> (chunk, tile column): all
+// chunks of `group_n` tile columns before the next group, column fastest, so the B panels of a group
+// (group_n * 256 * K * 2 bytes, about 48 MiB) stay in L2 while the A rows stream past them.
+__device__ __forceinline__ void raster(int pos, int chunks, int tiles_n, int group_n, int &chunk, int &tn) {
+    const int per_group = group_n * chunks;
+    const int group = pos / per_group;
+    const int width = min(group_n, tiles_n - group * group_n);
+    const int in_group = pos - group * per_group;
+    chunk = in_group / width;
+    tn = group * group_n + (in_group - chunk * width);
+}
+
 constexpr int kPhaseProduce = 1;  // AG: push shard.  RS: GEMM + partial stores.
 constexpr int kPhaseConsume = 2;  // AG: GEMM.        RS: reduction of owned tiles.
 
@@ -51,6 +63,7 @@ struct AgGemmPolicy {
     std::uint64_t epoch;
     int rank, world, m_local, n, k, ldc, phases;
     int tiles_n, chunks;              // chunks = m_local / 256 (row blocks per rank)
+    int group_n;                      // tile columns per raster group
     // push of this rank's shard (background work of the epilogue warps)
     const std::uint8_t *a_local;          // [m_local, k] bf16
     const std::uint64_t *peer_staging;    // [world] address of each peer's gathered-A buffer
@@ -70,7 +83,8 @@ struct AgGemmPolicy {
         // peers' pushes arrive, since every rank pushes to rank+1 first).
         const int order = idx / per_src, local = idx - order * per_src;
         const int src = (rank - order + world) % world;
-        const int chunk = local / tiles_n, tn = local - chunk * tiles_n;
+        int chunk, tn;
+        raster(local, chunks, tiles_n, group_n, chunk, tn);
         t.a_sel = src == rank ? 1 : 0;
         t.a_row = src == rank ? chunk * kRows : src * m_local + chunk * kRows;
         t.b_row = tn * BN;
@@ -152,6 +166,7 @@ struct GemmRsPolicy {
     std::uint64_t epoch;
     int rank, world, m_local, n, k, phases;
     int tiles_n, chunks;                 // tiles per owner = chunks * tiles_n
+    int group_n;                         // tile columns per raster group
     int reduced;                         // owned tiles this CTA has reduced so far (same in every thread)
 
     __device__ __forceinline__ bool next(int it, Tile &t) const {
@@ -164,9 +179,11 @@ struct GemmRsPolicy {
         // Tile j of every owner is computed before tile j + 1 of any owner, owners in the order
         // rank+1, rank+2, ..., rank: all partials of an owner's tile j exist after about (j + 1) * world
         // tile times everywhere, so the owner can reduce tile j while the GEMM is still running.
-        const int local = idx / world, order = idx - local * world;
+        const int position = idx / world, order = idx - position * world;
         const int owner = (rank + 1 + order) % world;
-        const int chunk = local / tiles_n, tn = local - chunk * tiles_n;
+        int chunk, tn;
+        raster(position, chunks, tiles_n, group_n, chunk, tn);
+        const int local = chunk * tiles_n + tn;
         t.a_sel = 0;
         t.a_row = owner * m_local + chunk * kRows;
         t.b_row = tn * BN;
@@ -273,9 +290,12 @@ struct GemmRsPolicy {
         if (!(phases & kPhaseConsume))
             return false;
         const int per_owner = chunks * tiles_n;
-        const int tile = blockIdx.x + reduced * gridDim.x;
-        if (tile >= per_owner)
+        const int position = blockIdx.x + reduced * gridDim.x;  // owned tiles in the order they are computed
+        if (position >= per_owner)
             return false;
+        int chunk, tn;
+        raster(position, chunks, tiles_n, group_n, chunk, tn);
+        const int tile = chunk * tiles_n + tn;
         __shared__ int missing;
         if (thread == 0)
             missing = 0;
@@ -299,7 +319,10 @@ struct GemmRsPolicy {
         if (!(phases & kPhaseConsume))
             return;
         const int per_owner = chunks * tiles_n;
-        for (int tile = blockIdx.x + reduced * gridDim.x; tile < per_owner; tile += gridDim.x) {
+        for (int position = blockIdx.x + reduced * gridDim.x; position < per_owner; position += gridDim.x) {
+            int chunk, tn;
+            raster(position, chunks, tiles_n, group_n, chunk, tn);
+            const int tile = chunk * tiles_n + tn;
             // Threads 0..world-1 wait for one source each; the named barrier publishes it.
             bool ok = true;
             if (thread < world)
@@ -318,6 +341,13 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                GemmRsPolicy params) {
     GemmRsPolicy policy = params;
     gemm_mainloop<kHalves>(policy, &map_a, &map_b, policy.status);
+}
+
+// Tile columns whose B panels (256 rows of K bf16 each) add up to about 48 MiB.
+int raster_group(int n, int k) {
+    const long long column_bytes = static_cast<long long>(BN) * k * 2;
+    const long long tiles_n = (n + BN - 1) / BN;
+    return static_cast<int>(std::max(1LL, std::min(tiles_n, (48LL << 20) / column_bytes)));
 }
 
 int sm_count() {
@@ -359,7 +389,7 @@ AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const vo
     }
     parts = std::min(parts, kRows);
     AgGemmPolicy p{static_cast<__nv_bfloat16 *>(c), flags, status, epoch, rank, world, m_local, n, k, n,
-                   phases, (n + BN - 1) / BN, chunks,
+                   phases, (n + BN - 1) / BN, chunks, raster_group(n, k),
                    static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, arrivals, parts, 0};
     ag_gemm_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_staging, map_b, map_local, p);
     return ab::launch_result("ag_gemm_bf16");
@@ -394,7 +424,7 @@ AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials
         return -3;
     GemmRsPolicy p{peer_partials, peer_flags, static_cast<const __nv_bfloat16 *>(partials), flags,
                    static_cast<__nv_bfloat16 *>(out), static_cast<__nv_bfloat16 *>(stage), status, epoch, rank,
-                   world, m_local, n, k, phases, tiles_n, chunks, 0};
+                   world, m_local, n, k, phases, tiles_n, chunks, raster_group(n, k), 0};
     gemm_rs_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_a, map_b, p);
     return ab::launch_result("gemm_rs_bf16");
 }

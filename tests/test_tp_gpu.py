@@ -9,7 +9,8 @@ def _rel(got, want):
     return ((got.float() - want).norm() / want.norm().clamp_min(1e-6)).item()
 
 
-@pytest.mark.parametrize("world,m_local,k,n_local", [(2, 256, 256, 256), (4, 512, 512, 384), (3, 256, 1024, 520)])
+@pytest.mark.parametrize("world,m_local,k,n_local", [(2, 256, 256, 256), (4, 512, 512, 384), (3, 256, 1024, 520),
+                                                   (2, 512, 16384, 2000)])  # last: two raster groups
 def test_all_gather_gemm_matches_fp32(world, m_local, k, n_local):
     from aboleth_b200.parallel import LocalTpGroup
 
@@ -26,7 +27,8 @@ def test_all_gather_gemm_matches_fp32(world, m_local, k, n_local):
         assert _rel(outs[r], full @ b[r].float().t()) < 5e-3
 
 
-@pytest.mark.parametrize("world,m_local,k_local,n", [(2, 256, 256, 256), (4, 256, 384, 520), (3, 512, 128, 1024)])
+@pytest.mark.parametrize("world,m_local,k_local,n", [(2, 256, 256, 256), (4, 256, 384, 520), (3, 512, 128, 1024),
+                                                   (2, 512, 16384, 2000)])  # last: two raster groups
 def test_gemm_reduce_scatter_matches_fp32(world, m_local, k_local, n):
     from aboleth_b200.parallel import LocalTpGroup
 
