@@ -26,6 +26,7 @@
 // No reference kernel exists for these; the baseline is NCCL all-gather /
 // reduce-scatter around a library GEMM.
 #include <algorithm>
+#include <cstdlib>
 
 #include "gemm_sm100.cuh"
 
@@ -167,7 +168,9 @@ struct GemmRsPolicy {
     int rank, world, m_local, n, k, phases;
     int tiles_n, chunks;                 // tiles per owner = chunks * tiles_n
     int group_n;                         // tile columns per raster group
+    int interleave;                      // 1: owners interleaved tile by tile, owned tiles reduced in the background
     int reduced;                         // owned tiles this CTA has reduced so far (same in every thread)
+    static constexpr int kSourcesInFlight = 8;
 
     __device__ __forceinline__ bool next(int it, Tile &t) const {
         if (!(phases & kPhaseProduce))
@@ -176,10 +179,19 @@ struct GemmRsPolicy {
         const int per_owner = chunks * tiles_n;
         if (idx >= world * per_owner)
             return false;
-        // Tile j of every owner is computed before tile j + 1 of any owner, owners in the order
-        // rank+1, rank+2, ..., rank: all partials of an owner's tile j exist after about (j + 1) * world
-        // tile times everywhere, so the owner can reduce tile j while the GEMM is still running.
-        const int position = idx / world, order = idx - position * world;
+        // Owners in the order rank+1, rank+2, ..., rank.  Interleaved: tile j of every owner before tile
+        // j + 1 of any owner, so all partials of an owner's tile j exist after about (j + 1) * world tile
+        // times everywhere and the owner reduces it while the GEMM is still running; this pays when an
+        // owner has several tiles per CTA to reduce.  Otherwise owner by owner: the last wave computes
+        // own tiles, which need no transfer, and the reduction follows it.
+        int position, order;
+        if (interleave) {
+            position = idx / world;
+            order = idx - position * world;
+        } else {
+            order = idx / per_owner;
+            position = idx - order * per_owner;
+        }
         const int owner = (rank + 1 + order) % world;
         int chunk, tn;
         raster(position, chunks, tiles_n, group_n, chunk, tn);
@@ -253,7 +265,6 @@ struct GemmRsPolicy {
         const int chunk = tile / tiles_n, tn = tile - chunk * tiles_n;
         const int rows = min(kRows, m_local - chunk * kRows), cols = min(BN, n - tn * BN);
         const int vec_per_row = cols / 8;
-        // Two 16-byte vectors per thread and per source in flight.
         for (int i = thread; i < rows * vec_per_row; i += 2 * nthreads) {
             const int i2 = i + nthreads;
             const bool two = i2 < rows * vec_per_row;
@@ -262,17 +273,31 @@ struct GemmRsPolicy {
             const std::size_t offa = static_cast<std::size_t>(chunk * kRows + ra) * n + tn * BN + va * 8;
             const std::size_t offb = static_cast<std::size_t>(chunk * kRows + rb) * n + tn * BN + vb * 8;
             float acc[2][8] = {};
-            for (int s = 0; s < world; ++s) {
-                const __nv_bfloat16 *base = partials + static_cast<std::size_t>(s) * m_local * n;
-                const uint4 ya = aboleth::detail::ld_stream16(base + offa);
-                const uint4 yb = aboleth::detail::ld_stream16(base + offb);
-                const std::uint32_t wa[4] = {ya.x, ya.y, ya.z, ya.w}, wb[4] = {yb.x, yb.y, yb.z, yb.w};
+            // Up to eight sources' vectors are loaded before any is added: sixteen 16-byte loads in
+            // flight per thread instead of two.
+            for (int s0 = 0; s0 < world; s0 += kSourcesInFlight) {
+                uint4 y[kSourcesInFlight][2];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    acc[0][2 * q] += __uint_as_float(wa[q] << 16);
-                    acc[0][2 * q + 1] += __uint_as_float(wa[q] & 0xffff0000u);
-                    acc[1][2 * q] += __uint_as_float(wb[q] << 16);
-                    acc[1][2 * q + 1] += __uint_as_float(wb[q] & 0xffff0000u);
+                for (int j = 0; j < kSourcesInFlight; ++j) {
+                    if (s0 + j < world) {
+                        const __nv_bfloat16 *base = partials + static_cast<std::size_t>(s0 + j) * m_local * n;
+                        y[j][0] = aboleth::detail::ld_stream16(base + offa);
+                        y[j][1] = aboleth::detail::ld_stream16(base + offb);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < kSourcesInFlight; ++j) {
+                    if (s0 + j < world) {
+                        const std::uint32_t wa[4] = {y[j][0].x, y[j][0].y, y[j][0].z, y[j][0].w};
+                        const std::uint32_t wb[4] = {y[j][1].x, y[j][1].y, y[j][1].z, y[j][1].w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            acc[0][2 * q] += __uint_as_float(wa[q] << 16);
+                            acc[0][2 * q + 1] += __uint_as_float(wa[q] & 0xffff0000u);
+                            acc[1][2 * q] += __uint_as_float(wb[q] << 16);
+                            acc[1][2 * q + 1] += __uint_as_float(wb[q] & 0xffff0000u);
+                        }
+                    }
                 }
             }
 #pragma unroll
@@ -287,7 +312,7 @@ struct GemmRsPolicy {
     // Background work of the epilogue warps: reduce the next owned tile if every rank's partial of it
     // has already arrived (checked without waiting).  Returns false when there is nothing to do now.
     __device__ __forceinline__ bool background(int thread, int nthreads) {
-        if (!(phases & kPhaseConsume))
+        if (!(phases & kPhaseConsume) || !interleave)
             return false;
         const int per_owner = chunks * tiles_n;
         const int position = blockIdx.x + reduced * gridDim.x;  // owned tiles in the order they are computed
@@ -422,9 +447,14 @@ AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials
         cudaSuccess;
     if (!configured)
         return -3;
+    // Background reduction needs at least two owned tiles per CTA to pay for the transfers it moves
+    // into the last wave; ABOLETH_RS_ORDER=0 / 1 forces the owner-by-owner / interleaved order.
+    int interleave = tiles_n * chunks >= 2 * sm_count() ? 1 : 0;
+    if (const char *forced = std::getenv("ABOLETH_RS_ORDER"))
+        interleave = forced[0] == '1' ? 1 : 0;
     GemmRsPolicy p{peer_partials, peer_flags, static_cast<const __nv_bfloat16 *>(partials), flags,
                    static_cast<__nv_bfloat16 *>(out), static_cast<__nv_bfloat16 *>(stage), status, epoch, rank,
-                   world, m_local, n, k, phases, tiles_n, chunks, raster_group(n, k), 0};
+                   world, m_local, n, k, phases, tiles_n, chunks, raster_group(n, k), interleave, 0};
     gemm_rs_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_a, map_b, p);
     return ab::launch_result("gemm_rs_bf16");
 }
