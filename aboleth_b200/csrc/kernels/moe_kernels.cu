@@ -260,7 +260,6 @@ __global__ void __launch_bounds__(kThreads, 4) ep_dispatch_kernel(DispatchParams
     __shared__ float s_w[kMaxTopK];
     __shared__ int s_owner[kMaxTopK];
     __shared__ int s_slot[kMaxWorld];
-    __shared__ int s_nsel[kMaxWorld];
     __shared__ int s_dest[kMaxWorld];
     __shared__ int s_ndest;
     __shared__ float s_scale[128];  // hidden / scale_group <= 128
@@ -320,7 +319,6 @@ __global__ void __launch_bounds__(kThreads, 4) ep_dispatch_kernel(DispatchParams
                     }
                     p.source_slots[t * g.world + lane] = slot;
                     s_slot[lane] = slot;
-                    s_nsel[lane] = nsel;
                 }
                 const unsigned live = __ballot_sync(0xffffffffu, slot >= 0);
                 if (slot >= 0)

@@ -117,7 +117,7 @@ static_assert(!lookup_transport_caps("efa")->ordered_delivery);
 static_assert(lookup_transport_caps("efa")->imm_data);
 static_assert(lookup_transport_caps("nvshmem") == nullptr);
 static_assert(lookup_transport_caps("rdm", 3) == nullptr);
-static_assert(lookup_transport_caps("rdmaX", 4) != nullptr);
+static_assert(lookup_transport_caps("rdmaX", 4) == lookup_transport_caps("rdma"));
 static_assert(default_transport_cost_params().path_mtu == 4096);
 
 }  // namespace aboleth::abi

@@ -1,4 +1,5 @@
-"""Small host-side helpers: profiler ranges and provenance records."""
+"""Small host-side helpers: profiler ranges, provenance records and the requirement gate
+(``python -m aboleth_b200.utils.gated``)."""
 from .provenance import provenance
 from .ranges import host_range, ranges_enabled
 

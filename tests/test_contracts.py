@@ -105,3 +105,22 @@ def test_record_programs_and_compiled_phase():
     assert phase.binding.sender_threads % 32 == 0 and phase.binding.sender_grid[0] >= 1
     with pytest.raises(KeyError):
         ab.compile_phase(plan, "no.such.phase", rank=1, capacity=64, width_bytes=1024)
+
+
+def test_gate_skips_with_77_and_passes_exit_codes_through(tmp_path):
+    """Requirement gate (reference scripts/run-gated.sh:1-120): 77 = skipped, other codes untouched."""
+    import sys
+
+    from aboleth_b200.utils import gated
+
+    assert gated.missing("gpu", gpus=0) == "no GPU" and gated.missing("gpu", gpus=1) is None
+    assert gated.missing("multi-gpu", gpus=1) and gated.missing("gpus=4", gpus=8) is None
+    assert gated.missing("gpus=4", gpus=2) == "2 GPU(s), 4 needed"
+    assert gated.missing("mlx5", verbs_root=tmp_path) == "no mlx5 device"
+    (tmp_path / "mlx5_0").mkdir()
+    assert gated.missing("mlx5", verbs_root=tmp_path) is None and gated.missing("hca", verbs_root=tmp_path) is None
+    assert gated.run_gated(["gpus=2"], [sys.executable, "-c", "raise SystemExit(0)"], gpus=1) == gated.SKIP
+    assert gated.run_gated(["gpu"], [sys.executable, "-c", "raise SystemExit(3)"], gpus=1) == 3
+    assert gated.run_gated([], [sys.executable, "-c", "import time; time.sleep(30)"], timeout=0.5) == 124
+    assert gated.main(["--needs", "gpus=64", "--", sys.executable, "-c", "pass"]) == gated.SKIP
+    assert gated.main(["--needs", "gpu"]) == 2  # no command
