@@ -1,0 +1,79 @@
+"""Build and run the standalone C++ arm of the Tier-1 ladder (``benchmarks/native/bench_tier1.cu``).
+
+    python benchmarks/native_bench.py [--gpus N] [--bench pingpong|window|alltoall|all] [--bytes B ...]
+                                      [--sweep] [--out results.json]
+
+The program is one process for all ranks (rank r on GPU r, peers through CUDA peer access) and is
+written against ``aboleth/device.cuh`` alone; this driver only compiles it with nvcc for sm_100a,
+forwards the options and collects the JSON lines it prints.  ``--sweep`` repeats the ladder over
+8 B-equivalent (16 B), 4 KiB, 64 KiB and 1 MiB payloads.  Exit code 77 means "no GPU here".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+SOURCE = ROOT / "native" / "bench_tier1.cu"
+BINARY = ROOT / "native" / "build" / "bench_tier1"
+INCLUDE = ROOT.parent / "aboleth_b200" / "include"
+
+
+def build(force: bool = False) -> Path:
+    """Compile the program if the binary is older than its source or the Tier-1 header."""
+    newest = max(SOURCE.stat().st_mtime, (INCLUDE / "aboleth" / "device.cuh").stat().st_mtime)
+    if not force and BINARY.exists() and BINARY.stat().st_mtime >= newest:
+        return BINARY
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    BINARY.parent.mkdir(parents=True, exist_ok=True)
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
+           f"-I{INCLUDE}", str(SOURCE), "-o", str(BINARY)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("native bench build failed:\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+    return BINARY
+
+
+def run(args: list[str], timeout: float = 300.0) -> tuple[int, list[dict]]:
+    proc = subprocess.run([str(build()), *args], capture_output=True, text=True, timeout=timeout)
+    rows = [json.loads(line) for line in proc.stdout.splitlines() if line.startswith("{")]
+    if proc.returncode not in (0, 77):
+        sys.stderr.write(proc.stderr)
+    return proc.returncode, rows
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--out", default=None)
+    ap.add_argument("--build-only", action="store_true")
+    known, rest = ap.parse_known_args()
+    if known.build_only:
+        print(build(force=True))
+        return 0
+    rows: list[dict] = []
+    code = 0
+    sizes = ["16", "4096", "65536", "1048576"] if known.sweep else [None]
+    for size in sizes:
+        extra = rest if size is None else [*rest, "--bytes", size]
+        rc, out = run(extra)
+        rows += out
+        code = code or rc
+        if rc == 77:
+            break
+    for row in rows:
+        print(json.dumps(row))
+    if known.out:
+        sys.path.insert(0, str(ROOT))
+        from common import provenance  # benchmarks/common.py
+        Path(known.out).write_text(json.dumps({"bench": "native tier-1 ladder", "rows": rows,
+                                               "provenance": provenance()}, indent=1))
+    return code
+
+
+if __name__ == "__main__":
+    sys.exit(main())
