@@ -11,6 +11,8 @@
 
 #include <algorithm>
 #include <cctype>
+#include <set>
+#include <sstream>
 
 namespace spec {
 
@@ -356,7 +358,23 @@ void verify_submit(const Op &op, const Scope &scope) {
     std::set<std::string> in_batch;
     std::string previous;
     bool segment_open = false;  // inside a put chain not yet closed by a signal
+    // A coalesced submission lists the sizes of the submissions it was merged from
+    // ("segments=3+1+2"): a chain may also end at such a boundary without a signal.
+    std::set<std::size_t> boundaries;
+    if (op.has("segments")) {
+        std::size_t start = 0;
+        std::stringstream sizes(op.get("segments"));
+        std::string size;
+        while (std::getline(sizes, size, '+')) {
+            boundaries.insert(start);
+            start += static_cast<std::size_t>(std::stoul(size));
+        }
+        if (start != op.operands.size())
+            fail(op, "segments=" + op.get("segments") + " does not add up to the batch size");
+    }
     for (std::size_t i = 0; i < op.operands.size(); ++i) {
+        if (boundaries.count(i))
+            segment_open = false;
         const Op *cmd = scope.find(op.operands[i]);
         if (cmd == nullptr || !is_posted(*cmd))
             fail(op, "token " + op.operands[i] + " is not a posted command in scope");

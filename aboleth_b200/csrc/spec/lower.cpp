@@ -57,6 +57,7 @@ struct Emitter {
     // facts
     int batches = 0, commands = 0, reservations = 0, ready_stores = 0, completion_waits = 0;
     int barriers = 0, producer_barriers = 0, system_fences = 0, inline_puts = 0, trimmed = 0;
+    int deferred_placements = 0;
     int weak = 0, strong = 0, elided = 0, exclusive = 0, cooperative_puts = 0;
     std::vector<std::string> fences, flag_writes, flag_reads;
     int wait_sites = 0;
@@ -233,6 +234,7 @@ struct Emitter {
         j.key("barriers").value(barriers);
         j.key("producer_barriers").value(producer_barriers);
         j.key("system_fences").value(system_fences);
+        j.key("deferred_placements").value(deferred_placements);
         j.key("cooperative_puts").value(cooperative_puts);
         j.key("inline_puts").value(inline_puts);
         j.key("trimmed_puts").value(trimmed);
@@ -266,7 +268,50 @@ struct P2PEmitter : Emitter {
     // token order: one producer barrier (if the analysis asked for it), the
     // copies, then one CTA barrier before the first strong signal - or, when
     // nothing in the batch publishes the copies, a barrier and a system fence.
-    void emit_submit(const Op &submit, int in) {
+    // Copies of an earlier submission that no barrier has ordered yet (see `placed_later`).
+    bool deferred_copies = false;
+
+    // Does a later submission of the same block place this one's copies?  True when only bindings,
+    // plain stores and other commands lie between, nothing polls this submission, and the next
+    // submission with an effect either releases a strong, unpredicated signal (its CTA barrier and
+    // release cover every earlier store of the CTA) or ends in its own barrier and system fence.
+    // Nothing promised the copies any earlier: no signal of this submission names them and no
+    // completion of it is awaited.  Part of coalesce-submissions (the peer-memory form of it).
+    bool placed_later(const std::vector<Op> &ops, std::size_t at) const {
+        if (!options.on("coalesce-submissions"))
+            return false;
+        static const std::set<std::string> plain = {"endpoint", "local", "remote", "remote_at", "let", "load",
+                                                    "store", "tensor_store", "compute"};
+        for (std::size_t j = at + 1; j < ops.size(); ++j) {
+            const Op &next = ops[j];
+            if (next.kind == "poll" || next.kind == "wait") {
+                if (next.operands[0] == ops[at].result)
+                    return false;
+                continue;
+            }
+            if (plain.count(next.kind) || is_posted(next))
+                continue;
+            if (next.kind != "submit")
+                return false;
+            bool copies = false, strong = false, conditional = false;
+            for (const auto &token : next.operands) {
+                const Op &cmd = *defs.at(token);
+                copies = copies || cmd.kind == "post_put";
+                if (cmd.kind == "post_signal" && cmd.has("strong")) {
+                    strong = true;
+                    conditional = conditional || cmd.has("pred");
+                }
+            }
+            if (strong)
+                return !conditional;
+            if (copies && !placed_later(ops, j))
+                return true;  // ends in a barrier and a system fence of its own
+            // Otherwise that submission defers as well: keep looking for the placing one.
+        }
+        return false;
+    }
+
+    void emit_submit(const Op &submit, int in, bool defer_placement = false) {
         ++batches;
         if (submit.has("exclusiveIssuer"))
             ++exclusive;
@@ -316,7 +361,8 @@ struct P2PEmitter : Emitter {
                     ++elided;
                 const bool is_strong = op.has("strong");
                 (is_strong ? strong : weak) += 1;
-                if (is_strong && copies_pending) {
+                if (is_strong && (copies_pending || deferred_copies)) {
+                    deferred_copies = false;
                     line(level, "__syncthreads();  // every thread's copy precedes the release; no membar.sys");
                     ++barriers;
                     fences.push_back("bar.sync");
@@ -336,8 +382,13 @@ struct P2PEmitter : Emitter {
                 close_pred(level, op);
             }
         }
-        if (copies_pending) {
+        if (copies_pending && defer_placement) {
+            line(in, "// no signal follows here: the next submission's barrier and release / fence place these copies");
+            deferred_copies = true;
+            ++deferred_placements;
+        } else if (copies_pending || deferred_copies) {
             // Nothing in this submission publishes the copies: place them now.
+            deferred_copies = false;
             line(in, "__syncthreads();");
             line(in, "if (threadIdx.x == 0) detail::fence_acq_rel_sys();  // no signal follows: membar.sys");
             ++barriers;
@@ -348,7 +399,8 @@ struct P2PEmitter : Emitter {
     }
 
     void emit_block(const std::vector<Op> &ops, int indent) {
-        for (const Op &op : ops) {
+        for (std::size_t at = 0; at < ops.size(); ++at) {
+            const Op &op = ops[at];
             if (op.kind == "for") {
                 line(indent, "for (long long " + op.operands[0] + " = " + op.operands[1] + "; " +
                                  op.operands[0] + " < " + op.operands[2] + "; ++" + op.operands[0] + ") {");
@@ -370,7 +422,7 @@ struct P2PEmitter : Emitter {
                 // The transfer is asynchronous: it is carried out where its batch is submitted.
                 line(in, "// " + op.kind + " " + op.result + ": carried out at its submission");
             } else if (op.kind == "submit") {
-                emit_submit(op, in);
+                emit_submit(op, in, placed_later(ops, at));
             } else if (op.kind == "poll" || op.kind == "wait") {
                 line(in, "// completion of " + op.operands[0] + ": program order (vacuous on peer memory)");
             } else if (op.kind == "wait_signal") {

@@ -269,3 +269,45 @@ def test_ladder_programs_batch_as_the_benchmarks_expect():
     with compilation("proxy", rank=0, world_size=2, queue_capacity=64):
         queued = compile_program(windowed(65536, window=8)).facts
     assert queued["reservations"] == 1 and queued["completion"] == "poll"
+
+
+def _independent_puts(chain=8, *, poll_first=False):
+    from aboleth_b200.compiler import ProgramBuilder
+
+    b = ProgramBuilder("independent", threads=128, args=[
+        ("src", "ptr"), ("endpoints", "table"), ("dst_table", "table"), ("flag_table", "table"),
+        ("my_flag", "ptr"), ("epoch", "u64")])
+    e = b.endpoint("endpoints", 0)
+    tokens = [b.put(e, b.remote("dst_table", 0, offset=c * 1024), b.local(f"src + {c * 1024}"), bytes=1024)
+              for c in range(chain)]
+    if poll_first:
+        b.wait(tokens[0])
+    s = b.signal(e, b.remote("flag_table", 0), epoch="epoch", after=tokens[-1])
+    b.wait_signal("my_flag", "epoch")
+    b.wait(s)
+    return b
+
+
+def test_unchained_puts_coalesce_on_the_ring_and_share_one_release_on_peer_memory():
+    """Puts that are not chained by `after` form one submission each.  On the ring adjacent
+    submissions to one endpoint merge (segments recorded, verifier accepts a chain that ends at a
+    segment boundary).  On peer memory a submission that nothing polls leaves its placement to the
+    next submission's barrier + release, so eight puts and a signal cost one barrier and no
+    system fence; a poll of an early put or the switch being off keeps the fence."""
+    from aboleth_b200.compiler import compilation, compile_program
+
+    with compilation("proxy", rank=0, world_size=1):
+        ring = compile_program(_independent_puts())
+    assert ring.passes["form-batches"] == 8 and ring.passes["coalesce-submissions"] == 6
+    assert ring.facts["batches"] == 2 and ring.facts["commands"] == 9
+    with compilation("p2p", rank=0, world_size=1):
+        peer = compile_program(_independent_puts())
+    assert (peer.facts["barriers"], peer.facts["system_fences"], peer.facts["deferred_placements"]) == (1, 0, 7)
+    assert peer.cuda.count("fence_acq_rel_sys();  // no signal follows") == 0
+    with compilation("p2p", rank=0, world_size=1, passes="none"):
+        naive = compile_program(_independent_puts())
+    assert (naive.facts["barriers"], naive.facts["system_fences"], naive.facts["deferred_placements"]) == (8, 7, 0)
+    with compilation("p2p", rank=0, world_size=1):
+        polled = compile_program(_independent_puts(poll_first=True))
+    # the polled first put keeps its fence; the other seven are placed by the signal's barrier + release
+    assert (polled.facts["barriers"], polled.facts["system_fences"], polled.facts["deferred_placements"]) == (2, 1, 7)

@@ -5,7 +5,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _program(nbytes, chain):
+def _program(nbytes, chain, chained=True):
     from aboleth_b200.compiler import ProgramBuilder
 
     b = ProgramBuilder("selfloop", threads=128, args=[
@@ -16,15 +16,15 @@ def _program(nbytes, chain):
     previous = None
     for c in range(chain):
         previous = b.put(e, b.remote("dst_table", 0, offset=c * piece), b.local(f"src + {c * piece}"),
-                         bytes=piece, after=previous)
+                         bytes=piece, after=previous if chained else None)
     s = b.signal(e, b.remote("flag_table", 0), epoch="epoch", after=previous)
     b.wait_signal("my_flag", "epoch")
     b.wait(s)
     return b
 
 
-@pytest.mark.parametrize("backend", ["p2p", "proxy"])
-def test_emitted_chain_kernel_moves_data_and_publishes_once(backend, tmp_path, monkeypatch):
+@pytest.mark.parametrize("backend,chained", [("p2p", True), ("proxy", True), ("p2p", False), ("proxy", False)])
+def test_emitted_chain_kernel_moves_data_and_publishes_once(backend, chained, tmp_path, monkeypatch):
     import aboleth_b200 as ab
     from aboleth_b200.compiler import LoadedKernel, build_artifact, compilation, compile_program
 
@@ -42,8 +42,14 @@ def test_emitted_chain_kernel_moves_data_and_publishes_once(backend, tmp_path, m
         dst_table = torch.tensor([dst.data_ptr(), 0], dtype=torch.int64, device="cuda")
         flag_table = torch.tensor([flag.data_ptr(), 0], dtype=torch.int64, device="cuda")
         with compilation(backend, rank=0, world_size=1):
-            compiled = compile_program(_program(nbytes, 8))
-        assert compiled.facts["batches"] == 1 and compiled.facts["commands"] == 9
+            compiled = compile_program(_program(nbytes, 8, chained))
+        assert compiled.facts["commands"] == 9
+        if chained:
+            assert compiled.facts["batches"] == 1
+        elif backend == "p2p":  # unchained puts share the signal's barrier and release
+            assert compiled.facts["system_fences"] == 0 and compiled.facts["deferred_placements"] == 7
+        else:                   # adjacent submissions to one endpoint merged
+            assert compiled.facts["batches"] == 2
         kernel = LoadedKernel(build_artifact(compiled))
         for epoch in (1, 2):
             dst.zero_()
@@ -56,8 +62,9 @@ def test_emitted_chain_kernel_moves_data_and_publishes_once(backend, tmp_path, m
             assert torch.equal(dst, src) and flag.item() == epoch
         if backend == "proxy":
             stats = endpoint.stats()
-            assert stats["batches"] == 2 and stats["commands"] == 18 and stats["bytes"] == 2 * nbytes
-            assert endpoint.state()[:2] == (2, 2)
+            per_launch = 1 if chained else 2
+            assert stats["batches"] == 2 * per_launch and stats["commands"] == 18 and stats["bytes"] == 2 * nbytes
+            assert endpoint.state()[:2] == (2 * per_launch, 2 * per_launch)
     finally:
         runtime.close()
 
