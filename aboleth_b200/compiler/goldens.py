@@ -17,7 +17,7 @@ from pathlib import Path
 
 from . import programs
 from .driver import compile_program
-from .options import PIPELINE_ORDER, compilation, enabled_optimizations
+from .options import PIPELINE_ORDER, compilation
 
 CASES = {
     "alltoall_4096": lambda: programs.alltoall(4096),

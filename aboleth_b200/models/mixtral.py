@@ -11,7 +11,6 @@ Weights are random-init from a seed (there are no checkpoints on an offline box)
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import Optional
 

@@ -28,7 +28,7 @@ from uuid import UUID
 
 import torch
 
-from .abi import KIND_BITS, WIRE_CODES
+from .abi import WIRE_CODES
 from .bootstrap import Bootstrap, LocalBootstrap, decode_bundle, encode_bundle
 from .runtime import (AllocationHandle, AllocationProvider, LocalEndpoint, RegisteredBuffer,
                       RemoteBuffer, Runtime, Transport, connection_info_from_bytes,

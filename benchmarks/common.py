@@ -3,10 +3,7 @@ from __future__ import annotations
 
 import json
 import os
-import platform
-import subprocess
 import sys
-import time
 from pathlib import Path
 
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent))

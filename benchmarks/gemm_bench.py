@@ -10,7 +10,6 @@ Each timed launch is preceded by an L2 flush; times are medians of CUDA-event br
 Fractions are of the measured cuBLAS bf16 burst throughput recorded for this pool.
 """
 import argparse
-import json
 
 from common import emit
 

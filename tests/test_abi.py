@@ -2,7 +2,6 @@
 import ctypes
 import struct
 import subprocess
-import sys
 from pathlib import Path
 
 import pytest

@@ -6,7 +6,6 @@ with batch count, fence kind and flag writes asserted.
 """
 import json
 import os
-import subprocess
 from pathlib import Path
 
 import pytest

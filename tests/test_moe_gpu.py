@@ -214,7 +214,7 @@ def test_quant_fp8_matches_reference(round_scale):
 
 def test_bounded_wait_reports_timeout_without_hanging():
     """A receive half whose peers never publish gives up and reports status 1."""
-    from aboleth_b200.moe import PHASE_RECV, LocalMoEGroup, MoESpec
+    from aboleth_b200.moe import LocalMoEGroup, MoESpec
     from aboleth_b200.ops.comm import tier1_exercise
 
     # Tier-1 wait with a 50 ms budget on a flag nobody sets.

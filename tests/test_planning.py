@@ -1,12 +1,11 @@
 """Native planning passes against hand-computed cases (no GPU)."""
-import ctypes
 import json
 
 import pytest
 
 from aboleth_b200 import abi
 from aboleth_b200.compiler import compilation
-from aboleth_b200.endpoint_profiles import (SEED_PROFILES, EndpointProfile, ProbeSample, ProfileStore,
+from aboleth_b200.endpoint_profiles import (SEED_PROFILES, ProbeSample, ProfileStore,
                                             fit_profile, resolve_profiles)
 from aboleth_b200.moe import MoESpec, compile_moe_plan
 from aboleth_b200.planning import (CommunicationDataflow, CommunicationRegion, RegionEffect,

@@ -7,7 +7,6 @@ and codecs are exercised as on GPUs.
 import struct
 
 import pytest
-import torch
 
 from aboleth_b200 import (AutoTransportPolicy, TcpStoreBootstrap, TopologyInfo, Transport, World)
 from aboleth_b200.bootstrap import encode_bundle
