@@ -124,3 +124,29 @@ def test_gate_skips_with_77_and_passes_exit_codes_through(tmp_path):
     assert gated.run_gated([], [sys.executable, "-c", "import time; time.sleep(30)"], timeout=0.5) == 124
     assert gated.main(["--needs", "gpus=64", "--", sys.executable, "-c", "pass"]) == gated.SKIP
     assert gated.main(["--needs", "gpu"]) == 2  # no command
+
+
+def test_benchmark_report_tables_and_regression_check(tmp_path, capsys):
+    import importlib.util
+    import json
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location(
+        "report", Path(__file__).resolve().parent.parent / "benchmarks" / "report.py")
+    report = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(report)
+    ref = {"bench": "tp", "n_gpus": 2, "rows": [{"op": "ag", "n": 8, "fused_us": 100.0, "speedup": 1.2},
+                                                {"op": "rs", "n": 8, "fused_us": 200.0, "speedup": 1.1}]}
+    new = {"bench": "tp", "n_gpus": 2, "rows": [{"op": "ag", "n": 8, "fused_us": 125.0, "speedup": 1.19},
+                                                {"op": "rs", "n": 8, "fused_us": 190.0, "speedup": 1.3}]}
+    (tmp_path / "ref").mkdir()
+    (tmp_path / "new").mkdir()
+    (tmp_path / "ref" / "tp.json").write_text(json.dumps(ref))
+    (tmp_path / "new" / "tp.json").write_text("some log line\n" + json.dumps(new))
+    assert report.direction("fused_us") == -1 and report.direction("busbw_gbs") == 1 and report.direction("op") == 0
+    assert report.main([str(tmp_path / "ref")]) == 0
+    assert "| ag | 8 | 100 | 1.2 |" in capsys.readouterr().out
+    assert report.main(["--compare", str(tmp_path / "ref"), str(tmp_path / "new")]) == 1
+    out = capsys.readouterr().out
+    assert "fused_us: 100 -> 125" in out and "rs" not in out
+    assert report.main(["--compare", "--tolerance", "0.5", str(tmp_path / "ref"), str(tmp_path / "new")]) == 0
