@@ -148,5 +148,5 @@ def test_benchmark_report_tables_and_regression_check(tmp_path, capsys):
     assert "| ag | 8 | 100 | 1.2 |" in capsys.readouterr().out
     assert report.main(["--compare", str(tmp_path / "ref"), str(tmp_path / "new")]) == 1
     out = capsys.readouterr().out
-    assert "fused_us: 100 -> 125" in out and "rs" not in out
+    assert "fused_us: 100 -> 125" in out and "op=rs" not in out
     assert report.main(["--compare", "--tolerance", "0.5", str(tmp_path / "ref"), str(tmp_path / "new")]) == 0
