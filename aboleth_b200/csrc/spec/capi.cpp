@@ -100,7 +100,13 @@ char *ab200_spec_plan(const char *kind, const char *request) {
 }
 
 char *ab200_spec_affine(const char *expr) {
-    const spec::Affine a = spec::affine_in_pid(expr ? expr : "", {});
+    spec::Affine a;
+    try {
+        a = spec::affine_in_pid(expr ? expr : "", {});
+    } catch (const std::exception &) {
+        a = spec::Affine{};  // an expression that cannot be read is simply not proven
+        a.known = false;
+    }
     spec::Json j;
     j.begin_object();
     j.key("known").value(a.known);

@@ -423,6 +423,29 @@ void verify_block(const std::vector<Op> &ops, const Scope *parent) {
                     fail(op, "after=" + op.get(key) + " belongs to another endpoint");
             }
         }
+        // Operand counts of the binding and control operations: the passes and the
+        // lowerings index operands by position, so a short operation is refused here.
+        static const std::map<std::string, std::pair<std::size_t, const char *>> arity = {
+            {"let", {2, "<name> <expr>"}},
+            {"endpoint", {2, "<table> <index>"}},
+            {"local", {1, "<address> [key=] [at=] [valid=]"}},
+            {"remote", {2, "<table> <peer> [offset=]"}},
+            {"remote_at", {1, "<address> [key=]"}},
+            {"store", {1, "<address> value=<v> [offset=] [width=]"}},
+            {"for", {3, "<var> <begin> <end> { ... }"}},
+            {"if", {1, "<condition> { ... }"}},
+            {"drain", {1, "<endpoint>"}},
+            {"publish_head", {1, "<endpoint>"}},
+            {"post_nop", {1, "<endpoint>"}},
+        };
+        if (auto it = arity.find(op.kind); it != arity.end()) {
+            const bool exact = op.kind != "let" && op.kind != "if";  // expressions may tokenise further
+            if (op.operands.size() < it->second.first || (exact && op.operands.size() != it->second.first))
+                fail(op, std::string("expects ") + it->second.second);
+        }
+        if ((op.kind == "endpoint" || op.kind == "local" || op.kind == "remote" || op.kind == "remote_at" ||
+             op.kind == "begin_group") && op.result.empty())
+            fail(op, "defines a value and needs a %name = in front");
         if (op.kind == "put" || op.kind == "post_put") {
             if (op.operands.size() != 3 || !op.has("bytes"))
                 fail(op, "expects <endpoint> <remote> <local> bytes=<n>");

@@ -1,0 +1,123 @@
+// Runs the specializer's C entry points over a corpus of programs and over
+// deterministic corruptions of them.  Built with -fsanitize=address,undefined by
+// tests/test_sanitizers.py: the run passes when every intact program compiles and
+// no corrupted one makes the library crash, read out of bounds or overflow (a
+// diagnostic in the JSON envelope is the expected answer to a corrupted program).
+//
+//   spec_sanitize <corpus-dir> <cases>      cases are <dir>/<i>.prog + <dir>/<i>.opts
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <sstream>
+#include <string>
+#include <vector>
+
+extern "C" {
+char *ab200_spec_compile(const char *program, const char *options);
+char *ab200_spec_plan(const char *kind, const char *request);
+char *ab200_spec_affine(const char *expr);
+void ab200_spec_free(char *text);
+}
+
+namespace {
+
+std::string slurp(const std::string &path) {
+    std::ifstream in(path);
+    std::stringstream ss;
+    ss << in.rdbuf();
+    return ss.str();
+}
+
+bool compiles(const std::string &program, const std::string &options) {
+    char *out = ab200_spec_compile(program.c_str(), options.c_str());
+    const bool ok = out != nullptr && std::strncmp(out, "{\"ok\": true", 11) == 0;
+    ab200_spec_free(out);
+    return ok;
+}
+
+std::vector<std::string> lines_of(const std::string &text) {
+    std::vector<std::string> lines;
+    std::istringstream in(text);
+    for (std::string line; std::getline(in, line);)
+        lines.push_back(line);
+    return lines;
+}
+
+std::string join(const std::vector<std::string> &lines, std::size_t skip, std::size_t limit) {
+    std::string out;
+    for (std::size_t i = 0; i < lines.size() && i < limit; ++i)
+        if (i != skip)
+            out += lines[i] + "\n";
+    return out;
+}
+
+struct Lcg {
+    std::uint64_t state;
+    std::uint32_t next() {
+        state = state * 6364136223846793005ull + 1442695040888963407ull;
+        return static_cast<std::uint32_t>(state >> 33);
+    }
+};
+
+}  // namespace
+
+int main(int argc, char **argv) {
+    if (argc != 3) {
+        std::fprintf(stderr, "usage: spec_sanitize <corpus-dir> <cases>\n");
+        return 2;
+    }
+    const std::string dir = argv[1];
+    const int cases = std::atoi(argv[2]);
+    long accepted = 0, refused = 0;
+    for (int c = 0; c < cases; ++c) {
+        const std::string program = slurp(dir + "/" + std::to_string(c) + ".prog");
+        const std::string options = slurp(dir + "/" + std::to_string(c) + ".opts");
+        if (!compiles(program, options)) {
+            std::fprintf(stderr, "case %d: the intact program does not compile\n", c);
+            return 1;
+        }
+        const std::vector<std::string> lines = lines_of(program);
+        // Every prefix, and the program with each single line removed.
+        for (std::size_t i = 0; i <= lines.size(); ++i) {
+            (compiles(join(lines, lines.size(), i), options) ? accepted : refused)++;
+            if (i < lines.size())
+                (compiles(join(lines, i, lines.size()), options) ? accepted : refused)++;
+        }
+        // Byte-level damage: digits blown up, separators swapped, bytes dropped.
+        Lcg rng{0x9e3779b97f4a7c15ull + static_cast<std::uint64_t>(c)};
+        for (int round = 0; round < 300; ++round) {
+            std::string damaged = program;
+            const int edits = 1 + static_cast<int>(rng.next() % 4);
+            for (int e = 0; e < edits && !damaged.empty(); ++e) {
+                const std::size_t at = rng.next() % damaged.size();
+                switch (rng.next() % 5) {
+                case 0: damaged.erase(at, 1 + rng.next() % 8); break;
+                case 1: damaged.insert(at, "99999999999999999999"); break;
+                case 2: damaged[at] = "=,%[](){}-\" \n"[rng.next() % 13]; break;
+                case 3: damaged.insert(at, damaged.substr(at, rng.next() % 40)); break;
+                default: damaged[at] = static_cast<char>(rng.next() & 0x7f); break;
+                }
+            }
+            (compiles(damaged, options) ? accepted : refused)++;
+        }
+        // The options string is parsed by the library too.
+        for (const char *bad : {"backend=", "backend=nosuch", "inline_bytes=x", "queue_capacity=-1",
+                                "enable=,,,", "stop_after=form-batches", "completion_interval=0"})
+            (compiles(program, bad) ? accepted : refused)++;
+    }
+    for (const char *expr : {"pid", "(pid + 3) % 8", "lane*4+peer", "pid*", "((((", "", "pid % 0",
+                             "99999999999999999999*pid", "pid + pid + pid", "-pid"}) {
+        char *out = ab200_spec_affine(expr);
+        ab200_spec_free(out);
+    }
+    for (const char *kind : {"plan-shapes", "plan-endpoints", "plan-storage", "plan-transport",
+                             "simplify-dataflow", "nosuch", ""})
+        for (const char *request : {"", "{", "{}", "[]", "{\"a\":", "{\"min\":1,\"max\":0}", "null"}) {
+            char *out = ab200_spec_plan(kind, request);
+            ab200_spec_free(out);
+        }
+    std::printf("corrupted programs: %ld accepted, %ld refused\n", accepted, refused);
+    return 0;
+}

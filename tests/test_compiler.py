@@ -189,6 +189,15 @@ def test_verifier_diagnostics():
         compilation("gin").__enter__()
     with pytest.raises(CompileError, match="written for transport 'rdma'"):
         compile_program("program p backend=rdma\n")
+    # Operations that the passes index by position are refused when they come up short.
+    with pytest.raises(CompileError, match="remote: expects <table> <peer>"):
+        compile_program("program p backend=p2p\n%e = endpoint t 0\n%r = remote t\n")
+    with pytest.raises(CompileError, match="endpoint: expects <table> <index>"):
+        compile_program("program p backend=p2p\n%e = endpoint t\n")
+    with pytest.raises(CompileError, match="needs a %name = in front"):
+        compile_program("program p backend=p2p\nendpoint t 0\n")
+    with pytest.raises(CompileError, match="for: expects <var> <begin> <end>"):
+        compile_program("program p backend=p2p\nfor i 4 {\n}\n")
 
 
 def test_passes_grammar_and_key_coverage(monkeypatch):
