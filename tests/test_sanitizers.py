@@ -19,9 +19,9 @@ NATIVE = Path(__file__).resolve().parent / "native"
 pytestmark = pytest.mark.skipif(shutil.which("g++") is None, reason="needs g++")
 
 
-def _build(out: Path, sources, sanitize: str, extra=()):
+def _build(out: Path, sources, sanitize: str, extra=(), libs=()):
     cmd = ["g++", "-std=c++17", "-O1", "-g", f"-fsanitize={sanitize}", "-fno-omit-frame-pointer",
-           f"-I{PKG / 'include'}", *extra, *map(str, sources), "-o", str(out), "-pthread"]
+           f"-I{PKG / 'include'}", *extra, *map(str, sources), "-o", str(out), "-pthread", *libs]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0 and "sanitize" in proc.stderr and "cannot find" in proc.stderr:
         pytest.skip("the sanitizer runtime is not installed")
@@ -53,3 +53,22 @@ def test_specializer_survives_corrupted_programs_under_asan_ubsan(tmp_path):
     proc = subprocess.run([str(exe), str(tmp_path), str(cases)], capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, (proc.stdout + proc.stderr)[-6000:]
     assert "refused" in proc.stdout and "ERROR" not in proc.stderr
+
+
+def _cuda_home() -> Path:
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    return Path(nvcc).resolve().parent.parent
+
+
+def test_proxy_ring_with_many_producers_is_race_free_under_tsan(tmp_path):
+    cuda = _cuda_home()
+    if not (cuda / "include" / "cuda_runtime.h").exists():
+        pytest.skip("the CUDA headers are not installed")
+    exe = tmp_path / "proxy_ring_stress"
+    # The runtime's source is host C++ (no kernels): g++ compiles it as such.
+    _build(exe, ["-x", "c++", PKG / "csrc" / "host" / "runtime_core.cu", NATIVE / "proxy_ring_stress.cpp"],
+           "thread", extra=[f"-I{cuda / 'include'}"],
+           libs=[f"-L{cuda / 'lib64'}", f"-Wl,-rpath,{cuda / 'lib64'}", "-lcudart", "-ldl"])
+    proc = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, (proc.stdout + proc.stderr)[-6000:]
+    assert "failures: 0" in proc.stdout and "ThreadSanitizer" not in proc.stderr
