@@ -34,7 +34,8 @@ from .runtime import (AllocationHandle, AllocationProvider, Endpoint, EndpointMe
                       EndpointTable, LocalBuffer,
                       LocalEndpoint, Provider, RegisteredBuffer, RemoteBuffer, RemoteHandle, Runtime,
                       Transport, available_transports, connection_info_from_bytes, connection_transport,
-                      provider_caps)
+                      PortAddress, probe_providers, provider_caps, query_port_address, select_device,
+                      select_gid_index)
 from .shapes import ShapeFamilyPlan, plan_shape_family
 from .world import AutoTransportPolicy, LocalRegion, PeerRegionTable, TopologyInfo, World
 

@@ -80,7 +80,7 @@ def _targets() -> dict[str, dict]:
         "runtime": {
             "sources": host,
             "compile": [_nvcc(), *_ARCH, *common, "-c"],
-            "link": [_nvcc(), *_ARCH, "-shared", "-Xcompiler", "-fPIC", "-lpthread"],
+            "link": [_nvcc(), *_ARCH, "-shared", "-Xcompiler", "-fPIC", "-lpthread", "-ldl"],
         },
         "spec": {
             "sources": spec,

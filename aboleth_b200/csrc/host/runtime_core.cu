@@ -229,6 +229,9 @@ extern "C" {
 
 const char *aboleth_runtime_last_error() { return g_error.c_str(); }
 
+// Lets the runtime's other translation units report through the same thread-local string.
+void ab200_set_last_error(const char *message) { g_error = message ? message : ""; }
+
 std::uint32_t aboleth_runtime_provider_caps() {
     // No verbs, mlx5, EFA, libfabric, HIP or Ionic provider is compiled in.
     return visible_gpus() > 0 ? kAbolethProviderCuda : 0u;
@@ -264,14 +267,6 @@ int aboleth_runtime_destroy(void *runtime) {
     }
     delete rt;
     return 0;
-}
-
-int aboleth_runtime_select_device(int, char *, std::size_t) {
-    return fail("no verbs provider: there is no HCA to select");
-}
-
-int aboleth_runtime_select_gid_index(const char *, int) {
-    return fail("no verbs provider: there is no GID table to read");
 }
 
 void *aboleth_runtime_register_buffer(void *runtime, int gpu_index, void *address,

@@ -8,8 +8,9 @@
 // reference implements with ibverbs is implemented here with CUDA: a
 // registration is an entry in the runtime's key table (plus a CUDA IPC export
 // on request), and every queue transport is served by the host-proxy ring.
-// NIC-only entry points (HCA/GID selection, endpoint pairs over mlx5/EFA)
-// report "unavailable" through last_error.
+// Adapter / GID / port selection is answered from sysfs rather than through a
+// verbs context; endpoint pairs over mlx5/EFA report "unavailable" through
+// last_error.
 #pragma once
 
 #include <cstddef>
@@ -33,8 +34,19 @@ int aboleth_runtime_link_layer(void *runtime);
 int aboleth_runtime_lid(void *runtime);
 int aboleth_runtime_destroy(void *runtime);
 
+// Adapter, GID and port selection without a runtime, answered from sysfs
+// (csrc/host/providers.cpp): the mlx5 adapter sharing the deepest PCI path with
+// CUDA ordinal `gpu_index` (ABOLETH_HCA overrides; negative = first adapter), the
+// GID index a verbs client would address the fabric through (InfiniBand 0, RoCE
+// prefers a v2 entry, ABOLETH_GID_INDEX overrides; port 0 = ABOLETH_PORT or 1), and
+// the local address of an RC path (link layer 1 InfiniBand / 2 Ethernet, path MTU
+// as an ibv_mtu enumerator, honouring ABOLETH_PATH_MTU).  Each returns -1 with
+// aboleth_runtime_last_error() when the machine presents no such adapter.
 int aboleth_runtime_select_device(int gpu_index, char *name_out, std::size_t name_capacity);
 int aboleth_runtime_select_gid_index(const char *device_name, int port);
+int aboleth_runtime_query_port_address(const char *device_name, int port, std::uint16_t *lid_out,
+                                       std::uint8_t *link_layer_out, std::uint8_t *gid_out16,
+                                       int *gid_index_out, std::uint32_t *path_mtu_out);
 
 void *aboleth_runtime_register_buffer(void *runtime, int gpu_index, void *address,
                                       std::size_t bytes, std::uint64_t generation);
@@ -66,6 +78,14 @@ int aboleth_runtime_local_endpoint_gpu_resident_queues(void *endpoint, std::uint
 int aboleth_runtime_destroy_local_endpoint(void *endpoint);
 
 // ---- additions of this build (no counterpart in the reference C ABI) --------
+
+// What the machine presents, whether or not this build has a code path for it:
+// a kAbolethProvider* bit is set when the provider's library resolves through
+// dlopen (never a link-time dependency) and a device for it is listed.
+// aboleth_runtime_provider_caps() is this mask restricted to the providers this
+// build can drive (CUDA).
+std::uint32_t ab200_probe_providers();
+void ab200_set_last_error(const char *message);
 
 // CUDA IPC plumbing for World.register / exchange_regions.
 int ab200_ipc_export(const void *address, void *handle64, std::uint64_t *base,

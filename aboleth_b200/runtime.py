@@ -108,6 +108,12 @@ def _lib():
     lib.ab200_endpoint_descriptor.argtypes = [c.c_void_p, c.c_void_p]
     lib.ab200_endpoint_inject_failure.argtypes = [c.c_void_p, c.c_uint64, c.c_int]
     lib.ab200_endpoint_stats.argtypes = [c.c_void_p, c.POINTER(c.c_uint64)]
+    lib.ab200_probe_providers.restype = c.c_uint32
+    lib.aboleth_runtime_select_device.argtypes = [c.c_int, c.c_char_p, c.c_size_t]
+    lib.aboleth_runtime_select_gid_index.argtypes = [c.c_char_p, c.c_int]
+    lib.aboleth_runtime_query_port_address.argtypes = [
+        c.c_char_p, c.c_int, c.POINTER(c.c_uint16), c.POINTER(c.c_uint8), c.c_void_p,
+        c.POINTER(c.c_int), c.POINTER(c.c_uint32)]
     lib._ab_typed = True
     return lib
 
@@ -119,6 +125,67 @@ def last_error() -> str:
 def provider_caps() -> int:
     """Bit mask of providers that are compiled in, loadable and present."""
     return int(_lib().aboleth_runtime_provider_caps())
+
+
+def probe_providers() -> int:
+    """Bit mask of providers whose library resolves through ``dlopen`` and for which
+    the machine lists a device, whether or not this build can drive them.
+
+    :func:`provider_caps` is this mask restricted to what the build has a code path
+    for (CUDA); the difference tells a caller that an adapter is present but would
+    be served through the host-proxy ring.
+    """
+    return int(_lib().ab200_probe_providers())
+
+
+def select_device(gpu_index: int = -1) -> str:
+    """Name of the mlx5 adapter nearest (deepest shared PCI path) to CUDA ordinal
+    ``gpu_index``; ``ABOLETH_HCA`` overrides, a negative ordinal takes the first one.
+    Raises :class:`RuntimeError` when the machine lists no such adapter
+    (reference: ``aboleth_runtime_select_device``, include/aboleth/runtime_c.h:142-150).
+    """
+    buffer = ctypes.create_string_buffer(64)
+    if _lib().aboleth_runtime_select_device(int(gpu_index), buffer, len(buffer)) != 0:
+        raise RuntimeError(last_error())
+    return buffer.value.decode()
+
+
+def select_gid_index(device_name: str = "", port: int = 0) -> int:
+    """GID index a verbs client would use on ``device_name``: 0 on InfiniBand, a
+    RoCE v2 entry on Ethernet, ``ABOLETH_GID_INDEX`` over both."""
+    index = _lib().aboleth_runtime_select_gid_index(device_name.encode(), int(port))
+    if index < 0:
+        raise RuntimeError(last_error())
+    return int(index)
+
+
+@dataclass(frozen=True)
+class PortAddress:
+    """Local end of a reliable-connected path (``aboleth_runtime_query_port_address``)."""
+    lid: int
+    link_layer: int  # 1 InfiniBand (addressed by LID), 2 Ethernet (addressed by GRH)
+    gid: bytes
+    gid_index: int
+    path_mtu: int  # ibv_mtu enumerator: 1 = 256 bytes ... 5 = 4096 bytes
+
+    @property
+    def is_global(self) -> bool:
+        return self.link_layer != 1
+
+    @property
+    def path_mtu_bytes(self) -> int:
+        return 128 << self.path_mtu
+
+
+def query_port_address(device_name: str = "", port: int = 0) -> PortAddress:
+    lid, layer = ctypes.c_uint16(), ctypes.c_uint8()
+    gid = (ctypes.c_uint8 * 16)()
+    index, mtu = ctypes.c_int(), ctypes.c_uint32()
+    if _lib().aboleth_runtime_query_port_address(device_name.encode(), int(port), ctypes.byref(lid),
+                                                 ctypes.byref(layer), gid, ctypes.byref(index),
+                                                 ctypes.byref(mtu)) != 0:
+        raise RuntimeError(last_error())
+    return PortAddress(lid.value, layer.value, bytes(gid), index.value, mtu.value)
 
 
 def available_transports() -> tuple[Transport, ...]:
