@@ -45,7 +45,16 @@ _WIRE_BACK = {code: Transport(name) for name, code in WIRE_CODES.items()}
 
 
 def _node_identity() -> str:
-    """``hostname:boot_id``: two containers with one hostname stay distinct."""
+    """``hostname:boot_id``: two containers with one hostname stay distinct.
+
+    ``ABOLETH_NODE_IDENTITY`` replaces it, so that ranks of one host can stand in for
+    several nodes (the reference tests its multi-node bring-up the same way, with two
+    "nodes" on one machine: test/CMakeLists.txt ``hardware.world-multinode-local``).
+    """
+    import os
+    forced = os.environ.get("ABOLETH_NODE_IDENTITY", "")
+    if forced:
+        return forced
     host = socket.gethostname()
     try:
         boot = UUID(pathlib.Path("/proc/sys/kernel/random/boot_id").read_text().strip())

@@ -150,3 +150,34 @@ def test_benchmark_report_tables_and_regression_check(tmp_path, capsys):
     out = capsys.readouterr().out
     assert "fused_us: 100 -> 125" in out and "op=rs" not in out
     assert report.main(["--compare", "--tolerance", "0.5", str(tmp_path / "ref"), str(tmp_path / "new")]) == 0
+
+
+def test_slurm_launcher_derives_the_rank_environment(tmp_path):
+    import subprocess
+    import sys
+
+    from aboleth_b200.utils import launch
+
+    assert launch.expand_nodelist("gpu[01-03,07],login1") == ["gpu01", "gpu02", "gpu03", "gpu07", "login1"]
+    assert launch.expand_nodelist("n[9-11]-ib") == ["n9-ib", "n10-ib", "n11-ib"]
+    assert launch.expand_nodelist("solo") == ["solo"]
+    with pytest.raises(ValueError, match="unbalanced"):
+        launch.expand_nodelist("gpu[01-03")
+    with pytest.raises(ValueError, match="cannot read the range"):
+        launch.expand_nodelist("gpu[a-b]")
+    slurm = {"SLURM_JOB_NODELIST": "gpu[01-08]", "SLURM_STEP_NODELIST": "gpu[05-06]", "SLURM_PROCID": "9",
+             "SLURM_NTASKS": "16", "SLURM_LOCALID": "1", "SLURM_JOB_ID": "4123456"}
+    env = launch.slurm_environment(slurm)
+    # The store lives on the first node of the step, not of the job.
+    assert env["MASTER_ADDR"] == "gpu05" and env["MASTER_PORT"] == "23456"
+    assert (env["RANK"], env["WORLD_SIZE"], env["LOCAL_RANK"]) == ("9", "16", "1")
+    assert launch.slurm_environment({**slurm, "MASTER_PORT": "29999"})["MASTER_PORT"] == "29999"
+    with pytest.raises(RuntimeError, match="run this through srun"):
+        launch.slurm_environment({})
+    # End to end: the command sees the derived variables.
+    import os
+    out = subprocess.run([sys.executable, "-m", "aboleth_b200.utils.launch", "--", sys.executable, "-c",
+                          "import os; print(os.environ['RANK'], os.environ['MASTER_ADDR'])"],
+                         env={**os.environ, **slurm}, capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0 and out.stdout.split() == ["9", "gpu05"], out.stderr
+    assert launch.main([]) == 2

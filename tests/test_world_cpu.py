@@ -55,6 +55,36 @@ def test_world_exchange_three_cpu_ranks(transport, kind):
         assert out["transport"] == ("p2p" if kind == 1 else "proxy")
 
 
+def _two_node_rank(rank, world_size, transport):
+    import os
+    os.environ["ABOLETH_NODE_IDENTITY"] = f"node{rank // 2}:fake-boot-id"
+    boot = TcpStoreBootstrap.from_env(timeout=30)
+    with World(rank, world_size, device="cpu", bootstrap=boot) as world:
+        try:
+            world.connect_all(transport, remote_transport="proxy")
+        except ValueError as error:
+            return {"error": str(error)}
+        arena = world.runtime.allocate(256)
+        reg = world.register(arena)
+        table = world.exchange_regions([world.region("recv", reg, offset=0, length=256)], tag="n")
+        return {"kinds": [h & 7 for h in table.endpoint_handles.tolist()], "geo": world.transport_geography,
+                "transport": world.transport.value}
+
+
+def test_two_fake_nodes_on_one_host_mix_transports():
+    """Four ranks, two per "node": peer memory inside a node, the ring across nodes."""
+    results = run_ranks(_two_node_rank, 4, "auto")
+    assert all(k == "ok" for k, _ in results.values()), results
+    for rank in range(4):
+        kinds = results[rank][1]["kinds"]
+        for peer in range(4):
+            expected = 0 if peer == rank else (1 if peer // 2 == rank // 2 else 2)
+            assert kinds[peer] == expected, (rank, kinds)
+    # Asking for peer memory to a rank of another node is refused on every rank.
+    refused = run_ranks(_two_node_rank, 4, "p2p")
+    assert all(k == "ok" and "is not on the local node" in v["error"] for k, v in refused.values()), refused
+
+
 def test_auto_policy_threshold():
     policy = AutoTransportPolicy()
     assert policy.select(can_p2p=True, payload_bytes=16 * 1024, remote_transport=Transport.RDMA) == Transport.P2P
