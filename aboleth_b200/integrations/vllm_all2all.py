@@ -116,14 +116,9 @@ class AbolethPrepareAndFinalize:
 
 
 def register_with_vllm() -> bool:
-    """Expose the backend name to an installed vLLM if its registry can be found.
+    """Give an installed vLLM the ``aboleth`` backend (see :mod:`.vllm_plugin`).
     Returns False (and changes nothing) when vLLM is absent or its layout differs."""
-    try:
-        from vllm.distributed.device_communicators import all2all  # type: ignore
-    except Exception:  # noqa: BLE001
-        return False
-    registry = getattr(all2all, "ALL2ALL_BACKENDS", None)
-    if isinstance(registry, dict):
-        registry["aboleth"] = AbolethAll2AllManager
-        return True
-    return False
+    from . import vllm_plugin
+
+    report = vllm_plugin.install()
+    return report["classes"] and report["manager_registry"]
