@@ -79,3 +79,45 @@ def grouped_gemm_bf16(a: torch.Tensor, w: torch.Tensor, counts: torch.Tensor,
     call("ab_grouped_gemm_bf16", ptr(a), ptr(w), ptr(out), ptr(counts), ptr(offsets), experts,
          a.shape[0], n, k, ptr(gemm_status(a.device)), stream_ptr())
     return out
+
+
+declare("ab_dequant_block_scaled", [_VP, _VP, _VP] + [_I] * 4 + [ctypes.c_longlong] * 2 + [_I, _VP])
+
+
+def dequant_block_scaled(q: torch.Tensor, scales: torch.Tensor, *, block: tuple[int, int] = (1, 128),
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[r, c] = q[r, c] * scales[r // block[0], c // block[1]]`` as bf16.
+
+    ``q`` is ``torch.float8_e4m3fn`` ``[rows, cols]``; ``scales`` is fp32
+    ``[ceil(rows / block[0]), cols / block[1]]``: ``(1, 128)`` for activations (what
+    :func:`aboleth_b200.ops.moe_ops.quant_fp8` and the dispatch kernel produce), ``(128, 128)``
+    for weights.  Exact when the scales are powers of two.
+    """
+    assert q.dtype == torch.float8_e4m3fn and q.is_cuda and q.dim() == 2 and q.stride(1) == 1
+    assert scales.dtype == torch.float32 and scales.dim() == 2 and scales.stride(1) == 1
+    rows, cols = q.shape
+    row_block, col_block = block
+    assert scales.shape[0] == -(-rows // row_block) and scales.shape[1] == -(-cols // col_block), \
+        f"scales {tuple(scales.shape)} do not cover {tuple(q.shape)} in blocks of {block}"
+    if out is None:
+        out = torch.empty(rows, cols, dtype=torch.bfloat16, device=q.device)
+    assert out.dtype == torch.bfloat16 and out.shape == (rows, cols) and out.stride(1) == 1
+    call("ab_dequant_block_scaled", ptr(q), ptr(scales), ptr(out), rows, cols, row_block, col_block,
+         q.stride(0), out.stride(0), scales.stride(0), stream_ptr())
+    return out
+
+
+def gemm_e4m3_block_scaled(a: torch.Tensor, a_scales: torch.Tensor, b: torch.Tensor, b_scales: torch.Tensor, *,
+                           a_block: tuple[int, int] = (1, 128), b_block: tuple[int, int] = (128, 128),
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[M, N] = (a * a_scales) @ (b * b_scales).T`` for block-scaled e4m3 operands (1 x 128
+    activation scales, 128 x 128 weight scales by default); bf16 output, fp32 accumulation.
+
+    The operands are expanded to bf16 by :func:`dequant_block_scaled` and multiplied by the
+    tcgen05 bf16 GEMM: the result carries the block scales exactly (for power-of-two scales) at
+    bf16 tensor-core rate and fp8 storage.  A weight that is used repeatedly should be expanded
+    once with :func:`dequant_block_scaled` and passed to :func:`gemm_bf16`.
+    """
+    assert a.shape[1] == b.shape[1]
+    return gemm_bf16(dequant_block_scaled(a, a_scales, block=a_block),
+                     dequant_block_scaled(b, b_scales, block=b_block), out)

@@ -100,3 +100,46 @@ def test_gemm_e4m3_matches_fp32(m, n, k):
     got = gemm_e4m3(ai, bi).float()
     torch.cuda.synchronize()
     assert torch.equal(got, (ai.float() @ bi.float().t()).to(torch.bfloat16).float())
+
+
+@pytest.mark.parametrize("m,n,k,pow2", [(256, 384, 512, True), (1000, 520, 384, False)])
+def test_block_scaled_e4m3_gemm_matches_fp32(m, n, k, pow2):
+    """1 x 128 activation scales and 128 x 128 weight scales: the expansion to bf16 is the fp32
+    product rounded once (exact for power-of-two scales), and the GEMM over it matches an fp32
+    matmul of the dequantised operands."""
+    from aboleth_b200.ops import check_gemm_status
+    from aboleth_b200.ops.gemm import dequant_block_scaled, gemm_e4m3_block_scaled
+    from aboleth_b200.ops.moe_ops import quant_fp8
+
+    g = torch.Generator(device="cuda").manual_seed(m * 7 + n)
+    x = torch.randn(m, k, generator=g, device="cuda").to(torch.bfloat16)
+    a_q, a_s = quant_fp8(x, round_scale=pow2)
+    w = 0.02 * torch.randn(n, k, generator=g, device="cuda")
+    rows_b, cols_b = -(-n // 128), k // 128
+    padded = torch.zeros(rows_b * 128, k, device="cuda")
+    padded[:n] = w
+    amax = padded.view(rows_b, 128, cols_b, 128).abs().amax(dim=(1, 3)).clamp_min(1e-10)
+    b_s = amax / 448.0
+    if pow2:
+        b_s = torch.exp2(torch.ceil(torch.log2(b_s)))
+    b_full = b_s.repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)
+    b_q = (w / b_full).clamp(-448, 448).to(torch.float8_e4m3fn)
+    a_full = a_s.repeat_interleave(128, dim=1)
+
+    a_deq = dequant_block_scaled(a_q, a_s)
+    b_deq = dequant_block_scaled(b_q, b_s.contiguous(), block=(128, 128))
+    torch.cuda.synchronize()
+    assert torch.equal(a_deq, (a_q.float() * a_full).to(torch.bfloat16))
+    assert torch.equal(b_deq, (b_q.float() * b_full).to(torch.bfloat16))
+    if pow2:  # nothing was rounded
+        assert torch.equal(a_deq.float(), a_q.float() * a_full)
+
+    out = gemm_e4m3_block_scaled(a_q, a_s, b_q, b_s.contiguous())
+    torch.cuda.synchronize()
+    check_gemm_status(out.device)
+    want = (a_q.float() * a_full) @ (b_q.float() * b_full).t()
+    assert _rel_err(out, want) < 5e-3
+    # A strided view (rows of a wider buffer) goes through the same kernel.
+    wide = torch.zeros(m, k + 64, dtype=torch.float8_e4m3fn, device="cuda")
+    wide[:, :k] = a_q
+    assert torch.equal(dequant_block_scaled(wide[:, :k], a_s), a_deq)
