@@ -116,6 +116,15 @@ class AllGatherGemm:
              self.k, self.push_parts, phases, stream_ptr())
         return out
 
+    def block_scaled(self, a_q: torch.Tensor, a_scales: torch.Tensor, b_local: torch.Tensor,
+                     out: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
+        """Block-scaled e4m3 activations (``a_q`` with 1 x 128 fp32 ``a_scales``): this rank's shard is
+        expanded to bf16 by :func:`aboleth_b200.ops.dequant_block_scaled` and then gathered and
+        multiplied as in :meth:`__call__`.  ``b_local`` is bf16: expand a block-scaled weight once,
+        with the same function and ``block=(128, 128)``."""
+        from ..ops.gemm import dequant_block_scaled
+        return self(dequant_block_scaled(a_q, a_scales), b_local, out, **kw)
+
     def check(self) -> None:
         status = self.status.tolist()
         if status[0]:
@@ -176,6 +185,13 @@ class GemmReduceScatter:
              (self.epoch + 1) // 2, self.rank, self.world_size, self.m_local, self.n, a.shape[1],
              phases, stream_ptr())
         return out
+
+    def block_scaled(self, a_q: torch.Tensor, a_scales: torch.Tensor, b_local: torch.Tensor,
+                     out: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
+        """As :meth:`__call__` for block-scaled e4m3 activations (1 x 128 fp32 scales), expanded to
+        bf16 first; ``b_local`` is bf16 (a block-scaled weight is expanded once, ahead of time)."""
+        from ..ops.gemm import dequant_block_scaled
+        return self(dequant_block_scaled(a_q, a_scales), b_local, out, **kw)
 
     def check(self) -> None:
         status = self.status.tolist()

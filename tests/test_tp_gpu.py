@@ -44,3 +44,38 @@ def test_gemm_reduce_scatter_matches_fp32(world, m_local, k_local, n):
         group.rs[r].check()
         want = total[r * m_local:(r + 1) * m_local]
         assert _rel(outs[r], want) < 8e-3  # partials travel as bf16
+
+
+def test_block_scaled_activations_through_both_fused_ops():
+    """e4m3 activations with 1 x 128 scales enter the fused kernels through the bf16 expansion."""
+    from aboleth_b200.ops.moe_ops import quant_fp8
+    from aboleth_b200.parallel import LocalTpGroup
+    from aboleth_b200.parallel.tp import CONSUME, PRODUCE
+
+    world, m_local, k, n = 2, 256, 256, 256
+    g = torch.Generator(device="cuda").manual_seed(5)
+    group = LocalTpGroup(world, m_local, k, n)
+    b = [torch.randn(n, k, generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+
+    shards = [quant_fp8(torch.randn(m_local, k, generator=g, device="cuda").to(torch.bfloat16), round_scale=True)
+              for _ in range(world)]
+    outs = [op.block_scaled(*shards[r], b[r], phases=PRODUCE) for r, op in enumerate(group.ag)]
+    outs = [op.block_scaled(*shards[r], b[r], outs[r], phases=CONSUME, advance=False)
+            for r, op in enumerate(group.ag)]
+    torch.cuda.synchronize()
+    full = torch.cat([q.float() * s.repeat_interleave(128, dim=1) for q, s in shards])
+    for r in range(world):
+        group.ag[r].check()
+        assert _rel(outs[r], full @ b[r].float().t()) < 5e-3
+
+    parts = [quant_fp8(torch.randn(world * m_local, k, generator=g, device="cuda").to(torch.bfloat16))
+             for _ in range(world)]
+    outs = [op.block_scaled(*parts[r], b[r], phases=PRODUCE) for r, op in enumerate(group.rs)]
+    outs = [op.block_scaled(*parts[r], b[r], outs[r], phases=CONSUME, advance=False)
+            for r, op in enumerate(group.rs)]
+    torch.cuda.synchronize()
+    total = sum((parts[r][0].float() * parts[r][1].repeat_interleave(128, dim=1)) @ b[r].float().t()
+                for r in range(world))
+    for r in range(world):
+        group.rs[r].check()
+        assert _rel(outs[r], total[r * m_local:(r + 1) * m_local]) < 8e-3
