@@ -319,3 +319,24 @@ def test_unchained_puts_coalesce_on_the_ring_and_share_one_release_on_peer_memor
         polled = compile_program(_independent_puts(poll_first=True))
     # the polled first put keeps its fence; the other seven are placed by the signal's barrier + release
     assert (polled.facts["barriers"], polled.facts["system_fences"], polled.facts["deferred_placements"]) == (2, 1, 7)
+
+
+def test_pipeline_is_a_fixed_point_on_its_own_output():
+    """Scheduled IR fed back through the same pipeline comes out unchanged, and lowers to the same
+    CUDA C++ (the reference runs each pass twice under its IDEMPOTENT test option,
+    test/compiler/CMakeLists.txt)."""
+    from pathlib import Path
+
+    goldens = Path(__file__).resolve().parent / "goldens"
+    checked = 0
+    for scheduled in sorted(goldens.glob("*.ir")):
+        _, backend, variant, _ = scheduled.name.split(".")
+        text = scheduled.read_text()
+        with compilation(backend, rank=0, world_size=2, passes=variant):
+            again = compile_program(text)
+        assert again.ir == text, scheduled.name
+        assert again.cuda == scheduled.with_suffix(".cu").read_text(), scheduled.name
+        assert all(count == 0 for name, count in again.passes.items()
+                   if name in ("form-batches", "coalesce-submissions")), (scheduled.name, again.passes)
+        checked += 1
+    assert checked >= 80
