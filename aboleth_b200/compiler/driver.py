@@ -26,7 +26,7 @@ class CompileError(ValueError):
 def _lib() -> ctypes.CDLL:
     lib = _native.load("spec")
     if not getattr(lib, "_ab_typed", False):
-        for name in ("ab200_spec_compile", "ab200_spec_plan"):
+        for name in ("ab200_spec_compile", "ab200_spec_plan", "ab200_spec_materialize"):
             fn = getattr(lib, name)
             fn.restype = ctypes.c_void_p
             fn.argtypes = [ctypes.c_char_p, ctypes.c_char_p]
@@ -87,9 +87,24 @@ class CompiledProgram:
     source: str = field(repr=False, default="")
 
 
+def materialize_phases(program_text: str, plan_text: str) -> str:
+    """``materialize-transport-phase``: replace every ``invoke_phase <id> <args...>`` of the program
+    by the body of the fragment with that program id in the external transport program ``plan_text``.
+
+    The plan is a program of its own (``program <name> kind=transport_program``) whose body holds
+    ``phase <name> program_id=<id> interval=<k> capacities=<c0,c1,...>`` records and
+    ``fragment <name> program_id=<id> params=<p:type,...> { ... }`` definitions.  Planned waits of
+    the spliced body that carry no reuse distance receive the smallest completion interval and the
+    smallest peer queue capacity of the phases bound to that id
+    (reference: compiler/lib/Transforms/MaterializeTransportPhase.cpp:28-217).
+    """
+    return _call(_lib().ab200_spec_materialize, program_text, plan_text)["ir"]
+
+
 def compile_program(program: Union[str, ProgramBuilder], options: Optional[CompileOptions] = None,
-                    **overrides) -> CompiledProgram:
-    """Run the pass pipeline and the lowering for the current (or given) options."""
+                    *, plan: Optional[str] = None, **overrides) -> CompiledProgram:
+    """Run the pass pipeline and the lowering for the current (or given) options.  ``plan`` is the
+    external transport program for a kernel that contains ``invoke_phase`` operations."""
     from dataclasses import replace
 
     opts = options or current_options()
@@ -97,6 +112,8 @@ def compile_program(program: Union[str, ProgramBuilder], options: Optional[Compi
         opts = replace(opts, **overrides)
     text = program if isinstance(program, str) else program.text(
         backend=opts.backend, rank=opts.rank, world_size=opts.world_size)
+    if plan is not None:
+        text = materialize_phases(text, plan)
     result = _call(_lib().ab200_spec_compile, text, opts.to_native())
     name = text.split()[1] if text.startswith("program") else "program"
     compiled = CompiledProgram(name=name, ir=result["ir"], cuda=result.get("cuda"),

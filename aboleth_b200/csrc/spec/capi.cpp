@@ -4,6 +4,9 @@
 //       parse -> verify -> pass pipeline -> verify -> lower; returns a JSON object
 //       {"ok", "error", "ir", "cuda", "facts", "passes"} that the caller frees with
 //       ab200_spec_free().
+//   char *ab200_spec_materialize(const char *program, const char *plan)
+//       materialize-transport-phase: every invoke_phase of `program` replaced by the
+//       fragment of the external transport program `plan`; {"ok", "error", "ir", "invocations"}.
 //   char *ab200_spec_plan(const char *kind, const char *request)
 //       the planning passes (plan-shapes, plan-endpoints, plan-storage,
 //       plan-transport, simplify-dataflow); JSON in the same envelope.
@@ -43,6 +46,11 @@ char *ab200_spec_compile(const char *program_text, const char *options_text) {
         else if (program.get("backend") != options.backend)
             throw Error("program was written for transport '" + program.get("backend") +
                         "' but is being compiled for '" + options.backend + "'");
+        walk(program.body, [](const Op &op) {
+            if (op.kind == "invoke_phase")
+                throw Error("line " + std::to_string(op.line) +
+                            ": invoke_phase needs its external transport program: materialise the phases first");
+        });
         verify(program);
         struct Step {
             const char *name;
@@ -84,6 +92,25 @@ char *ab200_spec_compile(const char *program_text, const char *options_text) {
             j.key("cuda").value(lowered.cuda);
             j.key("facts").raw(lowered.facts);
         }
+        j.end_object();
+        return dup(j.str());
+    } catch (const std::exception &error) {
+        return dup(envelope_error(error.what()));
+    }
+}
+
+char *ab200_spec_materialize(const char *program_text, const char *plan_text) {
+    using namespace spec;
+    try {
+        Program program = parse(program_text ? program_text : "");
+        const Program plan = parse(plan_text ? plan_text : "");
+        const int count = materialize_transport_phase(program, plan);
+        verify(program);
+        Json j;
+        j.begin_object();
+        j.key("ok").value(true);
+        j.key("ir").value(print(program));
+        j.key("invocations").value(count);
         j.end_object();
         return dup(j.str());
     } catch (const std::exception &error) {

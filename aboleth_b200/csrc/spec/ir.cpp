@@ -459,8 +459,9 @@ void verify_block(const std::vector<Op> &ops, const Scope *parent) {
         } else if (op.kind == "wait" || op.kind == "planned_wait" || op.kind == "poll") {
             if (op.operands.size() != 1 || scope.find(op.operands[0]) == nullptr)
                 fail(op, "expects one token defined earlier");
-            if (op.kind == "planned_wait" && (!op.has("iteration") || !op.has("reuse")))
-                fail(op, "needs iteration= and reuse=");
+            // The bound is a reuse distance, or an interval a transport plan resolved already.
+            if (op.kind == "planned_wait" && (!op.has("iteration") || !(op.has("reuse") || op.has("interval"))))
+                fail(op, "needs iteration= and reuse= (or a planned interval=)");
         } else if (op.kind == "begin_group") {
             open_groups.insert(op.result);
         } else if (op.kind == "wait_group") {

@@ -178,13 +178,21 @@ int materialize_completion(Program &p, const Options &o) {
             slots = std::max(slots, 1u);
             unsigned k = 1;
             if (o.on("completion-planning")) {
-                unsigned bound = static_cast<unsigned>(to_integer(op.get("reuse")));
+                // A wait spliced from a transport plan carries the plan's resolved interval (and
+                // the smallest peer queue) instead of a reuse distance.
+                unsigned bound = static_cast<unsigned>(
+                    std::max(1ll, to_integer(op.has("reuse") ? op.get("reuse") : op.get("interval"))));
                 const unsigned prefer = o.completion_interval ? o.completion_interval
                                                               : o.caps->default_completion_interval;
                 if (prefer)
                     bound = std::min(bound, prefer);
-                if (o.caps->queue_capacity_limited && o.queue_capacity > 1)
-                    bound = std::min(bound, (o.queue_capacity - 1) / slots);
+                unsigned capacity = o.queue_capacity;
+                if (op.has("queue_capacity") && is_integer(op.get("queue_capacity"))) {
+                    const unsigned planned = static_cast<unsigned>(std::max(0ll, to_integer(op.get("queue_capacity"))));
+                    capacity = capacity ? std::min(capacity, planned) : planned;
+                }
+                if (o.caps->queue_capacity_limited && capacity > 1)
+                    bound = std::max(1u, std::min(bound, (capacity - 1) / slots));
                 k = std::max(bit_floor(bound), 1u);
             }
             const std::string iter = op.get("iteration");
@@ -195,6 +203,7 @@ int materialize_completion(Program &p, const Options &o) {
                 pred = "(" + pred + " || (" + op.get("final") + "))";
             op.kind = "wait";
             op.attrs.erase("reuse");
+            op.attrs.erase("queue_capacity");
             op.attrs.erase("final");
             op.attrs["pred"] = pred;
             op.attrs["interval"] = std::to_string(k);

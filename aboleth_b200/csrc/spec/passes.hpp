@@ -51,6 +51,10 @@ int defer_announcement(Program &p, const Options &o);
 int order_producers(Program &p, const Options &o);
 int analyze_issuers(Program &p, const Options &o);
 
+// Splice the fragments of an external transport program (`plan`) into `p` at every
+// invoke_phase; returns the number of invocations replaced (materialize_phase.cpp).
+int materialize_transport_phase(Program &p, const Program &plan);
+
 struct Lowered {
     std::string cuda;   // CUDA C++ translation unit
     std::string facts;  // JSON object

@@ -17,6 +17,7 @@
 extern "C" {
 char *ab200_spec_compile(const char *program, const char *options);
 char *ab200_spec_plan(const char *kind, const char *request);
+char *ab200_spec_materialize(const char *program, const char *plan);
 char *ab200_spec_affine(const char *expr);
 void ab200_spec_free(char *text);
 }
@@ -118,6 +119,34 @@ int main(int argc, char **argv) {
             char *out = ab200_spec_plan(kind, request);
             ab200_spec_free(out);
         }
+    // materialize-transport-phase over a damaged kernel and a damaged external program.
+    {
+        const std::string kernel = slurp(dir + "/phase.kernel"), plan = slurp(dir + "/phase.plan");
+        if (!kernel.empty()) {
+            char *intact = ab200_spec_materialize(kernel.c_str(), plan.c_str());
+            const bool ok = std::strncmp(intact, "{\"ok\": true", 11) == 0;
+            ab200_spec_free(intact);
+            if (!ok) {
+                std::fprintf(stderr, "the intact phase program does not materialise\n");
+                return 1;
+            }
+            Lcg rng{12345};
+            for (int round = 0; round < 2000; ++round) {
+                std::string k = kernel, p = plan;
+                std::string &victim = (round & 1) ? k : p;
+                const std::size_t at = rng.next() % victim.size();
+                switch (rng.next() % 4) {
+                case 0: victim.erase(at, 1 + rng.next() % 12); break;
+                case 1: victim.insert(at, "99999999999999999999"); break;
+                case 2: victim[at] = "=,%:(){} \n"[rng.next() % 11]; break;
+                default: victim.insert(at, victim.substr(at, rng.next() % 30)); break;
+                }
+                char *out = ab200_spec_materialize(k.c_str(), p.c_str());
+                (std::strncmp(out, "{\"ok\": true", 11) == 0 ? accepted : refused)++;
+                ab200_spec_free(out);
+            }
+        }
+    }
     std::printf("corrupted programs: %ld accepted, %ld refused\n", accepted, refused);
     return 0;
 }

@@ -340,3 +340,69 @@ def test_pipeline_is_a_fixed_point_on_its_own_output():
                    if name in ("form-batches", "coalesce-submissions")), (scheduled.name, again.passes)
         checked += 1
     assert checked >= 80
+
+
+_PLAN = """program moe.plan kind=transport_program
+phase dispatch program_id=3 interval=8 capacities=64,32
+phase dispatch.tail program_id=3 interval=4 capacities=128
+fragment send program_id=3 params=table:i64,peer:i64,dst:i64,src:i64,n:i64,it:i64 {
+  %e = endpoint table peer
+  %r = remote_at dst
+  %l = local src
+  %t = put %e %r %l bytes=n
+  planned_wait %t iteration=it
+}
+fragment publish program_id=4 params=ep:i64,flag:i64,epoch:i64 {
+  %e = endpoint ep 0
+  %r = remote_at flag
+  %s = signal %e %r epoch=epoch
+}
+"""
+
+_KERNEL = """program k backend=rdma
+arg endpoints table
+arg slots ptr
+arg staging ptr
+arg flags ptr
+arg count u64
+%mine = endpoint endpoints 1
+for i 0 4 {
+  invoke_phase 3 endpoints (i%2) (slots+i*4096) staging count*16 i
+}
+invoke_phase 4 %mine flags 7
+"""
+
+
+def test_transport_phases_are_spliced_from_an_external_program():
+    from aboleth_b200.compiler import materialize_phases
+
+    ir = materialize_phases(_KERNEL, _PLAN)
+    assert "invoke_phase" not in ir
+    # The loop body is the fragment with its parameters replaced and its values renamed.
+    assert "%e.p0 = endpoint endpoints (i%2)" in ir and "%r.p0 = remote_at (slots+i*4096)" in ir
+    assert "bytes=(count*16)" in ir  # an expression stays one operand
+    # The resolved plan: the smallest interval and the smallest peer capacity of the bound phases.
+    assert "planned_wait %t.p0 interval=4 iteration=i queue_capacity=32" in ir
+    # An endpoint value passed for an i64 placeholder replaces the binding itself.
+    assert "%s.p1 = signal %mine %r.p1 epoch=7" in ir and "endpoint %mine" not in ir
+    # The spliced program goes through the whole pipeline.
+    with compilation("rdma", rank=0, world_size=2):
+        compiled = compile_program(_KERNEL, plan=_PLAN)
+    assert compiled.cuda and "invoke_phase" not in compiled.ir
+    with compilation("rdma", rank=0, world_size=2), pytest.raises(CompileError, match="materialise the phases first"):
+        compile_program(_KERNEL)
+
+    def broken(kernel=_KERNEL, plan=_PLAN):
+        return lambda: materialize_phases(kernel, plan)
+
+    for make, message in (
+            (broken(kernel=_KERNEL.replace("invoke_phase 4", "invoke_phase 9")), "references missing transport fragment 9"),
+            (broken(kernel=_KERNEL.replace(" flags 7", " flags")), "argument count does not match fragment 'publish'"),
+            (broken(kernel=_KERNEL.replace("invoke_phase 4 %mine", "invoke_phase x %mine")), "programId must be an integer"),
+            (broken(plan=_PLAN + "fragment again program_id=4 params=a:i64 {\n}\n"), "duplicate programId 4"),
+            (broken(plan=_PLAN.replace("interval=8", "interval=0")), "requires a resolved completion interval"),
+            # A pointer may stand for an i64 only where the fragment binds it, not where it computes with it.
+            (broken(kernel=_KERNEL.replace("staging count*16 i", "staging slots i")), "argument #4 has type ptr"),
+            (broken(plan=_PLAN.replace("ep:i64", "ep:ptr")), "argument #0 has type endpoint, but fragment 'publish' expects ptr")):
+        with pytest.raises(CompileError, match=message):
+            make()

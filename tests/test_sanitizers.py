@@ -50,6 +50,9 @@ def test_specializer_survives_corrupted_programs_under_asan_ubsan(tmp_path):
     _build(exe, spec + [NATIVE / "spec_sanitize.cpp"], "address,undefined",
            extra=["-fno-sanitize-recover=undefined", f"-I{PKG / 'csrc' / 'spec'}"])
     cases = _corpus(tmp_path)
+    from tests import test_compiler
+    (tmp_path / "phase.kernel").write_text(test_compiler._KERNEL)
+    (tmp_path / "phase.plan").write_text(test_compiler._PLAN)
     proc = subprocess.run([str(exe), str(tmp_path), str(cases)], capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, (proc.stdout + proc.stderr)[-6000:]
     assert "refused" in proc.stdout and "ERROR" not in proc.stderr
