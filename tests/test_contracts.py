@@ -181,3 +181,30 @@ def test_slurm_launcher_derives_the_rank_environment(tmp_path):
                          env={**os.environ, **slurm}, capture_output=True, text=True, timeout=120)
     assert out.returncode == 0 and out.stdout.split() == ["9", "gpu05"], out.stderr
     assert launch.main([]) == 2
+
+
+def test_documents_name_files_that_exist():
+    """Every file a document names in backticks or links to is in the tree (the reference lints its
+    documents' links the same way, experiments/bench/linkcheck.sh)."""
+    import re
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    pkg = root / "aboleth_b200"
+    bases = [root, pkg, root / "tests", root / "benchmarks", root / "examples", root / "docs",
+             pkg / "include", pkg / "include" / "aboleth", pkg / "include" / "aboleth" / "abi",
+             *[p for p in pkg.rglob("*") if p.is_dir() and "_lib" not in p.parts and "__pycache__" not in p.parts]]
+    generated = {"manifest.json", "kernel.cubin"}  # written at run time
+    missing = []
+    for document in [root / "README.md", *sorted((root / "docs").glob("*.md"))]:
+        text = document.read_text()
+        named = set(re.findall(r"\]\(([^)#\s]+)\)", text))
+        for tick in re.findall(r"`([^`\s]+)`", text):
+            if re.search(r"\.(py|cu|cuh|h|hpp|cpp|md|json|txt|cmake)$", tick) and not set("*{<$") & set(tick):
+                named.add(tick)
+        for name in sorted(named):
+            if name.startswith("http") or name in generated:
+                continue
+            if not any((base / name).exists() for base in bases):
+                missing.append((document.name, name))
+    assert not missing, missing
