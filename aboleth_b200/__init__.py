@@ -40,7 +40,7 @@ from .shapes import ShapeFamilyPlan, plan_shape_family
 from .world import AutoTransportPolicy, LocalRegion, PeerRegionTable, TopologyInfo, World
 
 
-from . import moe, ops, parallel  # noqa: E402,F401
+from . import frontends, moe, ops, parallel  # noqa: E402,F401
 from .kv import (GENERIC_KV_TARGET_PROFILE, H200_NVLINK_KV_TARGET_PROFILE,  # noqa: E402
                  CompiledKVTransferManager, KVPoolLayout, KVRuntimeOverrides, KVTargetProfile,
                  select_kv_target_profile)

@@ -1,4 +1,6 @@
 """The public names a user of the reference package expects exist (no GPU)."""
+import pytest
+
 import aboleth_b200 as ab
 
 EXPECTED = """AllocationHandle AllocationProvider Artifact AutoTransportPolicy Bootstrap CapacityContract CommunicationDataflow
@@ -108,3 +110,39 @@ def test_device_library_lanes_and_compile_time_peers(tmp_path, monkeypatch):
                    '  aboleth::put_inline_small(ctx, aboleth::open(ctx, 2), aboleth::RemoteRegion{dst, 0}, 0x010203, 3);\n'
                    '  aboleth::quiet<1>(ctx);\n}\n')
     subprocess.run(["nvcc", *lib.nvcc_flags(), "-c", str(src), "-o", str(tmp_path / "lanes.o")], check=True)
+
+
+def test_extern_symbol_table_and_prototype_header_link(tmp_path, monkeypatch):
+    """The language-neutral binding: a client that includes nothing but the generated prototypes
+    calls every exported symbol and links against the archive."""
+    import subprocess
+
+    from aboleth_b200 import frontends
+
+    monkeypatch.setenv("ABOLETH_CACHE_DIR", str(tmp_path))
+    transports = ["p2p", "proxy"]
+    table = frontends.extern_symbols(transports)
+    names = [s.name for s in table]
+    assert len(names) == len(set(names)) == 2 * 8 + 1 and names[-1] == "aboleth_tier1_wait_signal"
+    put_signal = next(s for s in table if s.name == "aboleth_tier1_put_signal_proxy")
+    assert put_signal.arg_types == ("u64", "u32", "u64", "u32", "u64", "u32", "u32", "u64", "u32", "u64")
+    assert put_signal.arg_names[:2] == ("endpoints", "peer") and put_signal.return_type == "u64"
+    with pytest.raises(ValueError, match="unknown transports"):
+        frontends.extern_symbols(["gin"])
+
+    lib = ab.device_library(transports=transports, archive=True)
+    import json
+    assert set(names) == set(json.loads(lib.manifest.read_text())["symbols"])  # the table is the archive's
+    header = frontends.write_prototypes(lib, transports)
+    calls = []
+    for symbol in table:
+        args = ", ".join("a" if t == "u64" else "b" for t in symbol.arg_types)
+        calls.append(f"  s += {symbol.name}({args});")
+    src = tmp_path / "client.cu"
+    src.write_text(f'#include "aboleth/{header.name}"\n'
+                   "__global__ void k(unsigned long long a, unsigned b, unsigned long long *out) {\n"
+                   "  unsigned long long s = 0;\n" + "\n".join(calls) + "\n  *out = s;\n}\nint main() { return 0; }\n")
+    subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", *frontends.link_flags(lib), str(src),
+                    "-o", str(tmp_path / "client")], check=True)
+    with pytest.raises(ValueError, match="header-only"):
+        frontends.link_flags(ab.device_library(transports=["p2p"]))
