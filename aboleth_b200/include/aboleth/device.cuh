@@ -53,6 +53,10 @@
 #define ABOLETH_TIER1_ENDPOINTS_PER_PEER 1
 #endif
 
+#ifdef ABOLETH_DEBUG_BOUNDS
+#include "aboleth/debug_bounds.h"
+#endif
+
 namespace aboleth {
 
 using abi::PutDesc;
@@ -82,6 +86,9 @@ struct DeviceContext {
     const std::uint64_t *endpoints;
     std::uint32_t *doorbell_locks;
     unsigned long long *status = nullptr;
+#ifdef ABOLETH_DEBUG_BOUNDS
+    debug::Bounds bounds;  // debug builds only: the windows this kernel may write (debug_bounds.h)
+#endif
 };
 
 struct PeerRef {
@@ -139,6 +146,29 @@ __device__ __forceinline__ void st_stream16(void *p, const uint4 &v) {
 __device__ __forceinline__ void record(const DeviceContext &ctx, Status s) {
     if (ctx.status != nullptr && s != Status::Ok)
         atomicCAS(ctx.status, 0ull, static_cast<unsigned long long>(s));
+}
+
+// Debug builds: may this context write [address, address + bytes) on a peer?  A refused
+// destination is recorded (status Malformed; address, bytes and a count for the host) and
+// the caller skips the access.  Release builds always answer yes and compile to nothing.
+__device__ __forceinline__ bool may_write(const DeviceContext &ctx, std::uint64_t address,
+                                          std::uint64_t bytes) {
+#ifdef ABOLETH_DEBUG_BOUNDS
+    if (!debug::inside(ctx.bounds, address, bytes)) {
+        record(ctx, Status::Malformed);
+        if (ctx.bounds.violation != nullptr &&
+            atomicAdd(ctx.bounds.violation + 2, 1ull) == 0ull) {
+            ctx.bounds.violation[0] = address;
+            ctx.bounds.violation[1] = bytes;
+        }
+        return false;
+    }
+#else
+    (void)ctx;
+    (void)address;
+    (void)bytes;
+#endif
+    return true;
 }
 
 // Copy `bytes` with `nthreads` cooperating threads (this thread is `tid`).
@@ -230,6 +260,8 @@ __device__ __forceinline__ void put(
     const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
     const LocalRegion &src, std::uint32_t bytes) {
     if (ref.kind == abi::kKindP2P) {
+        if (!detail::may_write(ctx, dst.address, bytes))
+            return;
         detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
                              reinterpret_cast<const std::uint8_t *>(src.address),
                              bytes, 0, 1);
@@ -253,6 +285,8 @@ __device__ __forceinline__ void put_inline(
     const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
     std::uint64_t value) {
     if (ref.kind == abi::kKindP2P) {
+        if (!detail::may_write(ctx, dst.address, 8))
+            return;
         detail::st_relaxed_sys(reinterpret_cast<std::uint64_t *>(dst.address), value);
     } else if (ref.kind == abi::kKindProxy) {
         // The ring carries an 8-byte inline value as a weak signal command.
@@ -291,6 +325,8 @@ __device__ __forceinline__ void signal(
     const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &flag,
     std::uint64_t epoch) {
     if (ref.kind == abi::kKindP2P) {
+        if (!detail::may_write(ctx, flag.address, 8))
+            return;
         detail::st_release_sys(reinterpret_cast<std::uint64_t *>(flag.address), epoch);
     } else if (ref.kind == abi::kKindProxy) {
         abi::ProxyCommand cmd{epoch, flag.address, 8, 0, flag.key,
@@ -313,6 +349,8 @@ __device__ __forceinline__ void put_signal(
     const LocalRegion &src, std::uint32_t bytes, const RemoteRegion &flag,
     std::uint64_t epoch) {
     if (ref.kind == abi::kKindP2P) {
+        if (!detail::may_write(ctx, dst.address, bytes) || !detail::may_write(ctx, flag.address, 8))
+            return;
         detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
                              reinterpret_cast<const std::uint8_t *>(src.address),
                              bytes, 0, 1);
@@ -401,9 +439,10 @@ __device__ __forceinline__ void put_warp(
         __syncwarp();
         return;
     }
-    detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
-                         reinterpret_cast<const std::uint8_t *>(src.address), bytes,
-                         threadIdx.x & 31, 32);
+    if (detail::may_write(ctx, dst.address, bytes))  // warp-uniform: every lane sees the same arguments
+        detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
+                             reinterpret_cast<const std::uint8_t *>(src.address), bytes,
+                             threadIdx.x & 31, 32);
     __syncwarp();
     detail::fence_acq_rel_sys();
 }

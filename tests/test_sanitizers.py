@@ -75,3 +75,34 @@ def test_proxy_ring_with_many_producers_is_race_free_under_tsan(tmp_path):
     proc = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, (proc.stdout + proc.stderr)[-6000:]
     assert "failures: 0" in proc.stdout and "ThreadSanitizer" not in proc.stderr
+
+
+def test_debug_bounds_rule_on_the_host_and_in_a_debug_build_of_a_client(tmp_path):
+    """Debug builds of Tier-1 code refuse peer writes outside the registered windows: the rule is
+    checked on the host (with UBSan), and a client compiles for sm_100a with and without it."""
+    exe = tmp_path / "debug_bounds_host"
+    _build(exe, [NATIVE / "debug_bounds_host.cpp"], "address,undefined", extra=["-fno-sanitize-recover=undefined"])
+    proc = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert proc.returncode == 0 and "failures: 0" in proc.stdout, proc.stdout + proc.stderr
+    nvcc = shutil.which("nvcc")
+    if nvcc is None:
+        pytest.skip("needs nvcc for the device half")
+    client = tmp_path / "client.cu"
+    client.write_text('''#include "aboleth/device.cuh"
+__global__ void k(const std::uint64_t *eps, unsigned long long *status, unsigned long long dst,
+                  unsigned long long src, unsigned long long flag, const void *windows, unsigned count,
+                  unsigned long long *violation) {
+    aboleth::DeviceContext ctx{eps, nullptr, status};
+#ifdef ABOLETH_DEBUG_BOUNDS
+    ctx.bounds = aboleth::debug::Bounds{static_cast<const aboleth::debug::Window *>(windows), count, violation};
+#endif
+    aboleth::put_signal(ctx, 1, aboleth::RemoteRegion{dst, 0}, aboleth::LocalRegion{src, 0}, 4096,
+                        aboleth::RemoteRegion{flag, 0}, 1);
+    aboleth::put_warp(ctx, aboleth::open(ctx, 1), aboleth::RemoteRegion{dst, 0}, aboleth::LocalRegion{src, 0}, 4096);
+    aboleth::put_inline(ctx, 1, aboleth::RemoteRegion{dst, 0}, 7);
+    aboleth::signal(ctx, 1, aboleth::RemoteRegion{flag, 0}, 2);
+}
+''')
+    for define in ([], ["-DABOLETH_DEBUG_BOUNDS"]):
+        subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", *define,
+                        f"-I{PKG / 'include'}", "-c", str(client), "-o", str(tmp_path / "client.o")], check=True)
