@@ -5,6 +5,7 @@
     python benchmarks/gemm_bench.py --shape 4096 4096 4096 --steps 3 --no-library   # small case for a profiler
     python benchmarks/gemm_bench.py --grouped            # grouped (per-expert) GEMM, Mixtral expert shapes
     python benchmarks/gemm_bench.py --fp8                # e4m3 operands, against torch._scaled_mm (cuBLASLt)
+    python benchmarks/gemm_bench.py --block-scaled       # e4m3 with 1x128 / 128x128 scales (expansion + bf16 GEMM)
 
 Each timed launch is preceded by an L2 flush; times are medians of CUDA-event brackets.
 Fractions are of the measured cuBLAS bf16 burst throughput recorded for this pool.
@@ -44,6 +45,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--grouped", action="store_true")
     ap.add_argument("--fp8", action="store_true", help="e4m3 operands (per-tensor scale), against torch._scaled_mm")
+    ap.add_argument("--block-scaled", action="store_true",
+                    help="e4m3 operands with 1x128 / 128x128 fp32 scales: the bf16 expansion (against the "
+                         "measured copy bandwidth) and the whole block-scaled GEMM")
     ap.add_argument("--no-library", action="store_true", help="skip the cuBLAS arm (profiler runs)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
@@ -74,6 +78,30 @@ def main() -> int:
                 row.update(cublas_loop_us=ms2 * 1e3, cublas_loop_tflops=flops / ms2 / 1e9)
             rows.append(row)
             del x, w, y
+    elif args.block_scaled:
+        from aboleth_b200.ops import dequant_block_scaled, gemm_e4m3_block_scaled, quant_fp8
+
+        hbm = measured_peaks().get("hbm_gbs", 6650.0)
+        for m, n, k in ([tuple(args.shape)] if args.shape else DENSE):
+            a_q, a_s = quant_fp8(torch.randn(m, k, device="cuda").to(torch.bfloat16), round_scale=True)
+            b_q = (torch.randn(n, k, device="cuda")).to(torch.float8_e4m3fn)
+            b_s = torch.full((-(-n // 128), k // 128), 2.0 ** -6, device="cuda")
+            a_bf = torch.empty(m, k, dtype=torch.bfloat16, device="cuda")
+            c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            expand_ms = timed(lambda: dequant_block_scaled(a_q, a_s, out=a_bf), flush, args.steps)
+            whole_ms = timed(lambda: gemm_e4m3_block_scaled(a_q, a_s, b_q, b_s, out=c), flush, args.steps)
+            w_bf = dequant_block_scaled(b_q, b_s, block=(128, 128))
+            cached_ms = timed(lambda: gemm_bf16(dequant_block_scaled(a_q, a_s, out=a_bf), w_bf, c), flush, args.steps)
+            check_gemm_status("cuda")
+            flops = 2.0 * m * n * k
+            moved = m * k * 3 + a_s.numel() * 4  # one byte read, two written per element
+            rows.append({"m": m, "n": n, "k": k, "dtype": "e4m3 block-scaled (bf16 math)",
+                         "expand_activations_us": expand_ms * 1e3, "expand_gbs": moved / expand_ms / 1e6,
+                         "expand_frac_of_measured_copy": moved / expand_ms / 1e6 / hbm,
+                         "both_operands_expanded_us": whole_ms * 1e3, "both_tflops": flops / whole_ms / 1e9,
+                         "weight_expanded_once_us": cached_ms * 1e3, "weight_once_tflops": flops / cached_ms / 1e9,
+                         "weight_once_frac_of_measured": flops / cached_ms / 1e9 / peak})
+            del a_q, a_s, b_q, b_s, a_bf, w_bf, c
     elif args.fp8:
         from aboleth_b200.ops import gemm_e4m3
 
@@ -111,8 +139,9 @@ def main() -> int:
                 row.update(cublas_us=ms2 * 1e3, cublas_tflops=flops / ms2 / 1e9)
             rows.append(row)
             del a, b, c
-    emit({"bench": "grouped gemm bf16" if args.grouped else "gemm e4m3" if args.fp8 else "gemm bf16", "n_gpus": 1,
-          "dtype": "e4m3" if args.fp8 else "bf16",
+    emit({"bench": ("grouped gemm bf16" if args.grouped else "gemm e4m3 block-scaled" if args.block_scaled
+                    else "gemm e4m3" if args.fp8 else "gemm bf16"), "n_gpus": 1,
+          "dtype": "e4m3" if args.fp8 or args.block_scaled else "bf16",
           "l2": "flushed before every timed launch", "peak_bf16_tflops_measured": peak, "rows": rows},
          args.out)
     return 0

@@ -33,6 +33,7 @@ PRESETS = {
                    "decode-size dispatch / combine with a flushed L2"),
     "gemm": ("gemm_bench.py", [], (1,), "bf16 tcgen05 GEMM against cuBLAS"),
     "gemm-fp8": ("gemm_bench.py", ["--fp8"], (1,), "e4m3 GEMM against cuBLASLt"),
+    "gemm-fp8-block": ("gemm_bench.py", ["--block-scaled"], (1,), "block-scaled e4m3 GEMM: bf16 expansion + tcgen05 GEMM"),
     "gemm-grouped": ("gemm_bench.py", ["--grouped"], (1,), "grouped expert GEMM against a loop of cuBLAS calls"),
     "tp": ("tp_bench.py", [], (2, 4, 8), "AG->GEMM and GEMM->RS fused kernels against NCCL + cuBLAS"),
     "serve": ("serve_bench.py", ["--graph"], (1, 2, 4, 8), "Mixtral-style EP serving, decode replayed as a CUDA graph"),

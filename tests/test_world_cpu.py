@@ -63,10 +63,12 @@ def _two_node_rank(rank, world_size, transport):
         try:
             world.connect_all(transport, remote_transport="proxy")
         except ValueError as error:
+            boot.barrier("refused")  # rank 0 hosts the store: it stays until every rank has its answer
             return {"error": str(error)}
         arena = world.runtime.allocate(256)
         reg = world.register(arena)
         table = world.exchange_regions([world.region("recv", reg, offset=0, length=256)], tag="n")
+        boot.barrier("imported")  # nobody unmaps its segment while a peer is still importing it
         return {"kinds": [h & 7 for h in table.endpoint_handles.tolist()], "geo": world.transport_geography,
                 "transport": world.transport.value}
 
