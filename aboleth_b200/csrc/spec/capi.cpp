@@ -66,6 +66,7 @@ char *ab200_spec_compile(const char *program_text, const char *options_text) {
             {"order-publications", order_publications},
             {"elide-epochs", elide_epochs},
             {"defer-announcement", defer_announcement},
+            {"self-reclaim", mark_self_reclaim},
             {"order-producers", order_producers},
             {"analyze-issuers", analyze_issuers},
         };

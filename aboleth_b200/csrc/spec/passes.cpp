@@ -638,6 +638,65 @@ int defer_announcement(Program &p, const Options &o) {
     return changed;
 }
 
+// ---- self-reclaim ----------------------------------------------------------------------------------
+//
+// wait(token, predicate=p) with a predicate the USER wrote defers completion without a bound the
+// planner knows (docs of the reference, COMPILER_SEMANTICS.md:344-359): the submission is marked
+// selfReclaim (a producer that finds the queue full retires completions itself instead of assuming
+// the planned window) and the kernel has to retire what it deferred - it must end, on that endpoint,
+// with an unconditional completion or a drain.  Queue transports only; on peer memory completion is
+// vacuous.
+int mark_self_reclaim(Program &p, const Options &o) {
+    if (o.caps->load_store_addressable)
+        return 0;
+    Defs defs;
+    defs.collect(p.body);
+    int changed = 0;
+    // Endpoint of each user-predicated poll, and where it was seen (for the diagnostic).
+    std::map<std::string, int> deferred;
+    const auto endpoint_of_token = [&](const std::string &token) -> std::string {
+        const Op *def = defs.find(token);
+        if (def == nullptr)
+            return "";
+        if (def->kind == "submit" && !def->operands.empty())
+            if (const Op *cmd = defs.find(def->operands[0]))
+                return cmd->operands.empty() ? "" : cmd->operands[0];
+        return def->operands.empty() ? "" : def->operands[0];
+    };
+    // Program order, outermost blocks flattened: a later unconditional completion or drain retires.
+    std::function<void(Block &)> scan = [&](Block &block) {
+        for (Op &op : block) {
+            if ((op.kind == "poll" || op.kind == "wait") && !op.operands.empty()) {
+                const std::string ep = endpoint_of_token(op.operands[0]);
+                const bool user = op.has("pred") && op.get("pred") != "1" && !op.has("planned");
+                if (user) {
+                    deferred[ep] = op.line;
+                    if (o.on("self-reclaim"))
+                        for (Op &other : block)
+                            if (other.kind == "submit" && other.result == op.operands[0] &&
+                                !other.has("selfReclaim")) {
+                                other.attrs["selfReclaim"] = "";
+                                ++changed;
+                            }
+                } else if (!op.has("pred") || op.get("pred") == "1") {
+                    deferred.erase(ep);
+                }
+            } else if (op.kind == "drain" && !op.operands.empty()) {
+                deferred.erase(op.operands[0]);
+            }
+            if (!op.body.empty())
+                scan(op.body);
+        }
+    };
+    scan(p.body);
+    if (!deferred.empty())
+        throw Error("line " + std::to_string(deferred.begin()->second) +
+                    ": wait: a completion deferred by a user-written predicate is never retired on " +
+                    deferred.begin()->first + ": end the kernel with an unconditional wait or drain(" +
+                    deferred.begin()->first + ")");
+    return changed;
+}
+
 // ---- order-producers ---------------------------------------------------------------------------------
 
 namespace {

@@ -48,6 +48,7 @@ int coalesce_submissions(Program &p, const Options &o);
 int order_publications(Program &p, const Options &o);
 int elide_epochs(Program &p, const Options &o);
 int defer_announcement(Program &p, const Options &o);
+int mark_self_reclaim(Program &p, const Options &o);
 int order_producers(Program &p, const Options &o);
 int analyze_issuers(Program &p, const Options &o);
 

@@ -406,3 +406,25 @@ def test_transport_phases_are_spliced_from_an_external_program():
             (broken(plan=_PLAN.replace("ep:i64", "ep:ptr")), "argument #0 has type endpoint, but fragment 'publish' expects ptr")):
         with pytest.raises(CompileError, match=message):
             make()
+
+
+def test_user_predicated_completion_is_self_reclaimed_and_must_be_retired():
+    """wait(token, predicate=p) with a predicate the user wrote: the submission is marked selfReclaim
+    on a queue transport, and the kernel must end with an unconditional wait or a drain."""
+    def kernel(tail: str) -> str:
+        return ("program k backend=rdma\narg t table\narg buf ptr\narg it u64\n%e = endpoint t 1\n"
+                "for i 0 8 {\n  %r = remote t 1\n  %l = local buf\n  %p = put %e %r %l bytes=64\n"
+                "  wait %p pred=((i&3)==3)\n}\n" + tail)
+
+    with compilation("rdma", rank=0, world_size=2):
+        drained = compile_program(kernel("drain %e\n"))
+        assert "selfReclaim" in drained.ir and drained.passes["self-reclaim"] == 1
+        with pytest.raises(CompileError, match="deferred by a user-written predicate is never retired on %e"):
+            compile_program(kernel(""))
+    with compilation("rdma", rank=0, world_size=2, passes="-self-reclaim"):
+        unmarked = compile_program(kernel("drain %e\n"))  # the switch only controls the marking
+        assert "selfReclaim" not in unmarked.ir
+        with pytest.raises(CompileError, match="never retired"):
+            compile_program(kernel(""))
+    with compilation("p2p", rank=0, world_size=2):  # completion is vacuous on peer memory
+        assert "selfReclaim" not in compile_program(kernel("").replace("backend=rdma", "backend=p2p")).ir
