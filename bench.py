@@ -23,7 +23,6 @@ os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one 
 import statistics
 import sys
 import threading
-import time
 
 HIDDEN, EXPERTS, TOP_K, GROUP = 7168, 256, 8, 128
 METRIC = "EP dispatch+combine tokens/s (DeepSeek-V3 shape, fp8 1x128 dispatch, bf16 combine)"

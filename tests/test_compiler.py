@@ -5,7 +5,6 @@ world 2, rank 0, 4096 int8 bytes per peer, lowered through the whole pipeline,
 with batch count, fence kind and flag writes asserted.
 """
 import json
-import os
 from pathlib import Path
 
 import pytest

@@ -1,5 +1,4 @@
 """Native planning passes against hand-computed cases (no GPU)."""
-import json
 
 import pytest
 
