@@ -22,7 +22,7 @@ namespace {
 
 long long ceil_pow2(long long v) {
     long long b = 1;
-    while (b < v)
+    while (b < v && b < (1ll << 62))
         b *= 2;
     return b;
 }
@@ -34,8 +34,33 @@ long long floor_pow2(long long v) {
     return v < 1 ? 1 : b;
 }
 
+// Every quantity a planner reads (bytes, rows, lanes, iterations) is far below this; refusing
+// anything larger keeps sums and small products of them inside 64 bits.
+constexpr long long kLargestQuantity = 1ll << 40;
+constexpr long long kLargestWalk = 4096;  // iterations of one access walk that the planners enumerate
+
+long long quantity(const std::string &text) {
+    const long long value = to_integer(text);
+    if (value > kLargestQuantity || value < -kLargestQuantity)
+        throw Error("'" + text + "' is outside the range a plan can use");
+    return value;
+}
+
 long long num(const Op &op, const std::string &key, long long fallback = 0) {
-    return op.has(key) ? to_integer(op.get(key)) : fallback;
+    if (!op.has(key))
+        return fallback;
+    const long long value = to_integer(op.get(key));
+    if (value > kLargestQuantity || value < -kLargestQuantity)
+        throw Error(op.kind + " " + key + "=" + op.get(key) + " is outside the range a plan can use");
+    return value;
+}
+
+// a * b, or a diagnostic when the product leaves 64 bits.
+long long mul(long long a, long long b) {
+    long long out;
+    if (__builtin_mul_overflow(a, b, &out))
+        throw Error("a planned size does not fit 64 bits");
+    return out;
 }
 
 std::vector<std::string> list(const std::string &text) {
@@ -133,7 +158,7 @@ void plan_endpoints(const Program &p, Json &j) {
         const bool ranked = work.has("rank_count");
         if (ranked && !partitions.empty()) {
             for (const auto &lanes : list(partitions[0]->get("participantLanes")))
-                world_lanes = std::min(world_lanes, to_integer(lanes));
+                world_lanes = std::min(world_lanes, quantity(lanes));
             world_lanes = floor_pow2(world_lanes);
             ready_stride = fanout ? world_lanes : 1;
         }
@@ -237,7 +262,7 @@ void plan_storage(const Program &p, Json &j) {
             // rows=<begin>:<end>, end exclusive; through=<view rows> bounds an indexed view
             const std::string rows = access.get("rows", "0:" + std::to_string(declared));
             const std::size_t colon = rows.find(':');
-            long long end = to_integer(rows.substr(colon + 1));
+            long long end = quantity(rows.substr(colon + 1));
             if (access.has("through"))
                 end = std::min(end, num(access, "through"));
             reached = std::max(reached, std::min(end, declared));
@@ -425,15 +450,14 @@ struct Walk {
 bool interval_at(const Walk &w, long long iteration, long long &begin, long long &end) {
     if (w.unknown || iteration < 0 || iteration >= w.count)
         return false;
-    if (w.stride != 0 && iteration > (std::numeric_limits<long long>::max() - w.offset) / std::max(w.stride, 1LL))
+    // Checked arithmetic: a walk whose addresses leave 64 bits touches nothing we can reason about.
+    long long displacement;
+    if (__builtin_mul_overflow(iteration, w.stride, &displacement))
         return false;
-    long long displacement = iteration * w.stride;
     if (w.period > 0)
         displacement %= w.period;
-    begin = w.offset + displacement;
-    if (w.length > std::numeric_limits<long long>::max() - begin)
+    if (__builtin_add_overflow(w.offset, displacement, &begin) || __builtin_add_overflow(begin, w.length, &end))
         return false;
-    end = begin + w.length;
     return true;
 }
 
@@ -484,6 +508,9 @@ Step read_step(const Op &op) {
         w.unknown = num(access, "unknown", 0) != 0;
         if (w.length < 0 || w.count < 1 || w.period < 0)
             throw Error(op.kind + " " + s.name + ": access needs length >= 0, count >= 1, period >= 0");
+        if (w.count > kLargestWalk)  // overlaps are found by enumerating pairs of iterations
+            throw Error(op.kind + " " + s.name + ": an access of more than " + std::to_string(kLargestWalk) +
+                        " iterations is not enumerated; mark it unknown=1");
         s.unknown_access = s.unknown_access || w.unknown;
         (access.kind == "read" ? s.reads : s.writes).push_back(w);
     }
@@ -530,7 +557,7 @@ void plan_transport_program(const Program &p, Json &j) {
         const Op &phase = *s.op;
         const long long commands = num(phase, "commands", 1), iterations = num(phase, "iterations", 1),
                         payload = num(phase, "payload_bytes", 0);
-        if (commands <= 0 || iterations <= 0 || payload < 0)
+        if (commands <= 0 || iterations <= 0 || payload < 0 || iterations > kLargestWalk)
             throw Error("phase " + s.name + " has invalid transport planning facts");
         // Reuse distance: the smallest d such that iteration i and i + d touch the same source bytes.
         long long reuse = s.reads.empty() ? 1 : iterations;
@@ -562,7 +589,7 @@ void plan_transport_program(const Program &p, Json &j) {
             if (caps == nullptr)
                 throw Error("unknown peer transport '" + transports[t] + "'");
             if (!explicit_interval) {
-                const long long configured = peer_intervals.empty() ? 0 : to_integer(peer_intervals[t]);
+                const long long configured = peer_intervals.empty() ? 0 : quantity(peer_intervals[t]);
                 const long long preferred =
                     configured > 0 ? configured
                     : (payload <= tiny || caps->load_store_addressable) ? iterations
@@ -572,7 +599,7 @@ void plan_transport_program(const Program &p, Json &j) {
             }
             if (caps->queue_capacity_limited) {
                 queued = true;
-                const long long capacity = to_integer(capacities[t]);
+                const long long capacity = quantity(capacities[t]);
                 if (capacity < commands)
                     throw Error("phase " + s.name + ": endpoint capacity cannot hold one iteration");
                 capacity_limit = std::min(capacity_limit,

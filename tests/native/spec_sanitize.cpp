@@ -5,6 +5,7 @@
 // diagnostic in the JSON envelope is the expected answer to a corrupted program).
 //
 //   spec_sanitize <corpus-dir> <cases>      cases are <dir>/<i>.prog + <dir>/<i>.opts
+#include <cctype>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -12,6 +13,7 @@
 #include <fstream>
 #include <sstream>
 #include <string>
+#include <utility>
 #include <vector>
 
 extern "C" {
@@ -145,6 +147,59 @@ int main(int argc, char **argv) {
                 (std::strncmp(out, "{\"ok\": true", 11) == 0 ? accepted : refused)++;
                 ab200_spec_free(out);
             }
+        }
+    }
+    // The planners over their own requests with the numbers pushed to the edges (0, -1, 1, huge)
+    // and with byte damage: a planner answers with a plan or a diagnostic, never a crash.
+    for (int c = 0;; ++c) {
+        const std::string kind = slurp(dir + "/planner." + std::to_string(c) + ".kind");
+        const std::string request = slurp(dir + "/planner." + std::to_string(c) + ".req");
+        if (kind.empty())
+            break;
+        char *intact = ab200_spec_plan(kind.c_str(), request.c_str());
+        const bool ok = std::strncmp(intact, "{\"ok\": true", 11) == 0;
+        ab200_spec_free(intact);
+        if (!ok) {
+            std::fprintf(stderr, "planner case %d (%s): the intact request is refused\n", c, kind.c_str());
+            return 1;
+        }
+        // Every integer literal, one at a time, replaced by each edge value.
+        std::vector<std::pair<std::size_t, std::size_t>> numbers;
+        for (std::size_t i = 0; i < request.size();) {
+            const bool starts = std::isdigit(static_cast<unsigned char>(request[i])) &&
+                                (i == 0 || request[i - 1] == '=' || request[i - 1] == ',' || request[i - 1] == ' ' ||
+                                 request[i - 1] == ':');
+            if (!starts) {
+                ++i;
+                continue;
+            }
+            std::size_t j = i;
+            while (j < request.size() && std::isdigit(static_cast<unsigned char>(request[j])))
+                ++j;
+            numbers.emplace_back(i, j - i);
+            i = j;
+        }
+        for (const auto &[at, length] : numbers)
+            for (const char *edge : {"0", "-1", "1", "3", "4294967296", "9223372036854775807", "99999999999999999999"}) {
+                std::string damaged = request;
+                damaged.replace(at, length, edge);
+                char *out = ab200_spec_plan(kind.c_str(), damaged.c_str());
+                (std::strncmp(out, "{\"ok\": true", 11) == 0 ? accepted : refused)++;
+                ab200_spec_free(out);
+            }
+        Lcg rng{777u + static_cast<std::uint64_t>(c)};
+        for (int round = 0; round < 300; ++round) {
+            std::string damaged = request;
+            const std::size_t at = rng.next() % damaged.size();
+            switch (rng.next() % 4) {
+            case 0: damaged.erase(at, 1 + rng.next() % 10); break;
+            case 1: damaged[at] = "=,:() \n-"[rng.next() % 8]; break;
+            case 2: damaged.insert(at, damaged.substr(at, rng.next() % 40)); break;
+            default: damaged.resize(at); break;
+            }
+            char *out = ab200_spec_plan(kind.c_str(), damaged.c_str());
+            (std::strncmp(out, "{\"ok\": true", 11) == 0 ? accepted : refused)++;
+            ab200_spec_free(out);
         }
     }
     std::printf("corrupted programs: %ld accepted, %ld refused\n", accepted, refused);

@@ -53,6 +53,11 @@ def test_specializer_survives_corrupted_programs_under_asan_ubsan(tmp_path):
     from tests import test_compiler
     (tmp_path / "phase.kernel").write_text(test_compiler._KERNEL)
     (tmp_path / "phase.plan").write_text(test_compiler._PLAN)
+    import json
+    seeds = json.loads((Path(__file__).resolve().parent / "data" / "planner_requests.json").read_text())
+    for i, seed in enumerate(seeds):
+        (tmp_path / f"planner.{i}.kind").write_text(seed["kind"])
+        (tmp_path / f"planner.{i}.req").write_text(seed["request"])
     proc = subprocess.run([str(exe), str(tmp_path), str(cases)], capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, (proc.stdout + proc.stderr)[-6000:]
     assert "refused" in proc.stdout and "ERROR" not in proc.stderr
