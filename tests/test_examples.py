@@ -42,3 +42,11 @@ def test_tier1_client_compiles_against_the_device_library(tmp_path):
 def test_examples_run_on_one_gpu(script, args, tmp_path):
     proc = _run(script, *args, cache=tmp_path)
     assert proc.returncode == 0, proc.stdout + proc.stderr
+
+
+@pytest.mark.parametrize("transport", ["rdma", "p2p"])
+def test_planned_phase_example_splices_and_compiles(transport, tmp_path):
+    proc = _run("planned_phase.py", "--transport", transport, cache=tmp_path)
+    assert proc.returncode == 0, proc.stderr
+    assert "spliced wait: planned_wait %s.p0 interval=4 iteration=it queue_capacity=32" in proc.stdout
+    assert "pred=(((it) & 3) == 3)" in proc.stdout  # completes once per planned interval
