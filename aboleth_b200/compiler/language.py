@@ -163,6 +163,13 @@ class ProgramBuilder:
     def system_fence(self) -> None:
         self._emit("system_fence")
 
+    def invoke_phase(self, program_id: int, *arguments: Union[Expr, Value]) -> None:
+        """Run the externally planned transport phase ``program_id`` here.  The fragment comes from
+        the transport program given to ``compile_program(..., plan=...)``; values of this builder
+        (an endpoint, say) and expressions may be passed for its parameters."""
+        rendered = [str(self._own(a)) if isinstance(a, Value) else _e(a) for a in arguments]
+        self._emit(" ".join(["invoke_phase", str(int(program_id)), *rendered]))
+
     # -- frontend code the analyses need to see --------------------------------------------
     def store(self, base: Expr, *, offset: int, width: int, value: Expr) -> None:
         """A scalar store at a constant offset (candidate for inline forwarding)."""

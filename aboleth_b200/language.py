@@ -119,6 +119,11 @@ def system_fence() -> None:
     current_builder().system_fence()
 
 
+def invoke_phase(program_id: int, *arguments) -> None:
+    """Splice point of an externally planned transport phase (see ``ProgramBuilder.invoke_phase``)."""
+    current_builder().invoke_phase(program_id, *arguments)
+
+
 def drain(endpoint_value: Value) -> None:
     current_builder().drain(endpoint_value)
 

@@ -427,3 +427,18 @@ def test_user_predicated_completion_is_self_reclaimed_and_must_be_retired():
             compile_program(kernel(""))
     with compilation("p2p", rank=0, world_size=2):  # completion is vacuous on peer memory
         assert "selfReclaim" not in compile_program(kernel("").replace("backend=rdma", "backend=p2p")).ir
+
+
+def test_builder_states_phase_invocations():
+    from aboleth_b200.compiler import ProgramBuilder, materialize_phases
+
+    b = ProgramBuilder("k", args=[("endpoints", "table"), ("flags", "ptr"), ("it", "u64")])
+    mine = b.endpoint("endpoints", 1)
+    b.invoke_phase(4, mine, "flags + 8", "it + 1")
+    text = b.text(backend="rdma", rank=0, world_size=2)
+    assert f"invoke_phase 4 {mine} (flags + 8) (it + 1)" in text
+    ir = materialize_phases(text, _PLAN)
+    assert f"signal {mine} %r.p0 epoch=(it + 1)" in ir
+    other = ProgramBuilder("other")
+    with pytest.raises(TypeError, match="cannot cross programs"):
+        other.invoke_phase(4, mine)
