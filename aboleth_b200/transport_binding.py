@@ -15,7 +15,7 @@ records of python/aboleth/pattern.py); slot types are i1 / i32 / i64.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Sequence
 
 from .compiler.language import ProgramBuilder
 
@@ -241,6 +241,54 @@ class TransportProgramBinding:
         b.wait(ready, iteration=self.publication.iteration.name, reuse=reuse,
                final=f"{self.publication.iteration.name} + 1 == {self.publication.iterations.name}")
         return b
+
+
+    def to_fragment(self, program_id: int, *, interval: Optional[int] = None,
+                    capacities: Sequence[int] = (), reuse: Optional[int] = None) -> str:
+        """The attachment as a ``fragment`` of an external transport program, for
+        ``compile_program(kernel, plan=...)``: its parameters are the slots (all 64-bit
+        placeholders, in slot order), its body is :meth:`to_builder`'s.  With ``interval`` a
+        ``phase`` record carries the resolved completion interval and the peers' queue capacities,
+        and the fragment's wait takes them at the splice; with ``reuse`` the wait keeps a reuse
+        distance of its own instead."""
+        builder = self.to_builder(reuse=reuse or 1)
+        body = [line for line in builder.text(backend="p2p", rank=0, world_size=1).splitlines()
+                if line and not line.startswith(("program ", "arg "))]
+        if reuse is None:
+            body = [line.replace(" reuse=1", "") if line.lstrip().startswith("planned_wait") else line
+                    for line in body]
+        params = ",".join(f"{slot.name}:i64" for slot in self.slots())
+        symbol = _symbol(self.name)
+        text = ""
+        if interval is not None:
+            if interval < 1:
+                raise ValueError("a resolved completion interval is at least 1")
+            text += f"phase {symbol} program_id={program_id} interval={interval}"
+            if capacities:
+                text += " capacities=" + ",".join(str(int(c)) for c in capacities)
+            text += "\n"
+        elif reuse is None:
+            raise ValueError("a fragment needs a planned interval or a reuse distance")
+        return text + f"fragment {symbol} program_id={program_id} params={params} {{\n" + \
+            "".join(f"  {line}\n" for line in body) + "}\n"
+
+    def invoke_text(self, program_id: int, **slots: str) -> str:
+        """The ``invoke_phase`` line a kernel states at its insertion point: every slot once, in
+        slot order (values of the kernel's own program, argument names or expressions)."""
+        names = [slot.name for slot in self.slots()]
+        missing, extra = [n for n in names if n not in slots], [n for n in slots if n not in names]
+        if missing or extra:
+            raise ValueError(f"transport program {program_id}: missing slots {missing}, unknown slots {extra}")
+        rendered = []
+        for name in names:
+            text = str(slots[name])
+            rendered.append(f"({text})" if any(c.isspace() for c in text) and not text.startswith("(") else text)
+        return " ".join(["invoke_phase", str(int(program_id)), *rendered])
+
+
+def transport_program_text(name: str, fragments: Sequence[str]) -> str:
+    """An external transport program: the module ``compile_program(..., plan=...)`` reads."""
+    return f"program {_symbol(name)} kind=transport_program\n" + "".join(fragments)
 
 
 def _symbol(name: str) -> str:

@@ -229,3 +229,38 @@ def test_planned_fragments_compile_per_transport():
     assert fence.artifact == "inline_fragment" and [n for n, _ in publish.parameters] == ["endpoint", "only_if_advanced"]
     with pytest.raises(ValueError, match="max_bytes must be positive"):
         pp.planned_put_program(max_bytes=0)
+
+
+def test_binding_becomes_a_fragment_that_a_kernel_invokes():
+    """A physicalised attachment as a fragment of an external transport program: the kernel states
+    invoke_phase with the slots, the splice carries the planned interval, the pipeline lowers it."""
+    from aboleth_b200.compiler import compile_program, materialize_phases
+    from aboleth_b200.transport_binding import transport_program_text
+
+    compiled = ab.build_moe_pattern(ab.MoEPatternSpec(max_tokens=64, hidden=512, top_k=4, num_ranks=4)).compile()
+    phys = ab.physicalize_pattern(compiled, [
+        ab.PhaseBinding(None, "experts", "dispatch", "pack_kernel", "after_pack", 4, "fused_kernel",
+                        operations=("dispatch.values", "dispatch.count"), artifact=ab.Artifact.STANDALONE_KERNEL)])
+    binding = phys.binding("dispatch")
+    program_id = phys.manifest("dispatch").program_id
+    plan = transport_program_text("moe", [binding.to_fragment(program_id, interval=4, capacities=(64, 32))])
+    assert plan.startswith(f"program moe kind=transport_program\nphase dispatch program_id={program_id} "
+                           "interval=4 capacities=64,32\n")
+    assert "planned_wait" in plan and " reuse=" not in plan
+    names = [slot.name for slot in binding.slots()]
+    invoke = binding.invoke_text(program_id, **{name: f"a{i}" for i, name in enumerate(names)})
+    assert invoke.split()[:3] == ["invoke_phase", str(program_id), "a0"] and len(invoke.split()) == 2 + len(names)
+    with pytest.raises(ValueError, match="missing slots"):
+        binding.invoke_text(program_id)
+    with pytest.raises(ValueError, match="planned interval or a reuse distance"):
+        binding.to_fragment(program_id)
+    kernel = ("program pack backend=rdma\n" + "".join(f"arg a{i} u64\n" for i in range(len(names))) +
+              "for it 0 8 {\n  " + invoke + "\n}\n")
+    spliced = materialize_phases(kernel, plan)
+    assert "invoke_phase" not in spliced and "interval=4" in spliced and "queue_capacity=32" in spliced
+    with ab.compilation("rdma", rank=0, world_size=4):
+        lowered = compile_program(kernel, plan=plan)
+    assert lowered.cuda and lowered.facts["strong_signals"] >= 1
+    # A fragment may keep a reuse distance of its own instead of a planned interval.
+    own = binding.to_fragment(program_id, reuse=2)
+    assert "phase " not in own and " reuse=2" in own
