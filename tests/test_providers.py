@@ -120,7 +120,9 @@ def test_gid_choice_and_port_address(sysfs, monkeypatch):
 def test_probe_needs_both_the_library_and_a_device(sysfs, tmp_path, monkeypatch):
     if shutil.which("gcc") is None:
         pytest.skip("needs gcc for the stand-in libraries")
-    assert runtime.probe_providers() & (Provider.VERBS | Provider.MLX5 | Provider.EFA) == 0  # no libraries here
+    for name in ("IBVERBS", "MLX5", "EFA", "FABRIC"):  # whatever the machine has installed stays out of it
+        monkeypatch.setenv(f"ABOLETH_DL_{name}", str(tmp_path / "absent.so"))
+    assert runtime.probe_providers() & (Provider.VERBS | Provider.MLX5 | Provider.EFA) == 0  # no libraries
 
     def stand_in(name: str, symbol: str) -> str:
         src = tmp_path / f"{name}.c"
