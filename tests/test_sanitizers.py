@@ -78,6 +78,8 @@ def test_proxy_ring_with_many_producers_is_race_free_under_tsan(tmp_path):
            "thread", extra=[f"-I{cuda / 'include'}"],
            libs=[f"-L{cuda / 'lib64'}", f"-Wl,-rpath,{cuda / 'lib64'}", "-lcudart", "-ldl"])
     proc = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
+    if "unexpected memory mapping" in proc.stderr:  # the sanitizer cannot place its shadow under this kernel's ASLR
+        pytest.skip("ThreadSanitizer cannot start on this machine")
     assert proc.returncode == 0, (proc.stdout + proc.stderr)[-6000:]
     assert "failures: 0" in proc.stdout and "ThreadSanitizer" not in proc.stderr
 
