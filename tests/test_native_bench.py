@@ -24,6 +24,22 @@ def test_builds_and_reports_no_gpu_as_77():
         assert code == 77 and rows == []
 
 
+def test_nccl_host_arm_builds_and_needs_two_gpus():
+    import torch
+
+    driver = _driver()
+    try:
+        binary = driver.build_nccl()
+    except RuntimeError as error:
+        if "not installed" in str(error) or "no nccl.h" in str(error):
+            pytest.skip(str(error))
+        raise
+    assert binary.exists()
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        code, rows = driver.run_nccl(["--iters", "4", "--warmup", "3"])
+        assert code == 77 and rows == []
+
+
 @pytest.mark.gpu
 def test_loopback_ladder_on_one_gpu():
     driver = _driver()
