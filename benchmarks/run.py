@@ -37,6 +37,9 @@ PRESETS = {
     "gemm-grouped": ("gemm_bench.py", ["--grouped"], (1,), "grouped expert GEMM against a loop of cuBLAS calls"),
     "tp": ("tp_bench.py", [], (2, 4, 8), "AG->GEMM and GEMM->RS fused kernels against NCCL + cuBLAS"),
     "serve": ("serve_bench.py", ["--graph"], (1, 2, 4, 8), "Mixtral-style EP serving, decode replayed as a CUDA graph"),
+    "native": ("native_bench.py", ["--sweep"], (1, 2, 4, 8), "C++ arm of the Tier-1 ladder (one process, rank per GPU)"),
+    "nccl-host": ("native_bench.py", ["--arm", "nccl_host", "--sweep"], (2, 4, 8),
+                  "C++ NCCL host-API all-to-all baseline (grouped ncclSend / ncclRecv)"),
     "probe": ("-m aboleth_b200.endpoint_probe", [], (1, 2, 4, 8), "endpoint calibration (lanes x warps) and the fitted profile"),
 }
 
@@ -47,12 +50,15 @@ def command(name: str, gpus: int, out: Path, port: int) -> list[str]:
         raise SystemExit(f"preset {name!r} runs on {allowed} GPUs, not {gpus}")
     target = script.split() if script.startswith("-m") else [str((HERE / script).resolve())]
     launcher = [sys.executable]
-    if gpus > 1:
+    one_process = name in ("native", "nccl-host")  # these programs drive every GPU themselves
+    if gpus > 1 and not one_process:
         launcher += ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={gpus}",
                      "--master-addr", "127.0.0.1", "--master-port", str(port)]
     args = list(extra)
     if name == "headline":
         args = ["--gpus", str(gpus)] + args
+    elif one_process:
+        args += ["--gpus", str(gpus)]
     elif name == "probe" and gpus == 1:
         args += ["--loopback"]
     if name != "headline":
