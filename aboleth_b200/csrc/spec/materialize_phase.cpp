@@ -222,9 +222,18 @@ std::vector<Op> expand(const Op &invoke, const Fragment &fragment, const Program
             dropped_bindings.push_back(param.name);
     }
     // Values defined in the body get a suffix of their own per invocation.
+    // So do the names a fragment introduces itself (loop variables, lets): an argument
+    // expression that mentions the kernel's own `i` must not be captured by a fragment's `i`.
     walk(fragment.op->body, [&](const Op &op) {
         if (!op.result.empty())
             map[op.result] = op.result + ".p" + std::to_string(serial);
+        if ((op.kind == "for" || op.kind == "let") && !op.operands.empty()) {
+            const std::string &name = op.operands[0];
+            for (const Param &param : fragment.params)
+                if (param.name == name)
+                    fail_at(op, "'" + name + "' is a parameter of the fragment and cannot be redefined in it");
+            map[name] = name + "_p" + std::to_string(serial);
+        }
     });
     std::vector<Op> body;
     for (const Op &op : fragment.op->body) {

@@ -442,3 +442,23 @@ def test_builder_states_phase_invocations():
     other = ProgramBuilder("other")
     with pytest.raises(TypeError, match="cannot cross programs"):
         other.invoke_phase(4, mine)
+
+
+def test_fragment_names_do_not_capture_the_kernels_names():
+    """A loop variable or a let of the fragment is renamed per invocation, so an argument expression
+    that mentions the kernel's own variable of the same name keeps meaning the kernel's."""
+    from aboleth_b200.compiler import materialize_phases
+
+    plan = ("program p kind=transport_program\n"
+            "fragment rows program_id=2 params=table:i64,dst:i64,src:i64 {\n"
+            "  let stride 4096\n  %e = endpoint table 1\n  for i 0 4 {\n    %r = remote_at (dst+i*stride)\n"
+            "    %l = local (src+i*stride)\n    %t = put %e %r %l bytes=4096\n    wait %t\n  }\n}\n")
+    kernel = ("program k backend=rdma\narg endpoints table\narg out ptr\narg in ptr\n"
+              "for i 0 2 {\n  invoke_phase 2 endpoints (out+i*16384) (in+i*16384)\n}\n")
+    ir = materialize_phases(kernel, plan)
+    assert "for i_p0 0 4 {" in ir and "let stride_p0 4096" in ir
+    assert "remote_at ((out+i*16384)+i_p0*stride_p0)" in ir  # the kernel's i and the fragment's stay apart
+    with compilation("rdma", rank=0, world_size=2):
+        assert compile_program(kernel, plan=plan).cuda
+    with pytest.raises(CompileError, match="'dst' is a parameter of the fragment"):
+        materialize_phases(kernel, plan.replace("let stride 4096", "let dst 4096"))
