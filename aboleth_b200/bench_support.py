@@ -7,9 +7,7 @@ capacity or an explicit L2 flush between timed iterations.
 """
 from __future__ import annotations
 
-import json
 import statistics
-from pathlib import Path
 from typing import Optional
 
 import torch
@@ -20,15 +18,24 @@ from .parallel.ep import ExpertParallelLayer
 from .world import World
 
 L2_BYTES = 126 * 1024 * 1024
-NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool
+# NVLink 5 per direction per GPU: the rate a one-directional peer copy reached on 8 x B200
+# (benchmarks/peer_copy_bench.py measures it) and the nominal link rate.  Fractions are reported
+# against both.
+NVLINK_GBS = 770.0
+NVLINK_NOMINAL_GBS = 900.0
+
+_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+          "source": "fallback"}
+
+
+def set_peaks(peaks: dict) -> None:
+    """Roofline denominators measured on the machine at hand (copy bandwidth, cuBLAS rate); the
+    benchmark scripts load them from a record beside the checkout when there is one."""
+    _PEAKS.update(peaks)
 
 
 def measured_peaks() -> dict:
-    path = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
-    if path.exists():
-        return {**json.loads(path.read_text()), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
-            "source": "fallback"}
+    return dict(_PEAKS)
 
 
 def sync_ranks(distributed: bool) -> None:
@@ -70,7 +77,11 @@ class EpLayerBench:
     """DeepSeek-V3-shape MoE layer with seeded synthetic inputs."""
 
     def __init__(self, world: World, *, tokens: int, hidden: int, experts: int, top_k: int,
-                 group: int, seed: int, tag: str = "bench"):
+                 group: int, seed: int, tag: str = "bench", weighted: bool = True):
+        # weighted: the expert stage leaves expert-contiguous, unweighted rows and the combine
+        # kernel applies the gates (the product path); False: the experts apply the gates and the
+        # combine sums one partial row per record (the reference's split).
+        self.weighted = weighted
         self.world, self.tokens = world, tokens
         self.spec = MoESpec(capacity=tokens, hidden=hidden, top_k=top_k, experts=experts,
                             ranks=world.world_size, value_type="f8E4M3FN", scale_group=group)
@@ -91,7 +102,10 @@ class EpLayerBench:
     def step(self) -> torch.Tensor:
         i = self.counter % self.copies
         self.counter += 1
-        return self.layer.forward(self.x[i], self.logits[i])
+        return self.layer.forward(self.x[i], self.logits[i], self._experts(self.weighted))
+
+    def _experts(self, weighted: bool):
+        return self.layer.standin_experts_grouped if weighted else self.layer.standin_experts
 
     def check(self) -> None:
         torch.cuda.synchronize()
@@ -99,7 +113,7 @@ class EpLayerBench:
 
     def verify(self) -> int:
         """Rows of one step's output outside the fp8 tolerance of the fp32 oracle."""
-        out = self.layer.forward(self.x[0], self.logits[0]).float()
+        out = self.layer.forward(self.x[0], self.logits[0], self._experts(self.weighted)).float()
         torch.cuda.synchronize()
         ids = self.layer.slot.topk_ids[: self.tokens]
         weights = self.layer.slot.topk_weights[: self.tokens]
@@ -123,8 +137,11 @@ class EpLayerBench:
                 "dispatch_local_hbm_bytes": self.tokens * s.hidden * 2 + total * record,
                 "combine_local_hbm_bytes": total * s.hidden * 2 * 2 + self.tokens * s.hidden * 2}
 
-    def phase_times(self, *, steps: int, distributed: bool, flush: bool = False) -> dict:
+    def phase_times(self, *, steps: int, distributed: bool, flush: bool = False,
+                    weighted: Optional[bool] = None) -> dict:
         slot, layer = self.layer.slot, self.layer
+        weighted = self.weighted if weighted is None else weighted
+        experts = self._experts(weighted)
         if flush and self.flusher is None:
             self.flusher = L2Flusher(self.world.torch_device)
         ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
@@ -142,13 +159,14 @@ class EpLayerBench:
             e0.record()
             res = slot.dispatch(self.x[i], logits=self.logits[i])
             e1.record()
-            layer.standin_experts(res, slot.expert_output)
+            staged = experts(res, slot.expert_output)
+            offsets, rows = staged if isinstance(staged, tuple) else (None, slot.expert_output)
             if flush:
                 self.flusher()
             sync_ranks(distributed)
             torch.cuda._sleep(100_000)
             e2.record()
-            slot.combine(slot.expert_output)
+            slot.combine(rows, expert_offsets=offsets)
             e3.record()
             torch.cuda.synchronize()
             if it >= 3:
@@ -163,9 +181,12 @@ class EpLayerBench:
         if self.world.world_size > 1:
             td = traffic["dispatch_remote_bytes"] / (NVLINK_GBS * 1e3)  # us
             tc = traffic["combine_remote_bytes"] / (NVLINK_GBS * 1e3)
-            roof.update({"bound": "nvlink 770 GB/s per direction (measured peer copy)",
+            nominal = NVLINK_GBS / NVLINK_NOMINAL_GBS
+            roof.update({"bound": "nvlink egress per direction: 770 GB/s measured peer copy (900 nominal)",
                          "dispatch_roof_us": td, "combine_roof_us": tc,
-                         "dispatch_frac": td / d if d else None, "combine_frac": tc / c if c else None})
+                         "dispatch_frac": td / d if d else None, "combine_frac": tc / c if c else None,
+                         "dispatch_frac_of_900": td * nominal / d if d else None,
+                         "combine_frac_of_900": tc * nominal / c if c else None})
         else:
             td = traffic["dispatch_local_hbm_bytes"] / (peaks["hbm_gbs"] * 1e3)
             tc = traffic["combine_local_hbm_bytes"] / (peaks["hbm_gbs"] * 1e3)
@@ -173,20 +194,24 @@ class EpLayerBench:
                          "dispatch_roof_us": td, "combine_roof_us": tc,
                          "dispatch_frac": td / d if d else None, "combine_frac": tc / c if c else None})
         return {"dispatch_us": d, "combine_us": c, "tokens_per_rank": self.tokens, "roofline": roof,
+                "combine": "bf16 gate-weighted in kernel" if weighted else "bf16 unweighted sum of partials",
+                "dispatch_us_min": min(device_max_vector(d_ms, distributed)) * 1e3,
+                "combine_us_min": min(device_max_vector(c_ms, distributed)) * 1e3,
                 "l2": "flushed before each bracket" if flush else self.l2_policy}
 
     def end_to_end(self, *, steps: int, distributed: bool) -> dict:
         s = self.spec
         hosts = [(x.cpu().pin_memory(), l.cpu().pin_memory()) for x, l in zip(self.x, self.logits)]
         for k in range(3):
-            self.layer.forward_from_host(*hosts[k % len(hosts)], prefetch=hosts[(k + 1) % len(hosts)])
+            self.layer.forward_from_host(*hosts[k % len(hosts)], self._experts(self.weighted),
+                                         prefetch=hosts[(k + 1) % len(hosts)])
         torch.cuda.synchronize()
         sync_ranks(distributed)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for k in range(steps):
             # Step k's inputs were copied under step k-1's kernels; step k+1's copy starts now.
-            result = self.layer.forward_from_host(*hosts[k % len(hosts)],
+            result = self.layer.forward_from_host(*hosts[k % len(hosts)], self._experts(self.weighted),
                                                   prefetch=hosts[(k + 1) % len(hosts)])
             torch.cuda.current_stream().synchronize()  # the caller reads the result every step
             if int(result[0]) != 0:
@@ -202,14 +227,16 @@ class EpLayerBench:
                            "the previous step's kernels; the result is read back after every step"}
 
 
-def alltoall_sweep(world: World, distributed: bool, sizes=None, *, rounds: int = 20) -> list[dict]:
-    """Bus bandwidth of the all-to-all kernel; ``busbw = (n-1) * S / t`` with t the
-    mean round time of the slowest rank (definition: experiments/bench/README.md:111-131
-    of the reference)."""
+def alltoall_sweep(world: World, distributed: bool, sizes=None, *, rounds: int = 20,
+                   chains=(1, 8, 64), chain_sizes=(1 << 10, 1 << 16, 1 << 20)) -> list[dict]:
+    """Bus bandwidth of the all-to-all kernel over every power-of-two message size from 1 KiB to
+    256 MiB per peer, and of put/signal chains (``chain`` puts closed by one signal) at
+    ``chain_sizes``; ``busbw = (n-1) * S / t`` with t the mean round time of the slowest rank
+    (definition: experiments/bench/README.md:111-131 of the reference)."""
     from .ops import alltoall, check_payload, fill_payload
 
     n, rank, dev = world.world_size, world.rank, world.torch_device
-    sizes = sizes or [1 << 10, 1 << 14, 1 << 18, 1 << 22, 1 << 26]
+    sizes = list(sizes or [1 << e for e in range(10, 29)])
     top = max(sizes)
     max_lanes = 32
     arena = world.runtime.allocate(2 * n * top + n * max_lanes * 8)
@@ -221,33 +248,42 @@ def alltoall_sweep(world: World, distributed: bool, sizes=None, *, rounds: int =
     my_flags = arena[2 * n * top:].view(torch.int64)
     status = torch.zeros(2, dtype=torch.int64, device=dev)
     errors = torch.zeros(1, dtype=torch.int64, device=dev)
-    out, epoch = [], 0
+    tabs = (table.addresses("a2a_recv"), table.addresses("a2a_flags"))
+    out = []
     for size in sizes:
         for p in range(n):
             fill_payload(send[p * top:], size, 4242, rank, p)
-        for mode in ("vector", "bulk"):
+        # Keep a sweep short: fewer rounds once a round moves hundreds of megabytes.
+        r = max(3, min(rounds, (4 << 30) // max(size * max(n - 1, 1), 1)))
+        cases = [("vector", 1)] if size < (1 << 20) else [("bulk", 1)]
+        if size in (1 << 22, 1 << 26):
+            cases = [("vector", 1), ("bulk", 1)]
+        cases += [("vector", c) for c in chains if c > 1 and size in chain_sizes]
+        for mode, chain in cases:
             lanes = max(1, min(max_lanes, size // 16384))
+            if size // lanes // chain < 16:
+                continue
             my_flags.zero_()
-            epoch = 0
+            errors.zero_()
             sync_ranks(distributed)
-            kwargs = dict(stride=top, nbytes=size, rank=rank, world=n, lanes=lanes, mode=mode)
-            alltoall(send, table.addresses("a2a_recv"), table.addresses("a2a_flags"), my_flags,
-                     status, epoch0=epoch, rounds=3, **kwargs)
-            epoch += 3
+            kwargs = dict(stride=top, nbytes=size, rank=rank, world=n, lanes=lanes, mode=mode,
+                          chain=chain)
+            alltoall(send, *tabs, my_flags, status, epoch0=0, rounds=3, **kwargs)
             sync_ranks(distributed)
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
-            alltoall(send, table.addresses("a2a_recv"), table.addresses("a2a_flags"), my_flags,
-                     status, epoch0=epoch, rounds=rounds, **kwargs)
+            alltoall(send, *tabs, my_flags, status, epoch0=3, rounds=r, **kwargs)
             stop.record()
             torch.cuda.synchronize()
-            t = device_max(start.elapsed_time(stop), distributed) / rounds * 1e-3
+            t = device_max(start.elapsed_time(stop), distributed) / r * 1e-3
             for s in range(n):
                 if s != rank:
                     check_payload(arena[n * top + s * top:], size, 4242, s, rank, errors)
             sync_ranks(distributed)
             bus = (n - 1) * size / t / 1e9
-            out.append({"bytes_per_peer": size, "mode": mode, "lanes": lanes, "round_us": t * 1e6,
-                        "busbw_gbs": bus, "frac_of_770": bus / NVLINK_GBS,
+            out.append({"bytes_per_peer": size, "mode": mode, "chain": chain, "lanes": lanes,
+                        "rounds": r, "round_us": t * 1e6, "busbw_gbs": bus,
+                        "frac_of_770": bus / NVLINK_GBS, "frac_of_900": bus / NVLINK_NOMINAL_GBS,
                         "wrong_words": int(errors.item()), "status": status.tolist()})
+    del arena
     return out

@@ -286,12 +286,11 @@ AB_EXPORT int ab_alltoall(const void *send, const std::uint64_t *peer_recv,
         return -2;  // bulk-async copies move whole 16-byte units
     const dim3 grid(peers * lanes);
     if (mode == 1) {
-        static bool configured = false;
         const int smem = 4 * 16384;
-        if (!configured) {
-            cudaFuncSetAttribute(alltoall_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-            configured = true;
-        }
+        // Per device context, so set on every call rather than once per process.
+        if (cudaFuncSetAttribute(alltoall_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess)
+            return -3;
         alltoall_kernel<1><<<grid, 32, smem, stream>>>(p);
     } else {
         alltoall_kernel<0><<<grid, threads, 0, stream>>>(p);

@@ -195,8 +195,7 @@ int launch_grouped(const void *a, const void *w, void *c, const int *counts, con
         !make_map_bf16(&map_b, w, static_cast<std::uint64_t>(experts) * n, k, k, BN))
         return -2;
     constexpr unsigned smem = Geometry<HALVES>::kSmemBytes;
-    static bool configured = configure(gemm_tcgen05_kernel<HALVES, Policy>, smem);
-    if (!configured)
+    if (!configure(gemm_tcgen05_kernel<HALVES, Policy>, smem))  // per device context: set on every call
         return -3;
     const int tiles_n = (n + BN - 1) / BN;
     const long long column_bytes = static_cast<long long>(BN) * k * 2;
@@ -217,8 +216,7 @@ int launch_pair(const void *a, const void *b, PlainPolicy p, int lda, int ldb, u
         : make_map_e4m3(&map_a, a, p.m, p.k, lda, G::kRowsPerCta) && make_map_e4m3(&map_b, b, p.n, p.k, ldb, BN / 2);
     if (!mapped)
         return -2;
-    static bool configured = configure(gemm_pair_kernel<MH, Op, PlainPolicy>, G::kSmemBytes);
-    if (!configured)
+    if (!configure(gemm_pair_kernel<MH, Op, PlainPolicy>, G::kSmemBytes))  // per device context: set on every call
         return -3;
     // A persistent kernel must not launch more clusters than can be resident at once: the
     // surplus would start only after a resident one has finished all of its tiles.
@@ -257,8 +255,7 @@ AB_EXPORT int ab_gemm_bf16(const void *a, const void *b, void *c, int m, int n, 
     if (!make_map_bf16(&map_a, a, m, k, lda, kPlainRows) || !make_map_bf16(&map_b, b, n, k, ldb, BN))
         return -2;
     constexpr unsigned smem = Geometry<kPlainHalves>::kSmemBytes;
-    static bool configured = configure(gemm_tcgen05_kernel<kPlainHalves, PlainPolicy>, smem);
-    if (!configured)
+    if (!configure(gemm_tcgen05_kernel<kPlainHalves, PlainPolicy>, smem))  // per device context: set on every call
         return -3;
     const int grid = p.tiles_total < sm_count() ? p.tiles_total : sm_count();
     gemm_tcgen05_kernel<kPlainHalves, PlainPolicy><<<grid, kThreads, smem, stream>>>(map_a, map_b, p, status);

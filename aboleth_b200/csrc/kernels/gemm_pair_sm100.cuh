@@ -53,7 +53,12 @@ struct PairState {
     std::uint32_t tmem_base;
     volatile int abort;
     volatile int epi_ready;
+    volatile int epi_abort;  // epilogue warps: shared sample of `abort`
 };
+
+// Raise `abort` in this CTA and in its pair CTA: either of them giving up must end both, because
+// each one's barriers are completed by the other.
+__device__ __forceinline__ void raise_abort(PairState &st, unsigned rank);
 
 __device__ __forceinline__ unsigned cluster_rank() {
     unsigned r;
@@ -66,6 +71,12 @@ __device__ __forceinline__ std::uint32_t map_to_cta(std::uint32_t local, unsigne
     std::uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
     return remote;
+}
+
+__device__ __forceinline__ void raise_abort(PairState &st, unsigned rank) {
+    st.abort = 1;
+    const std::uint32_t remote = map_to_cta(smem_u32(const_cast<int *>(&st.abort)), rank ^ 1u);
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(1) : "memory");
 }
 
 __device__ __forceinline__ void cluster_sync() {
@@ -224,7 +235,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
 #endif
             for (int it = 0; !st.abort && policy.next(it, t); ++it) {
                 if (!policy.ready(t)) {
-                    st.abort = 1;
+                    raise_abort(st, rank);
                     set_status(status, aboleth::Status::Timeout, 0x3000 + t.tag);
                     break;
                 }
@@ -237,7 +248,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
                     t_wait += clock64() - w0;
 #endif
                     if (!got || st.abort) {
-                        st.abort = 1;
+                        raise_abort(st, rank);
                         set_status(status, aboleth::Status::Timeout, 0x3100 + stage);
                         break;
                     }
@@ -285,7 +296,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
                     t_full += clock64() - f0;
 #endif
                     if (!filled) {
-                        st.abort = 1;
+                        raise_abort(st, rank);
                         set_status(status, aboleth::Status::Timeout, 0x3300 + stage);
                         break;
                     }
@@ -305,7 +316,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
                             t_acc += clock64() - a0;
 #endif
                             if (!free_acc) {
-                                st.abort = 1;
+                                raise_abort(st, rank);
                                 set_status(status, aboleth::Status::Timeout, 0x3200 + slot);
                                 break;
                             }
@@ -342,8 +353,22 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
         constexpr int kEpiThreads = kEpilogueWarps * 32;
         uint4 *epi_stage = reinterpret_cast<uint4 *>(tiles + kStagesG * G::kStageBytes +
                                                      (warp - 2) * kEpilogueWarpStageBytes);
+        // `abort` is raised asynchronously by the producer or the MMA lane.  The four epilogue warps
+        // meet at named barrier 1, so they must all take the same way out: one thread samples the
+        // flag and the sample is what all 128 threads branch on.
+        auto epilogue_aborted = [&]() -> bool {
+            if (epi_thread == 0)
+                st.epi_abort = st.abort;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int sample = st.epi_abort;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            return sample != 0;
+        };
         Tile t;
-        for (int it = 0; !st.abort && policy.next(it, t); ++it) {
+        bool aborted = false;
+        for (int it = 0; policy.next(it, t); ++it) {
+            if ((aborted = epilogue_aborted()))
+                break;
             const unsigned use = use_of(it);
 #pragma unroll
             for (int h = 0; h < MH; ++h) {
@@ -360,7 +385,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
                     }
                 }
                 if (!mbar_wait(&st.tmem_full[slot], use)) {
-                    st.abort = 1;
+                    raise_abort(st, rank);
                     set_status(status, aboleth::Status::Timeout, 0x3400 + slot);
                     break;
                 }
@@ -383,10 +408,11 @@ __device__ __forceinline__ void gemm_mainloop_pair(Policy &policy, const CUtenso
                 policy.tile_done(t);
         }
         if constexpr (Policy::kBackground) {
-            while (!st.abort && policy.background(epi_thread, kEpiThreads)) {
+            while (!aborted && !(aborted = epilogue_aborted()) &&
+                   policy.background(epi_thread, kEpiThreads)) {
             }
         }
-        if (!st.abort)
+        if (!aborted && !epilogue_aborted())
             policy.finish(epi_thread, kEpiThreads, status);
     }
 

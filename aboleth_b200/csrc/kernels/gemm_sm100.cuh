@@ -45,6 +45,7 @@ struct SharedState {
     std::uint32_t tmem_base;
     volatile int abort;
     volatile int epi_ready;  // epilogue warps: shared outcome of one accumulator poll
+    volatile int epi_abort;  // epilogue warps: shared sample of `abort`
 };
 
 // ---- tcgen05 wrappers --------------------------------------------------------------
@@ -387,8 +388,22 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
         constexpr int kEpiThreads = kEpilogueWarps * 32;
         uint4 *epi_stage = reinterpret_cast<uint4 *>(tiles + kStagesG * G::kStageBytes +
                                                      (warp - 2) * kEpilogueWarpStageBytes);
+        // `abort` is raised asynchronously by the producer or the MMA lane.  The four epilogue warps
+        // meet at named barrier 1, so they must all take the same way out: one thread samples the
+        // flag and the sample is what all 128 threads branch on.
+        auto epilogue_aborted = [&]() -> bool {
+            if (epi_thread == 0)
+                st.epi_abort = st.abort;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int sample = st.epi_abort;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            return sample != 0;
+        };
         Tile t;
-        for (int it = 0; !st.abort && policy.next(it, t); ++it) {
+        bool aborted = false;
+        for (int it = 0; policy.next(it, t); ++it) {
+            if ((aborted = epilogue_aborted()))
+                break;
             const unsigned use = use_of(it);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) {
@@ -432,10 +447,11 @@ __device__ __forceinline__ void gemm_mainloop(Policy &policy, const CUtensorMap 
                 policy.tile_done(t);
         }
         if constexpr (Policy::kBackground) {
-            while (!st.abort && policy.background(epi_thread, kEpiThreads)) {
+            while (!aborted && !(aborted = epilogue_aborted()) &&
+                   policy.background(epi_thread, kEpiThreads)) {
             }
         }
-        if (!st.abort)
+        if (!aborted && !epilogue_aborted())
             policy.finish(epi_thread, kEpiThreads, status);
     }
 

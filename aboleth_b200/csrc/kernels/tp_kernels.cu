@@ -100,7 +100,12 @@ struct AgGemmPolicy {
     __device__ __forceinline__ bool ready(const Tile &t) const {
         if (t.a_sel)
             return true;
-        return aboleth::wait_signal_status(flags + t.tag, epoch) == Status::Ok;
+        if (aboleth::wait_signal_status(flags + t.tag, epoch) != Status::Ok)
+            return false;
+        // The chunk was written by peers with generic-proxy stores; the loads that follow are TMA
+        // (async proxy).  The acquire orders the generic side, this fence carries it across.
+        ab::fence_proxy_async();
+        return true;
     }
     __device__ __forceinline__ void store16(const Tile &t, int row, int col, const uint4 &v) const {
         *reinterpret_cast<uint4 *>(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col) = v;
@@ -402,10 +407,9 @@ AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const vo
     if (!make_map_bf16(&map_staging, staging, static_cast<std::uint64_t>(world) * m_local, k, k, kRows) ||
         !make_map_bf16(&map_b, b, n, k, k, BN) || !make_map_bf16(&map_local, a_local, m_local, k, k, kRows))
         return -2;
-    static bool configured =
-        cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) ==
-        cudaSuccess;
-    if (!configured)
+    // The attribute belongs to the current device's context, so it is set on every call (cheap)
+    // rather than remembered once per process.
+    if (cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
         return -3;
     const int chunks = m_local / kRows;
     if (parts < 1) {  // items of about 64 KiB: short enough to slot in between accumulator polls
@@ -442,10 +446,9 @@ AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials
     if (!make_map_bf16(&map_a, a, static_cast<std::uint64_t>(world) * m_local, k, k, kRows) ||
         !make_map_bf16(&map_b, b, n, k, k, BN))
         return -2;
-    static bool configured =
-        cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) ==
-        cudaSuccess;
-    if (!configured)
+    // The attribute belongs to the current device's context, so it is set on every call (cheap)
+    // rather than remembered once per process.
+    if (cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
         return -3;
     // Background reduction needs at least two owned tiles per CTA to pay for the transfers it moves
     // into the last wave; ABOLETH_RS_ORDER=0 / 1 forces the owner-by-owner / interleaved order.

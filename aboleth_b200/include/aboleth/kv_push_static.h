@@ -36,18 +36,38 @@
 //     never.  Order such calls on one stream or with events.
 //   * `batches` and `status` are the caller's device memory, as for `ab_kv_push`:
 //     `count` records of {src, dst, bytes, ready} (four 64-bit words each; src and dst
-//     16-byte aligned) and two 64-bit status words.
+//     16-byte aligned) and two 64-bit status words.  A run whose src or dst is not
+//     16-byte aligned is reported as malformed in the status words AND still copied
+//     (through the 8-byte or the byte path), so the data is right either way.
+//   * Every batch of one call must name a readiness cell OF ITS OWN.  There is one
+//     counter per batch: a cell that two batches share is published as soon as the
+//     first of them has finished, while the other may still be copying.  A caller that
+//     wants one cell for several runs (a readiness group of several layers) either
+//     makes them one contiguous batch, gives each its own cell and waits for all of
+//     them, or uses `ab_kv_push` with its group arguments.
+//   * The remembered address of the counter array belongs to the device context it
+//     was looked up in.  After cudaDeviceReset in the same process it is stale; a
+//     process that resets a device must not call this entry point for that device again.
 //
 // Returns 0 when the work was enqueued, a negative AB_KV_PUSH_STATIC_* code for a
 // rejected argument, or the positive cudaError_t of a failed runtime call.
 #pragma once
 
-#include <cstdint>
+#include <stdint.h>
+
 #include <cuda_runtime_api.h>
 
 #define AB_KV_PUSH_STATIC_MAX_BATCHES 4096
 #define AB_KV_PUSH_STATIC_BAD_ARGUMENT (-1)
 #define AB_KV_PUSH_STATIC_TOO_MANY (-2)
 
-extern "C" int ab_kv_push_static(const void *batches, int count, std::uint64_t epoch, int workers,
-                                 int threads, unsigned long long *status, cudaStream_t stream);
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int ab_kv_push_static(const void *batches, int count, uint64_t epoch, int workers, int threads,
+                      unsigned long long *status, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

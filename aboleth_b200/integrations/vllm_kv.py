@@ -175,9 +175,14 @@ class VLLMKVPeerRuntime:
                                  n * self._page_bytes, cell) for r, l, n in runs]
                 if len(batches) > self._arrivals.numel():
                     self._arrivals = torch.zeros(len(batches), dtype=torch.int32, device=self.world.torch_device)
+                # Every batch of the group publishes the group's cell: one shared arrival counter.
+                workers = plan.physicalization.generated_copy_workers
+                group_of, group_target, _ = kvcopy.pack_groups([b[3] for b in batches], workers,
+                                                               self.world.torch_device)
                 kvcopy.push(kvcopy.pack_batches(batches, self.world.torch_device), self._arrivals,
-                            len(batches), self._epoch, workers=plan.physicalization.generated_copy_workers,
-                            threads=self.target_profile.threads, status=self._status)
+                            len(batches), self._epoch, workers=workers,
+                            threads=self.target_profile.threads, status=self._status,
+                            group_of=group_of, group_target=group_target)
             if layered:
                 event = torch.cuda.Event()
                 event.record(stream)

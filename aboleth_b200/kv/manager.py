@@ -81,25 +81,24 @@ class CompiledKVTransferManager:
         for group in range(self.groups):
             layers = range(group * per_group, min((group + 1) * per_group, l.layers))
             cell = ready_base + ((slot * self.groups + group) * ranks + rank) * 8
-            # Every batch of the group targets the same cell; the last arrival publishes it,
-            # so the group is launched as ONE batch list with a shared arrival counter.
-            group_batches = []
             for layer in layers:
                 for s, d, n in runs:
                     src = self.pool[layer, s].data_ptr()
                     dst = slots_base + ((slot * l.layers + layer) * l.slot_pages + d) * l.page_bytes
-                    group_batches.append((src, dst, n * l.page_bytes, cell))
-            batches.append(group_batches)
-        launched = 0
-        for group, group_batches in enumerate(batches):
-            # One launch per readiness group: batches are chained so the group's cell is published
-            # after its last batch - each batch publishes the same epoch, later stores are idempotent.
-            packed = kvcopy.pack_batches(group_batches, self.world.torch_device)
-            if len(group_batches) > self._arrivals.numel():
-                self._arrivals = torch.zeros(len(group_batches), dtype=torch.int32, device=self.world.torch_device)
-            kvcopy.push(packed, self._arrivals, len(group_batches), epoch,
-                        workers=self.profile.copy_workers, threads=self.profile.threads, status=self.status)
-            launched += len(group_batches)
+                    batches.append((src, dst, n * l.page_bytes, cell))
+        # ONE launch for the whole transfer.  The batches of a readiness group name the same cell and
+        # share one arrival counter: the cell is published by the last worker of the group's last
+        # batch, never by a batch that merely finished first.
+        dev = self.world.torch_device
+        packed = kvcopy.pack_batches(batches, dev)
+        group_of, group_target, groups = kvcopy.pack_groups([b[3] for b in batches],
+                                                            self.profile.copy_workers, dev)
+        if groups > self._arrivals.numel():
+            self._arrivals = torch.zeros(groups, dtype=torch.int32, device=dev)
+        kvcopy.push(packed, self._arrivals, len(batches), epoch, workers=self.profile.copy_workers,
+                    threads=self.profile.threads, status=self.status, group_of=group_of,
+                    group_target=group_target)
+        launched = len(batches)
         return launched
 
     # -- consumer side ----------------------------------------------------------------------

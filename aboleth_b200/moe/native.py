@@ -8,6 +8,15 @@ device memory and is advanced by the combine kernel, so the pair can be
 captured in a CUDA graph.  API shape follows the reference's executor
 (python/aboleth/moe/native.py:34-178,433-615).
 
+The SENDER unpacks: besides the payload row and the wire-format metadata row it
+writes each record's expert ids, gate weights and positions into the
+destination's ``recv_ids`` / ``recv_weights`` / ``recv_pos`` arrays (positions
+come from one ``atom.add`` per chosen expert on the destination's
+``expert_acc`` counters), so the receiving rank runs no per-record pass.  The
+combine publishes returned records in blocks of ``return_block`` rows
+(``return_flags[peer, block]``) and reduces a token as soon as the blocks that
+hold its partial rows are there.
+
 ``LocalMoEGroup`` runs several ranks on ONE device inside one process by
 launching every rank's send half before any rank's receive half; it exists for
 tests and single-GPU development, not for performance.
@@ -25,7 +34,31 @@ from ..world import World
 from .spec import MoESpec
 
 PHASE_SEND, PHASE_RECV = 1, 2
-_REGIONS = ("recv_payload", "recv_meta", "recv_counts", "dispatch_flags", "returned", "return_flags")
+_REGIONS = ("recv_payload", "recv_meta", "recv_counts", "dispatch_flags", "returned", "return_flags",
+            "recv_ids", "recv_weights", "recv_pos", "expert_acc")
+RETURN_BLOCK = 64          # records per readiness block of the combine
+MAX_DISPATCH_CTAS = 2048   # rows of the per-CTA record-count table (token-ordered slots)
+
+
+def return_blocks(spec: MoESpec, block: int = RETURN_BLOCK) -> int:
+    return (spec.capacity + block - 1) // block
+
+
+def _region_sizes(spec: MoESpec) -> dict[str, int]:
+    s, rows = spec, spec.ranks * spec.capacity
+    return {
+        "recv_payload": rows * s.row_bytes,
+        "recv_meta": rows * s.metadata_words * 4,
+        "recv_counts": s.ranks * 8,
+        "dispatch_flags": s.ranks * 8,
+        "returned": rows * s.hidden * 2,
+        # [ranks, blocks + 1] int64: one flag per block of returned records, then "finished sending"
+        "return_flags": s.ranks * (return_blocks(s) + 1) * 8,
+        "recv_ids": rows * s.top_k * 4,
+        "recv_weights": rows * s.top_k * 4,
+        "recv_pos": rows * s.top_k * 4,
+        "expert_acc": s.experts * 4,
+    }
 
 
 def _align(n: int, a: int = 256) -> int:
@@ -52,16 +85,7 @@ class MoEBuffers:
     """Carves one rank's arena.  ``arena`` must be zero-initialised."""
 
     def __init__(self, spec: MoESpec, arena: torch.Tensor):
-        s = spec
-        rows = s.ranks * s.capacity
-        sizes = {
-            "recv_payload": rows * s.row_bytes,
-            "recv_meta": rows * s.metadata_words * 4,
-            "recv_counts": s.ranks * 8,
-            "dispatch_flags": s.ranks * 8,
-            "returned": rows * s.hidden * 2,
-            "return_flags": s.ranks * 8,
-        }
+        sizes = _region_sizes(spec)
         self.offsets, cursor = {}, 0
         for name in _REGIONS:
             self.offsets[name] = (cursor, sizes[name])
@@ -73,10 +97,7 @@ class MoEBuffers:
 
     @staticmethod
     def arena_bytes(spec: MoESpec) -> int:
-        rows = spec.ranks * spec.capacity
-        sizes = [rows * spec.row_bytes, rows * spec.metadata_words * 4, spec.ranks * 8,
-                 spec.ranks * 8, rows * spec.hidden * 2, spec.ranks * 8]
-        return sum(_align(x) for x in sizes)
+        return sum(_align(x) for x in _region_sizes(spec).values())
 
     def view(self, name: str) -> torch.Tensor:
         start, size = self.offsets[name]
@@ -97,26 +118,36 @@ class NativeMoESlot:
         self.recv_counts = b.view("recv_counts").view(torch.int64)
         self.dispatch_flags = b.view("dispatch_flags").view(torch.int64)
         self.returned = b.view("returned").view(torch.bfloat16).view(rows, s.hidden)
-        self.return_flags = b.view("return_flags").view(torch.int64)
+        self.return_block = RETURN_BLOCK
+        self.return_flags = b.view("return_flags").view(torch.int64).view(s.ranks, return_blocks(s) + 1)
         self.peer_tables = peer_tables  # name -> int64 [ranks] addresses
         owners = placement if isinstance(placement, (list, tuple)) else spec.owners(placement)
         self.owners_list = list(owners)
         self.owners = torch.tensor(self.owners_list, dtype=torch.int32, device=dev)
-        foreign = [e for e, o in enumerate(self.owners_list) if o != self.rank]
-        # Unused choice slots name an expert some other rank owns, at weight 0.
-        self.placeholder = foreign[0] if foreign else -1
+        # Unused choice slots of a record name an expert its destination does not own, at weight 0.
+        foreign = [next((e for e, o in enumerate(self.owners_list) if o != d), -1)
+                   for d in range(s.ranks)]
+        self.placeholder = foreign[self.rank]
+        self.placeholders = torch.tensor(foreign, dtype=torch.int32, device=dev)
         z = lambda *shape, dtype: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
         self.source_slots = torch.full((s.capacity, s.ranks), -1, dtype=torch.int32, device=dev)
         self.send_counts = z(s.ranks, dtype=torch.int64)
-        self.done = z(4, dtype=torch.int32)
+        self.done = z(8, dtype=torch.int32)
+        self.block_counts = z(MAX_DISPATCH_CTAS, s.ranks, dtype=torch.int32)
+        self.block_done = z(s.ranks, return_blocks(s), dtype=torch.int32)
         self.overflow = z(1, dtype=torch.int32)
         self.epoch = torch.ones(1, dtype=torch.int64, device=dev)
         self.status = z(2, dtype=torch.int64)
-        self.expert_ids = z(rows, s.top_k, dtype=torch.int32)
-        self.expert_weights = z(rows, s.top_k, dtype=torch.float32)
-        self.expert_pos = torch.full((rows, s.top_k), -1, dtype=torch.int32, device=dev)
+        # Written by the SENDING ranks (peer-visible); the expert stage reads them as they are.
+        self.expert_ids = b.view("recv_ids").view(torch.int32).view(rows, s.top_k)
+        self.expert_weights = b.view("recv_weights").view(torch.float32).view(rows, s.top_k)
+        self.expert_pos = b.view("recv_pos").view(torch.int32).view(rows, s.top_k)
+        self.expert_acc = b.view("expert_acc").view(torch.int32)
         self.expert_counts = z(s.experts, dtype=torch.int32)
-        self.expert_scales = z(rows, s.scale_cols, dtype=torch.float32) if s.fp8 else None
+        # The scales travel inside the metadata row; this is a strided view of them (row stride =
+        # metadata_words), not a copy.
+        self.expert_scales = (self.recv_meta.view(torch.float32)[:, 2 + 2 * s.top_k:]
+                              if s.fp8 else None)
         self.topk_ids = z(s.capacity, s.top_k, dtype=torch.int32)
         self.topk_weights = z(s.capacity, s.top_k, dtype=torch.float32)
         self.expert_output = z(rows, s.hidden, dtype=torch.bfloat16)
@@ -129,7 +160,9 @@ class NativeMoESlot:
         self.by_warp_threshold = 512
         # Optional device trace: %globaltimer stamps (ns) of kernel phases, see trace().
         self.trace_buffer: Optional[torch.Tensor] = None
-        self._ints = (ctypes.c_int * 16)()
+        # Warps per CTA that send in a fused warp-per-row combine; the others reduce.
+        self.send_warps = 6
+        self._ints = (ctypes.c_int * 24)()
         self._ptrs = (ctypes.c_uint64 * 32)()
         self._table = None
 
@@ -156,8 +189,10 @@ class NativeMoESlot:
         s, i = self.spec, self._ints
         by_warp = (num_tokens > self.by_warp_threshold) if self.by_warp is None else self.by_warp
         values = [self.rank, s.ranks, s.experts, s.top_k, s.hidden, s.scale_group, s.capacity,
-                  int(s.fp8), int(s.round_scale), self.placeholder, num_tokens, routing,
-                  int(renormalize), phases, weighted, int(by_warp)]
+                  int(s.fp8), int(s.round_scale), 0, num_tokens, routing,
+                  int(renormalize), phases, weighted, int(by_warp), self.return_block,
+                  self.send_warps, self.block_counts.shape[0]]
+        self.last_launch = {"by_warp": bool(by_warp), "grid": self.grid, "phases": phases}
         for k, v in enumerate(values):
             i[k] = v
         return i
@@ -191,11 +226,11 @@ class NativeMoESlot:
             raise ValueError("ids (int32) and weights (fp32) are required without logits")
         t = self.peer_tables
         pointers = [tokens, logits, ids, weights, self.topk_ids, self.topk_weights, self.owners,
-                    self.source_slots, self.send_counts, self.done, self.overflow, self.epoch,
-                    self.status, t["recv_payload"], t["recv_meta"], t["recv_counts"],
-                    t["dispatch_flags"], self.recv_meta, self.recv_counts, self.dispatch_flags,
-                    self.expert_ids, self.expert_weights, self.expert_pos, self.expert_counts,
-                    self.expert_scales, self.trace_buffer]
+                    self.placeholders, self.source_slots, self.send_counts, self.done, self.overflow,
+                    self.epoch, self.status, self.block_counts, t["recv_payload"], t["recv_meta"],
+                    t["recv_counts"], t["dispatch_flags"], t["recv_ids"], t["recv_weights"],
+                    t["recv_pos"], t["expert_acc"], self.recv_counts, self.dispatch_flags,
+                    self.expert_acc, self.expert_counts, self.trace_buffer]
         call("ab_ep_dispatch", self._geometry(n, routing, renormalize, phases),
              ctypes.c_float(s.quant_amax_floor), self._fill(pointers), self.grid, stream_ptr())
         self._last_tokens = n
@@ -225,7 +260,7 @@ class NativeMoESlot:
         pointers = [y, self.expert_ids, self.expert_pos, self.expert_weights, expert_offsets,
                     self.recv_meta, self.recv_counts, t["returned"], t["return_flags"],
                     self.return_flags, self.returned, self.source_slots, out, self.done,
-                    self.expert_counts, self.epoch, self.status, self.trace_buffer]
+                    self.block_done, self.epoch, self.status, self.trace_buffer]
         call("ab_ep_combine", self._geometry(n, 0, False, phases, int(expert_offsets is not None)),
              ctypes.c_float(s.quant_amax_floor), self._fill(pointers), self.grid, stream_ptr())
         return out[:n]
@@ -235,18 +270,24 @@ class NativeMoESlot:
         self.trace_buffer = torch.zeros(8, dtype=torch.int64, device=self.device)
 
     def trace(self) -> dict:
-        """Phase durations (us) of the last traced kernel: send, publish, wait, finish."""
+        """Phase stamps (us after CTA 0 started) of the last traced kernel.
+
+        Dispatch: ``first_cta_sent``, ``all_sent`` (the last CTA arrived and publishes),
+        ``peers_seen`` (every peer's flag observed), ``end``.  Combine: ``first_cta_sent``,
+        ``first_cta_reduced``, ``all_reduced`` (last CTA arrived), ``end`` (every peer said it
+        finished sending)."""
         t = self.trace_buffer.tolist()
-        us = lambda a, b: (t[b] - t[a]) / 1e3 if t[a] and t[b] else None  # noqa: E731
-        return {"send_us": us(0, 1), "publish_us": us(1, 2), "wait_us": us(2, 3),
-                "finish_us": us(3, 4), "total_us": us(0, 4),
-                "publisher_at_us": us(0, 5) if t[5] else None}
+        us = lambda b: (t[b] - t[0]) / 1e3 if t[0] and t[b] else None  # noqa: E731
+        return {"first_cta_sent": us(1), "all_sent_or_first_reduced": us(2), "peers_seen_or_all_reduced": us(3),
+                "end": us(4)}
 
     def reset(self) -> None:
         """Clear per-layer counters (only needed when a dispatch is not followed by a combine)."""
         self.expert_counts.zero_()
+        self.expert_acc.zero_()
         self.send_counts.zero_()
         self.done.zero_()
+        self.block_done.zero_()
 
     def check(self) -> None:
         """Raise if a kernel recorded a timeout / malformed record, or a segment overflowed."""
@@ -263,7 +304,8 @@ class NativeMoESlot:
         return {"rank": self.rank, "ranks": s.ranks, "capacity": s.capacity, "hidden": s.hidden,
                 "top_k": s.top_k, "experts": s.experts, "value_type": s.value_type,
                 "metadata_words": s.metadata_words, "arena_bytes": self.buffers.nbytes,
-                "launches_per_layer": 2, "grid": self.grid}
+                "launches_per_layer": 2, "grid": self.grid, "return_block": self.return_block,
+                "send_warps": self.send_warps, "last_launch": getattr(self, "last_launch", None)}
 
 
 class LocalMoEGroup:

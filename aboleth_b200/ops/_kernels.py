@@ -26,9 +26,9 @@ _SIGNATURES = {
     "ab_quant_fp8": [_VP, _VP, _VP, _I, _I, _I, _F, _I, _VP],
     "ab_router_topk": [_VP, _VP, _VP, _I, _I, _I, _I, _VP],
     "ab_expert_offsets": [_VP, _VP, _VP, _I, _I, _VP],
-    "ab_permute": [_VP] * 9 + [_I] * 5 + [_VP],
+    "ab_permute": [_VP] * 9 + [_I] * 6 + [_VP],
     "ab_unpermute": [_VP] * 7 + [_I] * 4 + [_VP],
-    "ab_standin_expert": [_VP] * 7 + [_I] * 6 + [_VP],
+    "ab_standin_expert": [_VP, _VP, _I] + [_VP] * 6 + [_I] * 6 + [_VP],
 }
 
 _launches = 0

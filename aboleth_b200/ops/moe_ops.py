@@ -58,9 +58,10 @@ def permute(src: torch.Tensor, dst: torch.Tensor, expert_ids: torch.Tensor,
     top_k = expert_ids.shape[-1]
     row_bytes = src.shape[-1] * src.element_size()
     cols = 0 if src_scales is None else src_scales.shape[-1]
+    stride = 0 if src_scales is None else _row_stride(src_scales)
     call("ab_permute", ptr(src), ptr(dst), ptr(src_scales), ptr(dst_scales), ptr(expert_ids),
          ptr(expert_pos), ptr(offsets), ptr(recv_counts), ptr(perm_row), world, capacity, top_k,
-         row_bytes, cols, stream_ptr())
+         row_bytes, cols, stride, stream_ptr())
 
 
 def unpermute(y: torch.Tensor, out: torch.Tensor, expert_ids: torch.Tensor,
@@ -72,12 +73,26 @@ def unpermute(y: torch.Tensor, out: torch.Tensor, expert_ids: torch.Tensor,
          stream_ptr())
 
 
+def _row_stride(scales: torch.Tensor) -> int:
+    """Row stride (elements) of a 2-D scale tensor whose rows are contiguous.  The scales of a
+    dispatch are a strided view of the received metadata rows, not a packed array."""
+    if scales.dim() != 2 or scales.stride(1) != 1:
+        raise ValueError("scales must be 2-D with contiguous rows")
+    return int(scales.stride(0))
+
+
 def standin_expert(payload: torch.Tensor, scales: Optional[torch.Tensor], y: torch.Tensor,
                    expert_ids: torch.Tensor, expert_weights: torch.Tensor,
                    expert_pos: torch.Tensor, recv_counts: torch.Tensor, *, world: int,
-                   capacity: int, group: int) -> None:
-    """Benchmark expert ``f_e(x) = x * (1 + (e mod 7) / 8)``, gate-weighted, record layout."""
+                   capacity: int, group: int, offsets: Optional[torch.Tensor] = None) -> None:
+    """Benchmark expert ``f_e(x) = x * (1 + (e mod 7) / 8)``.
+
+    Without ``offsets``: record layout, gate-weighted (one partial row per received record).
+    With ``offsets`` (int32 ``[experts]``): expert-contiguous layout, one unweighted row per
+    (record, choice) at ``offsets[id] + pos`` - what a grouped expert GEMM leaves behind.
+    """
     fp8 = payload.dtype == torch.float8_e4m3fn
-    call("ab_standin_expert", ptr(payload), ptr(scales), ptr(y), ptr(expert_ids),
-         ptr(expert_weights), ptr(expert_pos), ptr(recv_counts), world, capacity,
+    stride = 0 if scales is None else _row_stride(scales)
+    call("ab_standin_expert", ptr(payload), ptr(scales), stride, ptr(y), ptr(expert_ids),
+         ptr(expert_weights), ptr(expert_pos), ptr(offsets), ptr(recv_counts), world, capacity,
          expert_ids.shape[-1], y.shape[-1], group, int(fp8), stream_ptr())

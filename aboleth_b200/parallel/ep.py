@@ -11,11 +11,11 @@ from typing import Callable, Optional
 import torch
 
 from ..moe import DispatchResult, MoESpec, NativeMoESlot
-from ..ops import standin_expert
+from ..ops import expert_offsets, standin_expert
 from ..utils import host_range
 from ..world import World
 
-ExpertFn = Callable[[DispatchResult, torch.Tensor], Optional[torch.Tensor]]
+ExpertFn = Callable[[DispatchResult, torch.Tensor], object]
 
 
 class ExpertParallelLayer:
@@ -24,14 +24,30 @@ class ExpertParallelLayer:
         self.slot = NativeMoESlot.create(world, spec, tag=tag, grid=grid)
         self._host_result = torch.zeros(4, dtype=torch.int64).pin_memory()
         self._staging: Optional[list] = None
+        self._grouped: Optional[torch.Tensor] = None
 
     def standin_experts(self, result: DispatchResult, y: torch.Tensor) -> None:
-        """The benchmark's expert stage, ``f_e(x) = x * (1 + (e mod 7)/8)``, gate-weighted."""
+        """The benchmark's expert stage, ``f_e(x) = x * (1 + (e mod 7)/8)``, gate-weighted here:
+        one partial row per received record, which the combine sums unweighted."""
         s = self.spec
         standin_expert(result.expert_input, result.expert_scales, y, result.expert_ids,
                        result.expert_weights, result.expert_pos, result.recv_counts,
                        world=s.ranks, capacity=s.capacity, group=s.scale_group)
         return None
+
+    def standin_experts_grouped(self, result: DispatchResult, y: torch.Tensor):
+        """The same experts behind an expert-contiguous output, as a grouped expert GEMM leaves it:
+        one UNWEIGHTED row per (record, choice) at ``offsets[expert] + position``.  Returns the
+        offsets, so the combine kernel gathers each record's rows and applies the gates itself."""
+        s = self.spec
+        offsets, _ = expert_offsets(result.expert_counts)
+        rows = s.ranks * s.capacity * min(s.top_k, s.experts_per_rank)
+        if self._grouped is None or self._grouped.shape[0] < rows:
+            self._grouped = torch.empty(rows, s.hidden, dtype=torch.bfloat16, device=y.device)
+        standin_expert(result.expert_input, result.expert_scales, self._grouped, result.expert_ids,
+                       result.expert_weights, result.expert_pos, result.recv_counts,
+                       world=s.ranks, capacity=s.capacity, group=s.scale_group, offsets=offsets)
+        return offsets, self._grouped
 
     def forward(self, tokens: torch.Tensor, logits: torch.Tensor, experts: Optional[ExpertFn] = None,
                 *, renormalize: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -40,13 +56,15 @@ class ExpertParallelLayer:
         ``experts(result, y)`` either fills ``y`` (one gate-weighted partial row per
         received record) and returns None, or returns int32 ``[experts]`` offsets when
         it wrote ``y`` in expert-contiguous order and wants the combine kernel to apply
-        the gates.
+        the gates, or ``(offsets, rows)`` when it wrote its own buffer ``rows`` that way.
         """
         with host_range("ep.dispatch"):
             result = self.slot.dispatch(tokens, logits=logits, renormalize=renormalize)
         y = self.slot.expert_output
         with host_range("ep.experts"):
             offsets = (experts or self.standin_experts)(result, y)
+        if isinstance(offsets, tuple):  # (offsets, rows): the stage owns its output buffer
+            offsets, y = offsets
         with host_range("ep.combine"):
             return self.slot.combine(y, expert_offsets=offsets, out=out)
 

@@ -23,7 +23,9 @@ def provenance() -> dict:
             return ""
 
     record = {"time": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()), "host": platform.node(),
-              "git": git("rev-parse", "--short", "HEAD"), "torch": torch.__version__,
+              # A copy of the tree without its history names its revision in ABOLETH_GIT_REV.
+              "git": git("rev-parse", "--short", "HEAD") or os.environ.get("ABOLETH_GIT_REV", ""),
+              "torch": torch.__version__,
               "cuda": torch.version.cuda,
               "env": {k: v for k, v in os.environ.items() if k.startswith(("ABOLETH_", "NCCL_"))}}
     if torch.cuda.is_available():

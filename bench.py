@@ -4,8 +4,13 @@ DeepSeek-V3 shape (hidden 7168 bf16, 256 experts, top-8, fp8 e4m3 payload with
 1x128 fp32 scales), tokens/rank 4096, one rank per GPU.
 
 One step = fused dispatch (router softmax/top-k + quantise + send + unpack)
--> stand-in experts f_e(x) = x * (1 + (e mod 7)/8), gate-weighted
--> fused combine (return + per-token reduction).  The step is timed on the
+-> stand-in experts f_e(x) = x * (1 + (e mod 7)/8) that leave expert-contiguous, unweighted rows
+   (the layout of a grouped expert GEMM)
+-> fused combine (gate-weighted reduction in the kernel + return + per-token reduction).
+The combine that sums gate-weighted partials made by the experts (the reference's split) is timed
+beside it.  For N > 1 the same layer written with torch operators and NCCL all-to-all collectives
+is timed as a baseline, and the raw all-to-all sweep (1 KiB - 256 MiB per peer, chains of 1 / 8 /
+64 puts per signal) is reported.  The step is timed on the
 device; the value is tokens/s over the whole job (weak scaling: tokens/rank
 is fixed).  Phase times (dispatch, combine) and, for N > 1, all-to-all bus
 bandwidth are reported beside it.
@@ -18,14 +23,11 @@ from __future__ import annotations
 import argparse
 import json
 import os
-
-os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
-import statistics
 import sys
-import threading
 
 HIDDEN, EXPERTS, TOP_K, GROUP = 7168, 256, 8, 128
 METRIC = "EP dispatch+combine tokens/s (DeepSeek-V3 shape, fp8 1x128 dispatch, bf16 combine)"
+ROOT = os.path.dirname(os.path.abspath(__file__))
 
 
 def reference_arm(args) -> int:
@@ -45,56 +47,6 @@ def reference_arm(args) -> int:
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": reason}))
     return 0
-
-
-class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons of one GPU through NVML (read-only)."""
-
-    def __init__(self, index: int, period: float = 0.1):
-        super().__init__(daemon=True)
-        self.index, self.period = index, period
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._halt = threading.Event()
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.nv = pynvml
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
-        except Exception:  # noqa: BLE001
-            self.nv = None
-
-    def run(self):
-        if self.nv is None:
-            return
-        nv = self.nv
-        names = {
-            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
-            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
-            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
-            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
-            getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake",
-        }
-        while not self._halt.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
-                try:
-                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
-                except Exception:  # noqa: BLE001
-                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
-                for bit, name in names.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:  # noqa: BLE001
-                pass
-            self._halt.wait(self.period)
-
-    def stop(self) -> dict:
-        self._halt.set()
-        self.join(timeout=2)
-        median = statistics.median(self.samples) if self.samples else None
-        return {"sm_mhz": median, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(self.samples)}
 
 
 def main() -> int:
@@ -125,7 +77,15 @@ def main() -> int:
     device = torch.device("cuda", local_rank)
 
     import aboleth_b200 as ab
-    from aboleth_b200.bench_support import (EpLayerBench, alltoall_sweep, device_max, sync_ranks)
+    from aboleth_b200 import bench_support
+    from aboleth_b200.bench_support import (EpLayerBench, alltoall_sweep, device_max,
+                                            device_max_vector, sync_ranks)
+    from aboleth_b200.utils.clocks import ClockSampler
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):  # roofline denominators measured on this machine
+        with open(peaks_path) as handle:
+            bench_support.set_peaks({**json.load(handle), "source": "measured"})
 
     distributed = world_size > 1
     if distributed:
@@ -165,6 +125,8 @@ def main() -> int:
 
     # ---- phase times (per-phase events, ranks aligned before each bracket) ----
     phases = layer.phase_times(steps=max(5, min(args.steps, 20)), distributed=distributed)
+    unweighted = layer.phase_times(steps=max(5, min(args.steps, 20)), distributed=distributed,
+                                   weighted=False)
 
     # ---- end to end through the public API: pinned host -> device, result back ----
     e2e = layer.end_to_end(steps=max(5, min(args.steps, 20)), distributed=distributed)
@@ -172,10 +134,30 @@ def main() -> int:
 
     extras = {}
     if not args.no_extras:
+        extras["combine_unweighted"] = {k: unweighted[k] for k in
+                                        ("dispatch_us", "combine_us", "combine", "roofline")}
         small = EpLayerBench(world, tokens=128, hidden=HIDDEN, experts=EXPERTS, top_k=TOP_K,
                              group=GROUP, seed=99 + rank, tag="decode")
+        for _ in range(3):
+            small.step()
         extras["decode_128_tokens"] = small.phase_times(steps=30, distributed=distributed, flush=True)
+        extras["decode_128_tokens_unweighted"] = small.phase_times(
+            steps=30, distributed=distributed, flush=True, weighted=False)
+        extras["decode_verify_errors"] = small.verify()
         if distributed:
+            sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+            import nccl_ep_baseline
+            from aboleth_b200.moe.reference import standin_layer_reference
+
+            def oracle(x, ids, weights):
+                return standin_layer_reference(x, ids, weights, fp8=True, group=GROUP)
+
+            common = dict(rank=rank, world=world_size, hidden=HIDDEN, experts=EXPERTS, top_k=TOP_K,
+                          group=GROUP, sync_ranks=sync_ranks, device_max_vector=device_max_vector,
+                          oracle=oracle)
+            extras["nccl_baseline"] = {
+                "prefill": nccl_ep_baseline.measure(layer.x, layer.logits, steps=5, **common),
+                "decode_128_tokens": nccl_ep_baseline.measure(small.x, small.logits, steps=10, **common)}
             extras["alltoall"] = alltoall_sweep(world, distributed)
 
     ms_per_step = total_ms / args.steps
@@ -191,7 +173,7 @@ def main() -> int:
                        "global_batch": world_size * args.tokens, "seq_len": args.tokens,
                        "parallelism": f"ep{world_size}", "hidden": HIDDEN, "experts": EXPERTS,
                        "top_k": TOP_K, "dispatch": "fp8 e4m3 + 1x128 fp32 scales",
-                       "combine": "bf16", "l2": layer.l2_policy},
+                       "combine": phases["combine"], "l2": layer.l2_policy},
             "dispatch_us": phases["dispatch_us"], "combine_us": phases["combine_us"],
             "dispatch_plus_combine_us": phases["dispatch_us"] + phases["combine_us"],
             "roofline": phases.get("roofline"),

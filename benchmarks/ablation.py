@@ -16,7 +16,7 @@ its NIC transport (experiments/bench/ablation.py; README.md:186).
 import argparse
 import statistics
 
-from common import emit
+from common import emit, start_clock_sampler
 
 import torch
 
@@ -35,6 +35,7 @@ def main() -> int:
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     torch.cuda.set_device(0)
+    start_clock_sampler(0)
     runtime = ab.Runtime(0)
     rows = []
     try:

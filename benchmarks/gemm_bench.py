@@ -12,11 +12,11 @@ Fractions are of the measured cuBLAS bf16 burst throughput recorded for this poo
 """
 import argparse
 
-from common import emit
+from common import emit, load_measured_peaks, start_clock_sampler
 
 import torch
 
-from aboleth_b200.bench_support import L2Flusher, measured_peaks
+from aboleth_b200.bench_support import L2Flusher
 from aboleth_b200.ops import check_gemm_status, gemm_bf16, grouped_gemm_bf16
 
 DENSE = [(8192, 3584, 8192), (8192, 8192, 3584), (8192, 28672, 8192), (8192, 8192, 8192), (4096, 4096, 4096)]
@@ -52,8 +52,9 @@ def main() -> int:
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     torch.cuda.set_device(0)
+    start_clock_sampler(0)
     flush = L2Flusher("cuda")
-    peak = measured_peaks().get("bf16_tflops", 1590.0)
+    peak = load_measured_peaks().get("bf16_tflops", 1590.0)
     rows = []
     if args.grouped:
         experts, n, k = 8, 28672, 4096
@@ -81,7 +82,7 @@ def main() -> int:
     elif args.block_scaled:
         from aboleth_b200.ops import dequant_block_scaled, gemm_e4m3_block_scaled, quant_fp8
 
-        hbm = measured_peaks().get("hbm_gbs", 6650.0)
+        hbm = load_measured_peaks().get("hbm_gbs", 6650.0)
         for m, n, k in ([tuple(args.shape)] if args.shape else DENSE):
             a_q, a_s = quant_fp8(torch.randn(m, k, device="cuda").to(torch.bfloat16), round_scale=True)
             b_q = (torch.randn(n, k, device="cuda")).to(torch.float8_e4m3fn)

@@ -103,6 +103,11 @@ def main() -> int:
     if known.build_only:
         print(build(force=True) if known.arm == "tier1" else build_nccl(force=True))
         return 0
+    sys.path.insert(0, str(ROOT.parent))
+    from aboleth_b200.utils.clocks import ClockSampler
+
+    sampler = ClockSampler(0)   # the C++ arms run as child processes; GPU 0 is sampled around them
+    sampler.start()
     if known.arm == "nccl_host":
         rows, code = [], 0
         for size in (["1024", "16384", "262144", "4194304", "67108864"] if known.sweep else [None]):
@@ -117,6 +122,7 @@ def main() -> int:
             sys.path.insert(0, str(ROOT))
             from common import provenance  # benchmarks/common.py
             Path(known.out).write_text(json.dumps({"bench": "nccl host all-to-all", "rows": rows,
+                                                   "clocks": sampler.stop(),
                                                    "provenance": provenance()}, indent=1))
         return code
     rows: list[dict] = []
@@ -135,6 +141,7 @@ def main() -> int:
         sys.path.insert(0, str(ROOT))
         from common import provenance  # benchmarks/common.py
         Path(known.out).write_text(json.dumps({"bench": "native tier-1 ladder", "rows": rows,
+                                               "clocks": sampler.stop(),
                                                "provenance": provenance()}, indent=1))
     return code
 

@@ -11,12 +11,12 @@ FLOPs / measured cuBLAS peak and NVLink bytes / 770 GB/s.
 """
 import argparse
 
-from common import emit, setup, teardown
+from common import emit, load_measured_peaks, setup, teardown
 
 import torch
 import torch.distributed as dist
 
-from aboleth_b200.bench_support import NVLINK_GBS, L2Flusher, device_max, measured_peaks, sync_ranks
+from aboleth_b200.bench_support import NVLINK_GBS, L2Flusher, device_max, sync_ranks
 from aboleth_b200.ops import gemm_bf16
 from aboleth_b200.parallel import AllGatherGemm, GemmReduceScatter
 
@@ -26,7 +26,7 @@ def main() -> int:
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--ffn", type=int, default=28672)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--push-parts", type=int, default=0, help="CTAs per (peer, chunk) of the push; 0 = auto")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
@@ -35,7 +35,7 @@ def main() -> int:
     m_local = args.tokens // w
     g = torch.Generator(device=dev).manual_seed(rank)
     flush = L2Flusher(dev)
-    peaks = measured_peaks()
+    peaks = load_measured_peaks()
     rows = []
 
     def timed(fn):
@@ -52,7 +52,10 @@ def main() -> int:
             if it >= 3:
                 times.append(device_max(a.elapsed_time(b), distributed))
         times.sort()
+        spread.append({"min_us": times[0] * 1e3, "max_us": times[-1] * 1e3, "steps": len(times)})
         return times[len(times) // 2] * 1e3  # median, us
+
+    spread: list[dict] = []   # one entry per timed() call, in call order
 
     def roof(flops, nvlink_bytes):
         t_flop = flops / (peaks["bf16_tflops"] * 1e12) * 1e6
@@ -67,6 +70,7 @@ def main() -> int:
     t_ours = timed(lambda: gemm_bf16(a_full, b_col, out))
     t_lib = timed(lambda: torch.matmul(a_full, b_col.t(), out=out))
     rows.append({"op": "gemm (no collective)", "ours_us": t_ours, "cublas_us": t_lib,
+                 "ours_spread": spread[-2], "cublas_spread": spread[-1],
                  "ours_tflops": flops / t_ours / 1e6, "cublas_tflops": flops / t_lib / 1e6,
                  "frac_of_measured_peak": flops / t_ours / 1e6 / peaks["bf16_tflops"]})
 
@@ -88,6 +92,7 @@ def main() -> int:
     bound, t_flop, t_link = roof(flops, link)
     rows.append({"op": "all-gather -> GEMM", "m": args.tokens, "k": args.hidden, "n": args.ffn // w,
                  "fused_us": t_fused, "nccl_plus_cublas_us": t_base, "speedup": t_base / t_fused,
+                 "fused_spread": spread[-2], "baseline_spread": spread[-1],
                  "roof_us": bound, "roof_flops_us": t_flop, "roof_nvlink_us": t_link,
                  "frac_of_roof": bound / t_fused})
 
@@ -113,6 +118,7 @@ def main() -> int:
     bound, t_flop, t_link = roof(flops, link)
     rows.append({"op": "GEMM -> reduce-scatter", "m": args.tokens, "k": k_local, "n": args.hidden,
                  "fused_us": t_fused, "nccl_plus_cublas_us": t_base, "speedup": t_base / t_fused,
+                 "fused_spread": spread[-2], "baseline_spread": spread[-1],
                  "roof_us": bound, "roof_flops_us": t_flop, "roof_nvlink_us": t_link,
                  "frac_of_roof": bound / t_fused})
     emit({"bench": "tp fused collectives", "n_gpus": w, "dtype": "bf16", "peaks": peaks, "rows": rows,

@@ -99,3 +99,40 @@ def test_engine_pull_runtime_on_one_device():
             runtime.start_pull_blocks(local_block_ids=[64], remote_block_ids=[0], remote_rank=1)
         with pytest.raises(ValueError, match="other rank"):
             runtime.start_pull_blocks(local_block_ids=[1], remote_block_ids=[0], remote_rank=0)
+
+
+def test_shared_readiness_cell_is_published_after_the_last_batch():
+    """Eight batches of very different sizes publish ONE cell.  A consumer CTA of the same launch
+    waits for the cell and sums the destinations at once: with one arrival counter per group the
+    sum is the sources' sum every time; a counter per batch would publish after the smallest."""
+    from aboleth_b200.kv import copy as kvcopy
+
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    sizes = [4096, 8 << 20, 16384, 2 << 20, 256, 6 << 20, 65536, 1 << 20]
+    workers = 16
+    total = sum(sizes)
+    src = torch.randint(1, 255, (total,), generator=g, device="cuda", dtype=torch.uint8)
+    dst = torch.zeros(total, dtype=torch.uint8, device="cuda")
+    cell = torch.zeros(1, dtype=torch.int64, device="cuda")
+    observed = torch.zeros(1, dtype=torch.int64, device="cuda")
+    status = torch.zeros(2, dtype=torch.int64, device="cuda")
+    arrivals = torch.zeros(8, dtype=torch.int32, device="cuda")
+    records, at = [], 0
+    for s in sizes:
+        records.append((src.data_ptr() + at, dst.data_ptr() + at, s, cell.data_ptr()))
+        at += s
+    batches = kvcopy.pack_batches(records, "cuda")
+    group_of, group_target, groups = kvcopy.pack_groups([r[3] for r in records], workers, "cuda")
+    assert groups == 1 and group_target.tolist() == [len(sizes) * workers]
+    want = int(src.view(torch.int64).sum().item())
+    for epoch in range(1, 201):
+        dst.zero_()
+        kvcopy.push_observed(batches, arrivals, len(sizes), epoch, workers=workers, threads=256,
+                             status=status, cell=cell, observed=observed, group_of=group_of,
+                             group_target=group_target)
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 0], (epoch, status.tolist())
+        assert int(observed.item()) == want, epoch
+        assert int(cell.item()) == epoch and arrivals.tolist() == [0] * 8
+    assert torch.equal(dst, src)
