@@ -175,6 +175,20 @@ class EpLayerBench:
         d = statistics.median(device_max_vector(d_ms, distributed)) * 1e3
         c = statistics.median(device_max_vector(c_ms, distributed)) * 1e3
         self.check()
+        # The kernels' own phase stamps for one more step (this rank's view).
+        slot.enable_trace()
+        sync_ranks(distributed)
+        res = slot.dispatch(self.x[0], logits=self.logits[0])
+        torch.cuda.synchronize()
+        kernel_trace = {"dispatch": slot.trace()}
+        staged = experts(res, slot.expert_output)
+        offsets, rows = staged if isinstance(staged, tuple) else (None, slot.expert_output)
+        slot.trace_buffer.zero_()
+        sync_ranks(distributed)
+        slot.combine(rows, expert_offsets=offsets)
+        torch.cuda.synchronize()
+        kernel_trace["combine"] = slot.trace()
+        slot.trace_buffer = None
         traffic = self._traffic()
         peaks = measured_peaks()
         roof = {"traffic": traffic, "denominators": peaks["source"]}
@@ -195,6 +209,7 @@ class EpLayerBench:
                          "dispatch_frac": td / d if d else None, "combine_frac": tc / c if c else None})
         return {"dispatch_us": d, "combine_us": c, "tokens_per_rank": self.tokens, "roofline": roof,
                 "combine": "bf16 gate-weighted in kernel" if weighted else "bf16 unweighted sum of partials",
+                "kernel_trace_us": kernel_trace,
                 "dispatch_us_min": min(device_max_vector(d_ms, distributed)) * 1e3,
                 "combine_us_min": min(device_max_vector(c_ms, distributed)) * 1e3,
                 "l2": "flushed before each bracket" if flush else self.l2_policy}

@@ -51,33 +51,51 @@ __device__ __forceinline__ float quant_div(float x, float scale) {
 #endif
 }
 
-__device__ __forceinline__ std::uint32_t fp8x4(float a, float b, float c, float d, float scale) {
-    const float lo = -kFp8Max, hi = kFp8Max;
-    a = fminf(fmaxf(quant_div(a, scale), lo), hi);
-    b = fminf(fmaxf(quant_div(b, scale), lo), hi);
-    c = fminf(fmaxf(quant_div(c, scale), lo), hi);
-    d = fminf(fmaxf(quant_div(d, scale), lo), hi);
+// Four values times the reciprocal scale `inv` -> four e4m3 codes.  The conversion saturates at
+// +-448 by itself, so no clamp is spent here (a NaN input stays NaN).
+__device__ __forceinline__ std::uint32_t fp8x4(float a, float b, float c, float d, float inv) {
+#ifdef ABOLETH_EXACT_QUANT_DIV
+    const float scale = inv;  // the caller passes the scale itself
+    a = quant_div(a, scale); b = quant_div(b, scale); c = quant_div(c, scale); d = quant_div(d, scale);
+#else
+    a *= inv; b *= inv; c *= inv; d *= inv;
+#endif
     const std::uint32_t p0 = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
     const std::uint32_t p1 = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
     return p0 | (p1 << 16);
 }
 
-// Sixteen bf16 values (two 16-byte vectors) -> absolute maximum.
+// Sixteen bf16 values (two 16-byte vectors) -> absolute maximum.  Signs are masked off two values
+// at a time and the packed maximum unit compares them; one conversion at the end.
 __device__ __forceinline__ float amax16(const uint4 &a, const uint4 &b) {
-    float m = 0.f;
     const std::uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    __nv_bfloat162 m;
+    *reinterpret_cast<std::uint32_t *>(&m) = w[0] & 0x7fff7fffu;
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-        m = fmaxf(m, fmaxf(fabsf(bf16_lo(w[i])), fabsf(bf16_hi(w[i]))));
-    return m;
+    for (int i = 1; i < 8; ++i) {
+        __nv_bfloat162 v;
+        *reinterpret_cast<std::uint32_t *>(&v) = w[i] & 0x7fff7fffu;
+        m = __hmax2(m, v);
+    }
+    const std::uint32_t bits = *reinterpret_cast<std::uint32_t *>(&m);
+    return fmaxf(bf16_lo(bits), bf16_hi(bits));
 }
 
+// Sixteen bf16 values -> sixteen e4m3 codes at `scale`.  The default multiplies by the correctly
+// rounded reciprocal of the scale (exact for power-of-two scales, within 1.5 ulp of the division
+// otherwise: far below an e4m3 quantum, so only a value that sits on a rounding tie can land on the
+// other neighbouring code).  ABOLETH_EXACT_QUANT_DIV divides instead.
 __device__ __forceinline__ uint4 quant16(const uint4 &a, const uint4 &b, float scale) {
+#ifdef ABOLETH_EXACT_QUANT_DIV
+    const float inv = scale;
+#else
+    const float inv = __frcp_rn(scale);
+#endif
     uint4 q;
-    q.x = fp8x4(bf16_lo(a.x), bf16_hi(a.x), bf16_lo(a.y), bf16_hi(a.y), scale);
-    q.y = fp8x4(bf16_lo(a.z), bf16_hi(a.z), bf16_lo(a.w), bf16_hi(a.w), scale);
-    q.z = fp8x4(bf16_lo(b.x), bf16_hi(b.x), bf16_lo(b.y), bf16_hi(b.y), scale);
-    q.w = fp8x4(bf16_lo(b.z), bf16_hi(b.z), bf16_lo(b.w), bf16_hi(b.w), scale);
+    q.x = fp8x4(bf16_lo(a.x), bf16_hi(a.x), bf16_lo(a.y), bf16_hi(a.y), inv);
+    q.y = fp8x4(bf16_lo(a.z), bf16_hi(a.z), bf16_lo(a.w), bf16_hi(a.w), inv);
+    q.z = fp8x4(bf16_lo(b.x), bf16_hi(b.x), bf16_lo(b.y), bf16_hi(b.y), inv);
+    q.w = fp8x4(bf16_lo(b.z), bf16_hi(b.z), bf16_lo(b.w), bf16_hi(b.w), inv);
     return q;
 }
 
@@ -129,14 +147,15 @@ __device__ __forceinline__ void warp_softmax_topk_n(const float *logits, int exp
                 best_e = e;
             }
         }
-        for (int off = 16; off > 0; off >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-            const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
-            if (ob > best || (ob == best && oe < best_e)) {
-                best = ob;
-                best_e = oe;
-            }
-        }
+        // Warp-wide argmax in two reductions: the largest value (as an order-preserving integer),
+        // then the lowest expert index among the lanes that hold it.
+        const std::uint32_t raw = __float_as_uint(best);
+        const std::uint32_t key = raw ^ ((raw >> 31) ? 0xffffffffu : 0x80000000u);
+        const std::uint32_t top = __reduce_max_sync(0xffffffffu, key);
+        best_e = static_cast<int>(__reduce_min_sync(
+            0xffffffffu, key == top ? static_cast<unsigned>(best_e) : 0x7fffffffu));
+        const std::uint32_t back = top ^ ((top >> 31) ? 0x80000000u : 0xffffffffu);
+        best = __uint_as_float(back);
         const float w = __expf(best - mx) / sum;
         picked_sum += w;
         if (lane == j) {

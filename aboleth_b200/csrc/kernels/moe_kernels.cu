@@ -48,7 +48,8 @@ constexpr int kMaxTokensPerCta = 64;  // ordered slots: tokens one CTA may own
 constexpr unsigned kFull = 0xffffffffu;
 
 // Counter words in `done`.
-constexpr int kDoneDispatch = 0, kDoneCombine = 1, kBarrierCount = 2, kBarrierGen = 3, kDoneSenders = 4;
+constexpr int kDoneDispatch = 0, kDoneCombine = 1, kBarrierCount = 2, kBarrierGen = 3, kDoneSenders = 4,
+              kNextToken = 5;
 
 struct EpGeometry {
     int rank, world, experts, top_k, hidden, scale_group, capacity;
@@ -401,8 +402,7 @@ __global__ void __launch_bounds__(kThreads, 4) ep_dispatch_kernel(DispatchParams
     stamp(p.trace, 0, tracer);
     // Warp-per-token launches give CTA b the contiguous tokens [first, last); slots are handed out
     // in token order when a CTA's share fits the shared-memory tables.
-    int per_cta = (p.num_tokens + gridDim.x - 1) / gridDim.x;
-    per_cta = (per_cta + kWarps - 1) / kWarps * kWarps;
+    const int per_cta = (p.num_tokens + gridDim.x - 1) / gridDim.x;
     const bool ordered = BY_WARP && per_cta <= kMaxTokensPerCta;
 
     if constexpr (BY_WARP) if (p.phases & kPhaseSend) {
@@ -471,82 +471,88 @@ __global__ void __launch_bounds__(kThreads, 4) ep_dispatch_kernel(DispatchParams
         }
     }
     if constexpr (!BY_WARP) if (p.phases & kPhaseSend) {
-        const std::uint32_t *x32 = p.x;
         const int chunks = g.hidden / 16;  // 16 elements per thread-step
         const int lanes_per_group = g.scale_group / 16;
+        constexpr int kPayloadThreads = kThreads - 32;  // warps 1..7 move the row, warp 0 routes
         for (int t = blockIdx.x; t < p.num_tokens; t += gridDim.x) {
-            const std::uint32_t *xrow = x32 + static_cast<std::size_t>(t) * (g.hidden / 2);
-            // The first step's loads are in flight while warp 0 routes.
-            uint4 a0 = make_uint4(0, 0, 0, 0), b0 = a0;
-            if (tid < chunks) {
-                a0 = aboleth::detail::ld_stream16(xrow + tid * 8);
-                b0 = aboleth::detail::ld_stream16(xrow + tid * 8 + 4);
-            }
+            const std::uint32_t *xrow = p.x + static_cast<std::size_t>(t) * (g.hidden / 2);
             int pos = -1;
-            if (warp == 0) {
-                int id;
-                float w;
-                route_token(p, t, id, w);
-                const int owner = owner_of(p, id);
-                if (lane < g.top_k) {
-                    s_id[lane] = id;
-                    s_w[lane] = w;
-                    s_owner[lane] = owner;
-                }
-                const int slot = take_slot(p, owner);
-                if (lane < g.world) {
-                    p.source_slots[t * g.world + lane] = slot;
-                    s_slot[lane] = slot;
-                }
-                const unsigned live = __ballot_sync(kFull, slot >= 0);
-                if (slot >= 0)
-                    s_dest[__popc(live & ((1u << lane) - 1))] = lane;
-                if (lane == 0)
-                    s_ndest = __popc(live);
-                const int owner_slot = __shfl_sync(kFull, slot, owner >= 0 ? owner : 0);
-                if (owner >= 0 && owner_slot >= 0)
-                    pos = reserve_position(p, owner, id);
-            }
-            __syncthreads();
-            const int ndest = s_ndest;
-
-            // ---- payload: quantise once, store to every destination ----
-            for (int base = 0; base < chunks; base += kThreads) {
-                const int c = base + tid;
-                const bool live = c < chunks;
-                uint4 a = a0, b = b0;
-                if (base > 0) {
-                    a = make_uint4(0, 0, 0, 0);
-                    b = a;
-                    if (live) {
-                        a = aboleth::detail::ld_stream16(xrow + c * 8);
-                        b = aboleth::detail::ld_stream16(xrow + c * 8 + 4);
+            for (int base = 0; base < chunks; base += 2 * kPayloadThreads) {
+                // Quantisation needs no routing: the payload warps load and quantise two steps each
+                // while warp 0 routes the token; only the stores wait for the destinations.
+                uint4 a[2], b[2];
+                const int pt = tid - 32;
+                if (warp > 0) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int c = base + u * kPayloadThreads + pt;
+                        a[u] = make_uint4(0, 0, 0, 0);
+                        b[u] = a[u];
+                        if (c < chunks) {
+                            a[u] = aboleth::detail::ld_stream16(xrow + c * 8);
+                            b[u] = aboleth::detail::ld_stream16(xrow + c * 8 + 4);
+                        }
                     }
+                    if (g.value_fp8) {
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const int c = base + u * kPayloadThreads + pt;
+                            const float amax = group_max(amax16(a[u], b[u]), lanes_per_group);
+                            const float scale = quant_scale(amax, g.amax_floor, g.round_scale);
+                            a[u] = quant16(a[u], b[u], scale);
+                            if (c < chunks && c % lanes_per_group == 0)
+                                s_scale[c / lanes_per_group] = scale;
+                        }
+                    }
+                } else if (base == 0) {
+                    int id;
+                    float w;
+                    route_token(p, t, id, w);
+                    const int owner = owner_of(p, id);
+                    if (lane < g.top_k) {
+                        s_id[lane] = id;
+                        s_w[lane] = w;
+                        s_owner[lane] = owner;
+                    }
+                    const int slot = take_slot(p, owner);
+                    if (lane < g.world) {
+                        p.source_slots[t * g.world + lane] = slot;
+                        s_slot[lane] = slot;
+                    }
+                    const unsigned live = __ballot_sync(kFull, slot >= 0);
+                    if (slot >= 0)
+                        s_dest[__popc(live & ((1u << lane) - 1))] = lane;
+                    if (lane == 0)
+                        s_ndest = __popc(live);
+                    // Position inside the expert: asked for now, read after the payload went out.
+                    const int owner_slot = __shfl_sync(kFull, slot, owner >= 0 ? owner : 0);
+                    if (owner >= 0 && owner_slot >= 0)
+                        pos = reserve_position(p, owner, id);
                 }
-                if (g.value_fp8) {
-                    const float amax = group_max(amax16(a, b), lanes_per_group);
-                    const float scale = quant_scale(amax, g.amax_floor, g.round_scale);
-                    if (live) {
-                        const uint4 q = quant16(a, b, scale);
-                        if (c % lanes_per_group == 0)
-                            s_scale[c / lanes_per_group] = scale;
+                if (base == 0)
+                    __syncthreads();
+                if (warp > 0) {
+                    const int ndest = s_ndest;
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int c = base + u * kPayloadThreads + pt;
+                        if (c >= chunks)
+                            continue;
                         for (int i = 0; i < ndest; ++i) {
                             const int d = s_dest[i];
                             std::uint8_t *row = reinterpret_cast<std::uint8_t *>(p.peer_payload[d]) +
                                 (static_cast<std::size_t>(g.rank) * g.capacity + s_slot[d]) * row_bytes;
-                            aboleth::detail::st_stream16(row + c * 16, q);
+                            if (g.value_fp8) {
+                                aboleth::detail::st_stream16(row + c * 16, a[u]);
+                            } else {
+                                aboleth::detail::st_stream16(row + c * 32, a[u]);
+                                aboleth::detail::st_stream16(row + c * 32 + 16, b[u]);
+                            }
                         }
-                    }
-                } else if (live) {
-                    for (int i = 0; i < ndest; ++i) {
-                        const int d = s_dest[i];
-                        std::uint8_t *row = reinterpret_cast<std::uint8_t *>(p.peer_payload[d]) +
-                            (static_cast<std::size_t>(g.rank) * g.capacity + s_slot[d]) * row_bytes;
-                        aboleth::detail::st_stream16(row + c * 32, a);
-                        aboleth::detail::st_stream16(row + c * 32 + 16, b);
                     }
                 }
             }
+            const int ndest = s_ndest;
             if (warp == 0 && lane < g.top_k)
                 s_pos[lane] = pos;
             __syncthreads();
@@ -724,23 +730,38 @@ __device__ __forceinline__ void return_row_by_warp(const CombineParams &p, int r
             my_row = p.expert_offsets[p.expert_ids[row * g.top_k + lane]] + pos;
         my_gate = p.expert_weights[row * g.top_k + lane];
     }
-    for (int base = 0; base < vecs; base += 64) {
-        float acc[2][8] = {};
-        for (int j = 0; j < n; ++j) {
-            const int r = __shfl_sync(kFull, my_row, j);
-            const float w = __shfl_sync(kFull, my_gate, j);
-            if (r < 0)
-                continue;
-            const std::uint32_t *y = p.expert_out + static_cast<std::size_t>(r) * (g.hidden / 2);
+    // Four consecutive 512-byte pieces (2 KiB) of a row per pass, two rows in flight: long
+    // contiguous reads keep DRAM pages open, eight 16-byte loads per lane hide the latency.
+    constexpr int kPieces = 4;
+    for (int base = 0; base < vecs; base += 32 * kPieces) {
+        float acc[kPieces][8] = {};
+        for (int j0 = 0; j0 < n; j0 += 2) {
+            uint4 y[2][kPieces];
+            float w[2];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int v = base + u * 32 + lane;
-                if (v < vecs)
-                    add_bf16x8(acc[u], aboleth::detail::ld_stream16(y + v * 4), w);
+            for (int r2 = 0; r2 < 2; ++r2) {
+                const int r = __shfl_sync(kFull, my_row, (j0 + r2) & 31);
+                w[r2] = __shfl_sync(kFull, my_gate, (j0 + r2) & 31);
+                const bool live = j0 + r2 < n && r >= 0;
+                if (!live)
+                    w[r2] = 0.f;
+                const std::uint32_t *row = p.expert_out + static_cast<std::size_t>(live ? r : 0) * (g.hidden / 2);
+#pragma unroll
+                for (int u = 0; u < kPieces; ++u) {
+                    const int v = base + u * 32 + lane;
+                    y[r2][u] = make_uint4(0, 0, 0, 0);
+                    if (live && v < vecs)
+                        y[r2][u] = aboleth::detail::ld_stream16(row + v * 4);
+                }
             }
+#pragma unroll
+            for (int r2 = 0; r2 < 2; ++r2)
+#pragma unroll
+                for (int u = 0; u < kPieces; ++u)
+                    add_bf16x8(acc[u], y[r2][u], w[r2]);
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kPieces; ++u) {
             const int v = base + u * 32 + lane;
             if (v < vecs)
                 aboleth::detail::st_stream16(dst + v * 16, pack_bf16x8(acc[u]));
@@ -772,20 +793,26 @@ __device__ __forceinline__ bool reduce_token_by_warp(const CombineParams &p, int
     const std::uint32_t *my_src = p.returned +
         (static_cast<std::size_t>(lane < g.world ? lane : 0) * g.capacity + (slot < 0 ? 0 : slot)) * (g.hidden / 2);
     std::uint32_t *out = p.out + static_cast<std::size_t>(t) * (g.hidden / 2);
-    for (int base = 0; base < vecs; base += 64) {
-        float acc[2][8] = {};
+    constexpr int kChunks = 4;  // 16-byte vectors per lane in flight per source
+    for (int base = 0; base < vecs; base += 32 * kChunks) {
+        float acc[kChunks][8] = {};
         for (unsigned m = live; m; m &= m - 1) {
             const std::uint32_t *y = reinterpret_cast<const std::uint32_t *>(
                 shfl_u64(reinterpret_cast<std::uint64_t>(my_src), __ffs(m) - 1));
+            uint4 r[kChunks];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
+            for (int u = 0; u < kChunks; ++u) {
                 const int v = base + u * 32 + lane;
+                r[u] = make_uint4(0, 0, 0, 0);
                 if (v < vecs)
-                    add_bf16x8(acc[u], aboleth::detail::ld_stream16(y + v * 4), 1.0f);
+                    r[u] = aboleth::detail::ld_stream16(y + v * 4);
             }
+#pragma unroll
+            for (int u = 0; u < kChunks; ++u)
+                add_bf16x8(acc[u], r[u], 1.0f);
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kChunks; ++u) {
             const int v = base + u * 32 + lane;
             if (v < vecs)
                 *reinterpret_cast<uint4 *>(out + v * 4) = pack_bf16x8(acc[u]);
@@ -794,12 +821,14 @@ __device__ __forceinline__ bool reduce_token_by_warp(const CombineParams &p, int
     return true;
 }
 
-__global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
+__global__ void __launch_bounds__(kThreads, 3) ep_combine_kernel(CombineParams p) {
     const EpGeometry &g = p.g;
     __shared__ int s_flag;
     __shared__ int s_rows[kMaxTopK];
     __shared__ float s_gate[kMaxTopK];
     __shared__ int s_count[kMaxWorld];
+    __shared__ int s_src_row[kMaxWorld];
+    __shared__ int s_nsrc;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
@@ -851,12 +880,18 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
                         reinterpret_cast<std::uint64_t *>(p.peer_return_flags[lane]) +
                             static_cast<std::size_t>(g.rank) * (p.nblk + 1) + p.nblk, epoch);
             }
-        } else if (p.phases & kPhaseRecv) {
-            const int reducers = kWarps - senders;
-            const int stride = gridDim.x * reducers;
-            for (int t = blockIdx.x * reducers + (warp - senders); t < p.num_tokens; t += stride)
-                if (!reduce_token_by_warp(p, t, epoch))
+        }
+        if (p.phases & kPhaseRecv) {
+            // Tokens are handed out in order through one counter: the dedicated reducer warps start at
+            // once, the sender warps join when they have nothing left to send.
+            for (;;) {
+                int t = 0;
+                if (lane == 0)
+                    t = static_cast<int>(atomicAdd(p.done + kNextToken, 1u));
+                t = __shfl_sync(kFull, t, 0);
+                if (t >= p.num_tokens || !reduce_token_by_warp(p, t, epoch))
                     break;
+            }
         }
     } else {
         if (p.phases & kPhaseSend) {
@@ -886,11 +921,19 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
                         o = aboleth::detail::ld_stream16(p.expert_out + static_cast<std::size_t>(row) * (g.hidden / 2) + v * 4);
                     } else {
                         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                        for (int j = 0; j < n; ++j) {
-                            if (s_rows[j] < 0)
-                                continue;
-                            add_bf16x8(acc, aboleth::detail::ld_stream16(
-                                p.expert_out + static_cast<std::size_t>(s_rows[j]) * (g.hidden / 2) + v * 4), s_gate[j]);
+                        for (int j0 = 0; j0 < n; j0 += 8) {
+                            uint4 y[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                y[u] = make_uint4(0, 0, 0, 0);
+                                if (j0 + u < n && s_rows[j0 + u] >= 0)
+                                    y[u] = aboleth::detail::ld_stream16(
+                                        p.expert_out + static_cast<std::size_t>(s_rows[j0 + u]) * (g.hidden / 2) + v * 4);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)
+                                if (j0 + u < n)
+                                    add_bf16x8(acc, y[u], s_gate[j0 + u]);
                         }
                         o = pack_bf16x8(acc);
                     }
@@ -921,8 +964,10 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
                 if (tid == 0)
                     s_flag = 0;
                 __syncthreads();
-                if (tid < g.world) {
-                    const int slot = p.source_slots[t * g.world + tid];
+                if (tid < 32) {
+                    // Lane d < world waits for the block that holds this token's partial from rank d;
+                    // the rows that exist are listed for the reduction.
+                    const int slot = tid < g.world ? p.source_slots[t * g.world + tid] : -1;
                     if (slot >= 0) {
                         const Status s = aboleth::wait_signal_status(
                             p.return_flags + static_cast<std::size_t>(tid) * (p.nblk + 1) + slot / p.block, epoch);
@@ -931,18 +976,30 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
                             s_flag = 1;
                         }
                     }
+                    const unsigned have = __ballot_sync(kFull, slot >= 0);
+                    if (slot >= 0)
+                        s_src_row[__popc(have & ((1u << tid) - 1))] = tid * g.capacity + slot;
+                    if (tid == 0)
+                        s_nsrc = __popc(have);
                 }
                 __syncthreads();
                 if (s_flag)
                     break;
+                const int nsrc = s_nsrc;
                 for (int v = tid; v < vecs; v += kThreads) {
                     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    for (int d = 0; d < g.world; ++d) {
-                        const int slot = p.source_slots[t * g.world + d];
-                        if (slot < 0)
-                            continue;
-                        add_bf16x8(acc, aboleth::detail::ld_stream16(
-                            p.returned + (static_cast<std::size_t>(d) * g.capacity + slot) * (g.hidden / 2) + v * 4), 1.0f);
+                    for (int i0 = 0; i0 < nsrc; i0 += 4) {
+                        uint4 r[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            r[u] = make_uint4(0, 0, 0, 0);
+                            if (i0 + u < nsrc)
+                                r[u] = aboleth::detail::ld_stream16(
+                                    p.returned + static_cast<std::size_t>(s_src_row[i0 + u]) * (g.hidden / 2) + v * 4);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            add_bf16x8(acc, r[u], 1.0f);
                     }
                     *reinterpret_cast<uint4 *>(p.out + static_cast<std::size_t>(t) * (g.hidden / 2) + v * 4) =
                         pack_bf16x8(acc);
@@ -966,6 +1023,7 @@ __global__ void __launch_bounds__(kThreads) ep_combine_kernel(CombineParams p) {
                                            &s_flag, 0x2100);
             if (tid == 0) {
                 p.done[kDoneCombine] = 0;
+                p.done[kNextToken] = 0;
                 (void)ok;  // a timeout is in the status word; the epoch still advances
                 *p.epoch = epoch + 1;
                 stamp(p.trace, 4, true);
@@ -1234,12 +1292,22 @@ AB_EXPORT int ab_ep_dispatch(const int *ints, float amax_floor, const std::uint6
     p.by_warp = ints[15];
     if (!geometry_ok(p.g) || p.num_tokens < 0 || p.num_tokens > p.g.capacity || grid < 0)
         return -1;
-    if (grid == 0)  // auto: one warp (throughput) or one CTA (latency) per token
-        grid = p.by_warp ? (p.num_tokens + kWarps - 1) / kWarps : p.num_tokens;
+    const int resident = p.by_warp ? resident_grid(ep_dispatch_kernel<true>, 1 << 30)
+                                   : resident_grid(ep_dispatch_kernel<false>, 1 << 30);
+    if (grid == 0) {
+        if (p.by_warp) {
+            // Every SM gets the same number of CTAs and every CTA the same number of tokens (one
+            // per warp at most while the device has room): the slowest SM sets the time.
+            int per_cta = (p.num_tokens + resident - 1) / (resident > 0 ? resident : 1);
+            per_cta = per_cta < 1 ? 1 : per_cta;
+            grid = (p.num_tokens + per_cta - 1) / per_cta;
+        } else {
+            grid = p.num_tokens;  // one CTA per token
+        }
+    }
     if (grid < 1 || !(p.phases & kPhaseSend))
         grid = 1;
-    grid = p.by_warp ? resident_grid(ep_dispatch_kernel<true>, grid)
-                     : resident_grid(ep_dispatch_kernel<false>, grid);
+    grid = grid < resident ? grid : resident;
     if (p.by_warp && grid > ints[18])
         grid = ints[18];  // rows of block_counts
     if (grid < 1)
@@ -1273,10 +1341,12 @@ AB_EXPORT int ab_ep_dispatch(const int *ints, float amax_floor, const std::uint6
     p.acc = reinterpret_cast<int *>(ptrs[i++]);
     p.expert_counts = reinterpret_cast<int *>(ptrs[i++]);
     p.trace = reinterpret_cast<unsigned long long *>(ptrs[i++]);
-    if (p.routing == 1 && (p.ids_out == nullptr || p.weights_out == nullptr || p.logits == nullptr))
-        return -1;
-    if (p.routing != 1 && (p.ids_in == nullptr || p.weights_in == nullptr))
-        return -1;
+    if (p.num_tokens > 0) {  // an empty batch may come with null (empty) tensors
+        if (p.routing == 1 && (p.ids_out == nullptr || p.weights_out == nullptr || p.logits == nullptr))
+            return -1;
+        if (p.routing != 1 && (p.ids_in == nullptr || p.weights_in == nullptr))
+            return -1;
+    }
     if (p.by_warp)
         ep_dispatch_kernel<true><<<grid, kThreads, 0, stream>>>(p);
     else

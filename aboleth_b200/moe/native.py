@@ -36,11 +36,12 @@ from .spec import MoESpec
 PHASE_SEND, PHASE_RECV = 1, 2
 _REGIONS = ("recv_payload", "recv_meta", "recv_counts", "dispatch_flags", "returned", "return_flags",
             "recv_ids", "recv_weights", "recv_pos", "expert_acc")
-RETURN_BLOCK = 64          # records per readiness block of the combine
+RETURN_BLOCK = 64          # records per readiness block of the combine (every rank must use the same)
+MIN_RETURN_BLOCK = 16      # the flag arrays are sized for blocks this small
 MAX_DISPATCH_CTAS = 2048   # rows of the per-CTA record-count table (token-ordered slots)
 
 
-def return_blocks(spec: MoESpec, block: int = RETURN_BLOCK) -> int:
+def return_blocks(spec: MoESpec, block: int = MIN_RETURN_BLOCK) -> int:
     return (spec.capacity + block - 1) // block
 
 
@@ -119,7 +120,7 @@ class NativeMoESlot:
         self.dispatch_flags = b.view("dispatch_flags").view(torch.int64)
         self.returned = b.view("returned").view(torch.bfloat16).view(rows, s.hidden)
         self.return_block = RETURN_BLOCK
-        self.return_flags = b.view("return_flags").view(torch.int64).view(s.ranks, return_blocks(s) + 1)
+        self.return_flags = b.view("return_flags").view(torch.int64)   # [ranks, blocks + 1] at run time
         self.peer_tables = peer_tables  # name -> int64 [ranks] addresses
         owners = placement if isinstance(placement, (list, tuple)) else spec.owners(placement)
         self.owners_list = list(owners)
@@ -187,6 +188,8 @@ class NativeMoESlot:
     def _geometry(self, num_tokens: int, routing: int, renormalize: bool, phases: int,
                   weighted: int = 0):
         s, i = self.spec, self._ints
+        if self.return_block < MIN_RETURN_BLOCK:
+            raise ValueError(f"return_block must be at least {MIN_RETURN_BLOCK}")
         by_warp = (num_tokens > self.by_warp_threshold) if self.by_warp is None else self.by_warp
         values = [self.rank, s.ranks, s.experts, s.top_k, s.hidden, s.scale_group, s.capacity,
                   int(s.fp8), int(s.round_scale), 0, num_tokens, routing,
