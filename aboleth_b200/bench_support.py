@@ -65,6 +65,37 @@ def device_max_vector(values: list[float], distributed: bool) -> list[float]:
     return t.tolist()
 
 
+class RankAligner:
+    """A kernel that ends on every rank within a flag's flight time of the others: each rank
+    stores a flag to every peer and waits (bounded) for all of theirs.  Enqueued right before a
+    timed bracket, it takes the ranks' launch skew out of the bracket - the same purpose as the
+    reference's timer-alignment all-reduce (experiments/dsl/moe/moe_common.py:173-202), on the
+    device instead of through a collective."""
+
+    def __init__(self, world: World, tag: str = "align"):
+        self.world, self.epoch = world, 0
+        n = world.world_size
+        if n == 1:
+            return
+        self.arena = world.runtime.allocate(2 * n * 16 + n * 8)
+        reg = world.register(self.arena, network=False)
+        table = world.exchange_regions([
+            world.region("align_recv", reg, offset=n * 16, length=n * 16),
+            world.region("align_flags", reg, offset=2 * n * 16, length=n * 8)], tag=tag)
+        self.tabs = (table.addresses("align_recv"), table.addresses("align_flags"))
+        self.flags = self.arena[2 * n * 16:].view(torch.int64)
+        self.status = torch.zeros(2, dtype=torch.int64, device=world.torch_device)
+
+    def __call__(self) -> None:
+        if self.world.world_size == 1:
+            return
+        from .ops import alltoall
+        alltoall(self.arena, *self.tabs, self.flags, self.status, stride=16, nbytes=16,
+                 epoch0=self.epoch, rank=self.world.rank, world=self.world.world_size, lanes=1,
+                 rounds=1, mode="vector", threads=32)
+        self.epoch += 1
+
+
 class L2Flusher:
     def __init__(self, device):
         self.buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
@@ -98,6 +129,7 @@ class EpLayerBench:
                        for _ in range(self.copies)]
         self.counter = 0
         self.flusher: Optional[L2Flusher] = None
+        self.align = RankAligner(world, tag=f"{tag}.align")
 
     def step(self) -> torch.Tensor:
         i = self.counter % self.copies
@@ -156,6 +188,7 @@ class EpLayerBench:
             # Keep the GPU busy while the host enqueues, so that the bracket
             # measures the kernel and not the host's launch latency.
             torch.cuda._sleep(100_000)
+            self.align()   # the ranks leave this kernel together: launch skew stays out of the bracket
             e0.record()
             res = slot.dispatch(self.x[i], logits=self.logits[i])
             e1.record()
@@ -165,6 +198,7 @@ class EpLayerBench:
                 self.flusher()
             sync_ranks(distributed)
             torch.cuda._sleep(100_000)
+            self.align()
             e2.record()
             slot.combine(rows, expert_offsets=offsets)
             e3.record()

@@ -8,14 +8,17 @@
 //     records per destination, one bounded grid barrier, a scan of the CTA counts.  The combine
 //     of the same layer returns records in slot order, so a token-ordered segment lets the
 //     source rank reduce token t while later records are still in flight;
-//   * position inside the expert: one `atom.add` per chosen expert on the OWNER's counter array
-//     over NVLink, issued before the payload and consumed after it;
+//   * position inside the expert: one LOCAL `atom.add` per chosen expert gives the record's
+//     position among THIS rank's records for that expert; the per-expert totals travel with the
+//     record counts, and the receiver's offset table places source s after sources < s.  (A
+//     position taken from the owner's counter over NVLink was tried first: its round trip queues
+//     behind the payload in both directions and lengthened the send by a fifth at 8 GPUs.)
 //   * payload: the row is quantised once to e4m3 with one fp32 scale per `scale_group` columns
 //     and stored straight into every destination's receive segment (no send staging);
 //   * metadata row (wire format) and the unpacked view the expert stage reads (expert ids,
 //     gate weights, positions) are written by the sender too;
 //   * the last CTA to arrive writes each peer's record count and ONE `st.release.sys` flag per
-//     peer, then waits (bounded) for the peers' flags and snapshots the expert counters.
+//     peer, then waits (bounded) for the peers' flags and totals the per-source expert counts.
 // Every other CTA exits after its stores: no CTA polls while another still sends.
 //
 // COMBINE (one launch).  Sender warps walk the received records in slot order, round-robin over
@@ -79,12 +82,13 @@ struct DispatchParams {
     int *block_counts;             // [grid, world] records per CTA and destination (ordered slots)
     // peers (device arrays of addresses, [world])
     const std::uint64_t *peer_payload, *peer_meta, *peer_counts, *peer_flags;
-    const std::uint64_t *peer_ids, *peer_weights, *peer_pos, *peer_acc;
+    const std::uint64_t *peer_ids, *peer_weights, *peer_pos, *peer_expert_counts;
+    int *send_expert_counts;       // [experts] (record, choice) pairs this rank sent per expert
     // receiver side (local)
     const unsigned long long *recv_counts;  // [world]
     const std::uint64_t *flags;             // [world]
-    int *acc;                      // [experts] counters the peers add to
-    int *expert_counts;            // [experts] snapshot handed to the expert stage
+    const int *recv_expert_counts; // [world, experts]: row s written by rank s
+    int *expert_counts;            // [experts] totals handed to the expert stage
     unsigned long long *trace;     // optional [8] %globaltimer stamps
 };
 
@@ -213,9 +217,10 @@ __device__ __forceinline__ int owner_of(const DispatchParams &p, int id) {
     return (lane < p.g.top_k && id >= 0 && id < p.g.experts) ? p.owners[id] : -1;
 }
 
-// One atom.add on the owner's counter of expert `id`: the record's position inside that expert.
+// The record's position among this rank's records for expert `id` (a local atomic).
 __device__ __forceinline__ int reserve_position(const DispatchParams &p, int owner, int id) {
-    return atomicAdd_system(reinterpret_cast<int *>(p.peer_acc[owner]) + id, 1);
+    (void)owner;
+    return atomicAdd(p.send_expert_counts + id, 1);
 }
 
 // One warp sends one token whose routing is (id, w, owner) in lanes < top_k and whose slot at
@@ -238,7 +243,7 @@ __device__ __forceinline__ void send_token_by_warp(const DispatchParams &p, int 
         }
     }
     const unsigned live = __ballot_sync(kFull, slot >= 0);
-    // Position inside the expert, reserved on the owner; the answer is needed after the payload.
+    // Position inside the expert's group of this source; needed after the payload.
     const int owner_slot = __shfl_sync(kFull, slot, owner >= 0 ? owner : 0);
     int pos = -1;
     if (owner >= 0 && owner_slot >= 0)
@@ -366,10 +371,12 @@ __device__ __forceinline__ void finish_dispatch(const DispatchParams &p, std::ui
         aboleth::detail::ld_relaxed_sys(reinterpret_cast<const std::uint64_t *>(p.recv_counts + tid)) >
             static_cast<std::uint64_t>(g.capacity))
         ab::set_status(p.status, Status::Malformed, 0x1100 + tid);
-    // Every peer's additions were answered before that peer released its flag.
+    // Row s of the table was written by rank s before it released its flag.
     for (int e = tid; e < g.experts; e += kThreads) {
-        p.expert_counts[e] = ld_volatile_int(p.acc + e);
-        p.acc[e] = 0;
+        int total = 0;
+        for (int src = 0; src < g.world; ++src)
+            total += ld_volatile_int(p.recv_expert_counts + src * g.experts + e);
+        p.expert_counts[e] = total;
     }
     stamp(p.trace, 4, tid == 0);
 }
@@ -524,7 +531,7 @@ __global__ void __launch_bounds__(kThreads, 4) ep_dispatch_kernel(DispatchParams
                         s_dest[__popc(live & ((1u << lane) - 1))] = lane;
                     if (lane == 0)
                         s_ndest = __popc(live);
-                    // Position inside the expert: asked for now, read after the payload went out.
+                    // Position inside the expert's group: asked for now, read after the payload went out.
                     const int owner_slot = __shfl_sync(kFull, slot, owner >= 0 ? owner : 0);
                     if (owner >= 0 && owner_slot >= 0)
                         pos = reserve_position(p, owner, id);
@@ -620,6 +627,15 @@ __global__ void __launch_bounds__(kThreads, 4) ep_dispatch_kernel(DispatchParams
                     aboleth::detail::ld_relaxed_sys(reinterpret_cast<const std::uint64_t *>(p.send_counts + tid)),
                     static_cast<std::uint64_t>(g.capacity)));
             }
+            // Every expert's pair count goes to its owner (row `rank` of the owner's table).
+            for (int e = tid; e < g.experts; e += kThreads) {
+                const int owner = p.owners[e];
+                int *row = reinterpret_cast<int *>(p.peer_expert_counts[owner]) +
+                           static_cast<std::size_t>(g.rank) * g.experts;
+                asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(row + e),
+                             "r"(ld_volatile_int(p.send_expert_counts + e)) : "memory");
+                p.send_expert_counts[e] = 0;
+            }
             __syncthreads();
             if (tid < g.world) {
                 std::uint64_t *cnt = reinterpret_cast<std::uint64_t *>(p.peer_counts[tid]) + g.rank;
@@ -648,7 +664,7 @@ struct CombineParams {
     const std::uint32_t *expert_out;   // bf16 rows: weighted ? [pairs, hidden] : [world*capacity, hidden]
     const int *expert_ids, *expert_pos;
     const float *expert_weights;
-    const int *expert_offsets;         // [experts] start row of each expert's group (weighted)
+    const int *expert_offsets;         // [world, experts] first row of (source, expert) in expert_out (weighted)
     const int *recv_meta;
     const unsigned long long *recv_counts;
     // transport
@@ -720,16 +736,17 @@ __device__ __forceinline__ void return_row_by_warp(const CombineParams &p, int r
             aboleth::detail::st_stream16(dst + v * 16, aboleth::detail::ld_stream16(y + v * 4));
         return;
     }
-    int n = p.recv_meta[static_cast<std::size_t>(row) * meta_words(g) + 1];
-    n = n < 0 ? 0 : (n > g.top_k ? g.top_k : n);
+    // Choices are packed to the front of a record by its sender; unused ones carry position -1.
     int my_row = -1;
     float my_gate = 0.f;
-    if (lane < n) {
+    if (lane < g.top_k) {
         const int pos = p.expert_pos[row * g.top_k + lane];
-        if (pos >= 0)
-            my_row = p.expert_offsets[p.expert_ids[row * g.top_k + lane]] + pos;
+        const int id = p.expert_ids[row * g.top_k + lane];
         my_gate = p.expert_weights[row * g.top_k + lane];
+        if (pos >= 0 && id >= 0 && id < g.experts)
+            my_row = p.expert_offsets[src * g.experts + id] + pos;
     }
+    const int n = __popc(__ballot_sync(kFull, my_row >= 0));
     // Four consecutive 512-byte pieces (2 KiB) of a row per pass, two rows in flight: long
     // contiguous reads keep DRAM pages open, eight 16-byte loads per lane hide the latency.
     constexpr int kPieces = 4;
@@ -834,7 +851,6 @@ __global__ void __launch_bounds__(kThreads, 3) ep_combine_kernel(CombineParams p
     const int warp = tid >> 5;
     const std::uint64_t epoch = *p.epoch;
     const int vecs = g.hidden / 8;  // 16-byte vectors per bf16 row
-    const int words = meta_words(g);
     const bool tracer = blockIdx.x == 0 && tid == 0;
     stamp(p.trace, 0, tracer);
 
@@ -903,13 +919,15 @@ __global__ void __launch_bounds__(kThreads, 3) ep_combine_kernel(CombineParams p
                 const int row = src * g.capacity + slot;
                 int n = 1;
                 if (p.weighted) {
-                    n = p.recv_meta[static_cast<std::size_t>(row) * words + 1];
-                    n = n < 0 ? 0 : (n > g.top_k ? g.top_k : n);
+                    // ids, positions and gates are fetched together (no look at the record's choice
+                    // count first): unused choice slots carry position -1 and are skipped.
+                    n = g.top_k;
                     if (tid < n) {
                         const int id = p.expert_ids[row * g.top_k + tid];
                         const int pos = p.expert_pos[row * g.top_k + tid];
-                        s_rows[tid] = pos >= 0 ? p.expert_offsets[id] + pos : -1;
                         s_gate[tid] = p.expert_weights[row * g.top_k + tid];
+                        s_rows[tid] = (pos >= 0 && id >= 0 && id < g.experts)
+                                          ? p.expert_offsets[src * g.experts + id] + pos : -1;
                     }
                     __syncthreads();
                 }
@@ -1080,31 +1098,37 @@ __global__ void __launch_bounds__(kThreads) router_topk_kernel(
     }
 }
 
-// Exclusive scan of expert_counts -> offsets (one CTA; experts <= 1024 * 4).
+// counts [sources, experts] -> offsets [sources, experts]: the rows of expert e start at the
+// exclusive scan of the experts' totals (each rounded up to `align`), and inside an expert's
+// group the rows of source s follow those of the sources before it.  One CTA; experts <= 1024.
 __global__ void __launch_bounds__(1024) expert_offsets_kernel(
-    const int *counts, int *offsets, int *total, int experts, int align) {
+    const int *counts, int *offsets, int *total, int sources, int experts, int align) {
     __shared__ int s[1024];
-    int carry = 0;
-    for (int base = 0; base < experts; base += 1024) {
-        const int e = base + threadIdx.x;
-        int v = e < experts ? counts[e] : 0;
-        if (align > 1)
-            v = (v + align - 1) / align * align;
-        s[threadIdx.x] = v;
+    const int e = threadIdx.x;
+    int sum = 0;
+    if (e < experts)
+        for (int src = 0; src < sources; ++src)
+            sum += counts[src * experts + e];
+    int v = sum;
+    if (align > 1)
+        v = (v + align - 1) / align * align;
+    s[e] = e < experts ? v : 0;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {
+        const int add = e >= off ? s[e - off] : 0;
         __syncthreads();
-        for (int off = 1; off < 1024; off <<= 1) {
-            const int add = threadIdx.x >= off ? s[threadIdx.x - off] : 0;
-            __syncthreads();
-            s[threadIdx.x] += add;
-            __syncthreads();
-        }
-        if (e < experts)
-            offsets[e] = carry + s[threadIdx.x] - v;
-        carry += s[1023];
+        s[e] += add;
         __syncthreads();
     }
-    if (threadIdx.x == 0 && total != nullptr)
-        *total = carry;
+    if (e < experts) {
+        int at = s[e] - v;
+        for (int src = 0; src < sources; ++src) {
+            offsets[src * experts + e] = at;
+            at += counts[src * experts + e];
+        }
+    }
+    if (e == 0 && total != nullptr)
+        *total = s[1023];
 }
 
 // Gather received rows into expert-contiguous order:
@@ -1114,7 +1138,7 @@ __global__ void __launch_bounds__(kThreads) permute_kernel(
     const std::uint8_t *src, std::uint8_t *dst, const float *src_scales, float *dst_scales,
     const int *expert_ids, const int *expert_pos, const int *offsets,
     const unsigned long long *recv_counts, int *perm_row, int world, int capacity, int top_k,
-    int row_bytes, int cols, int src_scale_stride) {
+    int row_bytes, int cols, int src_scale_stride, int offset_stride) {
     const int total = world * capacity;
     for (int row = blockIdx.x; row < total; row += gridDim.x) {
         const int srcr = row / capacity;
@@ -1124,7 +1148,7 @@ __global__ void __launch_bounds__(kThreads) permute_kernel(
             const int pos = expert_pos[row * top_k + j];
             if (pos < 0)
                 continue;
-            const int out = offsets[expert_ids[row * top_k + j]] + pos;
+            const int out = offsets[srcr * offset_stride + expert_ids[row * top_k + j]] + pos;
             const uint4 *s = reinterpret_cast<const uint4 *>(src + static_cast<std::size_t>(row) * row_bytes);
             uint4 *d = reinterpret_cast<uint4 *>(dst + static_cast<std::size_t>(out) * row_bytes);
             for (int v = threadIdx.x; v < row_bytes / 16; v += kThreads)
@@ -1143,7 +1167,7 @@ __global__ void __launch_bounds__(kThreads) permute_kernel(
 __global__ void __launch_bounds__(kThreads) unpermute_kernel(
     const std::uint32_t *y, std::uint32_t *out, const int *expert_ids, const int *expert_pos,
     const float *expert_weights, const int *offsets, const unsigned long long *recv_counts,
-    int world, int capacity, int top_k, int hidden) {
+    int world, int capacity, int top_k, int hidden, int offset_stride) {
     const int total = world * capacity;
     const int vecs = hidden / 8;
     for (int row = blockIdx.x; row < total; row += gridDim.x) {
@@ -1158,7 +1182,8 @@ __global__ void __launch_bounds__(kThreads) unpermute_kernel(
                     continue;
                 const float w = expert_weights[row * top_k + j];
                 const uint4 r = *reinterpret_cast<const uint4 *>(
-                    y + static_cast<std::size_t>(offsets[expert_ids[row * top_k + j]] + pos) * (hidden / 2) + v * 4);
+                    y + static_cast<std::size_t>(offsets[srcr * offset_stride + expert_ids[row * top_k + j]] + pos) *
+                            (hidden / 2) + v * 4);
                 acc[0] += w * bf16_lo(r.x); acc[1] += w * bf16_hi(r.x);
                 acc[2] += w * bf16_lo(r.y); acc[3] += w * bf16_hi(r.y);
                 acc[4] += w * bf16_lo(r.z); acc[5] += w * bf16_hi(r.z);
@@ -1185,7 +1210,7 @@ __global__ void __launch_bounds__(kThreads) standin_expert_kernel(
     const std::uint8_t *payload, const float *scales, int scale_stride, std::uint32_t *y,
     const int *expert_ids, const float *expert_weights, const int *expert_pos, const int *offsets,
     const unsigned long long *recv_counts, int world, int capacity, int top_k, int hidden, int group,
-    int value_fp8) {
+    int value_fp8, int offset_stride) {
     const int total = world * capacity;
     __shared__ float s_coef[kMaxTopK];
     __shared__ int s_out[kMaxTopK];
@@ -1210,7 +1235,7 @@ __global__ void __launch_bounds__(kThreads) standin_expert_kernel(
             if (threadIdx.x < top_k) {
                 const int id = expert_ids[row * top_k + threadIdx.x];
                 const int pos = expert_pos[row * top_k + threadIdx.x];
-                s_out[threadIdx.x] = pos >= 0 ? offsets[id] + pos : -1;
+                s_out[threadIdx.x] = pos >= 0 ? offsets[srcr * offset_stride + id] + pos : -1;
                 s_coef[threadIdx.x] = 1.0f + static_cast<float>(id % 7) * 0.125f;
             }
         }
@@ -1335,10 +1360,11 @@ AB_EXPORT int ab_ep_dispatch(const int *ints, float amax_floor, const std::uint6
     p.peer_ids = reinterpret_cast<const std::uint64_t *>(ptrs[i++]);
     p.peer_weights = reinterpret_cast<const std::uint64_t *>(ptrs[i++]);
     p.peer_pos = reinterpret_cast<const std::uint64_t *>(ptrs[i++]);
-    p.peer_acc = reinterpret_cast<const std::uint64_t *>(ptrs[i++]);
+    p.peer_expert_counts = reinterpret_cast<const std::uint64_t *>(ptrs[i++]);
+    p.send_expert_counts = reinterpret_cast<int *>(ptrs[i++]);
     p.recv_counts = reinterpret_cast<const unsigned long long *>(ptrs[i++]);
     p.flags = reinterpret_cast<const std::uint64_t *>(ptrs[i++]);
-    p.acc = reinterpret_cast<int *>(ptrs[i++]);
+    p.recv_expert_counts = reinterpret_cast<const int *>(ptrs[i++]);
     p.expert_counts = reinterpret_cast<int *>(ptrs[i++]);
     p.trace = reinterpret_cast<unsigned long long *>(ptrs[i++]);
     if (p.num_tokens > 0) {  // an empty batch may come with null (empty) tensors
@@ -1423,11 +1449,11 @@ AB_EXPORT int ab_router_topk(const float *logits, int *ids, float *weights, int 
     return ab::launch_result("router_topk");
 }
 
-AB_EXPORT int ab_expert_offsets(const int *counts, int *offsets, int *total, int experts, int align,
-                                cudaStream_t stream) {
-    if (experts < 1)
+AB_EXPORT int ab_expert_offsets(const int *counts, int *offsets, int *total, int sources, int experts,
+                                int align, cudaStream_t stream) {
+    if (experts < 1 || experts > 1024 || sources < 1)
         return -1;
-    expert_offsets_kernel<<<1, 1024, 0, stream>>>(counts, offsets, total, experts, align);
+    expert_offsets_kernel<<<1, 1024, 0, stream>>>(counts, offsets, total, sources, experts, align);
     return ab::launch_result("expert_offsets");
 }
 
@@ -1435,7 +1461,7 @@ AB_EXPORT int ab_permute(const void *src, void *dst, const float *src_scales, fl
                          const int *expert_ids, const int *expert_pos, const int *offsets,
                          const unsigned long long *recv_counts, int *perm_row, int world,
                          int capacity, int top_k, int row_bytes, int cols, int src_scale_stride,
-                         cudaStream_t stream) {
+                         int offset_stride, cudaStream_t stream) {
     if (row_bytes % 16 || world < 1 || capacity < 1)
         return -1;
     const int total = world * capacity;
@@ -1443,21 +1469,21 @@ AB_EXPORT int ab_permute(const void *src, void *dst, const float *src_scales, fl
     permute_kernel<<<grid, kThreads, 0, stream>>>(
         static_cast<const std::uint8_t *>(src), static_cast<std::uint8_t *>(dst), src_scales,
         dst_scales, expert_ids, expert_pos, offsets, recv_counts, perm_row, world, capacity, top_k,
-        row_bytes, cols, src_scale_stride > 0 ? src_scale_stride : cols);
+        row_bytes, cols, src_scale_stride > 0 ? src_scale_stride : cols, offset_stride);
     return ab::launch_result("permute");
 }
 
 AB_EXPORT int ab_unpermute(const void *y, void *out, const int *expert_ids, const int *expert_pos,
                            const float *expert_weights, const int *offsets,
                            const unsigned long long *recv_counts, int world, int capacity, int top_k,
-                           int hidden, cudaStream_t stream) {
+                           int hidden, int offset_stride, cudaStream_t stream) {
     if (hidden % 8 || world < 1 || capacity < 1)
         return -1;
     const int total = world * capacity;
     const int grid = total < 148 * 8 ? total : 148 * 8;
     unpermute_kernel<<<grid, kThreads, 0, stream>>>(
         static_cast<const std::uint32_t *>(y), static_cast<std::uint32_t *>(out), expert_ids,
-        expert_pos, expert_weights, offsets, recv_counts, world, capacity, top_k, hidden);
+        expert_pos, expert_weights, offsets, recv_counts, world, capacity, top_k, hidden, offset_stride);
     return ab::launch_result("unpermute");
 }
 
@@ -1465,7 +1491,8 @@ AB_EXPORT int ab_standin_expert(const void *payload, const float *scales, int sc
                                 const int *expert_ids, const float *expert_weights,
                                 const int *expert_pos, const int *offsets,
                                 const unsigned long long *recv_counts, int world, int capacity,
-                                int top_k, int hidden, int group, int value_fp8, cudaStream_t stream) {
+                                int top_k, int hidden, int group, int value_fp8, int offset_stride,
+                                cudaStream_t stream) {
     if (hidden % 8 || world < 1 || capacity < 1 || top_k < 1 || top_k > kMaxTopK)
         return -1;
     const int total = world * capacity;
@@ -1474,6 +1501,6 @@ AB_EXPORT int ab_standin_expert(const void *payload, const float *scales, int sc
         static_cast<const std::uint8_t *>(payload), scales,
         scale_stride > 0 ? scale_stride : hidden / group, static_cast<std::uint32_t *>(y),
         expert_ids, expert_weights, expert_pos, offsets, recv_counts, world, capacity, top_k, hidden,
-        group, value_fp8);
+        group, value_fp8, offset_stride);
     return ab::launch_result("standin_expert");
 }

@@ -119,11 +119,12 @@ class MixtralEP:
         prepared = self.moe.prepare(x, weights, ids)
         slot = self.moe.runtime.selected[0]
         spec = slot.spec
-        offsets, total = expert_offsets(slot.expert_counts)
+        # One offset per (source rank, expert); row 0 is where each expert's group starts.
+        offsets, total = expert_offsets(slot.expert_counts_by_source)
         permute(prepared.expert_input, self.x_perm, prepared.global_ids, prepared.expert_pos, offsets,
                 prepared.recv_counts, world=spec.ranks, capacity=spec.capacity)
         lo, hi = self.first_expert, self.first_expert + self.local_experts
-        counts, offs = slot.expert_counts[lo:hi], offsets[lo:hi]
+        counts, offs = slot.expert_counts[lo:hi], offsets[0, lo:hi]
         # Rows that can be live under the selected variant's (rank-uniform) token bound.
         rows = min(self.x_perm.shape[0], spec.ranks * spec.capacity * min(c.top_k, self.local_experts))
         xp = self.x_perm[:rows]

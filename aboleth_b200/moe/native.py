@@ -10,9 +10,12 @@ captured in a CUDA graph.  API shape follows the reference's executor
 
 The SENDER unpacks: besides the payload row and the wire-format metadata row it
 writes each record's expert ids, gate weights and positions into the
-destination's ``recv_ids`` / ``recv_weights`` / ``recv_pos`` arrays (positions
-come from one ``atom.add`` per chosen expert on the destination's
-``expert_acc`` counters), so the receiving rank runs no per-record pass.  The
+destination's ``recv_ids`` / ``recv_weights`` / ``recv_pos`` arrays, so the
+receiving rank runs no per-record pass.  A position counts the record among
+ITS SOURCE RANK's records for that expert; each source also sends its
+per-expert totals (``recv_expert_counts[source, expert]``), and
+``expert_offsets`` turns that table into the first row of every (source,
+expert) group in the expert-contiguous layout.  The
 combine publishes returned records in blocks of ``return_block`` rows
 (``return_flags[peer, block]``) and reduces a token as soon as the blocks that
 hold its partial rows are there.
@@ -35,7 +38,7 @@ from .spec import MoESpec
 
 PHASE_SEND, PHASE_RECV = 1, 2
 _REGIONS = ("recv_payload", "recv_meta", "recv_counts", "dispatch_flags", "returned", "return_flags",
-            "recv_ids", "recv_weights", "recv_pos", "expert_acc")
+            "recv_ids", "recv_weights", "recv_pos", "recv_expert_counts")
 RETURN_BLOCK = 64          # records per readiness block of the combine (every rank must use the same)
 MIN_RETURN_BLOCK = 16      # the flag arrays are sized for blocks this small
 MAX_DISPATCH_CTAS = 2048   # rows of the per-CTA record-count table (token-ordered slots)
@@ -58,7 +61,7 @@ def _region_sizes(spec: MoESpec) -> dict[str, int]:
         "recv_ids": rows * s.top_k * 4,
         "recv_weights": rows * s.top_k * 4,
         "recv_pos": rows * s.top_k * 4,
-        "expert_acc": s.experts * 4,
+        "recv_expert_counts": s.ranks * s.experts * 4,
     }
 
 
@@ -75,8 +78,9 @@ class DispatchResult:
     expert_scales: Optional[torch.Tensor]  # [ranks*capacity, hidden/group] fp32
     expert_ids: torch.Tensor        # [ranks*capacity, k] int32
     expert_weights: torch.Tensor    # [ranks*capacity, k] fp32
-    expert_pos: torch.Tensor        # [ranks*capacity, k] int32 position inside its expert, -1 unused
-    expert_counts: torch.Tensor     # [experts] int32
+    expert_pos: torch.Tensor        # [ranks*capacity, k] int32 position inside its (source, expert) group, -1 unused
+    expert_counts: torch.Tensor     # [experts] int32 totals
+    expert_counts_by_source: torch.Tensor  # [ranks, experts] int32: what ``expert_offsets`` consumes
     recv_counts: torch.Tensor       # [ranks] int64
     topk_ids: torch.Tensor          # [capacity, k] int32 (this rank's tokens)
     topk_weights: torch.Tensor      # [capacity, k] fp32
@@ -143,7 +147,8 @@ class NativeMoESlot:
         self.expert_ids = b.view("recv_ids").view(torch.int32).view(rows, s.top_k)
         self.expert_weights = b.view("recv_weights").view(torch.float32).view(rows, s.top_k)
         self.expert_pos = b.view("recv_pos").view(torch.int32).view(rows, s.top_k)
-        self.expert_acc = b.view("expert_acc").view(torch.int32)
+        self.expert_counts_by_source = b.view("recv_expert_counts").view(torch.int32).view(s.ranks, s.experts)
+        self.send_expert_counts = z(s.experts, dtype=torch.int32)
         self.expert_counts = z(s.experts, dtype=torch.int32)
         # The scales travel inside the metadata row; this is a strided view of them (row stride =
         # metadata_words), not a copy.
@@ -232,14 +237,16 @@ class NativeMoESlot:
                     self.placeholders, self.source_slots, self.send_counts, self.done, self.overflow,
                     self.epoch, self.status, self.block_counts, t["recv_payload"], t["recv_meta"],
                     t["recv_counts"], t["dispatch_flags"], t["recv_ids"], t["recv_weights"],
-                    t["recv_pos"], t["expert_acc"], self.recv_counts, self.dispatch_flags,
-                    self.expert_acc, self.expert_counts, self.trace_buffer]
+                    t["recv_pos"], t["recv_expert_counts"], self.send_expert_counts, self.recv_counts,
+                    self.dispatch_flags, self.expert_counts_by_source, self.expert_counts,
+                    self.trace_buffer]
         call("ab_ep_dispatch", self._geometry(n, routing, renormalize, phases),
              ctypes.c_float(s.quant_amax_floor), self._fill(pointers), self.grid, stream_ptr())
         self._last_tokens = n
         return DispatchResult(self.recv_payload, self.expert_scales, self.expert_ids,
                               self.expert_weights, self.expert_pos, self.expert_counts,
-                              self.recv_counts, self.topk_ids, self.topk_weights)
+                              self.expert_counts_by_source, self.recv_counts, self.topk_ids,
+                              self.topk_weights)
 
     def combine(self, expert_output: Optional[torch.Tensor] = None, *,
                 expert_offsets: Optional[torch.Tensor] = None, num_tokens: Optional[int] = None,
@@ -249,7 +256,8 @@ class NativeMoESlot:
 
         Without ``expert_offsets`` the rows of ``expert_output`` are one partial
         per received record (``[ranks*capacity, hidden]``, already gate-weighted)
-        and are summed over ranks.  With ``expert_offsets`` (int32 ``[experts]``)
+        and are summed over ranks.  With ``expert_offsets`` (int32 ``[ranks, experts]``
+        from :func:`aboleth_b200.ops.expert_offsets` over ``expert_counts_by_source``)
         ``expert_output`` is in expert-contiguous order and the gate-weighted
         sum over each record's experts is taken inside the kernel.
         """
@@ -259,6 +267,8 @@ class NativeMoESlot:
         if y.dtype != torch.bfloat16 or y.shape[-1] != s.hidden or not y.is_contiguous():
             raise ValueError("expert_output must be contiguous bf16 [rows, hidden]")
         out = self.final_output if out is None else out
+        if expert_offsets is not None and tuple(expert_offsets.shape) != (s.ranks, s.experts):
+            raise ValueError("expert_offsets must be int32 [ranks, experts] (one row per source rank)")
         t = self.peer_tables
         pointers = [y, self.expert_ids, self.expert_pos, self.expert_weights, expert_offsets,
                     self.recv_meta, self.recv_counts, t["returned"], t["return_flags"],
@@ -287,7 +297,7 @@ class NativeMoESlot:
     def reset(self) -> None:
         """Clear per-layer counters (only needed when a dispatch is not followed by a combine)."""
         self.expert_counts.zero_()
-        self.expert_acc.zero_()
+        self.send_expert_counts.zero_()
         self.send_counts.zero_()
         self.done.zero_()
         self.block_done.zero_()

@@ -25,10 +25,10 @@ _SIGNATURES = {
     "ab_ep_combine": [_VP, _F, _VP, _I, _VP],
     "ab_quant_fp8": [_VP, _VP, _VP, _I, _I, _I, _F, _I, _VP],
     "ab_router_topk": [_VP, _VP, _VP, _I, _I, _I, _I, _VP],
-    "ab_expert_offsets": [_VP, _VP, _VP, _I, _I, _VP],
-    "ab_permute": [_VP] * 9 + [_I] * 6 + [_VP],
-    "ab_unpermute": [_VP] * 7 + [_I] * 4 + [_VP],
-    "ab_standin_expert": [_VP, _VP, _I] + [_VP] * 6 + [_I] * 6 + [_VP],
+    "ab_expert_offsets": [_VP, _VP, _VP, _I, _I, _I, _VP],
+    "ab_permute": [_VP] * 9 + [_I] * 7 + [_VP],
+    "ab_unpermute": [_VP] * 7 + [_I] * 5 + [_VP],
+    "ab_standin_expert": [_VP, _VP, _I] + [_VP] * 6 + [_I] * 7 + [_VP],
 }
 
 _launches = 0

@@ -41,12 +41,29 @@ def router_topk(logits: torch.Tensor, top_k: int, *, renormalize: bool = False
 
 
 def expert_offsets(counts: torch.Tensor, *, align: int = 1) -> tuple[torch.Tensor, torch.Tensor]:
-    """Exclusive scan of int32 ``counts`` (each rounded up to ``align``) -> (offsets, total)."""
+    """Row offsets of the expert-contiguous layout -> (offsets, total rows).
+
+    ``counts`` is int32 ``[sources, experts]`` (``DispatchResult.expert_counts_by_source``) or
+    ``[experts]``.  The group of expert ``e`` starts at the exclusive scan of the experts' totals
+    (each rounded up to ``align``); inside it the rows of source ``s`` follow those of the sources
+    before it.  ``offsets`` has the shape of ``counts``; ``offsets[0]`` (or ``offsets`` itself for
+    1-D counts) is the start of every expert's group, which is what a grouped GEMM needs.
+    """
+    assert counts.dtype == torch.int32 and counts.is_contiguous() and counts.dim() in (1, 2)
+    sources = counts.shape[0] if counts.dim() == 2 else 1
     offsets = torch.empty_like(counts)
     total = torch.empty(1, dtype=torch.int32, device=counts.device)
-    call("ab_expert_offsets", ptr(counts), ptr(offsets), ptr(total), counts.numel(), align,
+    call("ab_expert_offsets", ptr(counts), ptr(offsets), ptr(total), sources, counts.shape[-1], align,
          stream_ptr())
     return offsets, total
+
+
+def _offset_stride(offsets: Optional[torch.Tensor]) -> int:
+    """0 for one offset per expert, ``experts`` for one per (source rank, expert)."""
+    if offsets is None or offsets.dim() == 1:
+        return 0
+    assert offsets.dim() == 2 and offsets.is_contiguous()
+    return int(offsets.shape[1])
 
 
 def permute(src: torch.Tensor, dst: torch.Tensor, expert_ids: torch.Tensor,
@@ -54,14 +71,15 @@ def permute(src: torch.Tensor, dst: torch.Tensor, expert_ids: torch.Tensor,
             world: int, capacity: int, src_scales: Optional[torch.Tensor] = None,
             dst_scales: Optional[torch.Tensor] = None,
             perm_row: Optional[torch.Tensor] = None) -> None:
-    """Gather received rows into expert-contiguous order (``dst[offsets[e] + pos] = src[row]``)."""
+    """Gather received rows into expert-contiguous order (``dst[offsets[source, e] + pos] = src[row]``;
+    ``offsets`` from :func:`expert_offsets` over the per-source counts)."""
     top_k = expert_ids.shape[-1]
     row_bytes = src.shape[-1] * src.element_size()
     cols = 0 if src_scales is None else src_scales.shape[-1]
     stride = 0 if src_scales is None else _row_stride(src_scales)
     call("ab_permute", ptr(src), ptr(dst), ptr(src_scales), ptr(dst_scales), ptr(expert_ids),
          ptr(expert_pos), ptr(offsets), ptr(recv_counts), ptr(perm_row), world, capacity, top_k,
-         row_bytes, cols, stride, stream_ptr())
+         row_bytes, cols, stride, _offset_stride(offsets), stream_ptr())
 
 
 def unpermute(y: torch.Tensor, out: torch.Tensor, expert_ids: torch.Tensor,
@@ -70,7 +88,7 @@ def unpermute(y: torch.Tensor, out: torch.Tensor, expert_ids: torch.Tensor,
     """``out[row] = sum_j w[row, j] * y[offsets[id] + pos]`` in fp32, bf16 result."""
     call("ab_unpermute", ptr(y), ptr(out), ptr(expert_ids), ptr(expert_pos), ptr(expert_weights),
          ptr(offsets), ptr(recv_counts), world, capacity, expert_ids.shape[-1], y.shape[-1],
-         stream_ptr())
+         _offset_stride(offsets), stream_ptr())
 
 
 def _row_stride(scales: torch.Tensor) -> int:
@@ -88,11 +106,11 @@ def standin_expert(payload: torch.Tensor, scales: Optional[torch.Tensor], y: tor
     """Benchmark expert ``f_e(x) = x * (1 + (e mod 7) / 8)``.
 
     Without ``offsets``: record layout, gate-weighted (one partial row per received record).
-    With ``offsets`` (int32 ``[experts]``): expert-contiguous layout, one unweighted row per
-    (record, choice) at ``offsets[id] + pos`` - what a grouped expert GEMM leaves behind.
+    With ``offsets`` (int32 ``[ranks, experts]``): expert-contiguous layout, one unweighted row per
+    (record, choice) at ``offsets[source, id] + pos`` - what a grouped expert GEMM leaves behind.
     """
     fp8 = payload.dtype == torch.float8_e4m3fn
     stride = 0 if scales is None else _row_stride(scales)
     call("ab_standin_expert", ptr(payload), ptr(scales), stride, ptr(y), ptr(expert_ids),
          ptr(expert_weights), ptr(expert_pos), ptr(offsets), ptr(recv_counts), world, capacity,
-         expert_ids.shape[-1], y.shape[-1], group, int(fp8), stream_ptr())
+         expert_ids.shape[-1], y.shape[-1], group, int(fp8), _offset_stride(offsets), stream_ptr())

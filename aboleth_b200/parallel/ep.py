@@ -40,7 +40,7 @@ class ExpertParallelLayer:
         one UNWEIGHTED row per (record, choice) at ``offsets[expert] + position``.  Returns the
         offsets, so the combine kernel gathers each record's rows and applies the gates itself."""
         s = self.spec
-        offsets, _ = expert_offsets(result.expert_counts)
+        offsets, _ = expert_offsets(result.expert_counts_by_source)
         rows = s.ranks * s.capacity * min(s.top_k, s.experts_per_rank)
         if self._grouped is None or self._grouped.shape[0] < rows:
             self._grouped = torch.empty(rows, s.hidden, dtype=torch.bfloat16, device=y.device)

@@ -25,6 +25,10 @@ import json
 import os
 import sys
 
+# Whatever NCCL logs (the caller's NCCL_DEBUG decides how much) goes to stderr: stdout carries the
+# one JSON line and nothing else.
+os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+
 HIDDEN, EXPERTS, TOP_K, GROUP = 7168, 256, 8, 128
 METRIC = "EP dispatch+combine tokens/s (DeepSeek-V3 shape, fp8 1x128 dispatch, bf16 combine)"
 ROOT = os.path.dirname(os.path.abspath(__file__))

@@ -40,7 +40,7 @@ def emulate(args) -> int:
         results = group.dispatch(xs, logits=logits)
         offsets = []
         for k, res in enumerate(results):
-            off, _ = expert_offsets(res.expert_counts)
+            off, _ = expert_offsets(res.expert_counts_by_source)
             standin_expert(res.expert_input, res.expert_scales, grouped[k], res.expert_ids,
                            res.expert_weights, res.expert_pos, res.recv_counts, world=r,
                            capacity=spec.capacity, group=spec.scale_group, offsets=off)

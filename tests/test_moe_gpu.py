@@ -120,14 +120,14 @@ def test_weighted_combine_with_permute_is_exact_for_integers(by_warp):
     results = group.dispatch(toks, ids=ids, weights=wts)
     ys, offs = [], []
     for r, res in enumerate(results):
-        offsets, total = expert_offsets(res.expert_counts)
+        offsets, total = expert_offsets(res.expert_counts_by_source)
         x_perm = torch.zeros(spec.ranks * spec.capacity * spec.top_k, spec.hidden,
                              dtype=torch.bfloat16, device="cuda")
         permute(res.expert_input, x_perm, res.expert_ids, res.expert_pos, offsets, res.recv_counts,
                 world=2, capacity=8)
         y = x_perm.clone()
         counts = res.expert_counts.cpu().tolist()
-        o = offsets.cpu().tolist()
+        o = offsets[0].cpu().tolist()  # row 0 of the table: where each expert's group starts
         for e in range(4):  # expert e multiplies by e + 1
             y[o[e]:o[e] + counts[e]] *= (e + 1)
         ys.append(y)
