@@ -1,8 +1,13 @@
 """Execution contract: may a phase run at a fixed compiled capacity, and what to do when not.
 
-A fixed-capacity launch (the CUDA-graph friendly form) is legal only when the valid count
-is dynamic, the padding is dead, addresses are graph-stable and the ranks run in lockstep;
-otherwise the declared fallback applies.  Reference: python/aboleth/execution.py:13-253.
+A launch at a fixed capacity (the form a CUDA graph can hold) moves the padding of a partly
+filled buffer along with its live prefix and assumes every rank takes the same path.  That is
+only sound under four proof obligations, which :meth:`ExecutionContract.unmet` lists by name:
+the live count is a run-time value, the padding is dead, the addresses do not change between
+replays, and the ranks advance in lockstep.  With an obligation open, the declared fallback
+applies (agree on the exact count first, run eagerly, or refuse).  The vocabulary - capacity
+contract, padding semantics, rank control, runtime guards, fallbacks - is the reference's
+(python/aboleth/execution.py:13-253).
 """
 from __future__ import annotations
 
@@ -10,48 +15,64 @@ from dataclasses import dataclass
 from enum import Enum
 
 
-class PaddingSemantics(Enum):
+class _Named(Enum):
+    """Enumerations here compare by identity and also accept their value as a string."""
+
+    @classmethod
+    def of(cls, value):
+        if isinstance(value, cls):
+            return value
+        try:
+            return cls(value)
+        except ValueError:
+            raise TypeError(f"{value!r} is not a {cls.__name__}; expected one of "
+                            f"{[member.value for member in cls]}") from None
+
+
+class PaddingSemantics(_Named):
+    UNKNOWN = "unknown"        # nothing is known about the bytes past the live prefix
+    PRESERVED = "preserved"    # a reader may look at them: they must not travel or be clobbered
+    DEAD = "dead"              # nobody reads them: moving or overwriting them is harmless
+
+
+class RankControl(_Named):
     UNKNOWN = "unknown"
-    PRESERVED = "preserved"
-    DEAD = "dead"
+    DYNAMIC = "dynamic"        # ranks may take different paths (a rank can skip a step)
+    LOCKSTEP = "lockstep"      # every rank runs every step with the same shape variant
 
 
-class RankControl(Enum):
-    UNKNOWN = "unknown"
-    DYNAMIC = "dynamic"
-    LOCKSTEP = "lockstep"
-
-
-class ExecutionFallback(Enum):
-    EXACT_AGREEMENT = "exact_agreement"
-    EAGER = "eager"
-    ERROR = "error"
+class ExecutionFallback(_Named):
+    EXACT_AGREEMENT = "exact_agreement"   # ranks agree on the live count, then launch exactly that
+    EAGER = "eager"                       # leave the graph: launch from the host with the live count
+    ERROR = "error"                       # refuse
 
 
 @dataclass(frozen=True)
 class CapacityContract:
+    """What is promised about a buffer of ``max_items`` slots of which a prefix is live."""
+
     max_items: int
     dynamic_valid_count: bool
     padding: PaddingSemantics
     graph_stable_addresses: bool
 
     def __post_init__(self) -> None:
-        if self.max_items <= 0:
-            raise ValueError("capacity max_items must be positive")
-        if not isinstance(self.padding, PaddingSemantics):
-            raise TypeError("capacity padding must be PaddingSemantics")
+        if self.max_items < 1:
+            raise ValueError(f"a capacity holds at least one item, got max_items={self.max_items}")
+        object.__setattr__(self, "padding", PaddingSemantics.of(self.padding))
 
 
 @dataclass(frozen=True)
 class RuntimeGuard:
+    """A condition only the running program can check, and what happens when it fails."""
+
     name: str
     fallback: ExecutionFallback
 
     def __post_init__(self) -> None:
-        if not self.name:
-            raise ValueError("runtime guard name cannot be empty")
-        if not isinstance(self.fallback, ExecutionFallback):
-            raise TypeError("runtime guard fallback must be ExecutionFallback")
+        if not self.name.strip():
+            raise ValueError("a runtime guard needs a name (it is how a failed guard is reported)")
+        object.__setattr__(self, "fallback", ExecutionFallback.of(self.fallback))
 
 
 @dataclass(frozen=True)
@@ -69,26 +90,33 @@ class ExecutionContract:
     fallback: ExecutionFallback = ExecutionFallback.EXACT_AGREEMENT
 
     def __post_init__(self) -> None:
-        if not isinstance(self.rank_control, RankControl):
-            raise TypeError("execution rank_control must be RankControl")
-        if not isinstance(self.fallback, ExecutionFallback):
-            raise TypeError("execution fallback must be ExecutionFallback")
-        names = [g.name for g in self.guards]
-        if len(names) != len(set(names)):
-            raise ValueError("runtime guard names must be unique")
+        object.__setattr__(self, "rank_control", RankControl.of(self.rank_control))
+        object.__setattr__(self, "fallback", ExecutionFallback.of(self.fallback))
+        seen: set[str] = set()
+        for guard in self.guards:
+            if guard.name in seen:
+                raise ValueError(f"two runtime guards are called {guard.name!r}")
+            seen.add(guard.name)
+
+    def unmet(self) -> tuple[str, ...]:
+        """The proof obligations of a fixed-capacity launch that this contract leaves open."""
+        c = self.capacity
+        checks = (("the live count is a run-time value", c.dynamic_valid_count),
+                  ("the padding is dead", c.padding is PaddingSemantics.DEAD),
+                  ("addresses are stable across graph replays", c.graph_stable_addresses),
+                  ("ranks run in lockstep", self.rank_control is RankControl.LOCKSTEP))
+        return tuple(name for name, holds in checks if not holds)
 
     @property
     def fixed_capacity_legal(self) -> bool:
-        c = self.capacity
-        return (c.dynamic_valid_count and c.padding is PaddingSemantics.DEAD
-                and c.graph_stable_addresses and self.rank_control is RankControl.LOCKSTEP)
+        return not self.unmet()
 
     def describe(self) -> dict:
         c = self.capacity
         return {"capacity": {"max_items": c.max_items, "dynamic_valid_count": c.dynamic_valid_count,
                              "padding": c.padding.value, "graph_stable_addresses": c.graph_stable_addresses},
                 "rank_control": self.rank_control.value, "fixed_capacity_legal": self.fixed_capacity_legal,
-                "fallback": self.fallback.value,
+                "open_obligations": list(self.unmet()), "fallback": self.fallback.value,
                 "guards": [{"name": g.name, "fallback": g.fallback.value} for g in self.guards]}
 
     def resolve(self, actual_items: int, *, graph_stable_addresses: bool = True,

@@ -16,6 +16,9 @@ from ..pattern import OpaqueCapabilities, Pattern
 
 @dataclass(frozen=True)
 class KVCacheMigrationSpec:
+    """Shape of one migration program: up to ``max_pages`` pages of ``page_bytes`` move per step
+    between ``num_ranks`` ranks, to at most ``max_consumers`` consumers (layers) per rank."""
+
     max_pages: int
     page_bytes: int
     num_ranks: int = 1
@@ -26,26 +29,22 @@ class KVCacheMigrationSpec:
     consumer_max_inflight: int = 1
 
     def __post_init__(self):
-        if self.max_pages <= 0:
-            raise ValueError("max_pages must be positive")
-        if self.page_bytes <= 0:
-            raise ValueError("page_bytes must be positive")
+        counts = {"max_pages": self.max_pages, "page_bytes": self.page_bytes, "num_ranks": self.num_ranks,
+                  "max_consumers": self.max_consumers, "consumer_max_inflight": self.consumer_max_inflight}
+        if self.slots is not None:
+            counts["slots"] = self.slots
+        small = [f"{name}={value}" for name, value in counts.items() if value < 1]
+        if small:
+            raise ValueError("KV migration spec: " + ", ".join(small) + " must be at least 1")
         if self.page_bytes % 8:
-            raise ValueError("page_bytes must be aligned to eight bytes")
-        if self.num_ranks <= 0:
-            raise ValueError("num_ranks must be positive")
-        if self.slots is not None and self.slots <= 0:
-            raise ValueError("slots must be positive")
-        if self.max_consumers <= 0:
-            raise ValueError("max_consumers must be positive")
-        if self.consumer_max_inflight <= 0:
-            raise ValueError("consumer_max_inflight must be positive")
+            raise ValueError(f"pages are copied in 8-byte words: page_bytes={self.page_bytes} is not a multiple of 8")
         if self.slots is not None and self.slots < self.required_slots:
-            raise ValueError("slot count cannot satisfy consumer lifetime")
+            raise ValueError(f"{self.slots} slots cannot cover a consumer that keeps {self.consumer_max_inflight} "
+                             f"in flight while the next fills (needs {self.required_slots})")
 
     @property
     def required_slots(self) -> int:
-        """An asynchronous consumer holds ``max_inflight`` slots while the next one fills."""
+        """Slots a consumer's lifetime demands: those it still reads plus the one being filled."""
         return self.consumer_max_inflight + 1 if self.consumer_asynchronous else 1
 
     @property

@@ -21,21 +21,28 @@ from ..pattern import P2PRealizationProfile, PhaseResources
 from ..phase import CompiledPhase, compile_phase
 from .kv_cache import KVCacheMigrationSpec, build_kv_cache_migration_pattern
 
+# The kernels of this library that realise a KV migration on peer memory.  ``kv_push_kernel``
+# (csrc/kernels/kv_kernels.cu) both stores page runs into the consumer's final storage and
+# publishes the readiness cell from the group's last worker, so "publication in the copy kernel"
+# needs no second kernel; a consumer that waits inside its own stream uses ``kv_wait_kernel``; a
+# host-driven copy-engine transfer publishes with a packed doorbell (one stream-ordered write).
 KV_CACHE_P2P_REALIZATION = P2PRealizationProfile(
-    direct_destination_kernel="kv_cache_direct_page_write_kernel",
-    direct_publication_kernels=(("coalesced_kernel", "kv_cache_consumer_publish_kernel"),
-                                ("separate_kernel", "kv_cache_consumer_publish_kernel"),
+    direct_destination_kernel="kv_push_kernel",
+    direct_publication_kernels=(("fused_kernel", None),
+                                ("consumer_prologue", "kv_wait_kernel"),
                                 ("packed_doorbell", None)),
-    parallel_copy_kernel="kv_cache_page_batch_copy_kernel",
+    parallel_copy_kernel="kv_push_kernel",
     parallel_publication_kernels=(("fused_kernel", None),
-                                  ("coalesced_kernel", "kv_cache_consumer_publish_kernel"),
-                                  ("consumer_prologue", None)),
+                                  ("consumer_prologue", "kv_wait_kernel")),
 )
 
 
 @dataclass(frozen=True)
 class KVCacheLayoutContract:
-    """What the caller promises about the batches it will submit."""
+    """Promises of the caller about every batch it will submit.  Each one buys something:
+    contiguous runs allow several pages per transfer, consumer-partitioned batches allow one
+    readiness cell per consumer, consumer-ordered batches allow layer-by-layer readiness, and
+    stable addresses allow a fixed-capacity (graph-held) launch."""
 
     contiguous_page_runs: bool = True
     consumer_partitioned: bool = True
@@ -43,8 +50,15 @@ class KVCacheLayoutContract:
     graph_stable_addresses: bool = True
 
 
+_POSITIVE_FIELDS = ("pages_per_transfer", "slot_count", "generated_copy_workers", "generated_block_elements",
+                    "copy_engine_streams", "copy_engine_max_runs", "consumers_per_readiness")
+_READINESS_GRANULARITIES = ("rank", "consumer")
+
+
 @dataclass(frozen=True)
 class KVCachePhysicalization:
+    """Everything the compiler decided about how pages move; the runtime only reads it."""
+
     name: str
     target_profile: str
     pages_per_transfer: int
@@ -62,18 +76,19 @@ class KVCachePhysicalization:
     consumers_per_readiness: int
 
     def __post_init__(self) -> None:
+        problems = [f"{field} is {getattr(self, field)}, it has to be at least 1"
+                    for field in _POSITIVE_FIELDS if getattr(self, field) < 1]
         if not self.target_profile:
-            raise ValueError("KV physicalization needs a target profile")
-        if self.readiness not in ("rank", "consumer"):
-            raise ValueError("unknown readiness granularity")
-        for name in ("pages_per_transfer", "slot_count", "generated_copy_workers", "generated_block_elements",
-                     "copy_engine_streams", "copy_engine_max_runs", "consumers_per_readiness"):
-            if getattr(self, name) <= 0:
-                raise ValueError(f"{name} must be positive")
+            problems.append("no target profile is named")
+        if self.readiness not in _READINESS_GRANULARITIES:
+            problems.append(f"readiness {self.readiness!r} is not one of {_READINESS_GRANULARITIES}")
         if self.copy_engine_threshold_bytes < 0:
-            raise ValueError("copy_engine_threshold_bytes cannot be negative")
+            problems.append("the copy-engine threshold is negative")
         if self.consumer_layer_pipeline and self.copy_engine_streams != 1:
-            raise ValueError("consumer-layer readiness requires one ordered copy stream")
+            # layers become ready in order only if their copies are issued in order
+            problems.append("layer-by-layer readiness needs exactly one copy stream")
+        if problems:
+            raise ValueError(f"KV physicalisation {self.name!r}: " + "; ".join(problems))
 
 
 @dataclass(frozen=True)

@@ -39,14 +39,17 @@ class MoEPatternSpec:
     preserve_return_staging: bool = False
 
     def __post_init__(self):
-        for name in ("max_tokens", "hidden", "top_k", "num_ranks", "slots", "expert_max_inflight"):
-            if getattr(self, name) <= 0:
-                raise ValueError(f"{name} must be positive")
+        sizes = {name: getattr(self, name)
+                 for name in ("max_tokens", "hidden", "top_k", "num_ranks", "slots", "expert_max_inflight")}
+        wrong = [f"{name}={value}" for name, value in sizes.items() if value < 1]
         if self.scale_width < 0:
-            raise ValueError("scale_width cannot be negative")
+            wrong.append(f"scale_width={self.scale_width}")
+        if wrong:
+            raise ValueError("MoE pattern spec: " + ", ".join(wrong) + " out of range")
         if not self.experts_asynchronous and self.expert_max_inflight != 1:
-            raise ValueError("synchronous experts require max inflight equal to one")
-        element_bytes(self.value_type), element_bytes(self.output_type)
+            raise ValueError("an expert stage that runs synchronously holds exactly one layer in flight")
+        for kind in (self.value_type, self.output_type):
+            element_bytes(kind)  # raises on an unknown element type
 
     @property
     def has_scales(self) -> bool:

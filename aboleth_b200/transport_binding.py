@@ -23,32 +23,47 @@ ARTIFACT_KINDS = ("inline_fragment", "bindable_epilogue", "standalone_kernel")
 _CUDA_TYPES = {"i1": "i32", "i32": "i32", "i64": "u64"}
 
 
+SLOT_KINDS = {"i1": "a predicate", "i32": "a 32-bit integer", "i64": "a 64-bit address or handle"}
+
+
+def _expect(slot: "BoundScalar", kind: str, role: str) -> None:
+    if slot.kind != kind:
+        raise ValueError(f"{role} {slot.name!r} is declared {slot.kind}; it has to be {kind} "
+                         f"({SLOT_KINDS[kind]})")
+
+
 @dataclass(frozen=True)
 class BoundScalar:
+    """One named scalar a client kernel supplies at the insertion point.  ``kind`` is the slot's
+    width class: ``i1`` predicate, ``i32`` count / key / counter, ``i64`` address or handle."""
+
     name: str
-    mlir_type: str
+    kind: str
 
     def __post_init__(self):
-        if not self.name:
-            raise ValueError("bound scalar requires a name")
-        if self.mlir_type not in ("i1", "i32", "i64"):
-            raise ValueError("bound scalar type must be i1, i32, or i64")
+        if not self.name or not (self.name[0].isalpha() or self.name[0] == "_"):
+            raise ValueError(f"slot name {self.name!r} is not an identifier")
+        if self.kind not in SLOT_KINDS:
+            raise ValueError(f"slot {self.name!r}: kind {self.kind!r} is not one of {sorted(SLOT_KINDS)}")
 
 
 @dataclass(frozen=True)
 class RegionSide:
+    """One end of a transfer: where the bytes are and the key that authorises the access."""
+
     pointer: BoundScalar
     key: BoundScalar
 
     def __post_init__(self):
-        if self.pointer.mlir_type != "i64":
-            raise ValueError("region pointers must use i64 slots")
-        if self.key.mlir_type != "i32":
-            raise ValueError("region keys must use i32 slots")
+        _expect(self.pointer, "i64", "region pointer")
+        _expect(self.key, "i32", "region key")
 
 
 @dataclass(frozen=True)
 class RegionBinding:
+    """A predicated transfer of at most ``max_bytes`` from ``local`` to ``remote`` that carries
+    out the logical ``operations`` named."""
+
     remote: RegionSide
     local: RegionSide
     byte_count: BoundScalar
@@ -57,44 +72,51 @@ class RegionBinding:
     operations: tuple[str, ...] = ()
 
     def __post_init__(self):
-        if self.byte_count.mlir_type != "i32":
-            raise ValueError("region byte count must use an i32 slot")
-        if self.predicate.mlir_type != "i1":
-            raise ValueError("region predicate must use an i1 slot")
-        if self.max_bytes <= 0:
-            raise ValueError("region max bytes must be positive")
+        _expect(self.byte_count, "i32", "byte count")
+        _expect(self.predicate, "i1", "transfer predicate")
+        if self.max_bytes < 1:
+            raise ValueError(f"a region moves at least one byte, max_bytes is {self.max_bytes}")
 
     def slots(self) -> tuple[BoundScalar, ...]:
-        return (self.remote.pointer, self.local.pointer, self.byte_count, self.local.key,
-                self.remote.key, self.predicate)
+        return tuple(slot for _, slot in self.roles())
 
-
-_REGION_ROLES = ("remote pointer", "local pointer", "byte count", "local key", "remote key", "predicate")
+    def roles(self) -> tuple[tuple[str, BoundScalar], ...]:
+        """(role, slot) in the order a program takes them."""
+        return (("remote pointer", self.remote.pointer), ("local pointer", self.local.pointer),
+                ("byte count", self.byte_count), ("local key", self.local.key),
+                ("remote key", self.remote.key), ("predicate", self.predicate))
 
 
 @dataclass(frozen=True)
 class PublicationBinding:
+    """The flag that publishes an attachment (epoch = iteration + 1) and the loop counters the
+    completion planner works with."""
+
     remote: RegionSide
     local: RegionSide
     iteration: BoundScalar
     iterations: BoundScalar
 
     def __post_init__(self):
-        if self.iteration.mlir_type != "i32" or self.iterations.mlir_type != "i32":
-            raise ValueError("publication iteration slots must use i32")
+        _expect(self.iteration, "i32", "iteration counter")
+        _expect(self.iterations, "i32", "iteration bound")
 
     def slots(self) -> tuple[BoundScalar, ...]:
-        return (self.remote.pointer, self.local.pointer, self.local.key, self.remote.key,
-                self.iteration, self.iterations)
+        return tuple(slot for _, slot in self.roles())
+
+    def roles(self) -> tuple[tuple[str, BoundScalar], ...]:
+        return (("remote pointer", self.remote.pointer), ("local pointer", self.local.pointer),
+                ("local key", self.local.key), ("remote key", self.remote.key),
+                ("iteration", self.iteration), ("iterations", self.iterations))
 
 
-_PUBLICATION_ROLES = ("remote pointer", "local pointer", "local key", "remote key", "iteration", "iterations")
-
+# The records below are what a bound program looks like from the client kernel's side: plain
+# names, in the order the program takes them.
 
 @dataclass(frozen=True)
 class KernelTransportArgument:
     name: str
-    mlir_type: str
+    kind: str
 
 
 @dataclass(frozen=True)
@@ -176,8 +198,7 @@ class TransportProgramBinding:
         if self.artifact not in ARTIFACT_KINDS:
             raise ValueError(f"unknown artifact kind {self.artifact!r}; expected one of "
                              + ", ".join(ARTIFACT_KINDS))
-        if self.endpoint.mlir_type != "i64":
-            raise ValueError("transport endpoint must use an i64 slot")
+        _expect(self.endpoint, "i64", "endpoint handle")
         if not self.operations or not self.regions:
             raise ValueError("transport binding requires operations and regions")
         realized = tuple(op for region in self.regions for op in region.operations)
@@ -189,25 +210,24 @@ class TransportProgramBinding:
         two roles is refused (the second role would be issued through the first one's storage)."""
         candidates = [("endpoint", self.endpoint)]
         for index, region in enumerate(self.regions):
-            candidates += [(f"region {index} {role}", slot) for role, slot in zip(_REGION_ROLES, region.slots())]
-        candidates += [(f"publication {role}", slot)
-                       for role, slot in zip(_PUBLICATION_ROLES, self.publication.slots())]
+            candidates += [(f"region {index} {role}", slot) for role, slot in region.roles()]
+        candidates += [(f"publication {role}", slot) for role, slot in self.publication.roles()]
         result, roles = [], {}
         for role, slot in candidates:
             previous = roles.get(slot.name)
             if previous is None:
-                roles[slot.name] = (role, slot.mlir_type)
+                roles[slot.name] = (role, slot.kind)
                 result.append(slot)
-            elif previous != (role, slot.mlir_type):
+            elif previous != (role, slot.kind):
                 raise ValueError(f"transport binding {self.name!r} binds slot {slot.name!r} to two roles: "
-                                 f"the {previous[0]} ({previous[1]}) and the {role} ({slot.mlir_type})")
+                                 f"the {previous[0]} ({previous[1]}) and the {role} ({slot.kind})")
         return tuple(result)
 
     def to_program(self, program_id: Optional[int] = None) -> KernelTransportProgram:
         return KernelTransportProgram(
             name=self.name, operations=self.operations, kernel=self.kernel,
             insertion_point=self.insertion_point,
-            arguments=tuple(KernelTransportArgument(s.name, s.mlir_type) for s in self.slots()),
+            arguments=tuple(KernelTransportArgument(s.name, s.kind) for s in self.slots()),
             transfers=tuple(KernelTransportTransfer(
                 operations=r.operations, destination=r.remote.pointer.name, source=r.local.pointer.name,
                 byte_count=r.byte_count.name, source_key=r.local.key.name,
@@ -226,7 +246,7 @@ class TransportProgramBinding:
         Every region becomes one predicated put; the puts are chained, the last one carries
         the strong signal (epoch = iteration + 1), and a planned wait with ``reuse`` lets the
         completion pass pick the interval."""
-        args = [(s.name, _CUDA_TYPES[s.mlir_type]) for s in self.slots()]
+        args = [(s.name, _CUDA_TYPES[s.kind]) for s in self.slots()]
         b = ProgramBuilder(_symbol(self.name), args=args, threads=threads)
         # The endpoint slot carries the handle itself: a one-entry table at the argument's address.
         endpoint = b.endpoint(f"(&{self.endpoint.name})", 0)
@@ -322,5 +342,5 @@ def invoke_transport_program(manifest: InvokeManifest, symbol: str, **slots: str
     if missing or extra:
         raise ValueError(f"transport program {manifest.program_id}: missing slots {missing}, unknown slots {extra}")
     casts = {"i64": "static_cast<std::uint64_t>", "i32": "static_cast<int>", "i1": "static_cast<int>"}
-    values = ", ".join(f"{casts[a.mlir_type]}({slots[a.name]})" for a in manifest.arguments)
+    values = ", ".join(f"{casts[a.kind]}({slots[a.name]})" for a in manifest.arguments)
     return f"{symbol}({values});"

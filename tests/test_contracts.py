@@ -37,7 +37,7 @@ def test_fixed_capacity_needs_every_proof():
         contract.resolve(65)
     with pytest.raises(RuntimeError, match="forbids a fallback"):
         _contract(rank_control=RankControl.DYNAMIC, fallback=ExecutionFallback.ERROR).resolve(1)
-    with pytest.raises(ValueError, match="must be unique"):
+    with pytest.raises(ValueError, match="two runtime guards are called"):
         _contract(guards=(RuntimeGuard("a", ExecutionFallback.EAGER), RuntimeGuard("a", ExecutionFallback.EAGER)))
     plan = compile_execution_plan(contract, (8, 256, 64))
     assert plan["variants"] == (8, 64) and plan["mode"] == "fixed_capacity"

@@ -19,7 +19,7 @@ def test_moe_pattern_graph_and_plan():
     assert plan.phase_schedule("dispatch.count").strategy == "inline_transport"
     assert plan.phase_schedule("return.values").strategy == "parallel_copy"
     assert plan.phase_schedule("return.values").publication_strategy == "fused_kernel"
-    with pytest.raises(ValueError, match="max inflight"):
+    with pytest.raises(ValueError, match="exactly one layer in flight"):
         ab.MoEPatternSpec(max_tokens=1, hidden=8, top_k=1, experts_asynchronous=False, expert_max_inflight=2)
 
 
@@ -42,7 +42,7 @@ def test_kv_migration_compiles_to_direct_pages():
     # pages that are not contiguous runs move one at a time
     single = ab.compile_kv_cache_migration(spec, layout_contract=ab.KVCacheLayoutContract(contiguous_page_runs=False))
     assert single.physicalization.pages_per_transfer == 1 and single.fallback_phase is None
-    with pytest.raises(ValueError, match="consumer lifetime"):
+    with pytest.raises(ValueError, match="slots cannot cover a consumer"):
         ab.KVCacheMigrationSpec(max_pages=8, page_bytes=64, slots=1)
 
 
