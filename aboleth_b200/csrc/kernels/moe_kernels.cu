@@ -1300,6 +1300,10 @@ bool geometry_ok(const EpGeometry &g) {
 
 }  // namespace
 
+// CTAs of the last dispatch (0) / combine (1) launch made by the calling host thread.
+static thread_local int g_last_grid[2] = {0, 0};
+AB_EXPORT int ab_ep_last_grid(int which) { return which == 0 || which == 1 ? g_last_grid[which] : -1; }
+
 // Argument blocks are passed as arrays of 64-bit words so the Python side needs
 // no struct mirror: ints[] carries the integer geometry, ptrs[] the addresses.
 //   ints: 0 rank, 1 world, 2 experts, 3 top_k, 4 hidden, 5 scale_group, 6 capacity, 7 value_fp8,
@@ -1373,6 +1377,7 @@ AB_EXPORT int ab_ep_dispatch(const int *ints, float amax_floor, const std::uint6
         if (p.routing != 1 && (p.ids_in == nullptr || p.weights_in == nullptr))
             return -1;
     }
+    g_last_grid[0] = grid;
     if (p.by_warp)
         ep_dispatch_kernel<true><<<grid, kThreads, 0, stream>>>(p);
     else
@@ -1423,7 +1428,8 @@ AB_EXPORT int ab_ep_combine(const int *ints, float amax_floor, const std::uint64
     p.trace = reinterpret_cast<unsigned long long *>(ptrs[i++]);
     if (p.weighted && p.expert_offsets == nullptr)
         return -1;
-    ep_combine_kernel<<<resident_grid(ep_combine_kernel, grid), kThreads, 0, stream>>>(p);
+    g_last_grid[1] = resident_grid(ep_combine_kernel, grid);
+    ep_combine_kernel<<<g_last_grid[1], kThreads, 0, stream>>>(p);
     return ab::launch_result("ep_combine");
 }
 

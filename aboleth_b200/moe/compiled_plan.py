@@ -31,6 +31,7 @@ class CompiledMoEPlan:
     return_launches: tuple
     forwarded_expert_output: bool
     removed_transfers: tuple[str, ...]
+    profile_max_lanes: tuple = ()       # (backend, lanes the matched endpoint profile allows), per partition
 
     def manifest(self) -> dict:
         s = self.spec
@@ -123,5 +124,7 @@ def compile_moe_plan(spec: MoESpec, world=None, *, profiles: Optional[dict[str, 
             phase, payload_bytes=s.capacity * row, max_items=s.capacity, partitions=partitions,
             profiles=profiles.values(), rank_count=s.ranks)) if partitions else ()
     removed = tuple(r["name"] for r in dataflow.removed)
+    limits = tuple((p.backend, min(p.max_lanes, available_lanes)) for p in profiles.values())
     return CompiledMoEPlan(spec, dataflow, storage, transport, launches["dispatch"], launches["return"],
-                           forwarded_expert_output="expert_copy" in removed, removed_transfers=removed)
+                           forwarded_expert_output="expert_copy" in removed, removed_transfers=removed,
+                           profile_max_lanes=limits)

@@ -24,7 +24,7 @@ class NativeMoEFamily:
                  slots: int = 1, owners: Optional[Sequence[int]] = None, tag: str = "moe-family",
                  value_type: str = "bf16", scale_group: int = 128, round_scale: bool = False,
                  quant_amax_floor: float = 1e-4, minimum_capacity: Optional[int] = None,
-                 decode_bound: Optional[int] = None):
+                 decode_bound: Optional[int] = None, profiles: Optional[dict] = None):
         self.world = world
         self.ranks = world.world_size
         self.capacity, self.hidden, self.top_k, self.experts = capacity, hidden, top_k, experts
@@ -38,11 +38,11 @@ class NativeMoEFamily:
             spec = MoESpec(capacity=variant.capacity, hidden=hidden, top_k=top_k, experts=experts,
                            ranks=self.ranks, value_type=value_type, scale_group=scale_group,
                            round_scale=round_scale, quant_amax_floor=quant_amax_floor)
-            self.plans[variant.capacity] = compile_moe_plan(spec, world)
+            self.plans[variant.capacity] = compile_moe_plan(spec, world, profiles=profiles)
             for slot in range(slots):
                 domain = self.family.control_domain(variant, slot)
                 self._slots[(variant.capacity, slot)] = NativeMoESlot.create(
-                    world, spec, tag=f"{tag}.{domain}",
+                    world, spec, tag=f"{tag}.{domain}", plan=self.plans[variant.capacity],
                     placement=list(owners) if owners is not None else "linear")
 
     def select(self, bound: int, slot: int = 0) -> NativeMoESlot:

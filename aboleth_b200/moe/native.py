@@ -69,6 +69,45 @@ def _align(n: int, a: int = 256) -> int:
     return (n + a - 1) // a * a
 
 
+@dataclass(frozen=True)
+class LaunchBinding:
+    """What the compiled plan of a shape variant decides about the executor's launches
+    (the reference binds grids, lanes, row slices, REUSE and the ready stride the same way:
+    python/aboleth/moe/native.py:193-289; in-place inputs :451-477; forwarded output :594-597).
+
+    The fused kernels are token-parallel rather than (peer, lane) programs, so a lane plan maps to
+    them as follows.  A dispatch that the planner fans out over every lane of its endpoint profile
+    is bandwidth-bound: one warp per token, token-ordered slots.  One that needs fewer lanes is
+    latency-bound: one CTA per token.  The combine gives ``sender_warps - 1`` warps of each CTA to
+    sending (the rest reduce) and publishes returned records in blocks of half a lane's row slice.
+    """
+
+    by_warp: bool
+    dispatch_lanes: int
+    return_lanes: int
+    send_warps: int
+    return_block: int
+    received_rows: int
+    borrow_tokens: bool          # the storage plan proved a prefix binding: read the caller's tensor in place
+    forward_expert_output: bool  # the expert stage writes the return source itself: no copy before the combine
+    profile: str
+
+    @classmethod
+    def from_plan(cls, spec: MoESpec, plan) -> "LaunchBinding":
+        dispatch, back = plan.dispatch_launches[0], plan.return_launches[0]
+        profile = dispatch.profile_identity
+        max_lanes = dict(plan.profile_max_lanes).get(dispatch.backend, dispatch.lanes)
+        rows_per_lane = max(1, spec.capacity // max(back.lanes, 1))
+        block = max(64, min(128, rows_per_lane // 2))
+        return cls(by_warp=dispatch.lanes >= max_lanes and dispatch.lanes > 1,
+                   dispatch_lanes=dispatch.lanes, return_lanes=back.lanes,
+                   send_warps=max(1, min(7, back.sender_warps - 1)),
+                   return_block=1 << (block.bit_length() - 1),
+                   received_rows=int(plan.storage["received_payload"]["physical_rows"]),
+                   borrow_tokens=bool(plan.storage.get("tokens", {}).get("prefix_binding", False)),
+                   forward_expert_output=bool(plan.forwarded_expert_output), profile=profile)
+
+
 @dataclass
 class DispatchResult:
     """What the expert stage consumes.  Rows are ``[ranks * capacity]``; rows of
@@ -84,6 +123,14 @@ class DispatchResult:
     recv_counts: torch.Tensor       # [ranks] int64
     topk_ids: torch.Tensor          # [capacity, k] int32 (this rank's tokens)
     topk_weights: torch.Tensor      # [capacity, k] fp32
+
+
+def _last_grid(which: int) -> int:
+    """CTAs of the last dispatch (0) or combine (1) launch of this thread."""
+    from ..ops._kernels import lib
+    fn = lib().ab_ep_last_grid
+    fn.restype, fn.argtypes = ctypes.c_int, [ctypes.c_int]
+    return int(fn(which))
 
 
 class MoEBuffers:
@@ -111,7 +158,8 @@ class MoEBuffers:
 
 class NativeMoESlot:
     def __init__(self, spec: MoESpec, rank: int, arena: torch.Tensor,
-                 peer_tables: dict[str, torch.Tensor], *, placement="linear", grid: Optional[int] = None):
+                 peer_tables: dict[str, torch.Tensor], *, placement="linear", grid: Optional[int] = None,
+                 plan=None):
         self.spec, self.rank = spec, int(rank)
         dev = arena.device
         self.device = dev
@@ -171,6 +219,23 @@ class NativeMoESlot:
         self._ints = (ctypes.c_int * 24)()
         self._ptrs = (ctypes.c_uint64 * 32)()
         self._table = None
+        self.launched: dict[str, dict] = {}   # what the last dispatch / combine actually launched
+        self.binding: Optional[LaunchBinding] = None
+        self._token_staging: Optional[torch.Tensor] = None
+        self._return_source: Optional[torch.Tensor] = None
+        if plan is not None:
+            self.bind_plan(plan)
+
+    def bind_plan(self, plan) -> LaunchBinding:
+        """Take the launch geometry and the buffer decisions from a compiled plan of this shape."""
+        binding = LaunchBinding.from_plan(self.spec, plan)
+        rows = self.spec.ranks * self.spec.capacity
+        if binding.received_rows != rows:
+            raise ValueError(f"the plan keeps {binding.received_rows} received rows, the slot was built for {rows}")
+        self.binding = binding
+        self.by_warp = binding.by_warp
+        self.send_warps, self.return_block = binding.send_warps, binding.return_block
+        return binding
 
     # -- construction over a World ------------------------------------------------
     @classmethod
@@ -200,7 +265,8 @@ class NativeMoESlot:
                   int(s.fp8), int(s.round_scale), 0, num_tokens, routing,
                   int(renormalize), phases, weighted, int(by_warp), self.return_block,
                   self.send_warps, self.block_counts.shape[0]]
-        self.last_launch = {"by_warp": bool(by_warp), "grid": self.grid, "phases": phases}
+        self.last_launch = {"by_warp": bool(by_warp), "requested_grid": self.grid, "phases": phases,
+                            "send_warps": self.send_warps, "return_block": self.return_block}
         for k, v in enumerate(values):
             i[k] = v
         return i
@@ -226,6 +292,13 @@ class NativeMoESlot:
             raise ValueError(f"{n} tokens exceed the slot capacity {s.capacity}")
         if tokens.dtype != torch.bfloat16 or tokens.shape[-1] != s.hidden or not tokens.is_contiguous():
             raise ValueError("tokens must be contiguous bf16 [n, hidden]")
+        if self.binding is not None and not self.binding.borrow_tokens:
+            # No prefix binding was proven for the token region: the kernel may not read the caller's
+            # tensor while the caller is free to overwrite it, so it gets a private copy.
+            if self._token_staging is None:
+                self._token_staging = torch.empty(s.capacity, s.hidden, dtype=torch.bfloat16, device=self.device)
+            self._token_staging[:n].copy_(tokens[:n])
+            tokens = self._token_staging
         routing = 1 if logits is not None else 0
         if routing:
             if logits.dtype != torch.float32 or logits.shape[-1] != s.experts:
@@ -242,6 +315,7 @@ class NativeMoESlot:
                     self.trace_buffer]
         call("ab_ep_dispatch", self._geometry(n, routing, renormalize, phases),
              ctypes.c_float(s.quant_amax_floor), self._fill(pointers), self.grid, stream_ptr())
+        self.launched["dispatch"] = {**self.last_launch, "tokens": n, "grid": _last_grid(0)}
         self._last_tokens = n
         return DispatchResult(self.recv_payload, self.expert_scales, self.expert_ids,
                               self.expert_weights, self.expert_pos, self.expert_counts,
@@ -267,6 +341,13 @@ class NativeMoESlot:
         if y.dtype != torch.bfloat16 or y.shape[-1] != s.hidden or not y.is_contiguous():
             raise ValueError("expert_output must be contiguous bf16 [rows, hidden]")
         out = self.final_output if out is None else out
+        if self.binding is not None and not self.binding.forward_expert_output:
+            # The plan could not forward the expert stage's destination into the return source:
+            # the residual copy the reference calls ``residual_expert_copy``.
+            if self._return_source is None or self._return_source.shape != y.shape:
+                self._return_source = torch.empty_like(y)
+            self._return_source.copy_(y)
+            y = self._return_source
         if expert_offsets is not None and tuple(expert_offsets.shape) != (s.ranks, s.experts):
             raise ValueError("expert_offsets must be int32 [ranks, experts] (one row per source rank)")
         t = self.peer_tables
@@ -276,6 +357,8 @@ class NativeMoESlot:
                     self.block_done, self.epoch, self.status, self.trace_buffer]
         call("ab_ep_combine", self._geometry(n, 0, False, phases, int(expert_offsets is not None)),
              ctypes.c_float(s.quant_amax_floor), self._fill(pointers), self.grid, stream_ptr())
+        self.launched["combine"] = {**self.last_launch, "tokens": n, "grid": _last_grid(1),
+                                    "weighted": expert_offsets is not None}
         return out[:n]
 
     def enable_trace(self) -> None:
@@ -317,8 +400,10 @@ class NativeMoESlot:
         return {"rank": self.rank, "ranks": s.ranks, "capacity": s.capacity, "hidden": s.hidden,
                 "top_k": s.top_k, "experts": s.experts, "value_type": s.value_type,
                 "metadata_words": s.metadata_words, "arena_bytes": self.buffers.nbytes,
-                "launches_per_layer": 2, "grid": self.grid, "return_block": self.return_block,
-                "send_warps": self.send_warps, "last_launch": getattr(self, "last_launch", None)}
+                "launches_per_layer": 2, "requested_grid": self.grid, "return_block": self.return_block,
+                "send_warps": self.send_warps,
+                "plan_binding": None if self.binding is None else vars(self.binding),
+                "launched": self.launched}
 
 
 class LocalMoEGroup:

@@ -11,6 +11,7 @@ from typing import Callable, Optional
 import torch
 
 from ..moe import DispatchResult, MoESpec, NativeMoESlot
+from ..moe.compiled_plan import compile_moe_plan
 from ..ops import expert_offsets, standin_expert
 from ..utils import host_range
 from ..world import World
@@ -21,7 +22,10 @@ ExpertFn = Callable[[DispatchResult, torch.Tensor], object]
 class ExpertParallelLayer:
     def __init__(self, world: World, spec: MoESpec, *, tag: str = "ep", grid: Optional[int] = None):
         self.world, self.spec = world, spec
-        self.slot = NativeMoESlot.create(world, spec, tag=tag, grid=grid)
+        # The compiled plan of this shape decides the launch geometry (latency or throughput path,
+        # sender warps, readiness block) and confirms that inputs and expert output need no copy.
+        self.plan = compile_moe_plan(spec, world)
+        self.slot = NativeMoESlot.create(world, spec, tag=tag, grid=grid, plan=self.plan)
         self._host_result = torch.zeros(4, dtype=torch.int64).pin_memory()
         self._staging: Optional[list] = None
         self._grouped: Optional[torch.Tensor] = None

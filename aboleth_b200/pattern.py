@@ -109,10 +109,22 @@ class PhaseResources:
     queue_capacity: int = 0
     buffer_depth: int = 1
     realization: Optional[P2PRealizationProfile] = None
+    # What the client's kernels can do; the schedule of every phase is chosen from these
+    # (reference: python/aboleth/pattern.py:628-790 ``PhaseResources``, 887-1079 selection).
+    direct_destination: bool = True            # an indexed transfer may write the final storage
+    fused_publication: bool = True             # the moving kernel can publish (last worker releases)
+    packed_doorbell: bool = False              # count and epoch travel in one 8-byte release store
+    coalesce_publication_wait: bool = True     # one kernel may publish and wait for several phases
+    coalesce_return_with_consumer: bool = False  # the consumer's prologue may publish and wait
+    consumer_grid_size: int = 0                # CTAs of that consumer (it needs one per peer)
+    iteration_count: int = 1                   # steps the plan is unrolled over (1: not cyclic)
+    parallel_threshold_bytes: int = 4096       # at or below this a phase rides in its producer
 
     def __post_init__(self):
         if self.available_lanes < 1 or self.buffer_depth < 1:
             raise ValueError("lanes and buffer depth must be positive")
+        if self.iteration_count < 1 or self.parallel_threshold_bytes < 0 or self.consumer_grid_size < 0:
+            raise ValueError("iteration count, threshold and consumer grid cannot be negative or zero-step")
 
 
 @dataclass(frozen=True)
@@ -159,37 +171,89 @@ class RegionRequirement:
     strides: tuple[int, ...]
 
 
+def _publication_for(profile_lookup, preferred: tuple[str, ...]) -> tuple[str, Optional[str]]:
+    """The first preferred publication strategy the client's kernels realise, with its kernel."""
+    for strategy in preferred:
+        try:
+            return strategy, profile_lookup(strategy)
+        except KeyError:
+            continue
+    raise ValueError(f"the realisation profile offers none of the publication strategies {preferred}")
+
+
 def _select_schedule(name: str, payload_bytes: int, backend: str, lanes: int, warps: int,
-                     resources: PhaseResources, buffers: tuple[str, ...]) -> PhaseSchedule:
+                     resources: PhaseResources, buffers: tuple[str, ...], *, per_item: bool = False,
+                     retargeted: bool = False) -> PhaseSchedule:
+    """How one phase is carried out.
+
+    ``per_item``: the phase moves indexed items (a workset), not one contiguous span.
+    ``retargeted``: the dataflow simplifier proved that the transfer may write the final storage.
+
+    Movement: a payload up to the threshold rides inside the kernel that produced it; an indexed
+    transfer with a legal direct destination is written in place by one kernel over the items;
+    anything else is a lane-parallel copy.  Publication, in order of preference and subject to
+    what the client's kernels offer: the moving kernel publishes itself (``fused_kernel``); count
+    and epoch share one release store (``packed_doorbell``); the consumer's prologue publishes and
+    waits (``consumer_prologue``: two ranks, a consumer grid that covers the peers); one kernel
+    publishes and waits for several phases (``coalesced_kernel``); or a kernel of its own
+    (``separate_kernel``).  Queue transports publish with their doorbell.
+    """
     peer_memory = backend == "p2p"
-    if payload_bytes <= INLINE_TRANSPORT_BYTES:
+    profile = resources.realization
+    publication_kernel: Optional[str] = None
+    grid_axes: tuple[str, ...] = ("peers", "lanes")
+    if payload_bytes <= resources.parallel_threshold_bytes:
         strategy, publication = "inline_transport", "inline"
-        why = f"{payload_bytes} B <= {INLINE_TRANSPORT_BYTES} B: the producing kernel carries it"
         kernel = f"{name}.producer"
-    elif peer_memory and lanes == 1:
-        strategy, publication = "direct_destination", "fused_kernel"
-        why = "peer memory, one lane: the producer writes the peer's storage and publishes"
-        kernel = (resources.realization.direct_destination_kernel if resources.realization
-                  else f"{name}.direct")
+        grid_axes = ("peers",)
+        why = f"{payload_bytes} B <= {resources.parallel_threshold_bytes} B: the producing kernel carries it"
+    elif not peer_memory:
+        strategy, publication = "parallel_copy", "packed_doorbell"
+        kernel = profile.parallel_copy_kernel if profile else f"{name}.copy"
+        why = f"{lanes} lanes post {payload_bytes} B to a queue; one doorbell per packed batch"
+    elif per_item and retargeted and resources.direct_destination:
+        strategy = "direct_destination"
+        kernel = profile.direct_destination_kernel if profile else f"{name}.direct"
+        grid_axes = ("items",)
+        preferred = (("packed_doorbell",) if resources.packed_doorbell else ()) + \
+            (("fused_kernel",) if resources.fused_publication else ()) + \
+            (("coalesced_kernel", "separate_kernel") if resources.coalesce_publication_wait
+             else ("separate_kernel", "coalesced_kernel"))
+        if profile:
+            publication, publication_kernel = _publication_for(profile.direct_publication_kernel, preferred)
+        else:
+            publication = preferred[0]
+        why = ("indexed items with unique destinations: written into the final storage in place; "
+               f"published by {publication.replace('_', ' ')}")
     else:
         strategy = "parallel_copy"
-        publication = "fused_kernel" if peer_memory else "packed_doorbell"
-        why = f"{lanes} lanes move {payload_bytes} B; " + (
-            "the last store of each lane is followed by its release" if peer_memory
-            else "one doorbell per packed batch")
-        kernel = (resources.realization.parallel_copy_kernel if resources.realization
-                  else f"{name}.copy")
+        kernel = profile.parallel_copy_kernel if profile else f"{name}.copy"
+        prologue = (not per_item and resources.coalesce_return_with_consumer and len(resources.peers) == 1
+                    and resources.consumer_grid_size >= max(len(resources.peers), 1))
+        preferred = (("fused_kernel",) if resources.fused_publication else ()) + \
+            (("consumer_prologue",) if prologue else ()) + \
+            (("coalesced_kernel", "separate_kernel") if resources.coalesce_publication_wait
+             else ("separate_kernel", "coalesced_kernel"))
+        if profile:
+            publication, publication_kernel = _publication_for(profile.parallel_publication_kernel, preferred)
+        else:
+            publication = preferred[0]
+        shape = "indexed items staged through a copy" if per_item else "one contiguous span per peer"
+        why = f"{lanes} lanes move {payload_bytes} B ({shape}); published by {publication.replace('_', ' ')}"
     coop = None
     if peer_memory and strategy != "inline_transport":
         per_lane = max(payload_bytes // max(lanes, 1), 256)
         coop = 32
         while coop < 4096 and coop * 8 < per_lane:
             coop *= 2
-    return PhaseSchedule(name=name, strategy=strategy, kernel=kernel, publication_kernel=None,
+    depth = resources.buffer_depth
+    if strategy == "parallel_copy" and not per_item and resources.iteration_count > 1:
+        depth = max(depth, 2)   # a cyclic plan refills one buffer while the other is read
+    return PhaseSchedule(name=name, strategy=strategy, kernel=kernel, publication_kernel=publication_kernel,
                          publication_strategy=publication, recycled_buffers=buffers,
-                         advanced_values=("epoch",), grid_axes=("peers", "lanes"),
+                         advanced_values=("epoch",), grid_axes=grid_axes,
                          payload_bytes=payload_bytes, block_elements=coop or 0, num_warps=warps,
-                         buffer_depth=resources.buffer_depth, rationale=why, p2p_coop_elements=coop)
+                         buffer_depth=depth, rationale=why, p2p_coop_elements=coop)
 
 
 @dataclass(frozen=True)
@@ -283,8 +347,11 @@ class CompiledPattern:
                                          reuse=resources.buffer_depth, buffer_slots=resources.buffer_depth,
                                          queue_capacity=resources.queue_capacity, lanes=lanes,
                                          payload_bytes=min(payload, 2 ** 31 - 1)))
+            retargeted = any(op["dst"] in str(r.get("why", "")) and "forwarded" in str(r.get("why", ""))
+                             for r in self.dataflow.removed)
             schedules[op["name"]] = _select_schedule(op["name"], payload, backends[0], lanes, warps,
-                                                     resources, (op["dst"],))
+                                                     resources, (op["dst"],), per_item=workset is not None,
+                                                     retargeted=retargeted)
         transport = plan_transport(dict(resources.peers), phases)
         return CompiledPatternPlan(self.name, self.dataflow, storage, transport, launches, schedules,
                                    self.bindings)

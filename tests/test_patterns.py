@@ -264,3 +264,50 @@ def test_binding_becomes_a_fragment_that_a_kernel_invokes():
     # A fragment may keep a reuse distance of its own instead of a planned interval.
     own = binding.to_fragment(program_id, reuse=2)
     assert "phase " not in own and " reuse=2" in own
+
+
+def test_publication_strategy_follows_resources_and_realisation():
+    """Every publication strategy is reachable, and which one a phase gets follows from what the
+    client's kernels offer (reference selection: python/aboleth/pattern.py:887-1079)."""
+    from aboleth_b200.pattern import P2PRealizationProfile, _select_schedule
+
+    profile = P2PRealizationProfile(
+        direct_destination_kernel="direct_k",
+        direct_publication_kernels=(("coalesced_kernel", "pub_k"), ("separate_kernel", "pub_k"),
+                                    ("packed_doorbell", None)),
+        parallel_copy_kernel="copy_k",
+        parallel_publication_kernels=(("fused_kernel", None), ("coalesced_kernel", "pub_k"),
+                                      ("consumer_prologue", None), ("separate_kernel", "pub_k")))
+    peers = {1: "p2p", 2: "p2p"}
+
+    def pick(resources, **facts):
+        return _select_schedule("phase", 1 << 20, "p2p", 4, 8, resources, ("dst",), **facts)
+
+    base = dict(peers=peers, realization=profile)
+    # indexed items with a proven direct destination: written in place
+    s = pick(ab.PhaseResources(**base), per_item=True, retargeted=True)
+    assert (s.strategy, s.kernel, s.publication_strategy, s.publication_kernel) == \
+        ("direct_destination", "direct_k", "coalesced_kernel", "pub_k")   # no fused form for direct writes here
+    s = pick(ab.PhaseResources(**base, coalesce_publication_wait=False), per_item=True, retargeted=True)
+    assert s.publication_strategy == "separate_kernel"
+    s = pick(ab.PhaseResources(**base, packed_doorbell=True), per_item=True, retargeted=True)
+    assert s.publication_strategy == "packed_doorbell" and s.publication_kernel is None
+    # the same items without the proof (or with direct writes disabled): staged parallel copy
+    s = pick(ab.PhaseResources(**base), per_item=True, retargeted=False)
+    assert (s.strategy, s.kernel, s.publication_strategy) == ("parallel_copy", "copy_k", "fused_kernel")
+    s = pick(ab.PhaseResources(**base, direct_destination=False, fused_publication=False),
+             per_item=True, retargeted=True)
+    assert (s.strategy, s.publication_strategy) == ("parallel_copy", "coalesced_kernel")
+    # contiguous spans: the consumer's prologue may take the publication over between two ranks
+    two = dict(peers={1: "p2p"}, realization=profile, fused_publication=False)
+    s = pick(ab.PhaseResources(**two, coalesce_return_with_consumer=True, consumer_grid_size=1))
+    assert s.publication_strategy == "consumer_prologue"
+    s = pick(ab.PhaseResources(**two, coalesce_return_with_consumer=True, consumer_grid_size=0))
+    assert s.publication_strategy == "coalesced_kernel"
+    # a cyclic plan double-buffers a contiguous copy; small payloads ride in their producer
+    assert pick(ab.PhaseResources(**base, iteration_count=8)).buffer_depth == 2
+    small = _select_schedule("phase", 512, "p2p", 1, 1, ab.PhaseResources(**base), ("dst",))
+    assert (small.strategy, small.publication_strategy) == ("inline_transport", "inline")
+    # queue transports publish with their doorbell
+    queued = _select_schedule("phase", 1 << 20, "proxy", 4, 8, ab.PhaseResources(peers={1: "proxy"}), ("dst",))
+    assert (queued.strategy, queued.publication_strategy) == ("parallel_copy", "packed_doorbell")
