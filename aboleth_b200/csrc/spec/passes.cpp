@@ -585,29 +585,95 @@ int order_publications(Program &p, const Options &o) {
 
 // ---- elide-epochs ------------------------------------------------------------------------------------
 
+// `expr` with every occurrence of the identifier `var` replaced by `(value)`.
+static std::string substitute_identifier(const std::string &expr, const std::string &var,
+                                         const std::string &value) {
+    std::string out;
+    for (std::size_t at = 0; at < expr.size();) {
+        const bool start = std::isalpha(static_cast<unsigned char>(expr[at])) || expr[at] == '_';
+        if (!start) {
+            out += expr[at++];
+            continue;
+        }
+        std::size_t end = at;
+        while (end < expr.size() && (std::isalnum(static_cast<unsigned char>(expr[end])) || expr[end] == '_'))
+            ++end;
+        const std::string word = expr.substr(at, end - at);
+        out += word == var ? "(" + value + ")" : word;
+        at = end;
+    }
+    return out;
+}
+
+// In a counted loop whose completion is polled only every k-th iteration, a signal published on
+// those iterations (and on the last) delivers every payload no later than the completion already
+// does; the other iterations' ordering points are dropped.  Receivers that wait for "at least
+// epoch e" see the same epochs, only later.  A CHECKED publication (compare-and-swap against the
+// epoch before it) then has to compare against the epoch LAST PUBLISHED rather than epoch - 1:
+// that value is carried through the loop in a variable set up in front of it and advanced whenever
+// the signal is published (reference: compiler/lib/Transforms/ElideEpochs.cpp:110-174, where the
+// value rides on an scf.for iteration argument).  A signal with an explicit `expected` is left
+// alone; so is a kernel that itself waits on a peer.
 int elide_epochs(Program &p, const Options &o) {
     if (!o.on("elide-epochs") || o.caps->load_store_addressable)
         return 0;
     if (contains_if(p.body, [](const Op &op) { return op.kind == "wait_signal"; }))
         return 0;  // a kernel that waits on peers must not skip what they wait for
-    int changed = 0;
-    walk(p.body, [&](Op &loop) {
-        if (loop.kind != "for" || loop.operands.size() != 3)
-            return;
-        // A planned poll in the loop body gives the predicate.
-        std::string pred;
-        for (const Op &op : loop.body)
-            if (op.kind == "poll" && op.has("planned") && op.get("pred") != "1")
-                pred = op.get("pred");
-        if (pred.empty())
-            return;
-        const std::string last = "((" + loop.operands[0] + ") == (" + loop.operands[2] + ") - 1)";
-        for (Op &op : loop.body) {
-            if (op.kind != "post_signal" || op.has("pred") || op.has("expected"))
+    int changed = 0, carried = 0;
+    for_each_block(p.body, [&](Block &block) {
+        for (std::size_t at = 0; at < block.size(); ++at) {
+            if (block[at].kind != "for" || block[at].operands.size() != 3)
                 continue;
-            op.attrs["pred"] = "(" + pred + " || " + last + ")";
-            op.attrs["elided"] = "";
-            ++changed;
+            std::vector<Op> setups;
+            {
+                Op &loop = block[at];
+                // A planned poll in the loop body gives the predicate.
+                std::string pred;
+                for (const Op &op : loop.body)
+                    if (op.kind == "poll" && op.has("planned") && op.get("pred") != "1")
+                        pred = op.get("pred");
+                if (pred.empty())
+                    continue;
+                const std::string last = "((" + loop.operands[0] + ") == (" + loop.operands[2] + ") - 1)";
+                const std::string due = "(" + pred + " || " + last + ")";
+                for (std::size_t j = 0; j < loop.body.size(); ++j) {
+                    if (loop.body[j].kind != "post_signal" || loop.body[j].has("pred") ||
+                        loop.body[j].has("expected"))
+                        continue;
+                    loop.body[j].attrs["pred"] = due;
+                    loop.body[j].attrs["elided"] = "";
+                    ++changed;
+                    if (loop.body[j].get("mode") != "SameQueueStrong")
+                        continue;
+                    // Checked: the epoch in the cell is the one this loop published last.
+                    const std::string name = "ab_published_" + std::to_string(carried++);
+                    const std::string epoch = loop.body[j].get("epoch");
+                    loop.body[j].attrs["expected"] = name;
+                    Op setup;
+                    setup.kind = "stmt";
+                    setup.line = loop.line;
+                    setup.operands = {"\"long long " + name + " = (" +
+                                      substitute_identifier(epoch, loop.operands[0], loop.operands[1]) +
+                                      ") - 1; (void)" + name + ";\""};
+                    setups.push_back(setup);
+                    Op advance;
+                    advance.kind = "stmt";
+                    advance.line = loop.body[j].line;
+                    advance.operands = {"\"if " + due + " " + name + " = (" + epoch + ");\""};
+                    // The value advances after the submission that carries the signal has read it.
+                    std::size_t where = j + 1;
+                    for (std::size_t k = j + 1; k < loop.body.size(); ++k)
+                        if (loop.body[k].kind == "submit" &&
+                            std::find(loop.body[k].operands.begin(), loop.body[k].operands.end(),
+                                      loop.body[j].result) != loop.body[k].operands.end()) {
+                            where = k + 1;
+                            break;
+                        }
+                    loop.body.insert(loop.body.begin() + where, advance);
+                }
+            }
+            block.insert(block.begin() + at, setups.begin(), setups.end());
+            at += setups.size();
         }
     });
     return changed;

@@ -11,6 +11,10 @@ extern "C" __global__ void stream_pipelined(unsigned long long payload, const un
     (void)WORLD;
     const unsigned long long v_e1 = endpoints[1] & ~7ull;
     (void)v_e1;
+    long long ab_published_0 = (((0) + 1)) - 1; (void)ab_published_0;
+    long long ab_published_1 = (((0) + 1)) - 1; (void)ab_published_1;
+    long long ab_published_2 = (((0) + 1)) - 1; (void)ab_published_2;
+    long long ab_published_3 = (((0) + 1)) - 1; (void)ab_published_3;
     for (long long round = 0; round < rounds; ++round) {
         const unsigned long long v_l2 = (unsigned long long)((payload + 0)) + (0);
         const unsigned v_l2_key = 0;
@@ -70,6 +74,10 @@ extern "C" __global__ void stream_pipelined(unsigned long long payload, const un
             cmds[7] = ((((((round) & 3) == 3) || ((round == rounds - 1))) || ((round) == (rounds) - 1))) ? abi::ProxyCommand{(unsigned long long)((round + 1)), v_r20, 8, 0, v_r20_key, abi::kProxyCommandStrongSignal} : abi::ProxyCommand{0, 0, 0, 0, 0, abi::kProxyCommandNop};
             t2::record(ab_status, proxy::submit(v_e1, cmds, 8, &seq_v_b3), 24577);
         }
+        if (((((round) & 3) == 3) || ((round == rounds - 1))) || ((round) == (rounds) - 1)) ab_published_3 = ((round + 1));
+        if (((((round) & 3) == 3) || ((round == rounds - 1))) || ((round) == (rounds) - 1)) ab_published_2 = ((round + 1));
+        if (((((round) & 3) == 3) || ((round == rounds - 1))) || ((round) == (rounds) - 1)) ab_published_1 = ((round + 1));
+        if (((((round) & 3) == 3) || ((round == rounds - 1))) || ((round) == (rounds) - 1)) ab_published_0 = ((round + 1));
         if (threadIdx.x == 0 && (((((round) & 3) == 3) || ((round == rounds - 1))))) t2::record(ab_status, proxy::poll(v_e1, seq_v_b3), 24833);
     }
     if (threadIdx.x == 0) t2::record(ab_status, proxy::drain(v_e1), 25090);

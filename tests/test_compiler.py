@@ -133,7 +133,19 @@ def test_coalescing_and_ordering_only_on_queue_transports():
 
 def test_elide_epochs_skips_kernels_that_wait_on_peers():
     prog = programs.stream("pipelined", 2, 256, reuse=4)
-    assert _compile(prog, "rdma").facts["elided_signals"] == 2
+    elided = _compile(prog, "rdma")
+    assert elided.facts["elided_signals"] == 2
+    # A checked publication compares against the epoch this loop published LAST: the value is set up in
+    # front of the loop (epoch of the first iteration, minus one) and advances after each published
+    # submission (reference: compiler/lib/Transforms/ElideEpochs.cpp:110-174).
+    lines = elided.ir.splitlines()
+    setup = next(i for i, l in enumerate(lines) if "long long ab_published_0 = (((0) + 1)) - 1" in l)
+    loop = next(i for i, l in enumerate(lines) if l.startswith("for round"))
+    signal = next(i for i, l in enumerate(lines) if "post_signal" in l and "expected=ab_published_0" in l)
+    submit = next(i for i, l in enumerate(lines) if "submit" in l and i > signal)
+    advance = next(i for i, l in enumerate(lines) if "ab_published_0 = ((round + 1))" in l)
+    assert setup < loop < signal < submit < advance
+    assert "expected=" not in _compile(prog, "rdma", passes="-elide-epochs").ir
     b = programs.stream("pipelined", 2, 256, reuse=4)
     b.wait_signal("payload", 1)
     assert _compile(b, "rdma").facts["elided_signals"] == 0
