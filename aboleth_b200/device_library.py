@@ -155,12 +155,18 @@ def generate_device_library(out: Path, *, transports: Sequence[str] = ("p2p",),
         shutil.rmtree(inc)
     shutil.copytree(include_dir(), inc)
     header = inc / "aboleth" / "device.cuh"
+    # The published header carries its options: it is marked as generated, and a specialised one
+    # pins its transport (the per-call kind test disappears; the other kind does not compile).
+    baked = "#define ABOLETH_TIER1_GENERATED 1\n"
     if specialize is not None:
-        # A specialised library makes other kinds a compile-time error instead of a status.
-        guard = ("\n// Specialised build: only '%s' endpoints are served.\n#define ABOLETH_TIER1_SPECIALIZED %d\n"
-                 % (specialize, abi.KIND_BITS[specialize]))
-        header.write_text(header.read_text().replace("#define ABOLETH_TIER1_ABI 2",
-                                                     "#define ABOLETH_TIER1_ABI 2" + guard))
+        baked += ("// Specialised build: only '%s' endpoints are served.\n#define ABOLETH_TIER1_SPECIALIZED %d\n"
+                  % (specialize, abi.KIND_BITS[specialize]))
+    header.write_text(header.read_text().replace("#define ABOLETH_TIER1_ABI 2",
+                                                 baked + "#define ABOLETH_TIER1_ABI 2", 1))
+    if specialize is not None:
+        transports = [t for t in transports if (t if t in SERVED else "proxy") == specialize]
+        if not transports:
+            raise ValueError(f"none of the requested transports is served by a library specialised for {specialize}")
     lanes = int(options.get("endpoints_per_peer", 1))
     if lanes != 1:
         header.write_text(header.read_text().replace(

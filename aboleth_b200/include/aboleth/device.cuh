@@ -39,12 +39,28 @@
 #endif
 
 #define ABOLETH_TIER1_ABI 2
+#ifndef ABOLETH_TIER1_GENERATED
+// 1 in a copy published by aboleth_b200.device_library (which bakes its options in), 0 in the tree.
 #define ABOLETH_TIER1_GENERATED 0
+#endif
 #define ABOLETH_TIER1_PUT_MANY 1
 #define ABOLETH_TIER1_PUT_SIGNAL 1
 #define ABOLETH_TIER1_PUT_MANY_FLUSH 1
+// ABOLETH_TIER1_SPECIALIZED pins the library to ONE transport: 1 = peer memory, 2 = host-proxy ring
+// (the kind bits of an endpoint handle).  A specialised library takes every handle to be of that
+// kind, so the per-call test of the kind bits is gone from every operation; the other kind's
+// HAS macro is 0 and asking for it at compile time (open_as<Kind>) does not compile.  Undefined:
+// both kinds are served and each call dispatches on the handle (reference: docs/TIERS.md:52-66).
+#ifdef ABOLETH_TIER1_SPECIALIZED
+#if ABOLETH_TIER1_SPECIALIZED != 1 && ABOLETH_TIER1_SPECIALIZED != 2
+#error "ABOLETH_TIER1_SPECIALIZED must be 1 (p2p) or 2 (proxy): no other transport is served directly"
+#endif
+#define ABOLETH_TIER1_HAS_P2P (ABOLETH_TIER1_SPECIALIZED == 1)
+#define ABOLETH_TIER1_HAS_PROXY (ABOLETH_TIER1_SPECIALIZED == 2)
+#else
 #define ABOLETH_TIER1_HAS_P2P 1
 #define ABOLETH_TIER1_HAS_PROXY 1
+#endif
 #define ABOLETH_TIER1_HAS_RDMA 0
 #define ABOLETH_TIER1_BOUNDED_WAITS 1
 #define ABOLETH_TIER1_SMALL_INLINE 1
@@ -97,6 +113,20 @@ struct PeerRef {
 };
 
 namespace detail {
+
+#ifdef ABOLETH_TIER1_SPECIALIZED
+inline constexpr std::uint32_t kOnlyKind = ABOLETH_TIER1_SPECIALIZED;
+#else
+inline constexpr std::uint32_t kOnlyKind = ~0u;  // both kinds, chosen per call
+#endif
+
+// Is this endpoint peer memory / the host ring?  Constant in a specialised library.
+__device__ __forceinline__ bool is_p2p(const PeerRef &ref) {
+    return kOnlyKind == ~0u ? detail::is_p2p(ref) : kOnlyKind == abi::kKindP2P;
+}
+__device__ __forceinline__ bool is_proxy(const PeerRef &ref) {
+    return kOnlyKind == ~0u ? detail::is_proxy(ref) : kOnlyKind == abi::kKindProxy;
+}
 
 __device__ __forceinline__ std::uint64_t globaltimer_ns() {
     std::uint64_t t;
@@ -227,6 +257,21 @@ __device__ __forceinline__ PeerRef open(const DeviceContext &ctx, int peer) {
     return PeerRef{raw & ~abi::kKindMask, static_cast<std::uint32_t>(raw & abi::kKindMask)};
 }
 
+// Does this build of the library serve endpoints of `Kind`?
+template <std::uint32_t Kind>
+inline constexpr bool kServes = detail::kOnlyKind == ~0u ? (Kind == abi::kKindP2P || Kind == abi::kKindProxy)
+                                                         : Kind == detail::kOnlyKind;
+
+// `open` for code that is written for one transport: it does not compile against a library that
+// was specialised for another.
+template <std::uint32_t Kind>
+__device__ __forceinline__ PeerRef open_as(const DeviceContext &ctx, int peer) {
+    static_assert(kServes<Kind>, "this Tier-1 library was specialised for another transport");
+    PeerRef ref = open(ctx, peer);
+    ref.kind = Kind;
+    return ref;
+}
+
 // ---- bounded receiver-side wait ------------------------------------------------
 
 // Wait until *flag >= epoch (epochs are monotonic, a later one satisfies an
@@ -259,13 +304,13 @@ __device__ __forceinline__ void wait_signal(
 __device__ __forceinline__ void put(
     const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
     const LocalRegion &src, std::uint32_t bytes) {
-    if (ref.kind == abi::kKindP2P) {
+    if (detail::is_p2p(ref)) {
         if (!detail::may_write(ctx, dst.address, bytes))
             return;
         detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
                              reinterpret_cast<const std::uint8_t *>(src.address),
                              bytes, 0, 1);
-    } else if (ref.kind == abi::kKindProxy) {
+    } else if (detail::is_proxy(ref)) {
         abi::ProxyCommand cmd{src.address, dst.address, bytes, src.key, dst.key,
                               abi::kProxyCommandWrite};
         detail::record(ctx, proxy::submit(ref.handle, &cmd, 1, nullptr));
@@ -284,11 +329,11 @@ __device__ __forceinline__ void put(
 __device__ __forceinline__ void put_inline(
     const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
     std::uint64_t value) {
-    if (ref.kind == abi::kKindP2P) {
+    if (detail::is_p2p(ref)) {
         if (!detail::may_write(ctx, dst.address, 8))
             return;
         detail::st_relaxed_sys(reinterpret_cast<std::uint64_t *>(dst.address), value);
-    } else if (ref.kind == abi::kKindProxy) {
+    } else if (detail::is_proxy(ref)) {
         // The ring carries an 8-byte inline value as a weak signal command.
         abi::ProxyCommand cmd{value, dst.address, 8, 0, dst.key,
                               abi::kProxyCommandWeakSignal};
@@ -310,7 +355,7 @@ __device__ __forceinline__ void put_inline_small(
     std::uint64_t value, int bytes) {
     if (bytes == 8) {
         put_inline(ctx, ref, dst, value);
-    } else if (ref.kind == abi::kKindP2P && bytes >= 1 && bytes <= 4) {
+    } else if (detail::is_p2p(ref) && bytes >= 1 && bytes <= 4) {
         volatile std::uint8_t *out = reinterpret_cast<volatile std::uint8_t *>(dst.address);
         for (int i = 0; i < bytes; ++i)
             out[i] = static_cast<std::uint8_t>(value >> (8 * i));
@@ -324,11 +369,11 @@ __device__ __forceinline__ void put_inline_small(
 __device__ __forceinline__ void signal(
     const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &flag,
     std::uint64_t epoch) {
-    if (ref.kind == abi::kKindP2P) {
+    if (detail::is_p2p(ref)) {
         if (!detail::may_write(ctx, flag.address, 8))
             return;
         detail::st_release_sys(reinterpret_cast<std::uint64_t *>(flag.address), epoch);
-    } else if (ref.kind == abi::kKindProxy) {
+    } else if (detail::is_proxy(ref)) {
         abi::ProxyCommand cmd{epoch, flag.address, 8, 0, flag.key,
                               abi::kProxyCommandStrongSignal};
         detail::record(ctx, proxy::submit(ref.handle, &cmd, 1, nullptr));
@@ -348,14 +393,14 @@ __device__ __forceinline__ void put_signal(
     const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
     const LocalRegion &src, std::uint32_t bytes, const RemoteRegion &flag,
     std::uint64_t epoch) {
-    if (ref.kind == abi::kKindP2P) {
+    if (detail::is_p2p(ref)) {
         if (!detail::may_write(ctx, dst.address, bytes) || !detail::may_write(ctx, flag.address, 8))
             return;
         detail::copy_strided(reinterpret_cast<std::uint8_t *>(dst.address),
                              reinterpret_cast<const std::uint8_t *>(src.address),
                              bytes, 0, 1);
         detail::st_release_sys(reinterpret_cast<std::uint64_t *>(flag.address), epoch);
-    } else if (ref.kind == abi::kKindProxy) {
+    } else if (detail::is_proxy(ref)) {
         abi::ProxyCommand cmds[2] = {
             {src.address, dst.address, bytes, src.key, dst.key, abi::kProxyCommandWrite},
             {epoch, flag.address, 8, 0, flag.key, abi::kProxyCommandStrongSignal}};
@@ -375,12 +420,12 @@ __device__ __forceinline__ void put_signal(
 // `count` puts as one batch; nothing is published.
 __device__ __forceinline__ void put_many(
     const DeviceContext &ctx, const PeerRef &ref, const PutDesc *descs, int count) {
-    if (ref.kind == abi::kKindP2P) {
+    if (detail::is_p2p(ref)) {
         for (int i = 0; i < count; ++i)
             detail::copy_strided(reinterpret_cast<std::uint8_t *>(descs[i].dst),
                                  reinterpret_cast<const std::uint8_t *>(descs[i].src),
                                  descs[i].bytes, 0, 1);
-    } else if (ref.kind == abi::kKindProxy) {
+    } else if (detail::is_proxy(ref)) {
         detail::record(ctx, proxy::submit_puts(ref.handle, descs, count, nullptr, 0, nullptr));
     } else {
         detail::record(ctx, Status::Malformed);
@@ -392,13 +437,13 @@ __device__ __forceinline__ void put_many(
 __device__ __forceinline__ void put_many_signal(
     const DeviceContext &ctx, const PeerRef &ref, const PutDesc *descs, int count,
     const RemoteRegion &flag, std::uint64_t epoch) {
-    if (ref.kind == abi::kKindP2P) {
+    if (detail::is_p2p(ref)) {
         for (int i = 0; i < count; ++i)
             detail::copy_strided(reinterpret_cast<std::uint8_t *>(descs[i].dst),
                                  reinterpret_cast<const std::uint8_t *>(descs[i].src),
                                  descs[i].bytes, 0, 1);
         detail::st_release_sys(reinterpret_cast<std::uint64_t *>(flag.address), epoch);
-    } else if (ref.kind == abi::kKindProxy) {
+    } else if (detail::is_proxy(ref)) {
         detail::record(ctx, proxy::submit_puts(ref.handle, descs, count, &flag, epoch, nullptr));
     } else {
         detail::record(ctx, Status::Malformed);
@@ -410,9 +455,9 @@ __device__ __forceinline__ void put_many_signal(
 // reusable and this is a no-op; on the ring it waits for the host to retire
 // the last batch this endpoint reserved.
 __device__ __forceinline__ void quiet(const DeviceContext &ctx, const PeerRef &ref) {
-    if (ref.kind == abi::kKindProxy)
+    if (detail::is_proxy(ref))
         detail::record(ctx, proxy::drain(ref.handle));
-    else if (ref.kind != abi::kKindP2P)
+    else if (!detail::is_p2p(ref))
         detail::record(ctx, Status::Malformed);
 }
 
@@ -433,7 +478,7 @@ __device__ __forceinline__ void put_many_flush(
 __device__ __forceinline__ void put_warp(
     const DeviceContext &ctx, const PeerRef &ref, const RemoteRegion &dst,
     const LocalRegion &src, std::uint32_t bytes) {
-    if (ref.kind != abi::kKindP2P) {
+    if (!detail::is_p2p(ref)) {
         if ((threadIdx.x & 31) == 0)
             put(ctx, ref, dst, src, bytes);
         __syncwarp();

@@ -146,3 +146,41 @@ def test_extern_symbol_table_and_prototype_header_link(tmp_path, monkeypatch):
                     "-o", str(tmp_path / "client")], check=True)
     with pytest.raises(ValueError, match="header-only"):
         frontends.link_flags(ab.device_library(transports=["p2p"]))
+
+
+def test_specialised_library_pins_its_transport_at_compile_time(tmp_path):
+    """A library specialised for peer memory compiles peer-memory clients, says so in its macros, and
+    refuses - at compile time - code written for the host ring (reference: docs/TIERS.md:52-66)."""
+    import shutil
+    import subprocess
+
+    from aboleth_b200.device_library import generate_device_library
+
+    nvcc = shutil.which("nvcc")
+    if nvcc is None:
+        pytest.skip("needs nvcc")
+    lib = generate_device_library(tmp_path / "p2p", transports=["p2p"], specialize="p2p")
+    text = lib.header.read_text()
+    assert "#define ABOLETH_TIER1_GENERATED 1" in text and "#define ABOLETH_TIER1_SPECIALIZED 1" in text
+    client = tmp_path / "client.cu"
+    body = '''#include "aboleth/device.cuh"
+static_assert(ABOLETH_TIER1_GENERATED == 1 && ABOLETH_TIER1_HAS_P2P == 1 && ABOLETH_TIER1_HAS_PROXY == 0, "macros");
+static_assert(aboleth::kServes<aboleth::abi::kKindP2P> && !aboleth::kServes<aboleth::abi::kKindProxy>, "kinds");
+__global__ void k(const std::uint64_t *eps, unsigned long long dst, unsigned long long src, unsigned long long flag) {
+    aboleth::DeviceContext ctx{eps, nullptr};
+    const aboleth::PeerRef ref = aboleth::open_as<aboleth::abi::%s>(ctx, 1);
+    aboleth::put_signal(ctx, ref, aboleth::RemoteRegion{dst, 0}, aboleth::LocalRegion{src, 0}, 64,
+                        aboleth::RemoteRegion{flag, 0}, 1);
+}
+'''
+    compile_cmd = [nvcc, *lib.nvcc_flags(), "-c", str(client), "-o", str(tmp_path / "client.o")]
+    client.write_text(body % "kKindP2P")
+    assert subprocess.run(compile_cmd, capture_output=True, text=True).returncode == 0
+    client.write_text((body % "kKindProxy").replace("ABOLETH_TIER1_HAS_PROXY == 0", "true"))
+    refused = subprocess.run(compile_cmd, capture_output=True, text=True)
+    assert refused.returncode != 0 and "specialised for another transport" in refused.stderr
+    # the tree's own header is the unspecialised, not-generated form
+    unspecialised = generate_device_library(tmp_path / "both", transports=["p2p", "proxy"])
+    assert "#define ABOLETH_TIER1_SPECIALIZED" not in unspecialised.header.read_text().split("#ifdef ABOLETH_TIER1_SPECIALIZED")[0]
+    with pytest.raises(ValueError, match="none of the requested transports"):
+        generate_device_library(tmp_path / "bad", transports=["p2p"], specialize="proxy")
