@@ -12,6 +12,7 @@
 #include <algorithm>
 #include <cstdlib>
 
+#include "gemm_mx_sm100.cuh"
 #include "gemm_pair_sm100.cuh"
 
 namespace {
@@ -232,6 +233,58 @@ int launch_pair(const void *a, const void *b, PlainPolicy p, int lda, int ldb, u
     return ab::launch_result(Op::kBK == 64 ? "gemm_bf16 (CTA pairs)" : "gemm_e4m3 (CTA pairs)");
 }
 
+// Block-scaled e4m3 GEMM, one CTA per 128 x 256 tile (gemm_mx_sm100.cuh).
+struct MxPolicy : PlainPolicy {
+    static constexpr bool kBackground = false, kDrainedHook = false, kScaled = false;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                              const __grid_constant__ CUtensorMap map_b,
+                                                              MxPolicy policy, mx::ScaleFactors sf,
+                                                              unsigned long long *status) {
+    mx::gemm_mx_mainloop(policy, &map_a, &map_b, sf, status);
+}
+
+// The exponent byte (ue8m0) of a positive power-of-two fp32; anything else is reported.
+__device__ __forceinline__ unsigned ue8m0_of(float scale, unsigned long long *status, unsigned detail) {
+    const unsigned bits = __float_as_uint(scale);
+    if ((bits & 0x807fffffu) != 0 || (bits >> 23) == 0 || (bits >> 23) == 255)
+        ab::set_status(status, aboleth::Status::Malformed, detail);
+    return (bits >> 23) & 0xffu;
+}
+
+// Activation scales fp32 [rows, k_blocks] (one per row and 128 K) -> atoms [row block][K block] of 512
+// bytes: byte (r % 32) * 16 + (r / 32) * 4 + s for row r of the block, the same value for s = 0..3.
+__global__ void pack_scales_a_kernel(const float *scales, long long ld, std::uint32_t *out, int rows,
+                                     int k_blocks, unsigned long long *status) {
+    const int row_blocks = (rows + 127) / 128;
+    const long long total = static_cast<long long>(row_blocks) * k_blocks * 128;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(i % 128);
+        const long long atom = i / 128;           // row_block * k_blocks + kb
+        const int kb = static_cast<int>(atom % k_blocks);
+        const int row = static_cast<int>(atom / k_blocks) * 128 + r;
+        const unsigned e = row < rows ? ue8m0_of(scales[row * ld + kb], status, 0x3500) : 127u;
+        out[atom * 128 + (r % 32) * 4 + r / 32] = e * 0x01010101u;
+    }
+}
+
+// Weight scales fp32 [n_blocks, k_blocks] (one per 128 x 128 block) -> atoms [K block][column block],
+// `b_blocks` (even, >= n_blocks) per K block; all 512 bytes of an atom carry its block's scale.
+__global__ void pack_scales_b_kernel(const float *scales, long long ld, std::uint32_t *out, int n_blocks,
+                                     int b_blocks, int k_blocks, unsigned long long *status) {
+    const long long total = static_cast<long long>(k_blocks) * b_blocks * 128;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long atom = i / 128;           // kb * b_blocks + nb
+        const int nb = static_cast<int>(atom % b_blocks);
+        const int kb = static_cast<int>(atom / b_blocks);
+        const unsigned e = nb < n_blocks ? ue8m0_of(scales[nb * ld + kb], status, 0x3501) : 127u;
+        out[i] = e * 0x01010101u;
+    }
+}
+
 }  // namespace
 
 // C[M,N] = A[M,K] * B[N,K]^T, all bf16 row-major, lda/ldb/ldc in elements.
@@ -291,4 +344,64 @@ AB_EXPORT int ab_grouped_gemm_bf16(const void *a, const void *w, void *c, const 
     if (total_rows / experts >= 512)
         return launch_grouped<2>(a, w, c, counts, offsets, experts, total_rows, n, k, status, stream);
     return launch_grouped<1>(a, w, c, counts, offsets, experts, total_rows, n, k, status, stream);
+}
+
+// Bytes of the packed scale factors of a block-scaled GEMM: A atoms for `m` rows, B atoms for `n` columns.
+AB_EXPORT long long ab_mx_scale_bytes(int m, int n, int k, int which) {
+    const long long k_blocks = (k + 127) / 128;
+    if (which == 0)
+        return static_cast<long long>((m + 127) / 128) * k_blocks * 512;
+    const long long b_blocks = static_cast<long long>((n + 255) / 256) * 2;
+    return k_blocks * b_blocks * 512;
+}
+
+// fp32 power-of-two scales -> ue8m0 atoms in the order the tensor core reads them.  which = 0: activation
+// scales [rows, K/128] (one per row and K block); which = 1: weight scales [ceil(rows/128), K/128].  A scale
+// that is not a positive power of two is reported as Malformed in `status` (the product would be wrong).
+AB_EXPORT int ab_mx_pack_scales(const float *scales, long long ld, void *out, int rows, int k, int which,
+                                unsigned long long *status, cudaStream_t stream) {
+    if (scales == nullptr || out == nullptr || rows < 1 || k < 128 || k % 128)
+        return -1;
+    const int k_blocks = k / 128;
+    if (which == 0) {
+        pack_scales_a_kernel<<<148, 256, 0, stream>>>(scales, ld, static_cast<std::uint32_t *>(out), rows,
+                                                      k_blocks, status);
+    } else {
+        const int n_blocks = (rows + 127) / 128, b_blocks = (rows + 255) / 256 * 2;
+        pack_scales_b_kernel<<<148, 256, 0, stream>>>(scales, ld, static_cast<std::uint32_t *>(out), n_blocks,
+                                                      b_blocks, k_blocks, status);
+    }
+    return ab::launch_result("mx_pack_scales");
+}
+
+// C[M,N] (bf16) = (A * sa) (B * sb)^T for e4m3 A [M,K] and B [N,K] (row-major, lda / ldb in bytes) whose
+// scales were packed by ab_mx_pack_scales: tcgen05.mma.kind::mxf8f6f4.block_scale, no expansion pass.
+// K must be a multiple of 128.
+AB_EXPORT int ab_gemm_e4m3_mx(const void *a, const void *b, void *c, const void *sfa, const void *sfb, int m,
+                              int n, int k, int lda, int ldb, int ldc, unsigned long long *status,
+                              cudaStream_t stream) {
+    if (m < 1 || n < 1 || k < 128 || k % 128 || lda % 16 || ldb % 16 || ldc % 8 || sfa == nullptr ||
+        sfb == nullptr ||
+        (reinterpret_cast<std::uintptr_t>(a) | reinterpret_cast<std::uintptr_t>(b) |
+         reinterpret_cast<std::uintptr_t>(c) | reinterpret_cast<std::uintptr_t>(sfa) |
+         reinterpret_cast<std::uintptr_t>(sfb)) & 15)
+        return -1;
+    MxPolicy p{};
+    p.c = static_cast<__nv_bfloat16 *>(c);
+    p.m = m, p.n = n, p.k = k, p.ldc = ldc;
+    p.tiles_n = (n + BN - 1) / BN;
+    p.pair = 0, p.rows = BM, p.bk = mx::kBlockK, p.alpha = 1.0f;
+    p.tiles_total = ((m + BM - 1) / BM) * p.tiles_n;
+    const long long column_bytes = static_cast<long long>(BN) * k;
+    p.group_n = static_cast<int>(std::max(1LL, std::min<long long>(p.tiles_n, (48LL << 20) / column_bytes)));
+    CUtensorMap map_a, map_b;
+    if (!make_map_e4m3(&map_a, a, m, k, lda, BM) || !make_map_e4m3(&map_b, b, n, k, ldb, BN))
+        return -2;
+    if (!configure(gemm_mx_kernel, mx::kSmemBytes))
+        return -3;
+    const mx::ScaleFactors sf{static_cast<const std::uint8_t *>(sfa), static_cast<const std::uint8_t *>(sfb),
+                              k / 128, (n + 255) / 256 * 2};
+    const int grid = p.tiles_total < sm_count() ? p.tiles_total : sm_count();
+    gemm_mx_kernel<<<grid, kThreads, mx::kSmemBytes, stream>>>(map_a, map_b, p, sf, status);
+    return ab::launch_result("gemm_e4m3_mx");
 }

@@ -107,17 +107,78 @@ def dequant_block_scaled(q: torch.Tensor, scales: torch.Tensor, *, block: tuple[
     return out
 
 
+declare("ab_mx_pack_scales", [_VP, ctypes.c_longlong, _VP, _I, _I, _I, _VP, _VP])
+declare("ab_gemm_e4m3_mx", [_VP] * 5 + [_I] * 6 + [_VP, _VP])
+
+
+def pack_scales_mx(scales: torch.Tensor, rows: int, k: int, *, weight: bool) -> torch.Tensor:
+    """Power-of-two fp32 block scales -> the ue8m0 scale-factor atoms the block-scaled MMA reads.
+
+    ``weight=False``: ``scales`` is ``[rows, k / 128]`` (one scale per row and 128-K block, what
+    ``quant_fp8(round_scale=True)`` and the dispatch kernel produce; a strided view is fine).
+    ``weight=True``: ``scales`` is ``[ceil(rows / 128), k / 128]`` (one per 128 x 128 block).  A weight's
+    packed scales can be kept and reused.  A scale that is not a positive power of two is reported
+    through :func:`check_gemm_status` (status 3), because ue8m0 cannot carry it.
+    """
+    assert scales.dtype == torch.float32 and scales.dim() == 2 and scales.stride(1) == 1 and k % 128 == 0
+    assert scales.shape == ((-(-rows // 128) if weight else rows), k // 128), tuple(scales.shape)
+    lib_bytes = _mx_scale_bytes(rows, rows, k, 1 if weight else 0)
+    out = torch.empty(lib_bytes, dtype=torch.uint8, device=scales.device)
+    call("ab_mx_pack_scales", ptr(scales), scales.stride(0), ptr(out), rows, k, int(weight),
+         ptr(gemm_status(scales.device)), stream_ptr())
+    return out
+
+
+def _mx_scale_bytes(m: int, n: int, k: int, which: int) -> int:
+    from ._kernels import lib
+    fn = lib().ab_mx_scale_bytes
+    fn.restype, fn.argtypes = ctypes.c_longlong, [ctypes.c_int] * 4
+    return int(fn(m, n, k, which))
+
+
+def gemm_e4m3_mx(a: torch.Tensor, a_packed: torch.Tensor, b: torch.Tensor, b_packed: torch.Tensor,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[M, N] = (a * sa) @ (b * sb).T`` for e4m3 operands with packed ue8m0 scales
+    (:func:`pack_scales_mx`): ``tcgen05.mma.kind::mxf8f6f4.block_scale``, the scales are applied by the
+    tensor core, nothing is expanded.  K must be a multiple of 128."""
+    assert a.dtype == b.dtype == torch.float8_e4m3fn and a.is_cuda and a.dim() == b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1 and a.shape[1] == b.shape[1] and a.shape[1] % 128 == 0
+    m, k = a.shape
+    n = b.shape[0]
+    assert a_packed.numel() == _mx_scale_bytes(m, n, k, 0) and b_packed.numel() == _mx_scale_bytes(m, n, k, 1)
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (m, n)
+    call("ab_gemm_e4m3_mx", ptr(a), ptr(b), ptr(out), ptr(a_packed), ptr(b_packed), m, n, k, a.stride(0),
+         b.stride(0), out.stride(0), ptr(gemm_status(a.device)), stream_ptr())
+    return out
+
+
 def gemm_e4m3_block_scaled(a: torch.Tensor, a_scales: torch.Tensor, b: torch.Tensor, b_scales: torch.Tensor, *,
                            a_block: tuple[int, int] = (1, 128), b_block: tuple[int, int] = (128, 128),
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           out: Optional[torch.Tensor] = None, path: str = "mx",
+                           b_packed: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[M, N] = (a * a_scales) @ (b * b_scales).T`` for block-scaled e4m3 operands (1 x 128
-    activation scales, 128 x 128 weight scales by default); bf16 output, fp32 accumulation.
+    activation scales, 128 x 128 weight scales); bf16 output, fp32 accumulation.
 
-    The operands are expanded to bf16 by :func:`dequant_block_scaled` and multiplied by the
-    tcgen05 bf16 GEMM: the result carries the block scales exactly (for power-of-two scales) at
-    bf16 tensor-core rate and fp8 storage.  A weight that is used repeatedly should be expanded
-    once with :func:`dequant_block_scaled` and passed to :func:`gemm_bf16`.
+    ``path="mx"`` (default): the scales go to the tensor core as ue8m0 and the product runs at the
+    fp8 rate (:func:`gemm_e4m3_mx`).  It needs power-of-two scales (``quant_fp8(round_scale=True)``),
+    the default block shapes and K a multiple of 128; pass a weight's ``b_packed`` scales to skip its
+    packing.  ``path="expand"``: the operands are expanded to bf16 by :func:`dequant_block_scaled` and
+    multiplied by the bf16 GEMM - any positive scales, any block shape, bf16 rate and one more pass
+    over the operands.
     """
     assert a.shape[1] == b.shape[1]
-    return gemm_bf16(dequant_block_scaled(a, a_scales, block=a_block),
-                     dequant_block_scaled(b, b_scales, block=b_block), out)
+    if path == "expand":
+        return gemm_bf16(dequant_block_scaled(a, a_scales, block=a_block),
+                         dequant_block_scaled(b, b_scales, block=b_block), out)
+    if path != "mx":
+        raise ValueError("path must be 'mx' or 'expand'")
+    if tuple(a_block) != (1, 128) or tuple(b_block) != (128, 128) or a.shape[1] % 128:
+        raise ValueError("the tensor-core path takes 1 x 128 activation and 128 x 128 weight scales and K % 128 == 0")
+    m, k = a.shape
+    n = b.shape[0]
+    a_packed = pack_scales_mx(a_scales, m, k, weight=False)
+    if b_packed is None:
+        b_packed = pack_scales_mx(b_scales, n, k, weight=True)
+    return gemm_e4m3_mx(a, a_packed, b, b_packed, out)

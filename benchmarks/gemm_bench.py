@@ -80,29 +80,45 @@ def main() -> int:
             rows.append(row)
             del x, w, y
     elif args.block_scaled:
-        from aboleth_b200.ops import dequant_block_scaled, gemm_e4m3_block_scaled, quant_fp8
+        from aboleth_b200.ops import (dequant_block_scaled, gemm_e4m3_block_scaled, gemm_e4m3_mx, pack_scales_mx,
+                                      quant_fp8)
 
-        hbm = load_measured_peaks().get("hbm_gbs", 6650.0)
         for m, n, k in ([tuple(args.shape)] if args.shape else DENSE):
-            a_q, a_s = quant_fp8(torch.randn(m, k, device="cuda").to(torch.bfloat16), round_scale=True)
+            x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+            a_q, a_s = quant_fp8(x, round_scale=True)
             b_q = (torch.randn(n, k, device="cuda")).to(torch.float8_e4m3fn)
             b_s = torch.full((-(-n // 128), k // 128), 2.0 ** -6, device="cuda")
-            a_bf = torch.empty(m, k, dtype=torch.bfloat16, device="cuda")
             c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
-            expand_ms = timed(lambda: dequant_block_scaled(a_q, a_s, out=a_bf), flush, args.steps)
-            whole_ms = timed(lambda: gemm_e4m3_block_scaled(a_q, a_s, b_q, b_s, out=c), flush, args.steps)
+            b_packed = pack_scales_mx(b_s, n, k, weight=True)      # a weight's scales are packed once
+            a_packed = pack_scales_mx(a_s, m, k, weight=False)
+            # the MMA alone, and with the per-call packing of the activation scales
+            mma_ms = timed(lambda: gemm_e4m3_mx(a_q, a_packed, b_q, b_packed, c), flush, args.steps)
+            whole_ms = timed(lambda: gemm_e4m3_block_scaled(a_q, a_s, b_q, b_s, out=c, b_packed=b_packed),
+                             flush, args.steps)
+            # the same product by expansion to bf16 (weight expanded once) and the plain bf16 kernel
             w_bf = dequant_block_scaled(b_q, b_s, block=(128, 128))
-            cached_ms = timed(lambda: gemm_bf16(dequant_block_scaled(a_q, a_s, out=a_bf), w_bf, c), flush, args.steps)
+            a_bf = torch.empty(m, k, dtype=torch.bfloat16, device="cuda")
+            expand_ms = timed(lambda: gemm_bf16(dequant_block_scaled(a_q, a_s, out=a_bf), w_bf, c), flush, args.steps)
+            bf16_ms = timed(lambda: gemm_bf16(x, w_bf, c), flush, args.steps)
             check_gemm_status("cuda")
             flops = 2.0 * m * n * k
-            moved = m * k * 3 + a_s.numel() * 4  # one byte read, two written per element
-            rows.append({"m": m, "n": n, "k": k, "dtype": "e4m3 block-scaled (bf16 math)",
-                         "expand_activations_us": expand_ms * 1e3, "expand_gbs": moved / expand_ms / 1e6,
-                         "expand_frac_of_measured_copy": moved / expand_ms / 1e6 / hbm,
-                         "both_operands_expanded_us": whole_ms * 1e3, "both_tflops": flops / whole_ms / 1e9,
-                         "weight_expanded_once_us": cached_ms * 1e3, "weight_once_tflops": flops / cached_ms / 1e9,
-                         "weight_once_frac_of_measured": flops / cached_ms / 1e9 / peak})
-            del a_q, a_s, b_q, b_s, a_bf, w_bf, c
+            row = {"m": m, "n": n, "k": k, "dtype": "e4m3 block-scaled (1x128 / 128x128, ue8m0 in tensor memory)",
+                   "mx_mma_us": mma_ms * 1e3, "mx_mma_tflops": flops / mma_ms / 1e9,
+                   "mx_with_scale_packing_us": whole_ms * 1e3, "mx_with_packing_tflops": flops / whole_ms / 1e9,
+                   "expanded_to_bf16_us": expand_ms * 1e3, "expanded_tflops": flops / expand_ms / 1e9,
+                   "bf16_kernel_us": bf16_ms * 1e3, "bf16_kernel_tflops": flops / bf16_ms / 1e9,
+                   "mx_over_bf16_kernel": bf16_ms / mma_ms, "mx_over_expansion": expand_ms / whole_ms,
+                   "mx_frac_of_measured_bf16_peak": flops / mma_ms / 1e9 / peak}
+            if not args.no_library:
+                # the library's fp8 GEMM (per-tensor scales: the closest form torch exposes here)
+                one = torch.ones((), device="cuda")
+                lib_ms = timed(lambda: torch._scaled_mm(a_q, b_q.t(), scale_a=one, scale_b=one,
+                                                        out_dtype=torch.bfloat16), flush, args.steps)
+                row.update({"cublaslt_fp8_per_tensor_us": lib_ms * 1e3,
+                            "cublaslt_fp8_per_tensor_tflops": flops / lib_ms / 1e9,
+                            "mx_vs_cublaslt_fp8": lib_ms / mma_ms})
+            rows.append(row)
+            del x, a_q, a_s, b_q, b_s, a_bf, w_bf, c, a_packed, b_packed
     elif args.fp8:
         from aboleth_b200.ops import gemm_e4m3
 

@@ -134,12 +134,49 @@ def test_block_scaled_e4m3_gemm_matches_fp32(m, n, k, pow2):
     if pow2:  # nothing was rounded
         assert torch.equal(a_deq.float(), a_q.float() * a_full)
 
-    out = gemm_e4m3_block_scaled(a_q, a_s, b_q, b_s.contiguous())
+    # Power-of-two scales go to the tensor core as ue8m0 (no expansion); others take the expansion.
+    out = gemm_e4m3_block_scaled(a_q, a_s, b_q, b_s.contiguous(), path="mx" if pow2 else "expand")
     torch.cuda.synchronize()
     check_gemm_status(out.device)
     want = (a_q.float() * a_full) @ (b_q.float() * b_full).t()
     assert _rel_err(out, want) < 5e-3
+    if pow2:
+        # fp32 accumulation of exact products of e4m3 values and power-of-two scales: the two paths
+        # differ only in the order of additions
+        other = gemm_e4m3_block_scaled(a_q, a_s, b_q, b_s.contiguous(), path="expand")
+        torch.cuda.synchronize()
+        assert _rel_err(out, other.float()) < 2e-3
     # A strided view (rows of a wider buffer) goes through the same kernel.
     wide = torch.zeros(m, k + 64, dtype=torch.float8_e4m3fn, device="cuda")
     wide[:, :k] = a_q
     assert torch.equal(dequant_block_scaled(wide[:, :k], a_s), a_deq)
+
+
+def test_block_scaled_mx_gemm_is_exact_on_integers_and_flags_bad_scales():
+    """Small integers and power-of-two scales: every product and partial sum is exact, so the
+    tensor-core path must reproduce the fp32 result bit for bit (after the bf16 rounding of the
+    output) - this pins the scale-factor layout: a wrong row or K segment changes the sum."""
+    from aboleth_b200.ops import check_gemm_status, gemm_e4m3_block_scaled
+    from aboleth_b200.ops.gemm import gemm_status
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    m, n, k = 300, 640, 512      # partial row tile, 2.5 column tiles, four K blocks
+    a = torch.randint(-2, 3, (m, k), generator=g, device="cuda").float()
+    b = torch.randint(-2, 3, (n, k), generator=g, device="cuda").float()
+    a_s = torch.exp2(torch.randint(-3, 4, (m, k // 128), generator=g, device="cuda").float())
+    b_s = torch.exp2(torch.randint(-3, 4, (-(-n // 128), k // 128), generator=g, device="cuda").float())
+    a_q, b_q = a.to(torch.float8_e4m3fn), b.to(torch.float8_e4m3fn)
+    out = gemm_e4m3_block_scaled(a_q, a_s, b_q, b_s)
+    torch.cuda.synchronize()
+    check_gemm_status(out.device)
+    a_full = a_s.repeat_interleave(128, dim=1)
+    b_full = b_s.repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)
+    want = ((a * a_full) @ (b * b_full).t()).to(torch.bfloat16)
+    assert torch.equal(out, want)
+    # a scale that is not a power of two cannot be carried as ue8m0: reported, not silently rounded
+    bad = a_s.clone()
+    bad[5, 1] = 0.3
+    gemm_e4m3_block_scaled(a_q, bad, b_q, b_s)
+    torch.cuda.synchronize()
+    assert gemm_status(out.device)[:2].tolist() == [3, 0x3500]
+    gemm_status(out.device).zero_()
