@@ -233,16 +233,115 @@ int launch_pair(const void *a, const void *b, PlainPolicy p, int lda, int ldb, u
     return ab::launch_result(Op::kBK == 64 ? "gemm_bf16 (CTA pairs)" : "gemm_e4m3 (CTA pairs)");
 }
 
-// Block-scaled e4m3 GEMM, one CTA per 128 x 256 tile (gemm_mx_sm100.cuh).
-struct MxPolicy : PlainPolicy {
+// Block-scaled e4m3 GEMM, one CTA per tile of `rows` x `cols` (gemm_mx_sm100.cuh): the plain
+// policy's raster order with this loop's tile shape.
+struct MxPolicy {
     static constexpr bool kBackground = false, kDrainedHook = false, kScaled = false;
+    __nv_bfloat16 *c;
+    int m, n, k, ldc;
+    int rows, cols;   // tile shape
+    int tiles_n, tiles_total, group_n;
+
+    __device__ __forceinline__ bool next(int it, Tile &t) const {
+        const int idx = blockIdx.x + it * gridDim.x;
+        if (idx >= tiles_total)
+            return false;
+        const int tiles_m = tiles_total / tiles_n;
+        const int per_group = group_n * tiles_m;
+        const int group = idx / per_group;
+        const int width = min(group_n, tiles_n - group * group_n);
+        const int local = idx - group * per_group;
+        const int tm = local / width, tn = group * group_n + (local - tm * width);
+        t.a_row = tm * rows;
+        t.b_row = tn * cols;
+        t.k_blocks = k / mx::kBlockK;
+        t.c_row = tm * rows;
+        t.c_col = tn * cols;
+        t.rows_valid = min(rows, m - tm * rows);
+        t.cols_valid = min(cols, n - tn * cols);
+        t.tag = 0;
+        t.a_sel = 0;
+        return true;
+    }
+    __device__ __forceinline__ bool ready(const Tile &) const { return true; }
+    __device__ __forceinline__ void store16(const Tile &t, int row, int col, const uint4 &v) const {
+        *reinterpret_cast<uint4 *>(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col) = v;
+    }
+    __device__ __forceinline__ void tile_done(const Tile &) const {}
+    __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
 };
 
+// Grouped block-scaled GEMM: GroupedPolicy's tile order with the block-scaled loop's tile shape.  An
+// expert's rows must start on a multiple of 128 (a scale-factor atom covers 128 rows); a start that does
+// not is reported as Malformed and ends the CTA's work.
+template <int HALVES>
+struct GroupedMxPolicy {
+    static constexpr int kRows = BM * HALVES, kCols = mx::MxGeometry<HALVES>::kCols;
+    static constexpr bool kBackground = false, kDrainedHook = false, kScaled = false;
+    __nv_bfloat16 *c;
+    const int *counts, *offsets;
+    unsigned long long *status;
+    int experts, n, k, ldc, tiles_n;
+    int group_n;
+    int e, base;   // cursor (per thread): expert `e` starts at linear tile `base`
+
+    __device__ __forceinline__ bool next(int it, Tile &t) {
+        const int idx = blockIdx.x + it * gridDim.x;
+        int tiles_m = 0;
+        while (e < experts) {
+            tiles_m = (counts[e] + kRows - 1) / kRows;
+            const int tiles_e = tiles_m * tiles_n;
+            if (idx < base + tiles_e)
+                break;
+            base += tiles_e;
+            ++e;
+        }
+        if (e >= experts)
+            return false;
+        if (offsets[e] & (BM - 1)) {
+            ab::set_status(status, aboleth::Status::Malformed, 0x3600 + e);
+            return false;
+        }
+        const int local = idx - base;
+        const int per_group = group_n * tiles_m;
+        const int group = local / per_group;
+        const int width = min(group_n, tiles_n - group * group_n);
+        const int in_group = local - group * per_group;
+        const int tm = in_group / width, tn = group * group_n + (in_group - tm * width);
+        const int row0 = offsets[e] + tm * kRows;
+        t.a_row = row0;
+        t.b_row = e * n + tn * kCols;
+        t.k_blocks = k / mx::kBlockK;
+        t.c_row = row0;
+        t.c_col = tn * kCols;
+        t.rows_valid = min(kRows, counts[e] - tm * kRows);
+        t.cols_valid = min(kCols, n - tn * kCols);
+        t.tag = e;
+        t.a_sel = 0;
+        return true;
+    }
+    __device__ __forceinline__ bool ready(const Tile &) const { return true; }
+    __device__ __forceinline__ void store16(const Tile &t, int row, int col, const uint4 &v) const {
+        *reinterpret_cast<uint4 *>(c + static_cast<std::size_t>(t.c_row + row) * ldc + t.c_col + col) = v;
+    }
+    __device__ __forceinline__ void tile_done(const Tile &) const {}
+    __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
+};
+
+template <int HALVES>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  GroupedMxPolicy<HALVES> params, mx::ScaleFactors sf, unsigned long long *status) {
+    GroupedMxPolicy<HALVES> policy = params;
+    mx::gemm_mx_mainloop<HALVES>(policy, &map_a, &map_b, sf, status);
+}
+
+template <int HALVES>
 __global__ void __launch_bounds__(kThreads, 1) gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a,
                                                               const __grid_constant__ CUtensorMap map_b,
                                                               MxPolicy policy, mx::ScaleFactors sf,
                                                               unsigned long long *status) {
-    mx::gemm_mx_mainloop(policy, &map_a, &map_b, sf, status);
+    mx::gemm_mx_mainloop<HALVES>(policy, &map_a, &map_b, sf, status);
 }
 
 // The exponent byte (ue8m0) of a positive power-of-two fp32; anything else is reported.
@@ -257,8 +356,8 @@ __device__ __forceinline__ unsigned ue8m0_of(float scale, unsigned long long *st
 // bytes: byte (r % 32) * 16 + (r / 32) * 4 + s for row r of the block, the same value for s = 0..3.
 __global__ void pack_scales_a_kernel(const float *scales, long long ld, std::uint32_t *out, int rows,
                                      int k_blocks, unsigned long long *status) {
-    const int row_blocks = (rows + 127) / 128;
-    const long long total = static_cast<long long>(row_blocks) * k_blocks * 128;
+    const long long row_blocks = mx::mx_row_blocks(rows);
+    const long long total = row_blocks * k_blocks * 128;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int r = static_cast<int>(i % 128);
@@ -270,20 +369,26 @@ __global__ void pack_scales_a_kernel(const float *scales, long long ld, std::uin
     }
 }
 
-// Weight scales fp32 [n_blocks, k_blocks] (one per 128 x 128 block) -> atoms [K block][column block],
-// `b_blocks` (even, >= n_blocks) per K block; all 512 bytes of an atom carry its block's scale.
+// Weight scales fp32 [n_blocks, k_blocks] (one per 128 x 128 block) -> atoms [K block][granule]: atom g
+// holds the scales of columns [64 g, 64 g + 128), so that a tile whose first column is any multiple of 64
+// (256- and 192-column tiles both) finds its two atoms at g and g + 2.  `granules` per K block.
 __global__ void pack_scales_b_kernel(const float *scales, long long ld, std::uint32_t *out, int n_blocks,
-                                     int b_blocks, int k_blocks, unsigned long long *status) {
-    const long long total = static_cast<long long>(k_blocks) * b_blocks * 128;
+                                     int granules, int k_blocks, unsigned long long *status) {
+    const long long total = static_cast<long long>(k_blocks) * granules * 128;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        const long long atom = i / 128;           // kb * b_blocks + nb
-        const int nb = static_cast<int>(atom % b_blocks);
-        const int kb = static_cast<int>(atom / b_blocks);
+        const long long atom = i / 128;           // kb * granules + g
+        const int w = static_cast<int>(i % 128);  // word of the atom: row (w / 4) + 32 * (w % 4)
+        const int g = static_cast<int>(atom % granules);
+        const int kb = static_cast<int>(atom / granules);
+        const int nb = (64 * g + (w >> 2) + 32 * (w & 3)) >> 7;
         const unsigned e = nb < n_blocks ? ue8m0_of(scales[nb * ld + kb], status, 0x3501) : 127u;
         out[i] = e * 0x01010101u;
     }
 }
+
+using mx::mx_granules;
+using mx::mx_row_blocks;
 
 }  // namespace
 
@@ -346,13 +451,53 @@ AB_EXPORT int ab_grouped_gemm_bf16(const void *a, const void *w, void *c, const 
     return launch_grouped<1>(a, w, c, counts, offsets, experts, total_rows, n, k, status, stream);
 }
 
+template <int HALVES>
+int launch_grouped_mx(const void *a, const void *sfa, const void *w, const void *sfb, void *c, const int *counts,
+                      const int *offsets, int experts, int total_rows, int n, int k,
+                      unsigned long long *status, cudaStream_t stream) {
+    using Policy = GroupedMxPolicy<HALVES>;
+    using G = mx::MxGeometry<HALVES>;
+    CUtensorMap map_a, map_b;
+    if (!make_map_e4m3(&map_a, a, total_rows, k, k, Policy::kRows) ||
+        !make_map_e4m3(&map_b, w, static_cast<std::uint64_t>(experts) * n, k, k, Policy::kCols))
+        return -2;
+    if (!configure(grouped_mx_kernel<HALVES>, G::kSmemBytes))
+        return -3;
+    Policy p{static_cast<__nv_bfloat16 *>(c), counts, offsets, status, experts, n, k, n,
+             (n + Policy::kCols - 1) / Policy::kCols, 1, 0, 0};
+    const long long column_bytes = static_cast<long long>(Policy::kCols) * k;
+    p.group_n = static_cast<int>(std::max(1LL, std::min<long long>(p.tiles_n, (48LL << 20) / column_bytes)));
+    const mx::ScaleFactors sf{static_cast<const std::uint8_t *>(sfa), static_cast<const std::uint8_t *>(sfb),
+                              k / 128, mx_granules(experts * n)};
+    // The tile count depends on counts the host never reads: a persistent grid of one CTA per SM.
+    grouped_mx_kernel<HALVES><<<sm_count(), kThreads, G::kSmemBytes, stream>>>(map_a, map_b, p, sf, status);
+    return ab::launch_result("grouped_gemm_e4m3_mx");
+}
+
+// Grouped block-scaled GEMM: a [total_rows, K] e4m3 in expert-contiguous order with every expert's first
+// row on a multiple of 128, w [experts, N, K] e4m3, N a multiple of 64; `sfa` = ab_mx_pack_scales of the
+// [total_rows, K/128] activation scales, `sfb` = of the [experts * N / 128, K/128] weight scales (the
+// weights seen as one [experts * N, K] matrix).  c [total_rows, N] bf16.
+AB_EXPORT int ab_grouped_gemm_e4m3_mx(const void *a, const void *sfa, const void *w, const void *sfb, void *c,
+                                      const int *counts, const int *offsets, int experts, int total_rows,
+                                      int n, int k, unsigned long long *status, cudaStream_t stream) {
+    if (experts < 1 || total_rows < 1 || n < 64 || n % 64 || k < 128 || k % 128 || sfa == nullptr ||
+        sfb == nullptr ||
+        (reinterpret_cast<std::uintptr_t>(a) | reinterpret_cast<std::uintptr_t>(w) |
+         reinterpret_cast<std::uintptr_t>(c) | reinterpret_cast<std::uintptr_t>(sfa) |
+         reinterpret_cast<std::uintptr_t>(sfb)) & 15)
+        return -1;
+    if (total_rows / experts >= 256)
+        return launch_grouped_mx<2>(a, sfa, w, sfb, c, counts, offsets, experts, total_rows, n, k, status, stream);
+    return launch_grouped_mx<1>(a, sfa, w, sfb, c, counts, offsets, experts, total_rows, n, k, status, stream);
+}
+
 // Bytes of the packed scale factors of a block-scaled GEMM: A atoms for `m` rows, B atoms for `n` columns.
 AB_EXPORT long long ab_mx_scale_bytes(int m, int n, int k, int which) {
     const long long k_blocks = (k + 127) / 128;
     if (which == 0)
-        return static_cast<long long>((m + 127) / 128) * k_blocks * 512;
-    const long long b_blocks = static_cast<long long>((n + 255) / 256) * 2;
-    return k_blocks * b_blocks * 512;
+        return mx_row_blocks(m) * k_blocks * 512;
+    return k_blocks * mx_granules(n) * 512;
 }
 
 // fp32 power-of-two scales -> ue8m0 atoms in the order the tensor core reads them.  which = 0: activation
@@ -367,9 +512,8 @@ AB_EXPORT int ab_mx_pack_scales(const float *scales, long long ld, void *out, in
         pack_scales_a_kernel<<<148, 256, 0, stream>>>(scales, ld, static_cast<std::uint32_t *>(out), rows,
                                                       k_blocks, status);
     } else {
-        const int n_blocks = (rows + 127) / 128, b_blocks = (rows + 255) / 256 * 2;
-        pack_scales_b_kernel<<<148, 256, 0, stream>>>(scales, ld, static_cast<std::uint32_t *>(out), n_blocks,
-                                                      b_blocks, k_blocks, status);
+        pack_scales_b_kernel<<<148, 256, 0, stream>>>(scales, ld, static_cast<std::uint32_t *>(out),
+                                                      (rows + 127) / 128, mx_granules(rows), k_blocks, status);
     }
     return ab::launch_result("mx_pack_scales");
 }
@@ -386,22 +530,42 @@ AB_EXPORT int ab_gemm_e4m3_mx(const void *a, const void *b, void *c, const void 
          reinterpret_cast<std::uintptr_t>(c) | reinterpret_cast<std::uintptr_t>(sfa) |
          reinterpret_cast<std::uintptr_t>(sfb)) & 15)
         return -1;
+    // 256 x 192 tiles (two row blocks share a B tile: about 5 % faster per FLOP) unless the 128 x 256
+    // shape wastes less of its last wave.  ABOLETH_GEMM_MX_TILE=1 / 2 forces one / two row blocks.
+    int halves = 1;
+    if (m > BM) {
+        const long long sms = sm_count();
+        const long long tiles1 = static_cast<long long>((m + 127) / 128) * ((n + 255) / 256);
+        const long long tiles2 = static_cast<long long>((m + 255) / 256) * ((n + 191) / 192);
+        const long long cost1 = (tiles1 + sms - 1) / sms * (128 * 256) * 105;
+        const long long cost2 = (tiles2 + sms - 1) / sms * (256 * 192) * 100;
+        halves = cost2 <= cost1 ? 2 : 1;
+    }
+    if (const char *forced = std::getenv("ABOLETH_GEMM_MX_TILE"))
+        halves = forced[0] == '1' ? 1 : 2;
     MxPolicy p{};
     p.c = static_cast<__nv_bfloat16 *>(c);
     p.m = m, p.n = n, p.k = k, p.ldc = ldc;
-    p.tiles_n = (n + BN - 1) / BN;
-    p.pair = 0, p.rows = BM, p.bk = mx::kBlockK, p.alpha = 1.0f;
-    p.tiles_total = ((m + BM - 1) / BM) * p.tiles_n;
-    const long long column_bytes = static_cast<long long>(BN) * k;
+    p.rows = BM * halves;
+    p.cols = halves == 1 ? mx::MxGeometry<1>::kCols : mx::MxGeometry<2>::kCols;
+    p.tiles_n = (n + p.cols - 1) / p.cols;
+    p.tiles_total = ((m + p.rows - 1) / p.rows) * p.tiles_n;
+    const long long column_bytes = static_cast<long long>(p.cols) * k;
     p.group_n = static_cast<int>(std::max(1LL, std::min<long long>(p.tiles_n, (48LL << 20) / column_bytes)));
     CUtensorMap map_a, map_b;
-    if (!make_map_e4m3(&map_a, a, m, k, lda, BM) || !make_map_e4m3(&map_b, b, n, k, ldb, BN))
+    if (!make_map_e4m3(&map_a, a, m, k, lda, p.rows) || !make_map_e4m3(&map_b, b, n, k, ldb, p.cols))
         return -2;
-    if (!configure(gemm_mx_kernel, mx::kSmemBytes))
-        return -3;
     const mx::ScaleFactors sf{static_cast<const std::uint8_t *>(sfa), static_cast<const std::uint8_t *>(sfb),
-                              k / 128, (n + 255) / 256 * 2};
+                              k / 128, mx_granules(n)};
     const int grid = p.tiles_total < sm_count() ? p.tiles_total : sm_count();
-    gemm_mx_kernel<<<grid, kThreads, mx::kSmemBytes, stream>>>(map_a, map_b, p, sf, status);
+    if (halves == 1) {
+        if (!configure(gemm_mx_kernel<1>, mx::MxGeometry<1>::kSmemBytes))
+            return -3;
+        gemm_mx_kernel<1><<<grid, kThreads, mx::MxGeometry<1>::kSmemBytes, stream>>>(map_a, map_b, p, sf, status);
+    } else {
+        if (!configure(gemm_mx_kernel<2>, mx::MxGeometry<2>::kSmemBytes))
+            return -3;
+        gemm_mx_kernel<2><<<grid, kThreads, mx::MxGeometry<2>::kSmemBytes, stream>>>(map_a, map_b, p, sf, status);
+    }
     return ab::launch_result("gemm_e4m3_mx");
 }

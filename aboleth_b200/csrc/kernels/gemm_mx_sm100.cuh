@@ -19,9 +19,11 @@
 // atom (512 B) and two B atoms (1 KiB) by untiled bulk copies on the same mbarrier; nothing is
 // multicast.
 //
-// One 128 x 256 accumulator (256 columns) plus 12 columns of scale factors: the second
-// accumulator buffer of the bf16 loop does not fit beside them, so the epilogue of a tile is not
-// overlapped with the next tile's main loop here.
+// Two tile shapes.  128 x 256: one accumulator of 256 columns plus 12 columns of scale factors.
+// 256 x 192: two 128-row accumulators of 192 columns that share each B tile (a quarter fewer
+// shared-memory bytes per FLOP, which is what bounds this loop) plus 16 columns of scale factors.
+// Either way tensor memory has no room for a second accumulator buffer, so the epilogue of a tile
+// is not overlapped with the next tile's main loop.
 //
 // Same roles, same bounded waits and the same policy interface as gemm_sm100.cuh.
 #pragma once
@@ -32,15 +34,23 @@ namespace ab::gemm::mx {
 
 constexpr int kBlockK = 128;                    // e4m3 elements (= bytes) of K per stage
 constexpr int kStagesMx = 3;
-constexpr unsigned kBytesA = BM * kBlockK;      // 16 KiB
-constexpr unsigned kBytesB = BN * kBlockK;      // 32 KiB
 constexpr unsigned kAtomBytes = 512;            // scale factors of 128 rows x 128 K
-constexpr unsigned kOffSfa = kBytesA + kBytesB;
-constexpr unsigned kOffSfb = kOffSfa + kAtomBytes;
-constexpr unsigned kStageStride = 50 * 1024;    // tiles + 3 atoms, rounded up to the swizzle alignment
-constexpr unsigned kStageTx = kBytesA + kBytesB + 3 * kAtomBytes;
-constexpr unsigned kSmemBytes = kStagesMx * kStageStride + kEpilogueStageBytes + 1024;
-constexpr unsigned kSfaCol = 256, kSfbCol = 260;  // tensor-memory columns behind the accumulator
+
+// HALVES row blocks of 128 rows per tile; the tile is 256 columns wide with one, 192 with two.
+template <int HALVES>
+struct MxGeometry {
+    static constexpr int kRows = BM * HALVES;
+    static constexpr int kCols = HALVES == 1 ? 256 : 192;
+    static constexpr unsigned kBytesA = kRows * kBlockK;
+    static constexpr unsigned kBytesB = kCols * kBlockK;
+    static constexpr unsigned kOffSfa = kBytesA + kBytesB;          // HALVES atoms
+    static constexpr unsigned kOffSfb = kOffSfa + HALVES * kAtomBytes;  // two atoms (256 columns' worth)
+    static constexpr unsigned kStageTx = kBytesA + kBytesB + (HALVES + 2) * kAtomBytes;
+    static constexpr unsigned kStageStride = (kStageTx + 1023) / 1024 * 1024;  // keeps tiles swizzle-aligned
+    static constexpr unsigned kSmemBytes = kStagesMx * kStageStride + kEpilogueStageBytes + 1024;
+    // tensor-memory columns: accumulators first, then A's scale factors (4 per row block), then B's (8)
+    static constexpr unsigned kSfaCol = HALVES * kCols, kSfbCol = kSfaCol + 4 * HALVES;
+};
 
 // Instruction descriptor of kind::mxf8f6f4.block_scale: e4m3 A and B (format 0), K-major, ue8m0
 // scales, N >> 3 at bit 17, M >> 4 at bit 24; `sf` (0..3) selects the byte of the scale columns
@@ -72,20 +82,31 @@ __device__ __forceinline__ void umma_mx(std::uint32_t d_tmem, std::uint64_t a_de
         : "memory");
 }
 
-// Where the packed scale factors of a problem live.  A: atoms [row block][K block]; B: atoms
-// [K block][column block], column block fastest and padded to an even count so that the two atoms
-// of a 256-column tile are adjacent.
+// Where the packed scale factors of a problem live.  A: atoms [row block][K block], one row block
+// more than the rows need.  B: atoms [K block][granule]; atom g covers columns
+// [64 g, 64 g + 128), so a tile that starts at any multiple of 64 columns reads atoms g and g + 2.
 struct ScaleFactors {
     const std::uint8_t *a;
     const std::uint8_t *b;
     int k_blocks;     // K / 128
-    int b_blocks;     // padded column blocks per K block
+    int b_blocks;     // granules per K block
+    const std::uint8_t *a_alt = nullptr;  // atoms of the second A operand (tiles with a_sel = 1)
 };
 
-template <typename Policy>
+// Row blocks of A's atoms and 64-column granules of B's.  One row block more than the rows need: a
+// 256-row tile may start on the last 128-row block (grouped problems) and still reads two atoms.
+__host__ __device__ inline long long mx_row_blocks(int m) { return static_cast<long long>((m + 127) / 128) + 1; }
+inline int mx_granules(int n) { return (n + 63) / 64 + 3; }
+
+template <int HALVES, typename Policy>
 __device__ __forceinline__ void gemm_mx_mainloop(Policy &policy, const CUtensorMap *map_a,
                                                  const CUtensorMap *map_b, const ScaleFactors sf,
-                                                 unsigned long long *status) {
+                                                 unsigned long long *status,
+                                                 const CUtensorMap *map_a_alt = nullptr) {
+    using G = MxGeometry<HALVES>;
+    constexpr unsigned kBytesA = G::kBytesA, kOffSfa = G::kOffSfa, kOffSfb = G::kOffSfb;
+    constexpr unsigned kStageStride = G::kStageStride, kStageTx = G::kStageTx;
+    constexpr unsigned kSfaCol = G::kSfaCol, kSfbCol = G::kSfbCol;
     extern __shared__ std::uint8_t smem_raw[];
     __shared__ SharedState st;
     std::uint8_t *tiles = reinterpret_cast<std::uint8_t *>(
@@ -104,6 +125,8 @@ __device__ __forceinline__ void gemm_mx_mainloop(Policy &policy, const CUtensorM
         mbar_fence_init();
         prefetch_tensormap(map_a);
         prefetch_tensormap(map_b);
+        if (map_a_alt != nullptr)
+            prefetch_tensormap(map_a_alt);
     }
     if (warp == 1)
         tmem_alloc(&st.tmem_base, kTmemCols);
@@ -124,8 +147,11 @@ __device__ __forceinline__ void gemm_mx_mainloop(Policy &policy, const CUtensorM
                     set_status(status, aboleth::Status::Timeout, 0x3000 + t.tag);
                     break;
                 }
-                const std::uint8_t *sfa = sf.a + static_cast<std::size_t>(t.a_row / BM) * sf.k_blocks * kAtomBytes;
-                const std::uint8_t *sfb = sf.b + static_cast<std::size_t>(t.b_row / 128) * kAtomBytes;
+                const bool alt = t.a_sel != 0 && map_a_alt != nullptr;
+                const CUtensorMap *tile_map_a = alt ? map_a_alt : map_a;
+                const std::uint8_t *sfa = (alt ? sf.a_alt : sf.a) +
+                                          static_cast<std::size_t>(t.a_row / BM) * sf.k_blocks * kAtomBytes;
+                const std::uint8_t *sfb = sf.b + static_cast<std::size_t>(t.b_row / 64) * kAtomBytes;
                 for (int kb = 0; kb < t.k_blocks; ++kb) {
                     if (!mbar_wait(&st.empty[stage], phase ^ 1) || st.abort) {
                         st.abort = 1;
@@ -134,12 +160,18 @@ __device__ __forceinline__ void gemm_mx_mainloop(Policy &policy, const CUtensorM
                     }
                     std::uint8_t *sa = tiles + stage * kStageStride;
                     mbar_expect_tx(&st.full[stage], kStageTx);
-                    tma_load_2d(sa, map_a, kb * kBlockK, t.a_row, &st.full[stage]);
+                    tma_load_2d(sa, tile_map_a, kb * kBlockK, t.a_row, &st.full[stage]);
                     tma_load_2d(sa + kBytesA, map_b, kb * kBlockK, t.b_row, &st.full[stage]);
-                    bulk_load(sa + kOffSfa, sfa + static_cast<std::size_t>(kb) * kAtomBytes, kAtomBytes,
-                              &st.full[stage]);
-                    bulk_load(sa + kOffSfb, sfb + static_cast<std::size_t>(kb) * sf.b_blocks * kAtomBytes,
-                              2 * kAtomBytes, &st.full[stage]);
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)  // row block h of the tile: its atoms are k_blocks apart
+                        bulk_load(sa + kOffSfa + h * kAtomBytes,
+                                  sfa + (static_cast<std::size_t>(h) * sf.k_blocks + kb) * kAtomBytes, kAtomBytes,
+                                  &st.full[stage]);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)  // columns [0, 128) and [128, 256) of the tile
+                        bulk_load(sa + kOffSfb + half * kAtomBytes,
+                                  sfb + (static_cast<std::size_t>(kb) * sf.b_blocks + 2 * half) * kAtomBytes,
+                                  kAtomBytes, &st.full[stage]);
                     if (++stage == kStagesMx) {
                         stage = 0;
                         phase ^= 1;
@@ -172,16 +204,22 @@ __device__ __forceinline__ void gemm_mx_mainloop(Policy &policy, const CUtensorM
                     // This K block's scale factors: shared memory -> tensor memory.  Copies and MMAs
                     // issued by one thread run in order, so the MMAs below read these scales and the
                     // copies of the next block wait for them.
-                    sf_copy(tmem_base + kSfaCol, sf_desc(sa + kOffSfa));
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)
+                        sf_copy(tmem_base + kSfaCol + 4 * h, sf_desc(sa + kOffSfa + h * kAtomBytes));
                     sf_copy(tmem_base + kSfbCol, sf_desc(sa + kOffSfb));
                     sf_copy(tmem_base + kSfbCol + 4, sf_desc(sa + kOffSfb + kAtomBytes));
-                    const std::uint64_t da = smem_desc_sw128(sa);
                     const std::uint64_t db = smem_desc_sw128(sa + kBytesA);
 #pragma unroll
-                    for (unsigned k = 0; k < 4; ++k) {
-                        // 32 e4m3 = 32 bytes further along K inside the swizzle atom.
-                        umma_mx(tmem_base, da + (k * 32 >> 4), db + (k * 32 >> 4), idesc_mx(BM, BN, k),
-                                tmem_base + kSfaCol, tmem_base + kSfbCol, (kb | static_cast<int>(k)) != 0);
+                    for (int h = 0; h < HALVES; ++h) {
+                        const std::uint64_t da = smem_desc_sw128(sa + h * (BM * kBlockK));
+#pragma unroll
+                        for (unsigned k = 0; k < 4; ++k) {
+                            // 32 e4m3 = 32 bytes further along K inside the swizzle atom.
+                            umma_mx(tmem_base + h * G::kCols, da + (k * 32 >> 4), db + (k * 32 >> 4),
+                                    idesc_mx(BM, G::kCols, k), tmem_base + kSfaCol + 4 * h, tmem_base + kSfbCol,
+                                    (kb | static_cast<int>(k)) != 0);
+                        }
                     }
                     umma_commit(&st.empty[stage]);  // stage reusable once MMAs and copies have read it
                     if (++stage == kStagesMx) {
@@ -211,21 +249,47 @@ __device__ __forceinline__ void gemm_mx_mainloop(Policy &policy, const CUtensorM
         for (int it = 0; policy.next(it, t); ++it) {
             if ((aborted = epilogue_aborted()))
                 break;
+            if constexpr (Policy::kBackground) {
+                // While the accumulator is not ready the four warps run the policy's background
+                // items (communication); one thread polls and a named barrier shares the decision.
+                for (;;) {
+                    if (epi_thread == 0)
+                        st.epi_ready = mbar_try_wait(&st.tmem_full[0], it & 1) ? 1 : 0;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const int ready_now = st.epi_ready;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (ready_now || !policy.background(epi_thread, kEpilogueWarps * 32))
+                        break;
+                }
+            }
             if (!mbar_wait(&st.tmem_full[0], it & 1)) {
                 st.abort = 1;
                 set_status(status, aboleth::Status::Timeout, 0x3400);
             } else {
                 tc_fence_after();
-                const std::uint32_t taddr = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16);
-                drain_rows32(policy, t, taddr, quarter * 32, epi_stage, lane);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) {
+                    const std::uint32_t taddr = tmem_base + (static_cast<std::uint32_t>(quarter * 32) << 16) +
+                                                h * G::kCols;
+                    drain_rows32(policy, t, taddr, h * BM + quarter * 32, epi_stage, lane);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0)
                     mbar_arrive(&st.tmem_empty[0]);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            if constexpr (Policy::kDrainedHook) {  // the accumulator is released: this overlaps the next main loop
+                policy.drained(t, epi_thread, kEpilogueWarps * 32);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
             if (warp == 2 && lane == 0)
                 policy.tile_done(t);
+        }
+        if constexpr (Policy::kBackground) {
+            while (!aborted && !(aborted = epilogue_aborted()) &&
+                   policy.background(epi_thread, kEpilogueWarps * 32)) {
+            }
         }
         if (!aborted && !epilogue_aborted())
             policy.finish(epi_thread, kEpilogueWarps * 32, status);

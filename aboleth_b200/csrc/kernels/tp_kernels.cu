@@ -28,7 +28,7 @@
 #include <algorithm>
 #include <cstdlib>
 
-#include "gemm_sm100.cuh"
+#include "gemm_mx_sm100.cuh"
 
 namespace {
 
@@ -56,7 +56,10 @@ constexpr int kPhaseConsume = 2;  // AG: GEMM.        RS: reduction of owned til
 
 // ---- all-gather -> GEMM -----------------------------------------------------------------
 
-struct AgGemmPolicy {
+// COLS: tile width; ESIZE: bytes per A element (2 = bf16; 1 = e4m3 with scale-factor atoms that
+// travel with the rows); KBLK: K elements per main-loop stage.
+template <int COLS, int ESIZE, int KBLK>
+struct AgGemmPolicyT {
     static constexpr bool kBackground = true, kDrainedHook = false, kScaled = false;
     __nv_bfloat16 *c;
     const std::uint64_t *flags;       // local: [world * chunks] epochs
@@ -72,6 +75,10 @@ struct AgGemmPolicy {
     unsigned *arrivals;                   // local scratch [world * chunks], zero between calls
     int parts;                            // items that share one (peer, chunk)
     int pushed;                           // items this CTA has pushed so far (same in every thread)
+    // e4m3 only: this rank's packed scale factors ([m_local / 128][K / 128] atoms) and where the
+    // gathered atoms start inside a staging buffer (behind the gathered rows).
+    const std::uint8_t *sfa_local = nullptr;
+    std::size_t staging_sfa_offset = 0;
 
     __device__ __forceinline__ bool next(int it, Tile &t) const {
         if (!(phases & kPhaseConsume))
@@ -88,12 +95,12 @@ struct AgGemmPolicy {
         raster(local, chunks, tiles_n, group_n, chunk, tn);
         t.a_sel = src == rank ? 1 : 0;
         t.a_row = src == rank ? chunk * kRows : src * m_local + chunk * kRows;
-        t.b_row = tn * BN;
-        t.k_blocks = (k + BK - 1) / BK;
+        t.b_row = tn * COLS;
+        t.k_blocks = (k + KBLK - 1) / KBLK;
         t.c_row = src * m_local + chunk * kRows;
-        t.c_col = tn * BN;
+        t.c_col = tn * COLS;
         t.rows_valid = min(kRows, m_local - chunk * kRows);
-        t.cols_valid = min(BN, n - tn * BN);
+        t.cols_valid = min(COLS, n - tn * COLS);
         t.tag = src * chunks + chunk;
         return true;
     }
@@ -122,7 +129,7 @@ struct AgGemmPolicy {
         if (item >= (world - 1) * chunks * parts)
             return false;
         ++pushed;
-        const std::size_t row_bytes = static_cast<std::size_t>(k) * 2;
+        const std::size_t row_bytes = static_cast<std::size_t>(k) * ESIZE;
         const int part = item % parts;
         const int pc = item / parts;
         const int hop = pc / chunks + 1, chunk = pc - (hop - 1) * chunks;
@@ -134,6 +141,14 @@ struct AgGemmPolicy {
         std::uint8_t *dst = reinterpret_cast<std::uint8_t *>(peer_staging[peer]) +
                             static_cast<std::size_t>(rank) * m_local * row_bytes + offset;
         aboleth::detail::copy_strided(dst, a_local + offset, (r1 - r0) * row_bytes, thread, nthreads);
+        if constexpr (ESIZE == 1) {
+            if (part == 0) {  // the chunk's scale factors: two row blocks of K / 128 atoms
+                const std::size_t chunk_sf = static_cast<std::size_t>(kRows / BM) * (k / KBLK) * mx::kAtomBytes;
+                std::uint8_t *sf_dst = reinterpret_cast<std::uint8_t *>(peer_staging[peer]) + staging_sfa_offset +
+                                       (static_cast<std::size_t>(rank) * chunks + chunk) * chunk_sf;
+                aboleth::detail::copy_strided(sf_dst, sfa_local + chunk * chunk_sf, chunk_sf, thread, nthreads);
+            }
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (thread == 0) {
             aboleth::detail::fence_acq_rel_sys();
@@ -150,6 +165,9 @@ struct AgGemmPolicy {
     }
 };
 
+using AgGemmPolicy = AgGemmPolicyT<BN, 2, BK>;
+using AgGemmMxPolicy = AgGemmPolicyT<mx::MxGeometry<kHalves>::kCols, 1, mx::kBlockK>;
+
 __global__ void __launch_bounds__(kThreads, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap map_staging,
                const __grid_constant__ CUtensorMap map_b,
@@ -158,9 +176,20 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_staging,
     gemm_mainloop<kHalves>(policy, &map_staging, &map_b, policy.status, &map_local);
 }
 
+// The same schedule on block-scaled e4m3 operands (tcgen05.mma.kind::mxf8f6f4.block_scale): half the
+// bytes cross NVLink and the product runs at the fp8 rate.
+__global__ void __launch_bounds__(kThreads, 1)
+ag_gemm_mx_kernel(const __grid_constant__ CUtensorMap map_staging,
+                  const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_local, AgGemmMxPolicy params, mx::ScaleFactors sf) {
+    AgGemmMxPolicy policy = params;
+    mx::gemm_mx_mainloop<kHalves>(policy, &map_staging, &map_b, sf, policy.status, &map_local);
+}
+
 // ---- GEMM -> reduce-scatter -----------------------------------------------------------------
 
-struct GemmRsPolicy {
+template <int COLS, int KBLK>
+struct GemmRsPolicyT {
     static constexpr bool kBackground = true, kDrainedHook = true, kScaled = false;
     const std::uint64_t *peer_partials;  // [world] address of each rank's partial buffer
     const std::uint64_t *peer_flags;     // [world] address of each rank's flag array
@@ -203,12 +232,12 @@ struct GemmRsPolicy {
         const int local = chunk * tiles_n + tn;
         t.a_sel = 0;
         t.a_row = owner * m_local + chunk * kRows;
-        t.b_row = tn * BN;
-        t.k_blocks = (k + BK - 1) / BK;
+        t.b_row = tn * COLS;
+        t.k_blocks = (k + KBLK - 1) / KBLK;
         t.c_row = chunk * kRows;  // row inside the owner's block
-        t.c_col = tn * BN;
+        t.c_col = tn * COLS;
         t.rows_valid = min(kRows, m_local - chunk * kRows);
-        t.cols_valid = min(BN, n - tn * BN);
+        t.cols_valid = min(COLS, n - tn * COLS);
         t.tag = owner * 65536 + local;  // owner and tile index inside the owner's block
         return true;
     }
@@ -220,7 +249,7 @@ struct GemmRsPolicy {
                                   static_cast<std::size_t>(rank) * m_local * n;
             *reinterpret_cast<uint4 *>(base + static_cast<std::size_t>(t.c_row + row) * n + t.c_col + col) = v;
         } else {
-            *reinterpret_cast<uint4 *>(stage + static_cast<std::size_t>(blockIdx.x) * (kRows * BN) + row * BN +
+            *reinterpret_cast<uint4 *>(stage + static_cast<std::size_t>(blockIdx.x) * (kRows * COLS) + row * COLS +
                                        col) = v;
         }
     }
@@ -230,7 +259,7 @@ struct GemmRsPolicy {
         const int owner = t.tag >> 16;
         if (owner == rank)
             return;
-        const __nv_bfloat16 *src = stage + static_cast<std::size_t>(blockIdx.x) * (kRows * BN);
+        const __nv_bfloat16 *src = stage + static_cast<std::size_t>(blockIdx.x) * (kRows * COLS);
         __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(peer_partials[owner]) +
                              static_cast<std::size_t>(rank) * m_local * n +
                              static_cast<std::size_t>(t.c_row) * n + t.c_col;
@@ -244,7 +273,7 @@ struct GemmRsPolicy {
                 const int i = i0 + u * nthreads;
                 if (i < total) {
                     const int r = i / vpr, c = i - r * vpr;
-                    v[u] = aboleth::detail::ld_stream16(src + r * BN + c * 8);
+                    v[u] = aboleth::detail::ld_stream16(src + r * COLS + c * 8);
                 }
             }
 #pragma unroll
@@ -268,15 +297,15 @@ struct GemmRsPolicy {
     // Sum the partials of owned tile `tile` over the ranks (fp32) into `out`.  All 128 epilogue threads.
     __device__ __forceinline__ void reduce_tile(int tile, int thread, int nthreads) const {
         const int chunk = tile / tiles_n, tn = tile - chunk * tiles_n;
-        const int rows = min(kRows, m_local - chunk * kRows), cols = min(BN, n - tn * BN);
+        const int rows = min(kRows, m_local - chunk * kRows), cols = min(COLS, n - tn * COLS);
         const int vec_per_row = cols / 8;
         for (int i = thread; i < rows * vec_per_row; i += 2 * nthreads) {
             const int i2 = i + nthreads;
             const bool two = i2 < rows * vec_per_row;
             const int ra = i / vec_per_row, va = i - ra * vec_per_row;
             const int rb = two ? i2 / vec_per_row : ra, vb = two ? i2 - rb * vec_per_row : va;
-            const std::size_t offa = static_cast<std::size_t>(chunk * kRows + ra) * n + tn * BN + va * 8;
-            const std::size_t offb = static_cast<std::size_t>(chunk * kRows + rb) * n + tn * BN + vb * 8;
+            const std::size_t offa = static_cast<std::size_t>(chunk * kRows + ra) * n + tn * COLS + va * 8;
+            const std::size_t offb = static_cast<std::size_t>(chunk * kRows + rb) * n + tn * COLS + vb * 8;
             float acc[2][8] = {};
             // Up to eight sources' vectors are loaded before any is added: sixteen 16-byte loads in
             // flight per thread instead of two.
@@ -366,6 +395,9 @@ struct GemmRsPolicy {
     }
 };
 
+using GemmRsPolicy = GemmRsPolicyT<BN, BK>;
+using GemmRsMxPolicy = GemmRsPolicyT<mx::MxGeometry<kHalves>::kCols, mx::kBlockK>;
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                GemmRsPolicy params) {
@@ -373,10 +405,17 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     gemm_mainloop<kHalves>(policy, &map_a, &map_b, policy.status);
 }
 
-// Tile columns whose B panels (256 rows of K bf16 each) add up to about 48 MiB.
-int raster_group(int n, int k) {
-    const long long column_bytes = static_cast<long long>(BN) * k * 2;
-    const long long tiles_n = (n + BN - 1) / BN;
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_rs_mx_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  GemmRsMxPolicy params, mx::ScaleFactors sf) {
+    GemmRsMxPolicy policy = params;
+    mx::gemm_mx_mainloop<kHalves>(policy, &map_a, &map_b, sf, policy.status);
+}
+
+// Tile columns whose B panels (`cols` rows of K elements of `esize` bytes each) add up to about 48 MiB.
+int raster_group(int n, int k, int cols = BN, int esize = 2) {
+    const long long column_bytes = static_cast<long long>(cols) * k * esize;
+    const long long tiles_n = (n + cols - 1) / cols;
     return static_cast<int>(std::max(1LL, std::min(tiles_n, (48LL << 20) / column_bytes)));
 }
 
@@ -424,11 +463,96 @@ AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const vo
     return ab::launch_result("ag_gemm_bf16");
 }
 
+// Block-scaled e4m3 form of ab_ag_gemm_bf16.  a_local [m_local, k] e4m3 with its packed scale factors
+// `sfa_local` (ab_mx_pack_scales: m_local / 128 row blocks of k / 128 atoms); b [n, k] e4m3 with packed
+// `sfb`.  staging holds the gathered rows [world*m_local, k] followed by the gathered atoms
+// [world * m_local / 128][k / 128][512]: ab_ag_gemm_mx_staging_bytes() bytes.  k a multiple of 128.
+AB_EXPORT long long ab_ag_gemm_mx_staging_bytes(int world, int m_local, int k) {
+    const long long rows = static_cast<long long>(world) * m_local;
+    return rows * k + rows / BM * (k / 128) * mx::kAtomBytes;
+}
+
+AB_EXPORT int ab_ag_gemm_e4m3_mx(const void *a_local, const void *sfa_local, const void *staging, const void *b,
+                                 const void *sfb, void *c, const std::uint64_t *peer_staging,
+                                 const std::uint64_t *peer_flags, const std::uint64_t *flags,
+                                 unsigned long long *status, unsigned *arrivals, std::uint64_t epoch, int rank,
+                                 int world, int m_local, int n, int k, int parts, int phases,
+                                 cudaStream_t stream) {
+    if (world < 1 || m_local < kRows || m_local % kRows || n < 8 || n % 8 || k < 128 || k % 128 || rank < 0 ||
+        rank >= world || sfa_local == nullptr || sfb == nullptr)
+        return -1;
+    constexpr int kCols = mx::MxGeometry<kHalves>::kCols;
+    constexpr unsigned smem = mx::MxGeometry<kHalves>::kSmemBytes;
+    CUtensorMap map_staging, map_b, map_local;
+    if (!make_map_e4m3(&map_staging, staging, static_cast<std::uint64_t>(world) * m_local, k, k, kRows) ||
+        !make_map_e4m3(&map_b, b, n, k, k, kCols) || !make_map_e4m3(&map_local, a_local, m_local, k, k, kRows))
+        return -2;
+    if (cudaFuncSetAttribute(ag_gemm_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return -3;
+    const int chunks = m_local / kRows;
+    if (parts < 1) {
+        const long long chunk_bytes = static_cast<long long>(kRows) * k;
+        parts = static_cast<int>(std::min<long long>(kRows, std::max<long long>(1, chunk_bytes / 65536)));
+    }
+    parts = std::min(parts, kRows);
+    AgGemmMxPolicy p{static_cast<__nv_bfloat16 *>(c), flags, status, epoch, rank, world, m_local, n, k, n,
+                     phases, (n + kCols - 1) / kCols, chunks, raster_group(n, k, kCols, 1),
+                     static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, arrivals, parts, 0,
+                     static_cast<const std::uint8_t *>(sfa_local),
+                     static_cast<std::size_t>(world) * m_local * k};
+    const mx::ScaleFactors sf{static_cast<const std::uint8_t *>(staging) + p.staging_sfa_offset,
+                              static_cast<const std::uint8_t *>(sfb), k / 128, mx::mx_granules(n),
+                              static_cast<const std::uint8_t *>(sfa_local)};
+    ag_gemm_mx_kernel<<<sm_count(), kThreads, smem, stream>>>(map_staging, map_b, map_local, p, sf);
+    return ab::launch_result("ag_gemm_e4m3_mx");
+}
+
 // a [world*m_local, k_local]; b [n, k_local]; partials: local [world, m_local, n] (peers write it);
 // out [m_local, n]; stage: local scratch of ab_gemm_rs_stage_bytes() bytes (staging tiles, one per CTA).
 // m_local multiple of 256, n multiple of 8 and tiles per owner < 65536.
 AB_EXPORT long long ab_gemm_rs_stage_bytes() {
     return static_cast<long long>(sm_count()) * kRows * BN * 2;
+}
+
+// Tiles per owner of the block-scaled form (192-column tiles): the flag arrays hold world times as many.
+AB_EXPORT int ab_gemm_rs_mx_tiles(int m_local, int n) {
+    constexpr int kCols = mx::MxGeometry<kHalves>::kCols;
+    return (m_local / kRows) * ((n + kCols - 1) / kCols);
+}
+
+// Block-scaled e4m3 form of ab_gemm_rs_bf16: a [world*m_local, k_local] and b [n, k_local] are e4m3 with
+// packed scale factors `sfa` / `sfb` (ab_mx_pack_scales); partials, out and stage as in the bf16 form;
+// flags hold world * ab_gemm_rs_mx_tiles() entries.  k_local a multiple of 128.
+AB_EXPORT int ab_gemm_rs_e4m3_mx(const void *a, const void *sfa, const void *b, const void *sfb,
+                                 const void *partials, void *out, void *stage,
+                                 const std::uint64_t *peer_partials, const std::uint64_t *peer_flags,
+                                 const std::uint64_t *flags, unsigned long long *status, std::uint64_t epoch,
+                                 int rank, int world, int m_local, int n, int k, int phases,
+                                 cudaStream_t stream) {
+    if (world < 1 || m_local < kRows || m_local % kRows || n < 8 || n % 8 || k < 128 || k % 128 || rank < 0 ||
+        rank >= world || stage == nullptr || sfa == nullptr || sfb == nullptr)
+        return -1;
+    constexpr int kCols = mx::MxGeometry<kHalves>::kCols;
+    constexpr unsigned smem = mx::MxGeometry<kHalves>::kSmemBytes;
+    const int tiles_n = (n + kCols - 1) / kCols, chunks = m_local / kRows;
+    if (tiles_n * chunks >= 65536)
+        return -1;
+    CUtensorMap map_a, map_b;
+    if (!make_map_e4m3(&map_a, a, static_cast<std::uint64_t>(world) * m_local, k, k, kRows) ||
+        !make_map_e4m3(&map_b, b, n, k, k, kCols))
+        return -2;
+    if (cudaFuncSetAttribute(gemm_rs_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return -3;
+    int interleave = tiles_n * chunks >= 2 * sm_count() ? 1 : 0;
+    if (const char *forced = std::getenv("ABOLETH_RS_ORDER"))
+        interleave = forced[0] == '1' ? 1 : 0;
+    GemmRsMxPolicy p{peer_partials, peer_flags, static_cast<const __nv_bfloat16 *>(partials), flags,
+                     static_cast<__nv_bfloat16 *>(out), static_cast<__nv_bfloat16 *>(stage), status, epoch, rank,
+                     world, m_local, n, k, phases, tiles_n, chunks, raster_group(n, k, kCols, 1), interleave, 0};
+    const mx::ScaleFactors sf{static_cast<const std::uint8_t *>(sfa), static_cast<const std::uint8_t *>(sfb),
+                              k / 128, mx::mx_granules(n)};
+    gemm_rs_mx_kernel<<<sm_count(), kThreads, smem, stream>>>(map_a, map_b, p, sf);
+    return ab::launch_result("gemm_rs_e4m3_mx");
 }
 
 AB_EXPORT int ab_gemm_rs_bf16(const void *a, const void *b, const void *partials, void *out, void *stage,

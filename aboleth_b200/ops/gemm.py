@@ -109,6 +109,7 @@ def dequant_block_scaled(q: torch.Tensor, scales: torch.Tensor, *, block: tuple[
 
 declare("ab_mx_pack_scales", [_VP, ctypes.c_longlong, _VP, _I, _I, _I, _VP, _VP])
 declare("ab_gemm_e4m3_mx", [_VP] * 5 + [_I] * 6 + [_VP, _VP])
+declare("ab_grouped_gemm_e4m3_mx", [_VP] * 7 + [_I] * 4 + [_VP, _VP])
 
 
 def pack_scales_mx(scales: torch.Tensor, rows: int, k: int, *, weight: bool) -> torch.Tensor:
@@ -151,6 +152,33 @@ def gemm_e4m3_mx(a: torch.Tensor, a_packed: torch.Tensor, b: torch.Tensor, b_pac
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (m, n)
     call("ab_gemm_e4m3_mx", ptr(a), ptr(b), ptr(out), ptr(a_packed), ptr(b_packed), m, n, k, a.stride(0),
          b.stride(0), out.stride(0), ptr(gemm_status(a.device)), stream_ptr())
+    return out
+
+
+def grouped_gemm_e4m3_mx(a: torch.Tensor, a_packed: torch.Tensor, w: torch.Tensor, w_packed: torch.Tensor,
+                         counts: torch.Tensor, offsets: torch.Tensor,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-expert block-scaled GEMM on ``tcgen05.mma.kind::mxf8f6f4.block_scale``: rows
+    ``[offsets[e], offsets[e] + counts[e])`` of ``a`` times ``w[e].T``, bf16 output.
+
+    ``a`` is e4m3 ``[rows, K]`` in expert-contiguous order with every expert's first row on a multiple
+    of 128 (``expert_offsets(..., align=128)``), ``a_packed = pack_scales_mx(a_scales, rows, K,
+    weight=False)``; ``w`` is e4m3 ``[E, N, K]`` (N a multiple of 128) and ``w_packed =
+    pack_scales_mx(w_scales.view(E * N // 128, K // 128), E * N, K, weight=True)``.  ``counts`` /
+    ``offsets`` are int32 ``[E]`` on the device and never read by the host.
+    """
+    fp8 = torch.float8_e4m3fn
+    assert a.dtype == w.dtype == fp8 and a.is_contiguous() and w.is_contiguous()
+    experts, n, k = w.shape
+    rows = a.shape[0]
+    assert a.shape[1] == k and k % 128 == 0 and n % 128 == 0 and counts.dtype == offsets.dtype == torch.int32
+    assert a_packed.numel() == _mx_scale_bytes(rows, experts * n, k, 0)
+    assert w_packed.numel() == _mx_scale_bytes(rows, experts * n, k, 1)
+    if out is None:
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=a.device)
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == (rows, n)
+    call("ab_grouped_gemm_e4m3_mx", ptr(a), ptr(a_packed), ptr(w), ptr(w_packed), ptr(out), ptr(counts),
+         ptr(offsets), experts, rows, n, k, ptr(gemm_status(a.device)), stream_ptr())
     return out
 
 

@@ -23,6 +23,8 @@ from ..world import World
 
 declare("ab_ag_gemm_bf16", [_VP] * 9 + [_U64] + [_I] * 7 + [_VP])
 declare("ab_gemm_rs_bf16", [_VP] * 9 + [_U64] + [_I] * 6 + [_VP])
+declare("ab_ag_gemm_e4m3_mx", [_VP] * 11 + [_U64] + [_I] * 7 + [_VP])
+declare("ab_gemm_rs_e4m3_mx", [_VP] * 11 + [_U64] + [_I] * 6 + [_VP])
 
 PRODUCE, CONSUME = 1, 2
 BM = 256  # rows per tile / chunk of the fused kernels
@@ -116,13 +118,50 @@ class AllGatherGemm:
              self.k, self.push_parts, phases, stream_ptr())
         return out
 
+    def mx(self, a_q: torch.Tensor, a_packed: torch.Tensor, b_q: torch.Tensor, b_packed: torch.Tensor,
+           out: Optional[torch.Tensor] = None, *, phases: int = PRODUCE | CONSUME,
+           advance: bool = True) -> torch.Tensor:
+        """The fused kernel on block-scaled e4m3 operands: ``a_q`` ``[m_local, k]`` and ``b_q``
+        ``[n_local, k]`` with scale factors packed by :func:`aboleth_b200.ops.pack_scales_mx`.  The
+        shard crosses NVLink as e4m3 (half the bytes of the bf16 form) with its scale-factor atoms
+        and the product runs on ``tcgen05.mma.kind::mxf8f6f4.block_scale``; bf16 output."""
+        from ..ops.gemm import _mx_scale_bytes
+        fp8 = torch.float8_e4m3fn
+        assert a_q.dtype == b_q.dtype == fp8 and a_q.is_contiguous() and b_q.is_contiguous()
+        assert a_q.shape == (self.m_local, self.k) and b_q.shape[1] == self.k and self.k % 128 == 0
+        n = b_q.shape[0]
+        assert a_packed.numel() == _mx_scale_bytes(self.m_local, n, self.k, 0)
+        assert b_packed.numel() == _mx_scale_bytes(self.m_local, n, self.k, 1)
+        rows = self.world_size * self.m_local
+        assert rows * self.k + rows // 128 * (self.k // 128) * 512 <= self.buffers.data_bytes
+        if out is None:
+            out = torch.empty(rows, n, dtype=torch.bfloat16, device=a_q.device)
+        if advance and (phases & PRODUCE):
+            self.epoch += 1
+        which = self.epoch & 1
+        peer_data, peer_flags = self.tables[which]
+        call("ab_ag_gemm_e4m3_mx", ptr(a_q), ptr(a_packed), ptr(self.buffers.data(which)), ptr(b_q),
+             ptr(b_packed), ptr(out), ptr(peer_data), ptr(peer_flags), ptr(self.buffers.flags(which)),
+             ptr(self.status), ptr(self.arrivals), (self.epoch + 1) // 2, self.rank, self.world_size,
+             self.m_local, n, self.k, self.push_parts, phases, stream_ptr())
+        return out
+
     def block_scaled(self, a_q: torch.Tensor, a_scales: torch.Tensor, b_local: torch.Tensor,
-                     out: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
-        """Block-scaled e4m3 activations (``a_q`` with 1 x 128 fp32 ``a_scales``): this rank's shard is
-        expanded to bf16 by :func:`aboleth_b200.ops.dequant_block_scaled` and then gathered and
-        multiplied as in :meth:`__call__`.  ``b_local`` is bf16: expand a block-scaled weight once,
-        with the same function and ``block=(128, 128)``."""
-        from ..ops.gemm import dequant_block_scaled
+                     out: Optional[torch.Tensor] = None, *, b_scales: Optional[torch.Tensor] = None,
+                     b_packed: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
+        """Block-scaled e4m3 activations (``a_q`` with 1 x 128 fp32 ``a_scales``).
+
+        With an e4m3 ``b_local`` and its 128 x 128 ``b_scales`` (or their packed form ``b_packed``) and
+        power-of-two scales everywhere, both operands stay e4m3 end to end (:meth:`mx`).  With a bf16
+        ``b_local`` this rank's shard is expanded to bf16 by
+        :func:`aboleth_b200.ops.dequant_block_scaled` and then gathered and multiplied as in
+        :meth:`__call__` (any positive scales)."""
+        from ..ops.gemm import dequant_block_scaled, pack_scales_mx
+        if b_local.dtype == torch.float8_e4m3fn:
+            if b_packed is None:
+                b_packed = pack_scales_mx(b_scales, b_local.shape[0], self.k, weight=True)
+            a_packed = pack_scales_mx(a_scales, self.m_local, self.k, weight=False)
+            return self.mx(a_q, a_packed, b_local, b_packed, out, **kw)
         return self(dequant_block_scaled(a_q, a_scales), b_local, out, **kw)
 
     def check(self) -> None:
@@ -151,7 +190,9 @@ class GemmReduceScatter:
 
     @staticmethod
     def _tiles(m_local: int, n: int) -> int:
-        return (m_local // BM) * ((n + 255) // 256)
+        # one flag per tile and source; the block-scaled kernel's tiles are 192 columns wide, the
+        # bf16 kernel's 256: sized for the narrower
+        return (m_local // BM) * ((n + 191) // 192)
 
     @staticmethod
     def arena_bytes(world_size: int, m_local: int, n: int) -> int:
@@ -186,11 +227,44 @@ class GemmReduceScatter:
              phases, stream_ptr())
         return out
 
+    def mx(self, a_q: torch.Tensor, a_packed: torch.Tensor, b_q: torch.Tensor, b_packed: torch.Tensor,
+           out: Optional[torch.Tensor] = None, *, phases: int = PRODUCE | CONSUME,
+           advance: bool = True) -> torch.Tensor:
+        """The fused kernel on block-scaled e4m3 operands (scale factors packed by
+        :func:`aboleth_b200.ops.pack_scales_mx`): the partial products come off
+        ``tcgen05.mma.kind::mxf8f6f4.block_scale`` and are exchanged and reduced as in the bf16 form."""
+        from ..ops.gemm import _mx_scale_bytes
+        fp8 = torch.float8_e4m3fn
+        assert a_q.dtype == b_q.dtype == fp8 and a_q.is_contiguous() and b_q.is_contiguous()
+        rows, k = a_q.shape
+        assert rows == self.world_size * self.m_local and b_q.shape == (self.n, k) and k % 128 == 0
+        assert a_packed.numel() == _mx_scale_bytes(rows, self.n, k, 0)
+        assert b_packed.numel() == _mx_scale_bytes(rows, self.n, k, 1)
+        if out is None:
+            out = torch.empty(self.m_local, self.n, dtype=torch.bfloat16, device=a_q.device)
+        if advance and (phases & PRODUCE):
+            self.epoch += 1
+        which = self.epoch & 1
+        peer_data, peer_flags = self.tables[which]
+        call("ab_gemm_rs_e4m3_mx", ptr(a_q), ptr(a_packed), ptr(b_q), ptr(b_packed),
+             ptr(self.buffers.data(which)), ptr(out), ptr(self.stage), ptr(peer_data), ptr(peer_flags),
+             ptr(self.buffers.flags(which)), ptr(self.status), (self.epoch + 1) // 2, self.rank,
+             self.world_size, self.m_local, self.n, k, phases, stream_ptr())
+        return out
+
     def block_scaled(self, a_q: torch.Tensor, a_scales: torch.Tensor, b_local: torch.Tensor,
-                     out: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
-        """As :meth:`__call__` for block-scaled e4m3 activations (1 x 128 fp32 scales), expanded to
-        bf16 first; ``b_local`` is bf16 (a block-scaled weight is expanded once, ahead of time)."""
-        from ..ops.gemm import dequant_block_scaled
+                     out: Optional[torch.Tensor] = None, *, b_scales: Optional[torch.Tensor] = None,
+                     b_packed: Optional[torch.Tensor] = None, **kw) -> torch.Tensor:
+        """As :meth:`__call__` for block-scaled e4m3 activations (1 x 128 fp32 scales).  An e4m3
+        ``b_local`` with 128 x 128 ``b_scales`` (or ``b_packed``) and power-of-two scales keeps both
+        operands e4m3 (:meth:`mx`); a bf16 ``b_local`` takes the expansion of ``a_q`` to bf16."""
+        from ..ops.gemm import dequant_block_scaled, pack_scales_mx
+        if b_local.dtype == torch.float8_e4m3fn:
+            k = a_q.shape[1]
+            if b_packed is None:
+                b_packed = pack_scales_mx(b_scales, self.n, k, weight=True)
+            a_packed = pack_scales_mx(a_scales, a_q.shape[0], k, weight=False)
+            return self.mx(a_q, a_packed, b_local, b_packed, out, **kw)
         return self(dequant_block_scaled(a_q, a_scales), b_local, out, **kw)
 
     def check(self) -> None:
@@ -228,6 +302,18 @@ class LocalTpGroup:
             outs[r] = op(a_shards[r], b_shards[r], phases=PRODUCE)
         return [op(a_shards[r], b_shards[r], outs[r], phases=CONSUME, advance=False)
                 for r, op in enumerate(self.ag)]
+
+    def ag_gemm_mx(self, a_q, a_packed, b_q, b_packed) -> list[torch.Tensor]:
+        """:meth:`ag_gemm` on block-scaled e4m3 shards (lists per rank, scales already packed)."""
+        outs = [op.mx(a_q[r], a_packed[r], b_q[r], b_packed[r], phases=PRODUCE) for r, op in enumerate(self.ag)]
+        return [op.mx(a_q[r], a_packed[r], b_q[r], b_packed[r], outs[r], phases=CONSUME, advance=False)
+                for r, op in enumerate(self.ag)]
+
+    def gemm_rs_mx(self, a_q, a_packed, b_q, b_packed) -> list[torch.Tensor]:
+        """:meth:`gemm_rs` on block-scaled e4m3 operands (lists per rank, scales already packed)."""
+        outs = [op.mx(a_q[r], a_packed[r], b_q[r], b_packed[r], phases=PRODUCE) for r, op in enumerate(self.rs)]
+        return [op.mx(a_q[r], a_packed[r], b_q[r], b_packed[r], outs[r], phases=CONSUME, advance=False)
+                for r, op in enumerate(self.rs)]
 
     def gemm_rs(self, a_parts: Sequence[torch.Tensor], b_shards: Sequence[torch.Tensor]) -> list[torch.Tensor]:
         outs = [None] * self.world_size

@@ -8,6 +8,10 @@ all-gather -> GEMM : M = 8192 tokens (M / world per rank), K = 8192, N = 28672 /
 GEMM -> reduce-scatter : M = 8192, K = 28672 / world, N = 8192
 Weights N(0, 0.02), activations N(0, 1), bf16.  Roofline per kernel = the slower of
 FLOPs / measured cuBLAS peak and NVLink bytes / 770 GB/s.
+
+``--fp8`` adds the block-scaled e4m3 forms (1 x 128 activation scales, 128 x 128 weight scales,
+both operands e4m3 end to end) against NCCL moving the e4m3 bytes around the library's fp8 GEMM
+(torch._scaled_mm with per-tensor scales, the closest form torch exposes).
 """
 import argparse
 
@@ -28,6 +32,7 @@ def main() -> int:
     ap.add_argument("--ffn", type=int, default=28672)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--push-parts", type=int, default=0, help="CTAs per (peer, chunk) of the push; 0 = auto")
+    ap.add_argument("--fp8", action="store_true", help="also time the block-scaled e4m3 forms")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     ab, world, distributed = setup()
@@ -121,6 +126,63 @@ def main() -> int:
                  "fused_spread": spread[-2], "baseline_spread": spread[-1],
                  "roof_us": bound, "roof_flops_us": t_flop, "roof_nvlink_us": t_link,
                  "frac_of_roof": bound / t_fused})
+    if args.fp8:
+        from aboleth_b200.ops import pack_scales_mx
+        from aboleth_b200.ops.moe_ops import quant_fp8
+
+        fp8 = torch.float8_e4m3fn
+        one = torch.ones((), device=dev)
+
+        def weight_fp8(weight):  # 128 x 128 power-of-two block scales
+            n, k = weight.shape
+            blocks = weight.float().view(n // 128, 128, k // 128, 128).abs().amax(dim=(1, 3)).clamp_min(1e-10)
+            scales = torch.exp2(torch.ceil(torch.log2(blocks / 448.0)))
+            full = scales.repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)
+            return (weight.float() / full).to(fp8), pack_scales_mx(scales, n, k, weight=True)
+
+        # all-gather -> GEMM, e4m3 shard + scale-factor atoms over NVLink
+        a_q, a_s = quant_fp8(a_local, round_scale=True)
+        a_packed = pack_scales_mx(a_s, m_local, args.hidden, weight=False)
+        b_q, b_packed = weight_fp8(b_col)
+        t_mx = timed(lambda: fused.mx(a_q, a_packed, b_q, b_packed, out))
+        fused.check()
+        gathered_q = torch.empty(args.tokens, args.hidden, dtype=fp8, device=dev)
+
+        def baseline_ag_fp8():
+            if distributed:
+                dist.all_gather_into_tensor(gathered_q.view(torch.uint8), a_q.view(torch.uint8))
+            else:
+                gathered_q.view(torch.uint8)[:m_local].copy_(a_q.view(torch.uint8))
+            torch._scaled_mm(gathered_q, b_q.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16, out=out)
+        t_base = timed(baseline_ag_fp8)
+        flops = 2.0 * args.tokens * args.hidden * (args.ffn // w)
+        link = (w - 1) * m_local * args.hidden * (1 + 1 / 32)
+        rows.append({"op": "all-gather -> GEMM, e4m3 block-scaled", "m": args.tokens, "k": args.hidden,
+                     "n": args.ffn // w, "fused_us": t_mx, "nccl_plus_cublaslt_fp8_us": t_base,
+                     "speedup": t_base / t_mx, "fused_spread": spread[-2], "baseline_spread": spread[-1],
+                     "fused_tflops": flops / t_mx / 1e6, "nvlink_bytes": link,
+                     "roof_nvlink_us": link / (NVLINK_GBS * 1e9) * 1e6,
+                     "over_bf16_fused": rows[1]["fused_us"] / t_mx})
+
+        # GEMM -> reduce-scatter on e4m3 operands (the partials still travel as bf16)
+        ar_q, ar_s = quant_fp8(a_row, round_scale=True)
+        ar_packed = pack_scales_mx(ar_s, args.tokens, k_local, weight=False)
+        br_q, br_packed = weight_fp8(b_row)
+        t_mx = timed(lambda: rs.mx(ar_q, ar_packed, br_q, br_packed, out_rs))
+        rs.check()
+
+        def baseline_rs_fp8():
+            torch._scaled_mm(ar_q, br_q.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16, out=partial)
+            if distributed:
+                dist.reduce_scatter_tensor(out_rs, partial)
+            else:
+                out_rs.copy_(partial[:m_local])
+        t_base = timed(baseline_rs_fp8)
+        flops = 2.0 * args.tokens * k_local * args.hidden
+        rows.append({"op": "GEMM -> reduce-scatter, e4m3 block-scaled", "m": args.tokens, "k": k_local,
+                     "n": args.hidden, "fused_us": t_mx, "nccl_plus_cublaslt_fp8_us": t_base,
+                     "speedup": t_base / t_mx, "fused_spread": spread[-2], "baseline_spread": spread[-1],
+                     "fused_tflops": flops / t_mx / 1e6, "over_bf16_fused": rows[2]["fused_us"] / t_mx})
     emit({"bench": "tp fused collectives", "n_gpus": w, "dtype": "bf16", "peaks": peaks, "rows": rows,
           "methodology": "L2 flushed before every timed launch; CUDA events after a busy-wait kernel; "
                          "median of steps; max over ranks"}, args.out)

@@ -152,15 +152,18 @@ def test_block_scaled_e4m3_gemm_matches_fp32(m, n, k, pow2):
     assert torch.equal(dequant_block_scaled(wide[:, :k], a_s), a_deq)
 
 
-def test_block_scaled_mx_gemm_is_exact_on_integers_and_flags_bad_scales():
+@pytest.mark.parametrize("tile,m,n,k", [("1", 300, 640, 512),     # 128 x 256 tiles: partial rows, 2.5 column tiles
+                                         ("2", 300, 640, 512),     # 256 x 192 tiles: tiles start at odd granules
+                                         ("2", 700, 1000, 384)])   # three row tiles, ragged last column tile
+def test_block_scaled_mx_gemm_is_exact_on_integers_and_flags_bad_scales(tile, m, n, k, monkeypatch):
     """Small integers and power-of-two scales: every product and partial sum is exact, so the
     tensor-core path must reproduce the fp32 result bit for bit (after the bf16 rounding of the
     output) - this pins the scale-factor layout: a wrong row or K segment changes the sum."""
     from aboleth_b200.ops import check_gemm_status, gemm_e4m3_block_scaled
     from aboleth_b200.ops.gemm import gemm_status
 
+    monkeypatch.setenv("ABOLETH_GEMM_MX_TILE", tile)
     g = torch.Generator(device="cuda").manual_seed(11)
-    m, n, k = 300, 640, 512      # partial row tile, 2.5 column tiles, four K blocks
     a = torch.randint(-2, 3, (m, k), generator=g, device="cuda").float()
     b = torch.randint(-2, 3, (n, k), generator=g, device="cuda").float()
     a_s = torch.exp2(torch.randint(-3, 4, (m, k // 128), generator=g, device="cuda").float())
@@ -180,3 +183,35 @@ def test_block_scaled_mx_gemm_is_exact_on_integers_and_flags_bad_scales():
     torch.cuda.synchronize()
     assert gemm_status(out.device)[:2].tolist() == [3, 0x3500]
     gemm_status(out.device).zero_()
+
+
+@pytest.mark.parametrize("counts", [[0, 5, 128, 200, 1, 131],        # small experts: 128-row tiles
+                                    [700, 0, 1031, 517, 300, 260]])   # 256-row tiles, ragged
+def test_grouped_block_scaled_gemm_is_exact_on_integers(counts):
+    """Expert-contiguous e4m3 rows (every expert on a 128-row boundary) times e4m3 expert weights, scales
+    applied by the tensor core.  Small integers and power-of-two scales make the result exact."""
+    from aboleth_b200.ops import check_gemm_status, grouped_gemm_e4m3_mx, pack_scales_mx
+
+    experts, n, k = len(counts), 640, 384
+    counts = torch.tensor(counts, dtype=torch.int32, device="cuda")
+    padded = (counts + 127) // 128 * 128
+    offsets = (torch.cumsum(padded, 0) - padded).to(torch.int32)
+    rows = int(padded.sum())
+    g = torch.Generator(device="cuda").manual_seed(17)
+    a = torch.randint(-2, 3, (rows, k), generator=g, device="cuda").float()
+    w = torch.randint(-2, 3, (experts, n, k), generator=g, device="cuda").float()
+    a_s = torch.exp2(torch.randint(-2, 3, (rows, k // 128), generator=g, device="cuda").float())
+    w_s = torch.exp2(torch.randint(-2, 3, (experts, n // 128, k // 128), generator=g, device="cuda").float())
+    fp8 = torch.float8_e4m3fn
+    out = torch.full((rows, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    grouped_gemm_e4m3_mx(a.to(fp8), pack_scales_mx(a_s, rows, k, weight=False), w.to(fp8),
+                         pack_scales_mx(w_s.view(experts * n // 128, k // 128), experts * n, k, weight=True),
+                         counts, offsets, out)
+    torch.cuda.synchronize()
+    check_gemm_status("cuda")
+    a_full = a * a_s.repeat_interleave(128, dim=1)
+    for e in range(experts):
+        lo, cnt = int(offsets[e]), int(counts[e])
+        w_full = w[e] * w_s[e].repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)
+        assert torch.equal(out[lo:lo + cnt], (a_full[lo:lo + cnt] @ w_full.t()).to(torch.bfloat16))
+        assert bool((out[lo + cnt:lo + int(padded[e])] == 7.0).all())   # padding rows are never written
