@@ -29,6 +29,8 @@ def main() -> int:
     ap.add_argument("--rounds", type=int, default=20)
     ap.add_argument("--chains", default="1,8,64")
     ap.add_argument("--max-lanes", type=int, default=32)
+    ap.add_argument("--graph-max", type=int, default=1 << 20,
+                    help="largest message for which the NCCL rounds are also timed as one captured CUDA graph")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     ab, world, distributed = setup()
@@ -99,6 +101,29 @@ def main() -> int:
             bus = (n - 1) * size / t / 1e9
             rows.append({"impl": "nccl all_to_all_single", "bytes_per_peer": size, "round_us": t * 1e6,
                          "busbw_gbs": bus, "frac_of_770": bus / NVLINK_GBS})
+            if size <= args.graph_max:
+                # The same rounds captured once in a CUDA graph: no per-round host launch cost, which is
+                # what the rounds-in-one-launch kernel above does not pay either.
+                try:
+                    graph = torch.cuda.CUDAGraph()
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side):
+                        with torch.cuda.graph(graph, stream=side):
+                            for _ in range(rounds):
+                                dist.all_to_all_single(view_out, view_in)
+                    torch.cuda.current_stream().wait_stream(side)
+                    graph.replay()
+                    torch.cuda.synchronize()
+                    t = timed(graph.replay, rounds)
+                    bus = (n - 1) * size / t / 1e9
+                    rows.append({"impl": "nccl all_to_all_single, graph-captured", "bytes_per_peer": size,
+                                 "rounds_per_graph": rounds, "round_us": t * 1e6, "busbw_gbs": bus,
+                                 "frac_of_770": bus / NVLINK_GBS})
+                    del graph
+                except RuntimeError as exc:   # a capture the library refuses is recorded, not fatal
+                    rows.append({"impl": "nccl all_to_all_single, graph-captured", "bytes_per_peer": size,
+                                 "error": str(exc)[:300]})
     emit({"bench": "alltoall+chains", "n_gpus": n, "rows": rows,
           "methodology": "rounds inside one launch; CUDA events; max over ranks; payload checked on device; "
                          "messages >= 128 MiB in total exceed L2, smaller ones are L2-resident by nature"},
