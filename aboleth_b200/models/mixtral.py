@@ -3,7 +3,10 @@
 Attention, norms and the router are replicated; every rank keeps ``experts / ranks``
 experts.  A MoE layer is: router logits -> top-k (own kernel) -> fused dispatch ->
 permute -> grouped expert GEMMs on tcgen05 (gate/up, SiLU-mul, down) -> fused combine
-with the gate weights applied inside the kernel.  Attention uses PyTorch's
+with the gate weights applied inside the kernel.  With ``fp8_experts=True`` the tokens are
+dispatched as e4m3 with 1 x 128 power-of-two scales, the expert weights are e4m3 with 128 x 128
+scales, and both grouped GEMMs run on the block-scaled tensor-core path (DeepSeek-V3's recipe);
+nothing is expanded to bf16 on the way.  Attention uses PyTorch's
 scaled-dot-product attention with a static KV cache; it is not one of this
 framework's kernels.
 
@@ -18,7 +21,8 @@ import torch
 import torch.nn.functional as F
 
 from ..integrations.vllm_all2all import AbolethAll2AllManager, AbolethPrepareAndFinalize
-from ..ops import expert_offsets, grouped_gemm_bf16, permute, router_topk
+from ..ops import (expert_offsets, grouped_gemm_bf16, grouped_gemm_e4m3_mx, pack_scales_mx, permute, quant_fp8,
+                   router_topk)
 from ..world import World
 
 
@@ -66,8 +70,12 @@ def _rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tenso
 
 class MixtralEP:
     def __init__(self, config: MixtralConfig, world: World, *, max_batch: int, max_prompt: int,
-                 seed: int = 0, manager: Optional[AbolethAll2AllManager] = None, cpu_group=None):
+                 seed: int = 0, manager: Optional[AbolethAll2AllManager] = None, cpu_group=None,
+                 fp8_experts: bool = False):
         c = self.config = config
+        self.fp8_experts = fp8_experts
+        if fp8_experts and (c.hidden % 128 or c.ffn % 128):
+            raise ValueError("fp8 experts need hidden and ffn sizes that are multiples of 128")
         self.world = world
         dev = self.device = world.torch_device
         ranks = world.world_size
@@ -101,21 +109,82 @@ class MixtralEP:
         facts = dict(dtype=torch.bfloat16, num_experts=c.experts, num_local_experts=self.local_experts,
                      num_max_tokens_per_rank=self.capacity, hidden=c.hidden, num_topk=c.top_k,
                      decode_bound=max_batch, min_tokens_per_rank=max_batch)
+        if fp8_experts:
+            facts.update(quant_dtype=torch.float8_e4m3fn, quant_block_shape=[128, 128], quant_round_scale=True)
         self.moe = AbolethPrepareAndFinalize(self.manager, facts, layer_name="moe")
         rows = ranks * self.capacity * min(c.top_k, self.local_experts)
-        self.x_perm = torch.zeros(rows, c.hidden, dtype=torch.bfloat16, device=dev)
-        self.h13 = torch.empty(rows, 2 * c.ffn, dtype=torch.bfloat16, device=dev) if rows * c.ffn < 2 ** 31 \
-            else None
+        if fp8_experts:
+            # Every expert's group starts on a 128-row boundary (a scale-factor atom covers 128 rows).
+            rows = (rows + self.local_experts * 127 + 127) // 128 * 128
+            for layer in self.layers:
+                for name in ("w13", "w2"):
+                    layer[name + "_q"], layer[name + "_scales"], layer[name + "_packed"] = \
+                        self._quantise_weight(layer[name])
+            self.x_perm = torch.zeros(rows, c.hidden, dtype=torch.float8_e4m3fn, device=dev)
+            # Padding rows are never written; ones / zeros keep their scales and activations finite.
+            self.x_scales = torch.ones(rows, c.hidden // 128, dtype=torch.float32, device=dev)
+            self.h13 = torch.zeros(rows, 2 * c.ffn, dtype=torch.bfloat16, device=dev)
+        else:
+            self.x_perm = torch.zeros(rows, c.hidden, dtype=torch.bfloat16, device=dev)
+            self.h13 = torch.empty(rows, 2 * c.ffn, dtype=torch.bfloat16, device=dev) \
+                if rows * c.ffn < 2 ** 31 else None
         self.y_perm = torch.empty(rows, c.hidden, dtype=torch.bfloat16, device=dev)
         self.kv = torch.zeros(c.layers, 2, max_batch, c.kv_heads, c.max_seq, c.head_dim,
                               dtype=torch.bfloat16, device=dev)
 
+    @staticmethod
+    def _quantise_weight(w: torch.Tensor):
+        """bf16 ``[E, N, K]`` -> (e4m3 weights, fp32 128 x 128 power-of-two scales ``[E, N/128, K/128]``,
+        the scales packed for the tensor core)."""
+        experts, n, k = w.shape
+        blocks = w.float().view(experts, n // 128, 128, k // 128, 128)
+        scales = torch.exp2(torch.ceil(torch.log2(blocks.abs().amax(dim=(2, 4)).clamp_min(1e-10) / 448.0)))
+        q = (blocks / scales[:, :, None, :, None]).view(experts, n, k).to(torch.float8_e4m3fn).contiguous()
+        packed = pack_scales_mx(scales.view(experts * n // 128, k // 128).contiguous(), experts * n, k, weight=True)
+        return q, scales, packed
+
+    def dequantised_experts(self, layer: dict):
+        """The bf16 weights the fp8 experts stand for (tests)."""
+        out = []
+        for name in ("w13", "w2"):
+            q, scales = layer[name + "_q"], layer[name + "_scales"]
+            full = scales.repeat_interleave(128, dim=1).repeat_interleave(128, dim=2)
+            out.append((q.float() * full).to(torch.bfloat16))
+        return out
+
     # -- one MoE layer --------------------------------------------------------------------
+    def _moe_layer_fp8(self, x: torch.Tensor, layer: dict, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        c = self.config
+        prepared = self.moe.prepare(x, weights, ids, quantized_input=True)
+        slot = self.moe.runtime.selected[0]
+        spec = slot.spec
+        offsets, _ = expert_offsets(slot.expert_counts_by_source, align=128)
+        permute(prepared.expert_input, self.x_perm, prepared.global_ids, prepared.expert_pos, offsets,
+                prepared.recv_counts, world=spec.ranks, capacity=spec.capacity, src_scales=prepared.scales,
+                dst_scales=self.x_scales)
+        lo, hi = self.first_expert, self.first_expert + self.local_experts
+        # Experts of other ranks hold no rows here, so the scan over all experts leaves the local groups packed.
+        counts, offs = slot.expert_counts[lo:hi], offsets[0, lo:hi]
+        live = spec.ranks * spec.capacity * min(c.top_k, self.local_experts)
+        rows = min(self.x_perm.shape[0], (live + self.local_experts * 127 + 127) // 128 * 128)
+        xp, h13 = self.x_perm[:rows], self.h13[:rows]
+        grouped_gemm_e4m3_mx(xp, pack_scales_mx(self.x_scales[:rows], rows, c.hidden, weight=False),
+                             layer["w13_q"], layer["w13_packed"], counts, offs, h13)
+        act = (F.silu(h13[:, : c.ffn]) * h13[:, c.ffn:]).contiguous()
+        act_q, act_s = quant_fp8(act, round_scale=True)
+        grouped_gemm_e4m3_mx(act_q, pack_scales_mx(act_s, rows, c.ffn, weight=False), layer["w2_q"],
+                             layer["w2_packed"], counts, offs, self.y_perm[:rows])
+        out = torch.empty(x.shape[0], c.hidden, dtype=torch.bfloat16, device=x.device)
+        self.moe.finalize(out, self.y_perm, expert_offsets=offsets)
+        return out
+
     def moe_layer(self, x: torch.Tensor, layer: dict) -> torch.Tensor:
         c = self.config
         tokens = x.shape[0]
         logits = (x @ layer["router"].t()).float().contiguous()
         ids, weights = router_topk(logits, c.top_k, renormalize=True)
+        if self.fp8_experts:
+            return self._moe_layer_fp8(x, layer, ids, weights)
         prepared = self.moe.prepare(x, weights, ids)
         slot = self.moe.runtime.selected[0]
         spec = slot.spec

@@ -65,3 +65,35 @@ def test_decode_graph_replays_the_eager_step():
         model.check()
         assert torch.equal(eager, graphed)
         assert ((a - b).norm() / a.norm()).item() < 2e-2
+
+
+def test_fp8_experts_run_block_scaled_end_to_end():
+    """e4m3 dispatch with power-of-two 1 x 128 scales -> permute with scales -> grouped block-scaled
+    GEMMs against e4m3 weights with 128 x 128 scales -> combine.  The oracle multiplies the
+    dequantised weights in fp32; the difference is the e4m3 rounding of the activations."""
+    import aboleth_b200 as ab
+    from aboleth_b200.models import MixtralConfig, MixtralEP
+    from aboleth_b200.ops import check_gemm_status
+
+    cfg = MixtralConfig(layers=1, hidden=256, experts=4, top_k=2, ffn=512, heads=4, kv_heads=2,
+                        vocab=128, max_seq=64)
+    with ab.World(0, 1, device=0) as world:
+        world.connect_all("p2p")
+        model = MixtralEP(cfg, world, max_batch=4, max_prompt=16, seed=3, fp8_experts=True)
+        g = torch.Generator(device="cuda").manual_seed(1)
+        x = torch.randn(37, 256, generator=g, device="cuda").to(torch.bfloat16)
+        layer = model.layers[0]
+        w13, w2 = model.dequantised_experts(layer)
+        for tokens in (37, 3):     # the prefill variant, then the decode-sized one
+            got = model.moe_layer(x[:tokens].contiguous(), layer).float()
+            want = model.reference_moe_layer(x[:tokens], layer, w13, w2)
+            torch.cuda.synchronize()
+            model.check()
+            check_gemm_status("cuda")
+            rel = ((got - want).norm() / want.norm()).item()
+            assert rel < 6e-2, rel
+        out = model.generate(torch.randint(0, 128, (4, 16), generator=g, device="cuda"), 3)
+        torch.cuda.synchronize()
+        model.check()
+        check_gemm_status("cuda")
+        assert out.shape == (4, 3)
