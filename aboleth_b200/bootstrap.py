@@ -268,6 +268,12 @@ class TcpStoreBootstrap:
     def _key(self, sequence: int, tag: str, rank: int) -> str:
         return f"aboleth/{sequence}/{tag}/{rank}"
 
+    @property
+    def store(self):
+        """The key-value store behind the collectives (``set`` / ``get`` / ``add``), for small
+        out-of-band messages between the same ranks; ``None`` once closed."""
+        return self._store
+
     def all_gather(self, tag: str, payload: bytes) -> dict[int, bytes]:
         if self._store is None:
             raise RuntimeError("Aboleth TCP bootstrap is closed")

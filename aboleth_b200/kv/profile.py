@@ -36,6 +36,21 @@ class KVRuntimeOverrides:
     copy_engine_threshold: Optional[int] = None
     consumers_per_readiness: Optional[int] = None
 
+    @classmethod
+    def from_mapping(cls, values) -> "KVRuntimeOverrides":
+        """From an engine's free-form connector options (``aboleth_kv_<field>`` or ``<field>``); absent
+        keys stay unset, present ones must be positive integers."""
+        chosen = {}
+        for name in ("copy_workers", "copy_engine_threshold", "consumers_per_readiness"):
+            raw = values.get(f"aboleth_kv_{name}", values.get(name))
+            if raw is None:
+                continue
+            number = int(raw)
+            if number < 1:
+                raise ValueError(f"KV runtime override {name}={raw!r} must be a positive integer")
+            chosen[name] = number
+        return cls(**chosen)
+
 
 def select_kv_target_profile(device_name: str = "", *, overrides: Optional[KVRuntimeOverrides] = None,
                              name: Optional[str] = None) -> KVTargetProfile:
