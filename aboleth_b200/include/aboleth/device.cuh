@@ -122,10 +122,10 @@ inline constexpr std::uint32_t kOnlyKind = ~0u;  // both kinds, chosen per call
 
 // Is this endpoint peer memory / the host ring?  Constant in a specialised library.
 __device__ __forceinline__ bool is_p2p(const PeerRef &ref) {
-    return kOnlyKind == ~0u ? detail::is_p2p(ref) : kOnlyKind == abi::kKindP2P;
+    return kOnlyKind == ~0u ? ref.kind == abi::kKindP2P : kOnlyKind == abi::kKindP2P;
 }
 __device__ __forceinline__ bool is_proxy(const PeerRef &ref) {
-    return kOnlyKind == ~0u ? detail::is_proxy(ref) : kOnlyKind == abi::kKindProxy;
+    return kOnlyKind == ~0u ? ref.kind == abi::kKindProxy : kOnlyKind == abi::kKindProxy;
 }
 
 __device__ __forceinline__ std::uint64_t globaltimer_ns() {
