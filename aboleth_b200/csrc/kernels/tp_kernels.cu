@@ -7,9 +7,12 @@
 //   main loop of the rank's own rows.  The item that completes a 256-row chunk for a
 //   peer publishes it with one release flag.  The TMA producer of a tile whose rows came from rank s waits
 //   (bounded) on the chunk's flag and then loads the tile from LOCAL staging -
-//   a remote tile crosses NVLink once, TMA never touches peer memory, nothing
-//   is multicast.  Tiles of the rank's own rows read A_local through a second
-//   tensor map and start at once; remote sources follow in arrival order.
+//   a remote tile crosses NVLink once and TMA never touches peer memory.  Tiles of the
+//   rank's own rows read A_local through a second tensor map and start at once; remote
+//   sources follow in arrival order.  When the staging buffers of all ranks are bound to one
+//   NVLink multicast object the push uses `multimem.st` instead: one store per 16 bytes
+//   is replicated by NVSwitch into every rank's staging, so the shard leaves the GPU once
+//   instead of world - 1 times (the flags stay one release store per receiver).
 //
 // GEMM -> REDUCE-SCATTER   out[Ml, N] = sum_ranks(A_local[world*Ml, Kl] * B_local[N, Kl]^T)[own rows]
 //   The epilogue converts each fp32 accumulator tile from TMEM to bf16 into a per-CTA
@@ -79,6 +82,9 @@ struct AgGemmPolicyT {
     // gathered atoms start inside a staging buffer (behind the gathered rows).
     const std::uint8_t *sfa_local = nullptr;
     std::size_t staging_sfa_offset = 0;
+    // Multicast address of the staging buffers (0 = none): one multimem store per 16 bytes reaches every
+    // peer's staging through NVSwitch, so the shard leaves this GPU once instead of world - 1 times.
+    std::uint64_t mc_staging = 0;
 
     __device__ __forceinline__ bool next(int it, Tile &t) const {
         if (!(phases & kPhaseConsume))
@@ -121,44 +127,59 @@ struct AgGemmPolicyT {
     __device__ __forceinline__ void finish(int, int, unsigned long long *) const {}
 
     // One push item = (peer, chunk, part), nearest peer first; the item that arrives last on
-    // (peer, chunk) publishes the chunk.  Called by the 128 epilogue threads together.
+    // (peer, chunk) publishes the chunk.  With a multicast mapping an item is (chunk, part): its
+    // stores reach every peer at once and the last part publishes the chunk to each peer in turn.
+    // Called by the 128 epilogue threads together.
     __device__ __forceinline__ bool background(int thread, int nthreads) {
         if (!(phases & kPhaseProduce))
             return false;
+        const bool multicast = mc_staging != 0;
         const int item = blockIdx.x + pushed * gridDim.x;
-        if (item >= (world - 1) * chunks * parts)
+        if (item >= (multicast ? 1 : world - 1) * chunks * parts)
             return false;
         ++pushed;
         const std::size_t row_bytes = static_cast<std::size_t>(k) * ESIZE;
         const int part = item % parts;
         const int pc = item / parts;
         const int hop = pc / chunks + 1, chunk = pc - (hop - 1) * chunks;
-        const int peer = (rank + hop) % world;
+        const int peer = (rank + hop) % world;     // unicast only
         const int rows = min(kRows, m_local - chunk * kRows);
         const int per = (rows + parts - 1) / parts;
         const int r0 = min(part * per, rows), r1 = min(r0 + per, rows);
         const std::size_t offset = (static_cast<std::size_t>(chunk) * kRows + r0) * row_bytes;
-        std::uint8_t *dst = reinterpret_cast<std::uint8_t *>(peer_staging[peer]) +
-                            static_cast<std::size_t>(rank) * m_local * row_bytes + offset;
-        aboleth::detail::copy_strided(dst, a_local + offset, (r1 - r0) * row_bytes, thread, nthreads);
+        const std::size_t shard = static_cast<std::size_t>(rank) * m_local * row_bytes;
+        std::uint8_t *base = reinterpret_cast<std::uint8_t *>(multicast ? mc_staging : peer_staging[peer]);
+        if (multicast)
+            aboleth::detail::copy_strided_multicast(base + shard + offset, a_local + offset, (r1 - r0) * row_bytes,
+                                                    thread, nthreads);
+        else
+            aboleth::detail::copy_strided(base + shard + offset, a_local + offset, (r1 - r0) * row_bytes, thread,
+                                          nthreads);
         if constexpr (ESIZE == 1) {
             if (part == 0) {  // the chunk's scale factors: two row blocks of K / 128 atoms
                 const std::size_t chunk_sf = static_cast<std::size_t>(kRows / BM) * (k / KBLK) * mx::kAtomBytes;
-                std::uint8_t *sf_dst = reinterpret_cast<std::uint8_t *>(peer_staging[peer]) + staging_sfa_offset +
+                std::uint8_t *sf_dst = base + staging_sfa_offset +
                                        (static_cast<std::size_t>(rank) * chunks + chunk) * chunk_sf;
-                aboleth::detail::copy_strided(sf_dst, sfa_local + chunk * chunk_sf, chunk_sf, thread, nthreads);
+                if (multicast)
+                    aboleth::detail::copy_strided_multicast(sf_dst, sfa_local + chunk * chunk_sf, chunk_sf, thread,
+                                                            nthreads);
+                else
+                    aboleth::detail::copy_strided(sf_dst, sfa_local + chunk * chunk_sf, chunk_sf, thread, nthreads);
             }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (thread == 0) {
             aboleth::detail::fence_acq_rel_sys();
-            unsigned *counter = arrivals + peer * chunks + chunk;
+            unsigned *counter = arrivals + (multicast ? 0 : peer) * chunks + chunk;
             if (atomicAdd(counter, 1u) == static_cast<unsigned>(parts) - 1) {
                 *counter = 0;  // self-cleaning
                 aboleth::detail::fence_acq_rel_sys();
-                std::uint64_t *flag = reinterpret_cast<std::uint64_t *>(peer_flags[peer]) +
-                                      rank * chunks + chunk;
-                aboleth::detail::st_release_sys(flag, epoch);
+                for (int p = multicast ? 0 : peer; p < (multicast ? world : peer + 1); ++p) {
+                    if (p == rank)
+                        continue;
+                    std::uint64_t *flag = reinterpret_cast<std::uint64_t *>(peer_flags[p]) + rank * chunks + chunk;
+                    aboleth::detail::st_release_sys(flag, epoch);
+                }
             }
         }
         return true;
@@ -433,14 +454,17 @@ int sm_count() {
 
 // a_local [m_local, k]; staging [world*m_local, k] (this rank's gathered-A buffer, peers write it);
 // b [n, k]; c [world*m_local, n].  m_local must be a multiple of 256.  peer_staging / peer_flags:
-// device int64 [world] address tables; flags: local int64 [world * m_local/256].
+// device int64 [world] address tables; flags: local int64 [world * m_local/256].  mc_staging: the
+// multicast address of the ranks' staging buffers (all bound at the same offset of one NVLink
+// multicast object), or 0 to push with one peer store per receiver.
 AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const void *b, void *c,
                               const std::uint64_t *peer_staging, const std::uint64_t *peer_flags,
                               const std::uint64_t *flags, unsigned long long *status,
                               unsigned *arrivals, std::uint64_t epoch, int rank, int world, int m_local,
-                              int n, int k, int parts, int phases, cudaStream_t stream) {
+                              int n, int k, int parts, int phases, std::uint64_t mc_staging,
+                              cudaStream_t stream) {
     if (world < 1 || m_local < kRows || m_local % kRows || n < 8 || n % 8 || k < 8 || k % 8 || rank < 0 ||
-        rank >= world)
+        rank >= world || (mc_staging & 15))
         return -1;
     CUtensorMap map_staging, map_b, map_local;
     if (!make_map_bf16(&map_staging, staging, static_cast<std::uint64_t>(world) * m_local, k, k, kRows) ||
@@ -459,6 +483,7 @@ AB_EXPORT int ab_ag_gemm_bf16(const void *a_local, const void *staging, const vo
     AgGemmPolicy p{static_cast<__nv_bfloat16 *>(c), flags, status, epoch, rank, world, m_local, n, k, n,
                    phases, (n + BN - 1) / BN, chunks, raster_group(n, k),
                    static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, arrivals, parts, 0};
+    p.mc_staging = mc_staging;
     ag_gemm_kernel<<<sm_count(), kThreads, kSmem, stream>>>(map_staging, map_b, map_local, p);
     return ab::launch_result("ag_gemm_bf16");
 }
@@ -477,9 +502,9 @@ AB_EXPORT int ab_ag_gemm_e4m3_mx(const void *a_local, const void *sfa_local, con
                                  const std::uint64_t *peer_flags, const std::uint64_t *flags,
                                  unsigned long long *status, unsigned *arrivals, std::uint64_t epoch, int rank,
                                  int world, int m_local, int n, int k, int parts, int phases,
-                                 cudaStream_t stream) {
+                                 std::uint64_t mc_staging, cudaStream_t stream) {
     if (world < 1 || m_local < kRows || m_local % kRows || n < 8 || n % 8 || k < 128 || k % 128 || rank < 0 ||
-        rank >= world || sfa_local == nullptr || sfb == nullptr)
+        rank >= world || sfa_local == nullptr || sfb == nullptr || (mc_staging & 15))
         return -1;
     constexpr int kCols = mx::MxGeometry<kHalves>::kCols;
     constexpr unsigned smem = mx::MxGeometry<kHalves>::kSmemBytes;
@@ -499,7 +524,7 @@ AB_EXPORT int ab_ag_gemm_e4m3_mx(const void *a_local, const void *sfa_local, con
                      phases, (n + kCols - 1) / kCols, chunks, raster_group(n, k, kCols, 1),
                      static_cast<const std::uint8_t *>(a_local), peer_staging, peer_flags, arrivals, parts, 0,
                      static_cast<const std::uint8_t *>(sfa_local),
-                     static_cast<std::size_t>(world) * m_local * k};
+                     static_cast<std::size_t>(world) * m_local * k, mc_staging};
     const mx::ScaleFactors sf{static_cast<const std::uint8_t *>(staging) + p.staging_sfa_offset,
                               static_cast<const std::uint8_t *>(sfb), k / 128, mx::mx_granules(n),
                               static_cast<const std::uint8_t *>(sfa_local)};

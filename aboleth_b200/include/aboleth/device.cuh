@@ -239,6 +239,34 @@ __device__ __forceinline__ void copy_strided(
     }
 }
 
+// One 16-byte store to a multicast address: NVSwitch replicates it into the same offset of every
+// GPU bound to the multicast object (this one included), so a broadcast leaves the GPU once.
+__device__ __forceinline__ void st_multicast16(void *multicast, const uint4 &v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(multicast),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// copy_strided onto a multicast address (both 16-byte aligned, `bytes` a multiple of 16).  The
+// stores are relaxed: publish with a release flag per receiver after a barrier, like any put.
+__device__ __forceinline__ void copy_strided_multicast(
+    std::uint8_t *multicast, const std::uint8_t *src, std::uint64_t bytes, unsigned tid, unsigned nthreads) {
+    const std::uint64_t vecs = bytes >> 4;
+    std::uint64_t i = tid;
+    for (; i + 3ull * nthreads < vecs; i += 4ull * nthreads) {
+        uint4 a = ld_stream16(src + (i << 4));
+        uint4 b = ld_stream16(src + ((i + nthreads) << 4));
+        uint4 c = ld_stream16(src + ((i + 2ull * nthreads) << 4));
+        uint4 d = ld_stream16(src + ((i + 3ull * nthreads) << 4));
+        st_multicast16(multicast + (i << 4), a);
+        st_multicast16(multicast + ((i + nthreads) << 4), b);
+        st_multicast16(multicast + ((i + 2ull * nthreads) << 4), c);
+        st_multicast16(multicast + ((i + 3ull * nthreads) << 4), d);
+    }
+    for (; i < vecs; i += nthreads)
+        st_multicast16(multicast + (i << 4), ld_stream16(src + (i << 4)));
+}
+
 }  // namespace detail
 
 }  // namespace aboleth

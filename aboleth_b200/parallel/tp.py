@@ -21,9 +21,9 @@ import torch
 from ..ops._kernels import _I, _U64, _VP, call, declare, lib, ptr, stream_ptr
 from ..world import World
 
-declare("ab_ag_gemm_bf16", [_VP] * 9 + [_U64] + [_I] * 7 + [_VP])
+declare("ab_ag_gemm_bf16", [_VP] * 9 + [_U64] + [_I] * 7 + [_U64, _VP])
 declare("ab_gemm_rs_bf16", [_VP] * 9 + [_U64] + [_I] * 6 + [_VP])
-declare("ab_ag_gemm_e4m3_mx", [_VP] * 11 + [_U64] + [_I] * 7 + [_VP])
+declare("ab_ag_gemm_e4m3_mx", [_VP] * 11 + [_U64] + [_I] * 7 + [_U64, _VP])
 declare("ab_gemm_rs_e4m3_mx", [_VP] * 11 + [_U64] + [_I] * 6 + [_VP])
 
 PRODUCE, CONSUME = 1, 2
@@ -72,11 +72,13 @@ class AllGatherGemm:
     """Column-parallel linear layer whose input is sharded by rows across ranks."""
 
     def __init__(self, rank: int, world_size: int, m_local: int, k: int, buffers: _Buffers,
-                 tables, *, push_parts: int = 0):
+                 tables, *, push_parts: int = 0, multicast: Optional[Sequence[int]] = None):
         if m_local % BM:
             raise ValueError("rows per rank must be a multiple of 256")
         self.rank, self.world_size, self.m_local, self.k = rank, world_size, m_local, k
         self.buffers, self.tables, self.push_parts = buffers, tables, push_parts  # 0: items of ~64 KiB
+        # Multicast address of each of the two staging buffers (0: push with one store per peer).
+        self.multicast = tuple(multicast) if multicast is not None else (0, 0)
         self.status = torch.zeros(2, dtype=torch.int64, device=buffers.arena.device)
         # Sender-side arrival counters of the push, one per (peer, chunk); the kernel resets them.
         self.arrivals = torch.zeros(world_size * (m_local // BM), dtype=torch.int32,
@@ -86,6 +88,25 @@ class AllGatherGemm:
     @staticmethod
     def arena_bytes(world_size: int, m_local: int, k: int) -> int:
         return _Buffers.nbytes(world_size * m_local * k * 2, world_size * (m_local // BM))
+
+    @classmethod
+    def create_multicast(cls, world: World, m_local: int, k: int, *, group=None, **kw) -> "AllGatherGemm":
+        """Like :meth:`create`, with the staging buffers in symmetric memory bound to an NVLink
+        multicast object (:class:`aboleth_b200.symmetric.SymmetricArena`): the shard is pushed with
+        ``multimem.st`` and leaves this GPU once instead of ``world - 1`` times.  Needs an
+        initialised ``torch.distributed`` group over the same ranks; falls back to peer stores
+        through the symmetric mappings when the fabric offers no multicast."""
+        from ..symmetric import SymmetricArena
+        n = world.world_size
+        arena = SymmetricArena(cls.arena_bytes(n, m_local, k), world.torch_device, group)
+        if arena.rank != world.rank or arena.world_size != n:
+            raise ValueError("the process group and the world disagree on rank or size")
+        buffers = _Buffers(arena.tensor, n * m_local * k * 2, n * (m_local // BM))
+        tables = [(arena.addresses(buffers.offsets[i][0]), arena.addresses(buffers.offsets[i][1])) for i in range(2)]
+        obj = cls(world.rank, n, m_local, k, buffers, tables,
+                  multicast=[arena.multicast(buffers.offsets[i][0]) for i in range(2)], **kw)
+        obj._arena = arena
+        return obj
 
     @classmethod
     def create(cls, world: World, m_local: int, k: int, *, tag: str = "ag_gemm", **kw) -> "AllGatherGemm":
@@ -115,7 +136,7 @@ class AllGatherGemm:
         call("ab_ag_gemm_bf16", ptr(a_local), ptr(self.buffers.data(which)), ptr(b_local), ptr(out),
              ptr(peer_data), ptr(peer_flags), ptr(self.buffers.flags(which)), ptr(self.status),
              ptr(self.arrivals), (self.epoch + 1) // 2, self.rank, self.world_size, self.m_local, n,
-             self.k, self.push_parts, phases, stream_ptr())
+             self.k, self.push_parts, phases, self.multicast[which], stream_ptr())
         return out
 
     def mx(self, a_q: torch.Tensor, a_packed: torch.Tensor, b_q: torch.Tensor, b_packed: torch.Tensor,
@@ -143,7 +164,7 @@ class AllGatherGemm:
         call("ab_ag_gemm_e4m3_mx", ptr(a_q), ptr(a_packed), ptr(self.buffers.data(which)), ptr(b_q),
              ptr(b_packed), ptr(out), ptr(peer_data), ptr(peer_flags), ptr(self.buffers.flags(which)),
              ptr(self.status), ptr(self.arrivals), (self.epoch + 1) // 2, self.rank, self.world_size,
-             self.m_local, n, self.k, self.push_parts, phases, stream_ptr())
+             self.m_local, n, self.k, self.push_parts, phases, self.multicast[which], stream_ptr())
         return out
 
     def block_scaled(self, a_q: torch.Tensor, a_scales: torch.Tensor, b_local: torch.Tensor,

@@ -33,6 +33,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--push-parts", type=int, default=0, help="CTAs per (peer, chunk) of the push; 0 = auto")
     ap.add_argument("--fp8", action="store_true", help="also time the block-scaled e4m3 forms")
+    ap.add_argument("--multicast", action="store_true",
+                    help="also time the all-gather -> GEMM with its push through an NVLink multicast mapping")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     ab, world, distributed = setup()
@@ -101,6 +103,15 @@ def main() -> int:
                  "roof_us": bound, "roof_flops_us": t_flop, "roof_nvlink_us": t_link,
                  "frac_of_roof": bound / t_fused})
 
+    fused_mc = None
+    if args.multicast and distributed:
+        fused_mc = AllGatherGemm.create_multicast(world, m_local, args.hidden, push_parts=args.push_parts)
+        t_mc = timed(lambda: fused_mc(a_local, b_col, out))
+        fused_mc.check()
+        rows.append({"op": "all-gather -> GEMM, multimem push", "multicast_mapping": bool(fused_mc.multicast[0]),
+                     "fused_us": t_mc, "fused_spread": spread[-1], "over_peer_store_push": t_fused / t_mc,
+                     "speedup_vs_nccl_plus_cublas": t_base / t_mc, "frac_of_roof": bound / t_mc})
+
     # ---- GEMM -> reduce-scatter ----
     k_local = args.ffn // w
     a_row = torch.randn(args.tokens, k_local, generator=g, device=dev).to(torch.bfloat16)
@@ -164,6 +175,14 @@ def main() -> int:
                      "roof_nvlink_us": link / (NVLINK_GBS * 1e9) * 1e6,
                      "over_bf16_fused": rows[1]["fused_us"] / t_mx})
 
+        if fused_mc is not None:
+            t_mc = timed(lambda: fused_mc.mx(a_q, a_packed, b_q, b_packed, out))
+            fused_mc.check()
+            rows.append({"op": "all-gather -> GEMM, e4m3 block-scaled, multimem push",
+                         "multicast_mapping": bool(fused_mc.multicast[0]), "fused_us": t_mc,
+                         "fused_spread": spread[-1], "over_peer_store_push": t_mx / t_mc,
+                         "fused_tflops": flops / t_mc / 1e6})
+
         # GEMM -> reduce-scatter on e4m3 operands (the partials still travel as bf16)
         ar_q, ar_s = quant_fp8(a_row, round_scale=True)
         ar_packed = pack_scales_mx(ar_s, args.tokens, k_local, weight=False)
@@ -186,6 +205,8 @@ def main() -> int:
     emit({"bench": "tp fused collectives", "n_gpus": w, "dtype": "bf16", "peaks": peaks, "rows": rows,
           "methodology": "L2 flushed before every timed launch; CUDA events after a busy-wait kernel; "
                          "median of steps; max over ranks"}, args.out)
+    if fused_mc is not None:
+        fused_mc._arena.close()
     teardown(world, distributed)
     return 0
 

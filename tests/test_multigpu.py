@@ -177,3 +177,100 @@ def test_endpoint_probe_two_gpus():
         assert reason is None and senders == 2
         assert profile is None or profile[0] in (4, 16)
     assert results[0][1] == results[1][1]  # the fit uses world rates: every rank derives the same profile
+
+
+def _tp_rank(rank, world_size, multicast):
+    """Both fused TP kernels on real peers, bf16 and block-scaled e4m3; with ``multicast`` the
+    all-gather pushes through an NVLink multicast mapping (``multimem.st``)."""
+    ab, boot, world = _setup(rank, world_size)
+    import torch.distributed as dist
+
+    from aboleth_b200.ops import pack_scales_mx
+    from aboleth_b200.parallel import AllGatherGemm, GemmReduceScatter
+    from aboleth_b200.symmetric import multicast_supported
+
+    if multicast:
+        if not multicast_supported():
+            world.close()
+            return "no multicast on this fabric"
+        port = int(os.environ["MASTER_PORT"]) + 1
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world_size,
+                                device_id=torch.device("cuda", rank))
+    m_local, k, n = 512, 1024, 520
+    g = torch.Generator(device="cuda").manual_seed(11)            # same seed: every rank knows every shard
+    shards = [torch.randint(-2, 3, (m_local, k), generator=g, device="cuda").float() for _ in range(world_size)]
+    scales = [torch.exp2(torch.randint(-2, 3, (m_local, k // 128), generator=g, device="cuda").float())
+              for _ in range(world_size)]
+    b = torch.randint(-2, 3, (n, k), generator=g, device="cuda").float()
+    b_s = torch.exp2(torch.randint(-2, 3, (-(-n // 128), k // 128), generator=g, device="cuda").float())
+    ag = (AllGatherGemm.create_multicast if multicast else AllGatherGemm.create)(world, m_local, k)
+    used_multicast = bool(ag.multicast[0])
+    boot.barrier("created")
+    fp8 = torch.float8_e4m3fn
+    ok = True
+    # bf16: small integers are exact in bf16 and in the fp32 accumulator
+    full = torch.cat(shards)
+    for _ in range(3):
+        out = ag(shards[rank].to(torch.bfloat16), b.to(torch.bfloat16))
+        torch.cuda.synchronize()
+        boot.barrier("ag")
+    ag.check()
+    ok = ok and bool(torch.equal(out, (full @ b.t()).to(torch.bfloat16)))
+    # block-scaled e4m3: the shard crosses with its scale-factor atoms
+    b_full = b * b_s.repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)
+    a_full = torch.cat([shards[r] * scales[r].repeat_interleave(128, dim=1) for r in range(world_size)])
+    for _ in range(2):
+        out = ag.mx(shards[rank].to(fp8), pack_scales_mx(scales[rank], m_local, k, weight=False), b.to(fp8),
+                    pack_scales_mx(b_s, n, k, weight=True))
+        torch.cuda.synchronize()
+        boot.barrier("ag_mx")
+    ag.check()
+    ok = ok and bool(torch.equal(out, (a_full @ b_full.t()).to(torch.bfloat16)))
+    if not multicast:
+        rs = GemmReduceScatter.create(world, m_local, n)
+        gk = torch.Generator(device="cuda").manual_seed(100 + rank)
+        a_part = torch.randint(-2, 3, (world_size * m_local, k), generator=gk, device="cuda").float()
+        a_sc = torch.exp2(torch.randint(-2, 3, (world_size * m_local, k // 128), generator=gk, device="cuda").float())
+        for _ in range(2):
+            got = rs.mx(a_part.to(fp8), pack_scales_mx(a_sc, world_size * m_local, k, weight=False), b.to(fp8),
+                        pack_scales_mx(b_s, n, k, weight=True))
+            torch.cuda.synchronize()
+            boot.barrier("rs_mx")
+        rs.check()
+        partial = ((a_part * a_sc.repeat_interleave(128, dim=1)) @ b_full.t()).to(torch.bfloat16).float()
+        gathered = [torch.zeros_like(partial) for _ in range(world_size)]
+        # the oracle needs every rank's partial: exchange them through the store as bytes
+        blobs = boot.all_gather("partials", partial.cpu().numpy().tobytes())
+        import numpy as np
+        for r in range(world_size):
+            gathered[r] = torch.from_numpy(np.frombuffer(blobs[r], dtype=np.float32).copy()).view_as(partial).cuda()
+        want = sum(gathered)[rank * m_local:(rank + 1) * m_local].to(torch.bfloat16)
+        ok = ok and bool(torch.equal(got, want))
+    boot.barrier("done")
+    if multicast:
+        ag._arena.close()
+        dist.destroy_process_group()
+    world.close()
+    return ok, used_multicast
+
+
+def test_fused_tp_kernels_two_gpus_bf16_and_block_scaled():
+    results = run_ranks(_tp_rank, 2, False, timeout=240)
+    for rank in range(2):
+        kind, value = results[rank]
+        assert kind == "ok", value
+        assert value == (True, False)
+
+
+def test_all_gather_gemm_pushes_through_nvlink_multicast():
+    results = run_ranks(_tp_rank, 2, True, timeout=240)
+    for rank in range(2):
+        kind, value = results[rank]
+        assert kind == "ok", value
+    if results[0][1] == "no multicast on this fabric":
+        pytest.skip("no NVLink multicast on this fabric")
+    for rank in range(2):
+        ok, used = results[rank][1]
+        assert ok
+    # the mapping is there whenever the fabric offers one; without it the same call falls back to peer stores
+    assert results[0][1][1] == results[1][1][1]
