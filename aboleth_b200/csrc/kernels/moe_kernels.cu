@@ -810,23 +810,36 @@ __device__ __forceinline__ bool reduce_token_by_warp(const CombineParams &p, int
     const std::uint32_t *my_src = p.returned +
         (static_cast<std::size_t>(lane < g.world ? lane : 0) * g.capacity + (slot < 0 ? 0 : slot)) * (g.hidden / 2);
     std::uint32_t *out = p.out + static_cast<std::size_t>(t) * (g.hidden / 2);
-    constexpr int kChunks = 4;  // 16-byte vectors per lane in flight per source
+    // Two 16-byte vectors per lane from each of up to four sources are in flight together (eight loads per
+    // lane): a token has five to six partials on eight ranks, so a group of 1 KiB costs two round trips to
+    // memory instead of one per source.
+    constexpr int kChunks = 2, kSources = 4;
     for (int base = 0; base < vecs; base += 32 * kChunks) {
         float acc[kChunks][8] = {};
-        for (unsigned m = live; m; m &= m - 1) {
-            const std::uint32_t *y = reinterpret_cast<const std::uint32_t *>(
-                shfl_u64(reinterpret_cast<std::uint64_t>(my_src), __ffs(m) - 1));
-            uint4 r[kChunks];
+        unsigned m = live;
+        while (m) {
+            uint4 r[kSources][kChunks];
 #pragma unroll
-            for (int u = 0; u < kChunks; ++u) {
-                const int v = base + u * 32 + lane;
-                r[u] = make_uint4(0, 0, 0, 0);
-                if (v < vecs)
-                    r[u] = aboleth::detail::ld_stream16(y + v * 4);
+            for (int q = 0; q < kSources; ++q) {
+                const bool more = m != 0;
+                // every lane takes part in the shuffle; an exhausted mask names lane 0 and loads nothing
+                const int from = more ? __ffs(m) - 1 : 0;
+                const std::uint32_t *y = reinterpret_cast<const std::uint32_t *>(
+                    shfl_u64(reinterpret_cast<std::uint64_t>(my_src), from));
+                m &= m - 1;
+#pragma unroll
+                for (int u = 0; u < kChunks; ++u) {
+                    const int v = base + u * 32 + lane;
+                    r[q][u] = make_uint4(0, 0, 0, 0);
+                    if (v < vecs && more)
+                        r[q][u] = aboleth::detail::ld_stream16(y + v * 4);
+                }
             }
 #pragma unroll
-            for (int u = 0; u < kChunks; ++u)
-                add_bf16x8(acc[u], r[u], 1.0f);
+            for (int q = 0; q < kSources; ++q)
+#pragma unroll
+                for (int u = 0; u < kChunks; ++u)
+                    add_bf16x8(acc[u], r[q][u], 1.0f);
         }
 #pragma unroll
         for (int u = 0; u < kChunks; ++u) {
