@@ -52,7 +52,7 @@ constexpr unsigned kFull = 0xffffffffu;
 
 // Counter words in `done`.
 constexpr int kDoneDispatch = 0, kDoneCombine = 1, kBarrierCount = 2, kBarrierGen = 3, kDoneSenders = 4,
-              kNextToken = 5;
+              kNextToken = 5, kNextRecord = 8;  // kNextRecord + d: next unclaimed record of destination d
 
 struct EpGeometry {
     int rank, world, experts, top_k, hidden, scale_group, capacity;
@@ -788,7 +788,10 @@ __device__ __forceinline__ void return_row_by_warp(const CombineParams &p, int r
 
 // One warp reduces one token's partial rows over the ranks that hold one, once the blocks that
 // hold them are published.  Returns false when a wait ran out (status recorded).
-__device__ __forceinline__ bool reduce_token_by_warp(const CombineParams &p, int t, std::uint64_t epoch) {
+// Part `part` of `parts` of token `t`: a token's row is cut into parts that different warps reduce, so the
+// chain of dependent loads behind the LAST records to arrive is a quarter as long.
+__device__ __forceinline__ bool reduce_token_by_warp(const CombineParams &p, int t, std::uint64_t epoch, int part,
+                                                     int parts) {
     const EpGeometry &g = p.g;
     const int lane = threadIdx.x & 31;
     const int vecs = g.hidden / 8;
@@ -814,7 +817,9 @@ __device__ __forceinline__ bool reduce_token_by_warp(const CombineParams &p, int
     // lane): a token has five to six partials on eight ranks, so a group of 1 KiB costs two round trips to
     // memory instead of one per source.
     constexpr int kChunks = 2, kSources = 4;
-    for (int base = 0; base < vecs; base += 32 * kChunks) {
+    const int groups = (vecs + 32 * kChunks - 1) / (32 * kChunks);
+    const int first = part * groups / parts * (32 * kChunks), last = (part + 1) * groups / parts * (32 * kChunks);
+    for (int base = first; base < min(last, vecs); base += 32 * kChunks) {
         float acc[kChunks][8] = {};
         unsigned m = live;
         while (m) {
@@ -885,15 +890,27 @@ __global__ void __launch_bounds__(kThreads, 3) ep_combine_kernel(CombineParams p
         const int senders = fused ? p.send_warps : ((p.phases & kPhaseSend) ? kWarps : 0);
         if (warp < senders) {
             const int stride = gridDim.x * senders;
-            for (int i = blockIdx.x * senders + warp; i < spread; i += stride) {
-                const int slot = i / g.world;
-                const int src = (g.rank + 1 + (i - slot * g.world)) % g.world;
-                if (slot >= s_count[src])
-                    continue;
-                return_row_by_warp(p, src * g.capacity + slot, src, slot);
-                __syncwarp();
-                if (lane == 0)
-                    complete_record(p, src, slot, s_count[src], epoch);
+            // A sender warp serves ONE destination (warps are dealt round-robin over the destinations,
+            // starting at rank + 1, so every link is busy all the time and the warps of the local
+            // destination, which finish early, turn into reducers) and claims that destination's records
+            // one at a time from a counter: warps that drew records with few expert rows take more, and
+            // the warps of a destination end together.  (A fixed stride left the slowest warps 40 % behind
+            // the first; one counter for all destinations made every warp wait on the link.)
+            // (With fewer sender warps than destinations a warp serves several, one after the other.)
+            for (int turn = (blockIdx.x * senders + warp) % g.world; turn < g.world; turn += stride) {
+                const int src = (g.rank + 1 + turn) % g.world;
+                for (;;) {
+                    int slot = 0;
+                    if (lane == 0)
+                        slot = static_cast<int>(atomicAdd(p.done + kNextRecord + src, 1u));
+                    slot = __shfl_sync(kFull, slot, 0);
+                    if (slot >= s_count[src])
+                        break;
+                    return_row_by_warp(p, src * g.capacity + slot, src, slot);
+                    __syncwarp();
+                    if (lane == 0)
+                        complete_record(p, src, slot, s_count[src], epoch);
+                }
             }
             stamp(p.trace, 1, tracer);
             // This warp has sent everything it will send.
@@ -913,12 +930,14 @@ __global__ void __launch_bounds__(kThreads, 3) ep_combine_kernel(CombineParams p
         if (p.phases & kPhaseRecv) {
             // Tokens are handed out in order through one counter: the dedicated reducer warps start at
             // once, the sender warps join when they have nothing left to send.
+            const int parts = min(4, (vecs + 63) / 64);
             for (;;) {
-                int t = 0;
+                int item = 0;
                 if (lane == 0)
-                    t = static_cast<int>(atomicAdd(p.done + kNextToken, 1u));
-                t = __shfl_sync(kFull, t, 0);
-                if (t >= p.num_tokens || !reduce_token_by_warp(p, t, epoch))
+                    item = static_cast<int>(atomicAdd(p.done + kNextToken, 1u));
+                item = __shfl_sync(kFull, item, 0);
+                const int t = item / parts;
+                if (t >= p.num_tokens || !reduce_token_by_warp(p, t, epoch, item - t * parts, parts))
                     break;
             }
         }
@@ -1055,6 +1074,8 @@ __global__ void __launch_bounds__(kThreads, 3) ep_combine_kernel(CombineParams p
             if (tid == 0) {
                 p.done[kDoneCombine] = 0;
                 p.done[kNextToken] = 0;
+                for (int d = 0; d < g.world; ++d)
+                    p.done[kNextRecord + d] = 0;
                 (void)ok;  // a timeout is in the status word; the epoch still advances
                 *p.epoch = epoch + 1;
                 stamp(p.trace, 4, true);

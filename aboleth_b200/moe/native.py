@@ -185,7 +185,7 @@ class NativeMoESlot:
         z = lambda *shape, dtype: torch.zeros(*shape, dtype=dtype, device=dev)  # noqa: E731
         self.source_slots = torch.full((s.capacity, s.ranks), -1, dtype=torch.int32, device=dev)
         self.send_counts = z(s.ranks, dtype=torch.int64)
-        self.done = z(8, dtype=torch.int32)
+        self.done = z(8 + 32, dtype=torch.int32)   # arrival counters, then one record cursor per destination
         self.block_counts = z(MAX_DISPATCH_CTAS, s.ranks, dtype=torch.int32)
         self.block_done = z(s.ranks, return_blocks(s), dtype=torch.int32)
         self.overflow = z(1, dtype=torch.int32)
