@@ -185,9 +185,10 @@ class EpLayerBench:
                 self.flusher()
             sync_ranks(distributed)
             e0, e1, e2, e3 = ev(), ev(), ev(), ev()
-            # Keep the GPU busy while the host enqueues, so that the bracket
-            # measures the kernel and not the host's launch latency.
-            torch.cuda._sleep(100_000)
+            # Keep the GPU busy (about 200 us) while the host enqueues the alignment kernel, the events
+            # and the phase, so that the bracket measures the kernel and not the host: a host that
+            # enqueues the phase after the alignment kernel has ended lets the ranks start apart.
+            torch.cuda._sleep(400_000)
             self.align()   # the ranks leave this kernel together: launch skew stays out of the bracket
             e0.record()
             res = slot.dispatch(self.x[i], logits=self.logits[i])
@@ -197,7 +198,7 @@ class EpLayerBench:
             if flush:
                 self.flusher()
             sync_ranks(distributed)
-            torch.cuda._sleep(100_000)
+            torch.cuda._sleep(400_000)
             self.align()
             e2.record()
             slot.combine(rows, expert_offsets=offsets)
@@ -287,7 +288,7 @@ def alltoall_sweep(world: World, distributed: bool, sizes=None, *, rounds: int =
     n, rank, dev = world.world_size, world.rank, world.torch_device
     sizes = list(sizes or [1 << e for e in range(10, 29)])
     top = max(sizes)
-    max_lanes = 32
+    max_lanes = 64   # 32 lanes per peer up to 32 MiB, 64 beyond (messages that no longer fit L2)
     arena = world.runtime.allocate(2 * n * top + n * max_lanes * 8)
     reg = world.register(arena, network=False)
     recv = world.region("a2a_recv", reg, offset=n * top, length=n * top)
@@ -309,7 +310,7 @@ def alltoall_sweep(world: World, distributed: bool, sizes=None, *, rounds: int =
             cases = [("vector", 1), ("bulk", 1)]
         cases += [("vector", c) for c in chains if c > 1 and size in chain_sizes]
         for mode, chain in cases:
-            lanes = max(1, min(max_lanes, size // 16384))
+            lanes = max(1, min(max_lanes if size >= (64 << 20) else 32, size // 16384))
             if size // lanes // chain < 16:
                 continue
             my_flags.zero_()

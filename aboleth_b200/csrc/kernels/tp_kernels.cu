@@ -94,11 +94,21 @@ struct AgGemmPolicyT {
         if (idx >= world * per_src)
             return false;
         // Source order: own rows first, then rank-1, rank-2, ... (the order in which
-        // peers' pushes arrive, since every rank pushes to rank+1 first).
-        const int order = idx / per_src, local = idx - order * per_src;
+        // peers' pushes arrive, since every rank pushes to rank+1 first).  A multicast push serves all
+        // peers chunk by chunk instead, so there the remote tiles are walked chunk-major: chunk 0 of
+        // every source, then chunk 1 of every source, ...
+        int order, chunk, tn;
+        if (mc_staging != 0 && idx >= per_src) {
+            const int remote = idx - per_src, per_chunk = (world - 1) * tiles_n;
+            chunk = remote / per_chunk;
+            const int in_chunk = remote - chunk * per_chunk;
+            order = in_chunk / tiles_n + 1;
+            tn = in_chunk - (order - 1) * tiles_n;
+        } else {
+            order = idx / per_src;
+            raster(idx - order * per_src, chunks, tiles_n, group_n, chunk, tn);
+        }
         const int src = (rank - order + world) % world;
-        int chunk, tn;
-        raster(local, chunks, tiles_n, group_n, chunk, tn);
         t.a_sel = src == rank ? 1 : 0;
         t.a_row = src == rank ? chunk * kRows : src * m_local + chunk * kRows;
         t.b_row = tn * COLS;

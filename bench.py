@@ -61,6 +61,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per rank (4096 prefill, 128 decode)")
     ap.add_argument("--no-extras", action="store_true", help="skip decode / all-to-all side measurements")
+    ap.add_argument("--no-comparators", action="store_true",
+                    help="keep the decode-size extras, skip the NCCL form of the layer and the all-to-all sweep")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -148,7 +150,7 @@ def main() -> int:
         extras["decode_128_tokens_unweighted"] = small.phase_times(
             steps=30, distributed=distributed, flush=True, weighted=False)
         extras["decode_verify_errors"] = small.verify()
-        if distributed:
+        if distributed and not args.no_comparators:
             sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
             import nccl_ep_baseline
             from aboleth_b200.moe.reference import standin_layer_reference

@@ -28,7 +28,8 @@ def main() -> int:
     ap.add_argument("--max-bytes", dest="max", type=int, default=1 << 26)
     ap.add_argument("--rounds", type=int, default=20)
     ap.add_argument("--chains", default="1,8,64")
-    ap.add_argument("--max-lanes", type=int, default=32)
+    ap.add_argument("--max-lanes", type=int, default=64,
+                    help="lanes (CTAs) per peer for messages of 64 MiB and more; smaller ones use at most 32")
     ap.add_argument("--graph-max", type=int, default=1 << 20,
                     help="largest message for which the NCCL rounds are also timed as one captured CUDA graph")
     ap.add_argument("--out", default=None)
@@ -68,7 +69,7 @@ def main() -> int:
                     continue
                 if chain > 1 and mode == "bulk":
                     continue
-                lanes = max(1, min(lanes_cap, size // 16384))
+                lanes = max(1, min(lanes_cap if size >= (64 << 20) else min(lanes_cap, 32), size // 16384))
                 if size // lanes // chain < 16:
                     continue
                 flags.zero_()
