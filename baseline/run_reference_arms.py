@@ -33,7 +33,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 BENCH = HERE / "_ref" / "bench"
-REFERENCE = Path(os.environ.get("ABOLETH_REFERENCE", "/root/reference")) / "experiments" / "bench"
+# The reference checkout: ABOLETH_REFERENCE, or a directory named `reference` next to this repository.
+REFERENCE = Path(os.environ.get("ABOLETH_REFERENCE", HERE.parent.parent / "reference")) / "experiments" / "bench"
 SOURCES = ["bench_tier1_nccl_host.cu", "bench_tier1_nvshmem.cu", "bench_tier1_arms.cuh", "bench_common.h",
            "kernels/bench_kernels.cuh", "kernels/comm_nvshmem.cuh"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
