@@ -184,3 +184,24 @@ __global__ void k(const std::uint64_t *eps, unsigned long long dst, unsigned lon
     assert "#define ABOLETH_TIER1_SPECIALIZED" not in unspecialised.header.read_text().split("#ifdef ABOLETH_TIER1_SPECIALIZED")[0]
     with pytest.raises(ValueError, match="none of the requested transports"):
         generate_device_library(tmp_path / "bad", transports=["p2p"], specialize="proxy")
+
+
+def test_pinned_environment_check_reports_every_pin(tmp_path):
+    from pathlib import Path
+
+    """The checker names each pinned package with what it found; a wrong pin of a required package
+    fails, a wrong pin of a baseline-only package only warns."""
+    import json
+
+    from aboleth_b200.utils import environment
+
+    pins = json.loads((Path(__file__).resolve().parent.parent / "repro" / "environment.json").read_text())
+    result = environment.compare(pins)
+    names = [row[0] for row in result["rows"]]
+    assert set(pins["packages"]) <= set(names) and "python" in names and "nvcc" in names
+    assert all(row[3] in ("ok", "warn", "fail") for row in result["rows"])
+    wrong = dict(pins, packages={**pins["packages"], "torch": "0.0.0"})
+    assert environment.compare(wrong)["ok"] is False
+    only_baseline = dict(pins, packages={**pins["packages"], "vllm": "0.0.0"})
+    rows = {row[0]: row[3] for row in environment.compare(only_baseline)["rows"]}
+    assert rows["vllm"] == "warn"
