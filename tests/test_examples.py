@@ -39,7 +39,7 @@ def test_tier1_client_compiles_against_the_device_library(tmp_path):
 @pytest.mark.parametrize("script,args", [
     ("tier2_chain.py", ()), ("tier2_chain.py", ("--transport", "proxy")), ("tier1_client.py", ()),
     ("moe_layer.py", ()), ("moe_layer.py", ("--bf16",)), ("kv_push.py", ()), ("tp_fused.py", ()),
-    ("vllm_modular_moe.py", ())])
+    ("vllm_modular_moe.py", ()), ("block_scaled_gemm.py", ()), ("fp8_experts.py", ())])
 def test_examples_run_on_one_gpu(script, args, tmp_path):
     proc = _run(script, *args, cache=tmp_path)
     assert proc.returncode == 0, proc.stdout + proc.stderr
