@@ -59,7 +59,7 @@ class Provider(IntEnum):
 class AllocationProvider(IntEnum):
     IB_VERBS = 1
     CUDA_IPC = 2
-    CUDA_VMM = 3  # reserved, as in the reference
+    CUDA_VMM = 3  # virtual-memory allocations with peer and multicast mappings: symmetric.SymmetricArena
     HOST_SHM = 16  # CPU-only ranks of this build; outside the reference's range
 
 
