@@ -620,4 +620,34 @@ int ab200_endpoint_stats(void *endpoint, std::uint64_t *four_words) {
     return 0;
 }
 
+// Snapshot of the submission queue: for each of `batches` batches starting at sequence `first`, a
+// 32-bit command count followed by that many 32-byte commands, as the producer wrote them.  A slot
+// keeps its contents after the worker retired it (until the ring wraps), so the last 64 batches can
+// be read at rest.  Returns the bytes written, or -1 (batch not produced yet, out of the ring's
+// window, or `capacity` too small).
+long long ab200_endpoint_snapshot(void *endpoint, std::uint64_t first, int batches, void *out,
+                                  std::size_t capacity) {
+    auto *ep = static_cast<Endpoint *>(endpoint);
+    if (ep == nullptr || out == nullptr || batches < 0)
+        return fail("snapshot: null endpoint or buffer");
+    const std::uint64_t completed = __atomic_load_n(&ep->queue->completed_sequence, __ATOMIC_ACQUIRE);
+    if (first + static_cast<std::uint64_t>(batches) > completed)
+        return fail("snapshot: batches that were not retired yet");
+    if (completed - first > abi::kProxySlotCount)
+        return fail("snapshot: batches already overwritten by the ring");
+    auto *cursor = static_cast<unsigned char *>(out);
+    std::size_t used = 0;
+    for (int b = 0; b < batches; ++b) {
+        const abi::ProxyBatchSlot &slot = ep->queue->slots[(first + b) % abi::kProxySlotCount];
+        const std::uint32_t count = slot.command_count;
+        const std::size_t bytes = sizeof(std::uint32_t) + count * sizeof(abi::ProxyCommand);
+        if (count > abi::kProxyMaximumCommands || used + bytes > capacity)
+            return fail("snapshot: buffer too small or slot damaged");
+        std::memcpy(cursor + used, &count, sizeof(count));
+        std::memcpy(cursor + used + sizeof(count), slot.commands, count * sizeof(abi::ProxyCommand));
+        used += bytes;
+    }
+    return static_cast<long long>(used);
+}
+
 }  // extern "C"

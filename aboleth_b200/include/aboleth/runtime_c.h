@@ -110,5 +110,10 @@ int ab200_endpoint_descriptor(void *endpoint, aboleth::abi::ProxyEndpointDescrip
 int ab200_endpoint_inject_failure(void *endpoint, std::uint64_t status, int batches);
 // Counters: batches consumed, commands executed, bytes moved, signals written.
 int ab200_endpoint_stats(void *endpoint, std::uint64_t *four_words);
+// Submission-queue snapshot for differential tests (the reference's pair_snapshot_sq,
+// include/aboleth/runtime_c.h:299-305): `batches` retired batches from sequence `first`, each as a
+// 32-bit command count followed by its 32-byte commands.  Returns bytes written or -1.
+long long ab200_endpoint_snapshot(void *endpoint, std::uint64_t first, int batches, void *out,
+                                  std::size_t capacity);
 
 }  // extern "C"

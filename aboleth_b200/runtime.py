@@ -108,6 +108,8 @@ def _lib():
     lib.ab200_endpoint_descriptor.argtypes = [c.c_void_p, c.c_void_p]
     lib.ab200_endpoint_inject_failure.argtypes = [c.c_void_p, c.c_uint64, c.c_int]
     lib.ab200_endpoint_stats.argtypes = [c.c_void_p, c.POINTER(c.c_uint64)]
+    lib.ab200_endpoint_snapshot.restype = c.c_longlong
+    lib.ab200_endpoint_snapshot.argtypes = [c.c_void_p, c.c_uint64, c.c_int, c.c_void_p, c.c_size_t]
     lib.ab200_probe_providers.restype = c.c_uint32
     lib.aboleth_runtime_select_device.argtypes = [c.c_int, c.c_char_p, c.c_size_t]
     lib.aboleth_runtime_select_gid_index.argtypes = [c.c_char_p, c.c_int]
@@ -670,6 +672,27 @@ class LocalEndpoint:
         words = (ctypes.c_uint64 * 4)()
         _lib().ab200_endpoint_stats(self._native, words)
         return dict(zip(("batches", "commands", "bytes", "signals"), map(int, words)))
+
+    def snapshot_queue(self, first: int = 0, batches: Optional[int] = None) -> list[list[bytes]]:
+        """The commands of retired batches ``first .. first + batches`` exactly as their producer
+        wrote them into the ring: one list of 32-byte command images per batch.  For differential
+        tests (two producers that should put the same bytes on the wire); the ring keeps the last
+        64 batches."""
+        self._ensure_open()
+        if batches is None:
+            batches = self.state()[1] - first
+        room = batches * (4 + 256 * 32)
+        buffer = (ctypes.c_ubyte * max(room, 4))()
+        used = _lib().ab200_endpoint_snapshot(self._native, int(first), int(batches), buffer, room)
+        if used < 0:
+            raise RuntimeError(f"queue snapshot failed: {last_error()}")
+        raw, out, at = bytes(buffer[:used]), [], 0
+        for _ in range(batches):
+            count = int.from_bytes(raw[at:at + 4], "little")
+            at += 4
+            out.append([raw[at + 32 * k:at + 32 * (k + 1)] for k in range(count)])
+            at += 32 * count
+        return out
 
     def local_buffer(self, buffer: RegisteredBuffer, offset: int = 0,
                      length: Optional[int] = None) -> LocalBuffer:

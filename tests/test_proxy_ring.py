@@ -113,3 +113,28 @@ def test_endpoint_config_versioning(rt):
         rt.create_local_endpoint(Transport.PROXY, config=abi.EndpointConfig(qp_type=1))
     with pytest.raises(RuntimeError, match="hca must be empty"):
         rt.create_local_endpoint(Transport.PROXY, config=abi.EndpointConfig(hca=b"mlx5_0"))
+
+
+def test_queue_snapshot_returns_what_the_producer_wrote(rt):
+    """The ring keeps a retired batch's commands until it wraps: a snapshot returns them byte for
+    byte, batch by batch; batches not produced yet, or already overwritten, are refused."""
+    ep = rt.create_local_endpoint(Transport.PROXY)
+    src, dst = rt.allocate(4096), rt.allocate(4096 + 8)
+    first = [abi.ProxyCommand(src.data_ptr(), dst.data_ptr(), 1024, 0, 0, abi.PROXY_WRITE),
+             abi.ProxyCommand(5, dst.data_ptr() + 4096, 8, 0, 0, abi.PROXY_STRONG_SIGNAL)]
+    second = [abi.ProxyCommand(src.data_ptr() + 1024, dst.data_ptr() + 1024, 512, 0, 0, abi.PROXY_WRITE)]
+    for commands in (first, second):
+        desc, seq = _submit(ep, commands)
+        assert _poll(desc, seq) == abi.STATUS_OK
+    snapshot = ep.snapshot_queue()
+    assert [len(batch) for batch in snapshot] == [2, 1]
+    assert snapshot[0] == [bytes(c) for c in first] and snapshot[1] == [bytes(c) for c in second]
+    assert ep.snapshot_queue(1, 1) == [snapshot[1]]
+    with pytest.raises(RuntimeError, match="not retired"):
+        ep.snapshot_queue(0, 3)
+    for _ in range(70):                                   # wrap the 64-slot ring
+        desc, seq = _submit(ep, second)
+        assert _poll(desc, seq) == abi.STATUS_OK
+    with pytest.raises(RuntimeError, match="overwritten"):
+        ep.snapshot_queue(0, 1)
+    assert ep.snapshot_queue(71, 1) == [snapshot[1]]

@@ -96,3 +96,54 @@ def test_tier1_put_signal_through_the_proxy_ring_and_injected_failure():
         assert endpoint.state()[2] == ab.abi.STATUS_COMPLETION_FAILURE
     finally:
         runtime.close()
+
+
+def test_emitted_chain_and_handwritten_header_put_the_same_commands_on_the_ring(tmp_path, monkeypatch):
+    """Differential: the kernel the specializer emits for "eight puts closed by one signal" and the
+    hand-written Tier-1 header's put_many_signal must write the same batch into the proxy ring,
+    command for command and byte for byte (addresses, sizes, keys, opcodes, the signal's value)."""
+    import aboleth_b200 as ab
+    from aboleth_b200.compiler import LoadedKernel, build_artifact, compilation, compile_program
+    from aboleth_b200.ops import tier1_exercise
+
+    monkeypatch.setenv("ABOLETH_CACHE_DIR", str(tmp_path))
+    torch.cuda.set_device(0)
+    runtime = ab.Runtime(0)
+    try:
+        nbytes, epoch = 1 << 16, 7
+        src = torch.arange(nbytes // 4, dtype=torch.int32, device="cuda").view(torch.uint8)
+        dst = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        cells = torch.zeros(4, dtype=torch.int64, device="cuda")       # [flag, inline destination, ...]
+        status = torch.zeros(2, dtype=torch.int64, device="cuda")
+
+        # hand-written header: one inline put (its own batch), then put_many_signal of eight pieces
+        by_hand = runtime.create_local_endpoint(ab.Transport.PROXY)
+        handles = torch.tensor([by_hand.handle], dtype=torch.int64, device="cuda")
+        tier1_exercise(handles, status, dst=dst.data_ptr(), src=src.data_ptr(), flag=cells[0:].data_ptr(),
+                       inline_dst=cells[1:].data_ptr(), wait_flag=cells[0:].data_ptr(), epoch=epoch,
+                       wait_epoch=epoch, nbytes=nbytes, peer=0, pieces=8)
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 0] and torch.equal(dst, src) and cells[0].item() == epoch
+        hand_batches = by_hand.snapshot_queue()
+
+        # emitted kernel: the same chain from the program builder, through its own endpoint
+        dst.zero_()
+        cells.zero_()
+        emitted = runtime.create_local_endpoint(ab.Transport.PROXY)
+        handles2 = torch.tensor([emitted.handle], dtype=torch.int64, device="cuda")
+        dst_table = torch.tensor([dst.data_ptr(), 0], dtype=torch.int64, device="cuda")
+        flag_table = torch.tensor([cells.data_ptr(), 0], dtype=torch.int64, device="cuda")
+        with compilation("proxy", rank=0, world_size=1):
+            kernel = LoadedKernel(build_artifact(compile_program(_program(nbytes, 8, chained=True))))
+        kernel.launch(1, 128, [src.data_ptr(), handles2.data_ptr(), dst_table.data_ptr(), flag_table.data_ptr(),
+                               cells.data_ptr(), epoch, status.data_ptr()],
+                      stream=torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 0] and torch.equal(dst, src) and cells[0].item() == epoch
+        emitted_batches = emitted.snapshot_queue()
+
+        chain = hand_batches[-1]                       # the batch of put_many_signal
+        assert len(chain) == 9 and len(emitted_batches) == 1
+        assert emitted_batches[0] == chain
+    finally:
+        runtime.close()
