@@ -33,9 +33,17 @@ PRESETS = {
                    "decode-size dispatch / combine with a flushed L2"),
     "gemm": ("gemm_bench.py", [], (1,), "bf16 tcgen05 GEMM against cuBLAS"),
     "gemm-fp8": ("gemm_bench.py", ["--fp8"], (1,), "e4m3 GEMM against cuBLASLt"),
-    "gemm-fp8-block": ("gemm_bench.py", ["--block-scaled"], (1,), "block-scaled e4m3 GEMM: bf16 expansion + tcgen05 GEMM"),
+    "gemm-fp8-block": ("gemm_bench.py", ["--block-scaled"], (1,),
+                       "block-scaled e4m3 GEMM on the fp8 tensor path, against its bf16 expansion, the bf16 kernel and cuBLASLt"),
     "gemm-grouped": ("gemm_bench.py", ["--grouped"], (1,), "grouped expert GEMM against a loop of cuBLAS calls"),
     "tp": ("tp_bench.py", [], (2, 4, 8), "AG->GEMM and GEMM->RS fused kernels against NCCL + cuBLAS"),
+    "tp-fp8": ("tp_bench.py", ["--fp8", "--multicast", "--steps", "20"], (2, 4, 8),
+               "the same plus the block-scaled e4m3 forms and the all-gather push through NVLink multicast"),
+    "peer-copy": ("peer_copy_bench.py", [], (2,), "copy-engine peer copy, one way and both ways: the NVLink denominator"),
+    "moe-emulated": ("ep_layer.py", ["--tokens", "2048", "--emulate-ranks", "2", "--steps", "2"], (1,),
+                     "two ranks of the EP layer on one GPU (the profiler's multi-rank case)"),
+    "tp-emulated": ("tp_local.py", ["--ranks", "2", "--tokens", "4096", "--hidden", "4096", "--ffn", "8192"], (1,),
+                    "two ranks of the fused TP kernels on one GPU (the profiler's multi-rank case)"),
     "serve": ("serve_bench.py", ["--graph"], (1, 2, 4, 8), "Mixtral-style EP serving, decode replayed as a CUDA graph"),
     "native": ("native_bench.py", ["--sweep"], (1, 2, 4, 8), "C++ arm of the Tier-1 ladder (one process, rank per GPU)"),
     "nccl-host": ("native_bench.py", ["--arm", "nccl_host", "--sweep"], (2, 4, 8),
@@ -50,14 +58,14 @@ def command(name: str, gpus: int, out: Path, port: int) -> list[str]:
         raise SystemExit(f"preset {name!r} runs on {allowed} GPUs, not {gpus}")
     target = script.split() if script.startswith("-m") else [str((HERE / script).resolve())]
     launcher = [sys.executable]
-    one_process = name in ("native", "nccl-host")  # these programs drive every GPU themselves
+    one_process = name in ("native", "nccl-host", "peer-copy")  # these programs drive every GPU themselves
     if gpus > 1 and not one_process:
         launcher += ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={gpus}",
                      "--master-addr", "127.0.0.1", "--master-port", str(port)]
     args = list(extra)
     if name == "headline":
         args = ["--gpus", str(gpus)] + args
-    elif one_process:
+    elif one_process and name != "peer-copy":
         args += ["--gpus", str(gpus)]
     elif name == "probe" and gpus == 1:
         args += ["--loopback"]

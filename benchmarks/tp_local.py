@@ -20,6 +20,7 @@ def main() -> int:
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=8192)
     ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--out", default=None, help="also write the result line to this file")
     args = ap.parse_args()
 
     import torch
@@ -48,8 +49,13 @@ def main() -> int:
             worst = max(worst, float((outs[r].float() - want).abs().max() / want.abs().max()))
             want = sum(a_parts[s][r * m_local:(r + 1) * m_local].float() @ b_rows[s].float().t() for s in range(w))
             worst = max(worst, float((red[r].float() - want).abs().max() / want.abs().max()))
-    print(json.dumps({"ranks": w, "tokens": args.tokens, "hidden": args.hidden, "ffn": args.ffn,
-                      "steps": args.steps, "worst_relative_error": worst}))
+    line = json.dumps({"ranks": w, "tokens": args.tokens, "hidden": args.hidden, "ffn": args.ffn,
+                       "steps": args.steps, "worst_relative_error": worst})
+    print(line)
+    if args.out:
+        from pathlib import Path
+        Path(args.out).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.out).write_text(line + "\n")
     return 0 if worst < 2e-2 else 1
 
 
