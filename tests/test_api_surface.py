@@ -205,3 +205,29 @@ def test_pinned_environment_check_reports_every_pin(tmp_path):
     only_baseline = dict(pins, packages={**pins["packages"], "vllm": "0.0.0"})
     rows = {row[0]: row[3] for row in environment.compare(only_baseline)["rows"]}
     assert rows["vllm"] == "warn"
+
+
+def test_every_benchmark_preset_builds_a_runnable_command():
+    """Each preset names a script that exists and flags that the script's parser knows; multi-rank presets go
+    through torchrun on 127.0.0.1."""
+    import importlib.util
+    import re
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    spec = importlib.util.spec_from_file_location("bench_run", root / "benchmarks" / "run.py")
+    run = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(run)
+    for name, (script, extra, allowed, what) in run.PRESETS.items():
+        assert what and allowed
+        gpus = max(allowed)
+        command = run.command(name, gpus, Path("out"), 29600)
+        if script.startswith("-m"):
+            continue
+        path = (root / "benchmarks" / script).resolve()
+        assert path.exists(), (name, path)
+        source = path.read_text()
+        for flag in [a for a in extra if a.startswith("--")] + (["--out"] if name != "headline" else []):
+            assert re.search(r'"%s"' % re.escape(flag), source), (name, flag)
+        if gpus > 1 and name not in ("native", "nccl-host", "peer-copy"):
+            assert "torch.distributed.run" in command and "127.0.0.1" in command
