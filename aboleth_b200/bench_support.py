@@ -310,7 +310,8 @@ def alltoall_sweep(world: World, distributed: bool, sizes=None, *, rounds: int =
             cases = [("vector", 1), ("bulk", 1)]
         cases += [("vector", c) for c in chains if c > 1 and size in chain_sizes]
         for mode, chain in cases:
-            lanes = max(1, min(max_lanes if size >= (64 << 20) else 32, size // 16384))
+            # 64 lanes only help the bulk-copy mode; the vector mode loses with them (384 against 617 GB/s)
+            lanes = max(1, min(max_lanes if (size >= (64 << 20) and mode == "bulk") else 32, size // 16384))
             if size // lanes // chain < 16:
                 continue
             my_flags.zero_()

@@ -69,7 +69,8 @@ def main() -> int:
                     continue
                 if chain > 1 and mode == "bulk":
                     continue
-                lanes = max(1, min(lanes_cap if size >= (64 << 20) else min(lanes_cap, 32), size // 16384))
+                wide = size >= (64 << 20) and mode == "bulk"   # more lanes only help the bulk-copy mode
+                lanes = max(1, min(lanes_cap if wide else min(lanes_cap, 32), size // 16384))
                 if size // lanes // chain < 16:
                     continue
                 flags.zero_()
