@@ -15,12 +15,14 @@
 // is the order `tcgen05.cp.32x128b.warpx4` wants: it copies 32 rows x 16 bytes from shared memory
 // into 32 lanes x 4 columns of tensor memory and repeats them over the four lane quarters; the
 // MMA then picks byte s of a column through the scale-factor id in its instruction descriptor.
-// Per K block the producer brings in the A tile (16 KiB), the B tile (32 KiB) by TMA and the A
-// atom (512 B) and two B atoms (1 KiB) by untiled bulk copies on the same mbarrier; nothing is
-// multicast.
+// Per K block the producer brings in the A tile and the B tile by TMA (16 + 32 KiB, or 32 + 24 KiB
+// for the wider tile) and one A atom per 128-row block plus two B atoms (512 bytes each) by untiled
+// bulk copies on the same mbarrier; nothing is multicast.  B's atoms are stored per 64-column
+// granule (atom g = columns [64 g, 64 g + 128)), so a tile that starts at any multiple of 64
+// columns finds its two atoms at g and g + 2.
 //
 // Two tile shapes.  128 x 256: one accumulator of 256 columns plus 12 columns of scale factors.
-// 256 x 192: two 128-row accumulators of 192 columns that share each B tile (a quarter fewer
+// 256 x 192: two 128-row accumulators of 192 columns that share each B tile (a fifth fewer
 // shared-memory bytes per FLOP, which is what bounds this loop) plus 16 columns of scale factors.
 // Either way tensor memory has no room for a second accumulator buffer, so the epilogue of a tile
 // is not overlapped with the next tile's main loop.
