@@ -9,7 +9,11 @@ C++ benchmark arms need only CUDA plus a library that ships with this image:
                CUDA graph).  Built against the NCCL of the PyTorch wheels.
 ``nvshmem``    experiments/bench/bench_tier1_nvshmem.cu: the same benchmark kernels over NVSHMEM
                (put + signal per peer, or ``--collective on`` for NVSHMEM's own all-to-all).  Built
-               against the ``nvidia-nvshmem`` wheel.
+               against the ``nvidia-nvshmem`` wheel.  Two settings of the LIBRARY (not of the
+               benchmark) are added to the ranks' environment unless already set: the unique-id
+               bootstrap is pointed at the loopback interface, and the symmetric heap is taken
+               from cudaMalloc + CUDA IPC instead of the virtual-memory API - with the latter the
+               ranks of this container do not return from ``nvshmemx_init_attr``.
 
 The sources are copied as they are from the reference checkout into ``baseline/_ref/bench`` (or
 used from there when the checkout is not present) and compiled by nvcc for sm_100a; nothing of
@@ -88,9 +92,13 @@ def run(arm: str, gpus: int, extra: list[str], *, port: int, timeout: float) -> 
     transport = "host" if arm == "nccl_host" else "ibrc"
     args = [str(binary), "--bench", "alltoall", "--transport", transport, *extra]
     procs = []
+    library_env = {}
+    if arm == "nvshmem":
+        library_env = {"NVSHMEM_BOOTSTRAP_UID_SOCK_IFNAME": "lo", "NVSHMEM_DISABLE_CUDA_VMM": "1"}
+        library_env = {k: v for k, v in library_env.items() if k not in os.environ}
     for rank in range(gpus):
         env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(gpus), LOCAL_RANK=str(rank),
-                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), **library_env)
         procs.append(subprocess.Popen(args, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     deadline = time.time() + timeout
     outputs = []
@@ -104,7 +112,8 @@ def run(arm: str, gpus: int, extra: list[str], *, port: int, timeout: float) -> 
             err += "\n[killed: timeout]"
         outputs.append((proc.returncode, out, err))
     code, out, err = outputs[0]
-    record: dict = {"arm": arm, "gpus": gpus, "command": " ".join(args[1:]), "returncodes": [o[0] for o in outputs]}
+    record: dict = {"arm": arm, "gpus": gpus, "command": " ".join(args[1:]), "returncodes": [o[0] for o in outputs],
+                    "library_env_added": library_env}
     lines = out.splitlines()
     record["table"] = [line for line in lines if line and not line.startswith("{")]
     try:
