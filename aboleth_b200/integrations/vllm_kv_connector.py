@@ -123,8 +123,10 @@ class CompletionBoard:
 class PullWorker:
     """Worker-side: starts pulls, waits per layer, retires finished ones."""
 
-    def __init__(self, runtime, board: Optional[CompletionBoard], *, wait_event: Callable[[Any], None]):
+    def __init__(self, runtime, board: Optional[CompletionBoard], *, wait_event: Callable[[Any], None],
+                 producer: bool = False):
         self.runtime, self.board, self._wait_event = runtime, board, wait_event
+        self.producer = producer                  # the prefill side reads the board, the decode side writes it
         self._inflight: dict[str, tuple] = {}     # request id -> (ticket, order)
 
     def register(self, kv_caches: dict) -> None:
@@ -153,15 +155,16 @@ class PullWorker:
         done = {rid for rid, (ticket, _) in self._inflight.items() if ticket.completion.query()}
         for rid in done:
             _, order = self._inflight.pop(rid)
-            if self.board is not None:
+            if self.board is not None and not self.producer:
                 self.board.post(order.remote_request_id)
         if done:
             self.runtime.check()
         return done
 
     def released_by_peer(self) -> set:
-        """Prefill side: requests whose blocks the decode side has finished reading."""
-        return self.board.collect() if self.board is not None else set()
+        """Prefill side: requests whose blocks the decode side has finished reading (nothing on the
+        decode side, which only posts)."""
+        return self.board.collect() if self.board is not None and self.producer else set()
 
 
 @functools.lru_cache(maxsize=1)
@@ -208,7 +211,7 @@ def vllm_kv_connector_class() -> Optional[type]:
                                             overrides=KVRuntimeOverrides.from_mapping(extra))
                 store = getattr(runtime.bootstrap, "store", None)
                 board = CompletionBoard(store) if store is not None else None
-                self.worker_side = PullWorker(runtime, board,
+                self.worker_side = PullWorker(runtime, board, producer=config.kv_role == "kv_producer",
                                               wait_event=lambda e: torch.cuda.current_stream().wait_event(e))
 
         # -- worker ----------------------------------------------------------------------------

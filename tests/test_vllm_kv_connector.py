@@ -84,7 +84,7 @@ def test_worker_waits_per_layer_and_reports_each_completion_once():
     store = _Store()
     runtime, waited = _Runtime(), []
     decode = PullWorker(runtime, CompletionBoard(store), wait_event=waited.append)
-    prefill = PullWorker(_Runtime(), CompletionBoard(store), wait_event=waited.append)
+    prefill = PullWorker(_Runtime(), CompletionBoard(store), wait_event=waited.append, producer=True)
     decode.register({"layer.0": object(), "layer.1": object()})
     assert runtime.registered == ("layer.0", "layer.1")
     assert not decode.has_active_layer_events
@@ -96,6 +96,7 @@ def test_worker_waits_per_layer_and_reports_each_completion_once():
     decode._inflight["d7"][0].completion.done = True
     assert decode.retire() == {"d7"} and runtime.checked == 1
     assert decode.retire() == set()
+    assert decode.released_by_peer() == set()    # the decode side never reads its own posts back
     assert prefill.released_by_peer() == {"r1"}  # the prefill side may free r1's blocks now
     assert prefill.released_by_peer() == set()
     decode._inflight["d8"][0].completion.done = True
