@@ -99,6 +99,15 @@ class PullScheduler:
                       "remote_rank": self.rank, "remote_request_id": request_id}
 
 
+    def released(self, request_ids: Iterable[str]) -> None:
+        """The decode side has read these requests' blocks: the engine frees them now."""
+        self._held.difference_update(request_ids)
+
+    @property
+    def held(self) -> frozenset:
+        return frozenset(self._held)
+
+
 class CompletionBoard:
     """Pull completions from the decode rank to the prefill rank through a key-value store
     (``set`` / ``get`` / ``add``, as the bootstrap's store offers)."""
@@ -255,6 +264,9 @@ def vllm_kv_connector_class() -> Optional[type]:
 
         def build_connector_meta(self, scheduler_output):
             return AbolethConnectorMetadata(self.scheduler_side.drain())
+
+        def update_connector_output(self, connector_output):
+            self.scheduler_side.released(getattr(connector_output, "finished_sending", None) or ())
 
         def request_finished(self, request, block_ids):
             by_length = getattr(getattr(request, "status", None), "name", "") == "FINISHED_LENGTH_CAPPED"

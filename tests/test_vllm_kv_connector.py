@@ -14,6 +14,9 @@ def test_prefill_side_keeps_blocks_and_describes_them():
     keep, params = prefill.finished("r1", {"do_remote_decode": True}, [3, 4, 9], True)
     assert keep and params == {"do_remote_prefill": True, "do_remote_decode": False,
                                "remote_block_ids": [3, 4, 9], "remote_rank": 0, "remote_request_id": "r1"}
+    assert prefill.held == {"r1"}
+    prefill.released(["r1", "unknown"])
+    assert prefill.held == frozenset()
 
 
 def test_decode_side_counts_whole_blocks_and_orders_one_pull():
