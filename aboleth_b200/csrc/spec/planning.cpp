@@ -55,14 +55,6 @@ long long num(const Op &op, const std::string &key, long long fallback = 0) {
     return value;
 }
 
-// a * b, or a diagnostic when the product leaves 64 bits.
-long long mul(long long a, long long b) {
-    long long out;
-    if (__builtin_mul_overflow(a, b, &out))
-        throw Error("a planned size does not fit 64 bits");
-    return out;
-}
-
 std::vector<std::string> list(const std::string &text) {
     std::vector<std::string> out;
     std::size_t start = 0;
