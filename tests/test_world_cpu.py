@@ -173,3 +173,14 @@ def test_single_rank_world_and_validation():
             world.connect_all("p2p")
     with pytest.raises(ValueError, match="bootstrap is required"):
         World(0, 2, device="cpu")
+
+
+def test_symmetric_arena_needs_a_process_group_and_reports_no_multicast_without_a_gpu():
+    import pytest
+    import torch
+
+    from aboleth_b200.symmetric import SymmetricArena, multicast_supported
+
+    assert multicast_supported() is False or torch.cuda.is_available()
+    with pytest.raises(RuntimeError, match="process group"):
+        SymmetricArena(1024, torch.device("cpu"))
